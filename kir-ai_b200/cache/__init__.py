@@ -1,0 +1,6 @@
+"""Paged key/value cache, block tables and per-request state slots."""
+from .manager import CacheManager, KVLayerView, StateLayerView
+from .pages import NO_PAGE, CacheError, GroupSpec, PagePool, PageTables, RequestPages, SlotPool
+
+__all__ = ["CacheManager", "KVLayerView", "StateLayerView", "NO_PAGE", "CacheError", "GroupSpec", "PagePool",
+           "PageTables", "RequestPages", "SlotPool"]

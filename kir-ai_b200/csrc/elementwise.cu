@@ -1,0 +1,438 @@
+// Row-wise kernels of the forward pass: embedding gather, RMSNorm with the
+// residual add fused in, per-head RMSNorm, rotary embedding, SwiGLU, the paged
+// key/value write, and the fusion of per-head norm + rotation + cache write.
+// Each is a template over the activation type (float for the true 32-bit path,
+// bf16 for serving); statistics, angles and the residual stream are 32-bit in
+// both.  Formulas: crates/llm-backend/src/core/math.rs:73-113 (RMSNorm),
+// :223-225 (SiLU), :515-529 (rotary, half-split pairs) of the reference.
+#include "common.cuh"
+
+// ----------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
+                                 int hidden, int vocab, int* __restrict__ error_flag) {
+    const int token = blockIdx.x;
+    const int id = ids[token];
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) atomicExch(error_flag, 1);
+        return;
+    }
+    const T* row = table + (size_t)id * hidden;
+    float* dst = out + (size_t)token * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32<T>(row[i]);
+}
+
+template <typename T>
+static int embedding_launch(const void* table, const int* ids, float* out, int tokens, int hidden, int vocab,
+                            int* error_flag, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    embedding_kernel<T><<<tokens, 256, 0, stream>>>((const T*)table, ids, out, hidden, vocab, error_flag);
+    return launch_status();
+}
+
+KIRAI_EXPORT int kirai_embedding_f32(const void* table, const int* ids, float* out, int tokens, int hidden, int vocab,
+                                     int* error_flag, cudaStream_t stream) {
+    return embedding_launch<float>(table, ids, out, tokens, hidden, vocab, error_flag, stream);
+}
+KIRAI_EXPORT int kirai_embedding_bf16(const void* table, const int* ids, float* out, int tokens, int hidden, int vocab,
+                                      int* error_flag, cudaStream_t stream) {
+    return embedding_launch<bf16>(table, ids, out, tokens, hidden, vocab, error_flag, stream);
+}
+
+// ------------------------------------------------------- residual add + RMSNorm
+// resid (32-bit, in place) += delta; out = resid * 1/sqrt(mean(resid^2) + eps) * weight.
+// With row_index != nullptr, output row r reads residual row row_index[r] and
+// leaves the residual stream untouched (the sum goes to resid_out instead).
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                   const float* __restrict__ weight, T* __restrict__ out,
+                                   const int* __restrict__ row_index, float* __restrict__ resid_out, int hidden,
+                                   float eps) {
+    __shared__ float scratch[32];
+    const int row = blockIdx.x;
+    const int src = row_index ? row_index[row] : row;
+    const float* x = resid + (size_t)src * hidden;
+    const T* d = delta ? delta + (size_t)src * hidden : nullptr;
+    float* sum_dst = row_index ? resid_out + (size_t)row * hidden : resid + (size_t)src * hidden;
+    float acc = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = x[i];
+        if (d) {
+            v += to_f32<T>(d[i]);
+            sum_dst[i] = v;
+        } else if (row_index) {
+            sum_dst[i] = v;
+        }
+        acc = fmaf(v, v, acc);
+    }
+    const float total = block_sum(acc, scratch);
+    const float variance = total / (float)hidden + eps;
+    const float scale = variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
+    T* y = out + (size_t)row * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        // each thread re-reads what it wrote itself above
+        y[i] = from_f32<T>(sum_dst[i] * scale * weight[i]);
+    }
+}
+
+template <typename T>
+static int add_rmsnorm_launch(float* resid, const void* delta, const float* weight, void* out, const int* row_index,
+                              float* resid_out, int rows, int hidden, float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (row_index && !resid_out) return KIRAI_ERR_BAD_SIZE;
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    add_rmsnorm_kernel<T><<<rows, threads, 0, stream>>>(resid, (const T*)delta, weight, (T*)out, row_index, resid_out,
+                                                        hidden, eps);
+    return launch_status();
+}
+
+KIRAI_EXPORT int kirai_add_rmsnorm_f32(float* resid, const void* delta, const float* weight, void* out,
+                                       const int* row_index, float* resid_out, int rows, int hidden, float eps,
+                                       cudaStream_t stream) {
+    return add_rmsnorm_launch<float>(resid, delta, weight, out, row_index, resid_out, rows, hidden, eps, stream);
+}
+KIRAI_EXPORT int kirai_add_rmsnorm_bf16(float* resid, const void* delta, const float* weight, void* out,
+                                        const int* row_index, float* resid_out, int rows, int hidden, float eps,
+                                        cudaStream_t stream) {
+    return add_rmsnorm_launch<bf16>(resid, delta, weight, out, row_index, resid_out, rows, hidden, eps, stream);
+}
+
+// ------------------------------------------------------------- per-head RMSNorm
+// x is [rows, heads, width] with a row stride (in elements); one warp per head.
+template <typename T>
+__global__ void head_rmsnorm_kernel(T* __restrict__ x, const float* __restrict__ weight, int rows, int heads, int width,
+                                    long row_stride, float eps) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= rows * heads) return;
+    T* head = x + (size_t)(warp / heads) * row_stride + (size_t)(warp % heads) * width;
+    float acc = 0.0f;
+    for (int i = lane; i < width; i += 32) {
+        const float v = to_f32<T>(head[i]);
+        acc = fmaf(v, v, acc);
+    }
+    acc = warp_sum(acc);
+    const float variance = acc / (float)width + eps;
+    const float scale = variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
+    for (int i = lane; i < width; i += 32) head[i] = from_f32<T>(to_f32<T>(head[i]) * scale * weight[i]);
+}
+
+template <typename T>
+static int head_rmsnorm_launch(void* x, const float* weight, int rows, int heads, int width, long row_stride, float eps,
+                               cudaStream_t stream) {
+    const long warps = (long)rows * heads;
+    if (warps <= 0) return 0;
+    const int threads = 128;
+    const long blocks = (warps * 32 + threads - 1) / threads;
+    head_rmsnorm_kernel<T><<<(unsigned)blocks, threads, 0, stream>>>((T*)x, weight, rows, heads, width, row_stride, eps);
+    return launch_status();
+}
+KIRAI_EXPORT int kirai_head_rmsnorm_f32(void* x, const float* weight, int rows, int heads, int width, long row_stride,
+                                        float eps, cudaStream_t stream) {
+    return head_rmsnorm_launch<float>(x, weight, rows, heads, width, row_stride, eps, stream);
+}
+KIRAI_EXPORT int kirai_head_rmsnorm_bf16(void* x, const float* weight, int rows, int heads, int width, long row_stride,
+                                         float eps, cudaStream_t stream) {
+    return head_rmsnorm_launch<bf16>(x, weight, rows, heads, width, row_stride, eps, stream);
+}
+
+// ------------------------------------------------------------------------ rotary
+// x is [rows, heads, width] with a row stride; pairs (i, i + rotary_dim/2), angle
+// = float(position) * inv_freq[i], all in 32-bit.
+template <typename T>
+__global__ void rope_kernel(T* __restrict__ x, const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                            int rows, int heads, int width, int rotary_dim, long row_stride) {
+    const int half = rotary_dim >> 1;
+    const long total = (long)rows * heads * half;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int i = (int)(idx % half);
+    const int head = (int)((idx / half) % heads);
+    const int row = (int)(idx / ((long)half * heads));
+    T* base = x + (size_t)row * row_stride + (size_t)head * width;
+    const float angle = (float)positions[row] * inv_freq[i];
+    float s, c;
+    sincosf(angle, &s, &c);
+    const float first = to_f32<T>(base[i]);
+    const float second = to_f32<T>(base[i + half]);
+    base[i] = from_f32<T>(first * c - second * s);
+    base[i + half] = from_f32<T>(second * c + first * s);
+}
+
+template <typename T>
+static int rope_launch(void* x, const int* positions, const float* inv_freq, int rows, int heads, int width,
+                       int rotary_dim, long row_stride, cudaStream_t stream) {
+    if (rotary_dim <= 0 || (rotary_dim & 1) || rotary_dim > width) return KIRAI_ERR_BAD_SIZE;
+    const long total = (long)rows * heads * (rotary_dim / 2);
+    if (total <= 0) return 0;
+    const int threads = 256;
+    rope_kernel<T><<<(unsigned)((total + threads - 1) / threads), threads, 0, stream>>>((T*)x, positions, inv_freq, rows,
+                                                                                      heads, width, rotary_dim,
+                                                                                      row_stride);
+    return launch_status();
+}
+KIRAI_EXPORT int kirai_rope_f32(void* x, const int* positions, const float* inv_freq, int rows, int heads, int width,
+                                int rotary_dim, long row_stride, cudaStream_t stream) {
+    return rope_launch<float>(x, positions, inv_freq, rows, heads, width, rotary_dim, row_stride, stream);
+}
+KIRAI_EXPORT int kirai_rope_bf16(void* x, const int* positions, const float* inv_freq, int rows, int heads, int width,
+                                 int rotary_dim, long row_stride, cudaStream_t stream) {
+    return rope_launch<bf16>(x, positions, inv_freq, rows, heads, width, rotary_dim, row_stride, stream);
+}
+
+// ---------------------------------------------------------------- paged KV write
+// One cache layer is [num_pages, 2, kv_heads, page_size, head_dim]; key rows at
+// index 0 and value rows at index 1 of the second axis.  The row of a token is
+// found through its request's block table: page = table[request, pos / page_size].
+__device__ __forceinline__ long kv_row_offset(int page, int which, int kv_head, int slot, int kv_heads, int page_size,
+                                              int head_dim) {
+    return ((((long)page * 2 + which) * kv_heads + kv_head) * page_size + slot) * (long)head_dim;
+}
+
+template <typename T>
+__global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v, T* __restrict__ cache,
+                                const int* __restrict__ block_table, const int* __restrict__ request_of_token,
+                                const int* __restrict__ positions, int rows, int kv_heads, int head_dim,
+                                long k_row_stride, long v_row_stride, int page_size, int table_width, int num_pages,
+                                int* __restrict__ error_flag) {
+    const long total = (long)rows * kv_heads * head_dim;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int i = (int)(idx % head_dim);
+    const int head = (int)((idx / head_dim) % kv_heads);
+    const int row = (int)(idx / ((long)head_dim * kv_heads));
+    const int pos = positions[row];
+    const int logical = pos / page_size;
+    const int page = logical < table_width ? block_table[(long)request_of_token[row] * table_width + logical] : -1;
+    if (page < 0 || page >= num_pages) {
+        atomicExch(error_flag, 2);
+        return;
+    }
+    const int slot = pos % page_size;
+    cache[kv_row_offset(page, 0, head, slot, kv_heads, page_size, head_dim) + i] =
+        k[(size_t)row * k_row_stride + (size_t)head * head_dim + i];
+    cache[kv_row_offset(page, 1, head, slot, kv_heads, page_size, head_dim) + i] =
+        v[(size_t)row * v_row_stride + (size_t)head * head_dim + i];
+}
+
+template <typename T>
+static int kv_write_launch(const void* k, const void* v, void* cache, const int* block_table,
+                           const int* request_of_token, const int* positions, int rows, int kv_heads, int head_dim,
+                           long k_row_stride, long v_row_stride, int page_size, int table_width, int num_pages,
+                           int* error_flag, cudaStream_t stream) {
+    const long total = (long)rows * kv_heads * head_dim;
+    if (total <= 0) return 0;
+    const int threads = 256;
+    kv_write_kernel<T><<<(unsigned)((total + threads - 1) / threads), threads, 0, stream>>>(
+        (const T*)k, (const T*)v, (T*)cache, block_table, request_of_token, positions, rows, kv_heads, head_dim,
+        k_row_stride, v_row_stride, page_size, table_width, num_pages, error_flag);
+    return launch_status();
+}
+KIRAI_EXPORT int kirai_kv_write_f32(const void* k, const void* v, void* cache, const int* block_table,
+                                    const int* request_of_token, const int* positions, int rows, int kv_heads,
+                                    int head_dim, long k_row_stride, long v_row_stride, int page_size, int table_width,
+                                    int num_pages, int* error_flag, cudaStream_t stream) {
+    return kv_write_launch<float>(k, v, cache, block_table, request_of_token, positions, rows, kv_heads, head_dim,
+                                  k_row_stride, v_row_stride, page_size, table_width, num_pages, error_flag, stream);
+}
+KIRAI_EXPORT int kirai_kv_write_bf16(const void* k, const void* v, void* cache, const int* block_table,
+                                     const int* request_of_token, const int* positions, int rows, int kv_heads,
+                                     int head_dim, long k_row_stride, long v_row_stride, int page_size, int table_width,
+                                     int num_pages, int* error_flag, cudaStream_t stream) {
+    return kv_write_launch<bf16>(k, v, cache, block_table, request_of_token, positions, rows, kv_heads, head_dim,
+                                 k_row_stride, v_row_stride, page_size, table_width, num_pages, error_flag, stream);
+}
+
+// ------------------------------------ fused per-head norm + rotary + cache write
+// qkv is [rows, (q_heads + 2 kv_heads) * head_dim]: query heads, then key heads,
+// then value heads.  One warp per (row, head): query heads are normed and
+// rotated in place; key heads are normed, rotated and written to the cache page
+// (and back in place); value heads are copied to the cache.  With norm weights
+// absent (nullptr) the norm is skipped; with inv_freq absent the rotation is.
+// head_dim <= 512 (16 values per lane).
+#define FUSED_MAX_PAIRS 8
+template <typename T>
+__global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_weight,
+                                             const float* __restrict__ k_weight, const float* __restrict__ inv_freq,
+                                             T* __restrict__ cache, const int* __restrict__ block_table,
+                                             const int* __restrict__ request_of_token,
+                                             const int* __restrict__ positions, int rows, int q_heads, int kv_heads,
+                                             int head_dim, int rotary_dim, float eps, int page_size, int table_width,
+                                             int num_pages, int write_cache, int* __restrict__ error_flag) {
+    const int heads_total = q_heads + 2 * kv_heads;
+    const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= (long)rows * heads_total) return;
+    const int row = (int)(warp / heads_total);
+    const int head = (int)(warp % heads_total);
+    T* x = qkv + (size_t)row * heads_total * head_dim + (size_t)head * head_dim;
+    const int pos = positions[row];
+    const bool is_q = head < q_heads;
+    const bool is_k = !is_q && head < q_heads + kv_heads;
+    const int kv_head = is_q ? 0 : (is_k ? head - q_heads : head - q_heads - kv_heads);
+
+    T* dst = nullptr;
+    if (!is_q && write_cache) {
+        const int logical = pos / page_size;
+        const int page =
+            logical < table_width ? block_table[(long)request_of_token[row] * table_width + logical] : -1;
+        if (page < 0 || page >= num_pages) {
+            if (lane == 0) atomicExch(error_flag, 2);
+            return;
+        }
+        dst = cache + kv_row_offset(page, is_k ? 0 : 1, kv_head, pos % page_size, kv_heads, page_size, head_dim);
+    }
+    if (!is_q && !is_k) {  // value head: plain copy
+        if (dst)
+            for (int i = lane; i < head_dim; i += 32) dst[i] = x[i];
+        return;
+    }
+    const int half_dim = head_dim >> 1;  // values are held as (i, i + head_dim/2) so that the norm sees all of them
+    float lo[FUSED_MAX_PAIRS], hi[FUSED_MAX_PAIRS];
+    float acc = 0.0f;
+#pragma unroll
+    for (int j = 0; j < FUSED_MAX_PAIRS; ++j) {
+        const int i = lane + 32 * j;
+        lo[j] = hi[j] = 0.0f;
+        if (i < half_dim) {
+            lo[j] = to_f32<T>(x[i]);
+            hi[j] = to_f32<T>(x[i + half_dim]);
+            acc = fmaf(lo[j], lo[j], acc);
+            acc = fmaf(hi[j], hi[j], acc);
+        }
+    }
+    const float* weight = is_q ? q_weight : k_weight;
+    float scale = 1.0f;
+    if (weight) {
+        acc = warp_sum(acc);
+        const float variance = acc / (float)head_dim + eps;
+        scale = variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
+    }
+    const int half_rot = rotary_dim >> 1;
+#pragma unroll
+    for (int j = 0; j < FUSED_MAX_PAIRS; ++j) {
+        const int i = lane + 32 * j;
+        if (i < half_dim) {
+            float a = lo[j], b = hi[j];
+            if (weight) {
+                a = a * scale * weight[i];
+                b = b * scale * weight[i + half_dim];
+            }
+            lo[j] = a;
+            hi[j] = b;
+        }
+    }
+    // Rotation pairs are (i, i + rotary_dim/2); with rotary_dim == head_dim they are the (lo, hi) held above.
+    if (inv_freq && rotary_dim == head_dim) {
+#pragma unroll
+        for (int j = 0; j < FUSED_MAX_PAIRS; ++j) {
+            const int i = lane + 32 * j;
+            if (i < half_rot) {
+                float s, c;
+                sincosf((float)pos * inv_freq[i], &s, &c);
+                const float a = lo[j], b = hi[j];
+                lo[j] = a * c - b * s;
+                hi[j] = b * c + a * s;
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < FUSED_MAX_PAIRS; ++j) {
+        const int i = lane + 32 * j;
+        if (i < half_dim) {
+            const T a = from_f32<T>(lo[j]), b = from_f32<T>(hi[j]);
+            x[i] = a;
+            x[i + half_dim] = b;
+            if (dst) {
+                dst[i] = a;
+                dst[i + half_dim] = b;
+            }
+        }
+    }
+}
+
+template <typename T>
+static int qk_norm_rope_kv_write_launch(void* qkv, const float* q_weight, const float* k_weight, const float* inv_freq,
+                                        void* cache, const int* block_table, const int* request_of_token,
+                                        const int* positions, int rows, int q_heads, int kv_heads, int head_dim,
+                                        int rotary_dim, float eps, int page_size, int table_width, int num_pages,
+                                        int write_cache, int* error_flag, cudaStream_t stream) {
+    if (head_dim > 64 * FUSED_MAX_PAIRS || (head_dim & 1)) return KIRAI_ERR_BAD_SIZE;
+    if (inv_freq && rotary_dim != head_dim) return KIRAI_ERR_UNSUPPORTED;  // partial rotation goes through rope_kernel
+    const long warps = (long)rows * (q_heads + 2 * kv_heads);
+    if (warps <= 0) return 0;
+    const int threads = 128;
+    qk_norm_rope_kv_write_kernel<T><<<(unsigned)((warps * 32 + threads - 1) / threads), threads, 0, stream>>>(
+        (T*)qkv, q_weight, k_weight, inv_freq, (T*)cache, block_table, request_of_token, positions, rows, q_heads,
+        kv_heads, head_dim, rotary_dim, eps, page_size, table_width, num_pages, write_cache, error_flag);
+    return launch_status();
+}
+KIRAI_EXPORT int kirai_qk_norm_rope_kv_write_f32(void* qkv, const float* q_weight, const float* k_weight,
+                                                 const float* inv_freq, void* cache, const int* block_table,
+                                                 const int* request_of_token, const int* positions, int rows,
+                                                 int q_heads, int kv_heads, int head_dim, int rotary_dim, float eps,
+                                                 int page_size, int table_width, int num_pages, int write_cache,
+                                                 int* error_flag, cudaStream_t stream) {
+    return qk_norm_rope_kv_write_launch<float>(qkv, q_weight, k_weight, inv_freq, cache, block_table, request_of_token,
+                                               positions, rows, q_heads, kv_heads, head_dim, rotary_dim, eps, page_size,
+                                               table_width, num_pages, write_cache, error_flag, stream);
+}
+KIRAI_EXPORT int kirai_qk_norm_rope_kv_write_bf16(void* qkv, const float* q_weight, const float* k_weight,
+                                                  const float* inv_freq, void* cache, const int* block_table,
+                                                  const int* request_of_token, const int* positions, int rows,
+                                                  int q_heads, int kv_heads, int head_dim, int rotary_dim, float eps,
+                                                  int page_size, int table_width, int num_pages, int write_cache,
+                                                  int* error_flag, cudaStream_t stream) {
+    return qk_norm_rope_kv_write_launch<bf16>(qkv, q_weight, k_weight, inv_freq, cache, block_table, request_of_token,
+                                              positions, rows, q_heads, kv_heads, head_dim, rotary_dim, eps, page_size,
+                                              table_width, num_pages, write_cache, error_flag, stream);
+}
+
+// ------------------------------------------------------------------------ SwiGLU
+// gate_up is [rows, 2 * inter]: the gate half, then the up half.  out = silu(gate) * up.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long rows, int inter) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * inter) return;
+    const long row = idx / inter;
+    const int i = (int)(idx % inter);
+    const float g = to_f32<T>(gate_up[row * 2 * inter + i]);
+    const float u = to_f32<T>(gate_up[row * 2 * inter + inter + i]);
+    out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+}
+template <typename T>
+static int swiglu_launch(const void* gate_up, void* out, int rows, int inter, cudaStream_t stream) {
+    const long total = (long)rows * inter;
+    if (total <= 0) return 0;
+    const int threads = 256;
+    swiglu_kernel<T><<<(unsigned)((total + threads - 1) / threads), threads, 0, stream>>>((const T*)gate_up, (T*)out,
+                                                                                        rows, inter);
+    return launch_status();
+}
+KIRAI_EXPORT int kirai_swiglu_f32(const void* gate_up, void* out, int rows, int inter, cudaStream_t stream) {
+    return swiglu_launch<float>(gate_up, out, rows, inter, stream);
+}
+KIRAI_EXPORT int kirai_swiglu_bf16(const void* gate_up, void* out, int rows, int inter, cudaStream_t stream) {
+    return swiglu_launch<bf16>(gate_up, out, rows, inter, stream);
+}
+
+// ------------------------------------------------------- residual accumulate
+// resid (32-bit) += delta, for arrangements whose sub-layer outputs are not
+// followed by a norm that could fold the add in.
+template <typename T>
+__global__ void add_residual_kernel(float* __restrict__ resid, const T* __restrict__ delta, long count) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < count) resid[idx] += to_f32<T>(delta[idx]);
+}
+template <typename T>
+static int add_residual_launch(float* resid, const void* delta, long count, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    add_residual_kernel<T><<<(unsigned)((count + 255) / 256), 256, 0, stream>>>(resid, (const T*)delta, count);
+    return launch_status();
+}
+KIRAI_EXPORT int kirai_add_residual_f32(float* resid, const void* delta, long count, cudaStream_t stream) {
+    return add_residual_launch<float>(resid, delta, count, stream);
+}
+KIRAI_EXPORT int kirai_add_residual_bf16(float* resid, const void* delta, long count, cudaStream_t stream) {
+    return add_residual_launch<bf16>(resid, delta, count, stream);
+}

@@ -1,0 +1,309 @@
+"""Python bindings of the hand-written CUDA kernels.
+
+Every function takes torch tensors that live on a CUDA device, checks dtypes,
+shapes and strides on the host, and launches on torch's current stream through
+the library's ``extern "C"`` entry points.  There is no CPU fallback: a tensor
+on another device, or a missing library, is an error.
+
+Kernels that can meet a bad index (a token id outside the vocabulary, a block
+table entry without a page) do not fault: they skip the access and set a device
+flag that ``check_device_errors`` reads.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+_lib = None
+_error_flags = {}
+
+_ERROR_NAMES = {
+    1: "a token id is outside the vocabulary",
+    2: "a token's position has no page in its request's block table (cache write)",
+    3: "a key position has no page in its request's block table (attention read)",
+    4: "a bounded wait inside a kernel ran out",
+}
+
+_REFUSALS = {
+    -2: "a size is outside what the kernel takes",
+    -3: "a pointer or stride is not aligned as the kernel needs",
+    -4: "this combination of options is not built",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def library() -> ctypes.CDLL:
+    """The shared library, built on first use."""
+    global _lib
+    if _lib is None:
+        path = _build.build()
+        _lib = ctypes.CDLL(path)
+    return _lib
+
+
+def _check(status: int, name: str) -> None:
+    if status == 0:
+        return
+    if status in _REFUSALS:
+        raise KernelError(f"{name}: refused: {_REFUSALS[status]}")
+    raise KernelError(f"{name}: CUDA error {status} at launch")
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(tensor: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
+
+
+def _need_cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for tensor in tensors:
+        if tensor is not None and not tensor.is_cuda:
+            raise KernelError("kernels run on CUDA tensors only; there is no CPU path")
+
+
+def _suffix(dtype: torch.dtype) -> str:
+    if dtype == torch.float32:
+        return "f32"
+    if dtype == torch.bfloat16:
+        return "bf16"
+    raise KernelError(f"kernels take float32 or bfloat16 activations, got {dtype}")
+
+
+def _call(name: str, *args) -> None:
+    fn = getattr(library(), name)
+    fn.restype = ctypes.c_int
+    _check(fn(*args), name)
+
+
+_i = ctypes.c_int
+_l = ctypes.c_long
+_f = ctypes.c_float
+
+
+def error_flag(device: torch.device) -> torch.Tensor:
+    """The int32 device word that kernels set instead of faulting."""
+    key = torch.device(device)
+    if key.index is None:
+        key = torch.device("cuda", torch.cuda.current_device())
+    if key not in _error_flags:
+        _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=key)
+    return _error_flags[key]
+
+
+def check_device_errors(device: torch.device) -> None:
+    """Reads the device flag (synchronises) and raises if a kernel set it."""
+    flag = error_flag(device)
+    value = int(flag.item())
+    if value != 0:
+        flag.zero_()
+        raise KernelError(f"a kernel reported: {_ERROR_NAMES.get(value, f'error {value}')}")
+
+
+# ------------------------------------------------------------------- embedding
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rows ``ids`` of ``table`` [V, H] widened to the 32-bit residual stream [T, H]."""
+    _need_cuda(table, ids)
+    assert table.dim() == 2 and table.is_contiguous() and ids.dtype == torch.int32 and ids.is_contiguous()
+    tokens, hidden = ids.numel(), table.shape[1]
+    if out is None:
+        out = torch.empty((tokens, hidden), dtype=torch.float32, device=table.device)
+    _call(f"kirai_embedding_{_suffix(table.dtype)}", _ptr(table), _ptr(ids), _ptr(out), _i(tokens), _i(hidden),
+          _i(table.shape[0]), _ptr(error_flag(table.device)), _stream())
+    return out
+
+
+# --------------------------------------------------------------------- RMSNorm
+def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, row_index: Optional[torch.Tensor] = None):
+    """``resid += delta`` (32-bit, in place), then RMSNorm of the sum in ``out_dtype``.
+
+    With ``row_index`` only those rows are produced; the residual stream is left as it
+    is and the summed rows are returned as the second value.
+    """
+    _need_cuda(resid, delta, weight, row_index)
+    assert resid.dtype == torch.float32 and resid.dim() == 2 and resid.is_contiguous()
+    assert weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == resid.shape[1]
+    hidden = resid.shape[1]
+    if delta is not None:
+        assert delta.shape == resid.shape and delta.dtype == out_dtype and delta.is_contiguous()
+    rows = resid.shape[0] if row_index is None else row_index.numel()
+    out = torch.empty((rows, hidden), dtype=out_dtype, device=resid.device)
+    summed = None
+    if row_index is not None:
+        assert row_index.dtype == torch.int32 and row_index.is_contiguous()
+        summed = torch.empty((rows, hidden), dtype=torch.float32, device=resid.device)
+    _call(f"kirai_add_rmsnorm_{_suffix(out_dtype)}", _ptr(resid), _ptr(delta), _ptr(weight), _ptr(out),
+          _ptr(row_index), _ptr(summed), _i(rows), _i(hidden), _f(eps), _stream())
+    return (out, summed) if row_index is not None else out
+
+
+def add_into_residual(resid: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """``resid`` (32-bit) += ``delta``, in place."""
+    _need_cuda(resid, delta)
+    assert resid.dtype == torch.float32 and resid.is_contiguous() and delta.is_contiguous() and delta.shape == resid.shape
+    _call(f"kirai_add_residual_{_suffix(delta.dtype)}", _ptr(resid), _ptr(delta), _l(resid.numel()), _stream())
+    return resid
+
+
+def _head_view(x: torch.Tensor):
+    """[rows, heads, width] with a dense (heads, width) part; returns the row stride."""
+    assert x.dim() == 3 and x.stride(2) == 1 and x.stride(1) == x.shape[2], "heads must be dense within a row"
+    return x.shape[0], x.shape[1], x.shape[2], x.stride(0)
+
+
+def head_rmsnorm_(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm over the last axis of ``x`` [rows, heads, width], in place, one weight [width] for all heads."""
+    _need_cuda(x, weight)
+    rows, heads, width, stride = _head_view(x)
+    assert weight.dtype == torch.float32 and weight.numel() == width and weight.is_contiguous()
+    _call(f"kirai_head_rmsnorm_{_suffix(x.dtype)}", _ptr(x), _ptr(weight), _i(rows), _i(heads), _i(width), _l(stride),
+          _f(eps), _stream())
+    return x
+
+
+# ---------------------------------------------------------------------- rotary
+def rope_(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int) -> torch.Tensor:
+    """Half-split rotary embedding of ``x`` [rows, heads, width] in place."""
+    _need_cuda(x, positions, inv_freq)
+    rows, heads, width, stride = _head_view(x)
+    assert positions.dtype == torch.int32 and positions.numel() == rows and positions.is_contiguous()
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2 and inv_freq.is_contiguous()
+    _call(f"kirai_rope_{_suffix(x.dtype)}", _ptr(x), _ptr(positions), _ptr(inv_freq), _i(rows), _i(heads), _i(width),
+          _i(rotary_dim), _l(stride), _stream())
+    return x
+
+
+# ------------------------------------------------------------------- cache write
+def _cache_dims(cache: torch.Tensor):
+    assert cache.dim() == 5 and cache.shape[1] == 2 and cache.is_contiguous(), "cache layer is [pages, 2, kv_heads, page, d]"
+    return cache.shape[0], cache.shape[2], cache.shape[3], cache.shape[4]
+
+
+def kv_write(k: torch.Tensor, v: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+             request_of_token: torch.Tensor, positions: torch.Tensor) -> None:
+    """Writes key rows ``k`` and value rows ``v`` [T, kv_heads, d] to their pages."""
+    _need_cuda(k, v, cache, block_table, request_of_token, positions)
+    num_pages, kv_heads, page_size, head_dim = _cache_dims(cache)
+    rows, kh, kd, k_stride = _head_view(k)
+    rows_v, vh, vd, v_stride = _head_view(v)
+    assert (rows, kh, kd) == (rows_v, vh, vd) and (kh, kd) == (kv_heads, head_dim)
+    assert k.dtype == cache.dtype == v.dtype
+    assert block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous()
+    _call(f"kirai_kv_write_{_suffix(k.dtype)}", _ptr(k), _ptr(v), _ptr(cache), _ptr(block_table),
+          _ptr(request_of_token), _ptr(positions), _i(rows), _i(kv_heads), _i(head_dim), _l(k_stride), _l(v_stride),
+          _i(page_size), _i(block_table.shape[1]), _i(num_pages), _ptr(error_flag(k.device)), _stream())
+
+
+def qk_norm_rope_kv_write_(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int,
+                           q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                           inv_freq: Optional[torch.Tensor], eps: float, cache: Optional[torch.Tensor],
+                           block_table: torch.Tensor, request_of_token: torch.Tensor, positions: torch.Tensor,
+                           write_cache: bool = True) -> None:
+    """Fused per-head q/k RMSNorm, rotation and paged cache write on ``qkv`` [T, (nq + 2 nkv) d], in place."""
+    _need_cuda(qkv, q_weight, k_weight, inv_freq, cache, block_table, request_of_token, positions)
+    assert qkv.dim() == 2 and qkv.is_contiguous() and qkv.shape[1] == (q_heads + 2 * kv_heads) * head_dim
+    num_pages, page_size = 0, 1
+    if kv_heads == 0:
+        write_cache = False
+    if write_cache:
+        num_pages, c_heads, page_size, c_dim = _cache_dims(cache)
+        assert (c_heads, c_dim) == (kv_heads, head_dim) and cache.dtype == qkv.dtype
+    for w in (q_weight, k_weight):
+        assert w is None or (w.dtype == torch.float32 and w.numel() == head_dim and w.is_contiguous())
+    assert inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2)
+    _call(f"kirai_qk_norm_rope_kv_write_{_suffix(qkv.dtype)}", _ptr(qkv), _ptr(q_weight), _ptr(k_weight),
+          _ptr(inv_freq), _ptr(cache if write_cache else None), _ptr(block_table), _ptr(request_of_token),
+          _ptr(positions), _i(qkv.shape[0]), _i(q_heads), _i(kv_heads), _i(head_dim), _i(head_dim), _f(eps),
+          _i(page_size), _i(block_table.shape[1]), _i(num_pages), _i(1 if write_cache else 0),
+          _ptr(error_flag(qkv.device)), _stream())
+
+
+# --------------------------------------------------------------------- attention
+def paged_attention_plain(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                          request_of_token: torch.Tensor, positions: torch.Tensor, window: Optional[int],
+                          scale: float) -> torch.Tensor:
+    """Causal grouped-query attention of ``q`` [T, nq, d] over the paged cache; returns [T, nq * d]."""
+    _need_cuda(q, cache, block_table, request_of_token, positions)
+    num_pages, kv_heads, page_size, head_dim = _cache_dims(cache)
+    rows, q_heads, qd, q_stride = _head_view(q)
+    assert qd == head_dim and q.dtype == cache.dtype
+    out = torch.empty((rows, q_heads * head_dim), dtype=q.dtype, device=q.device)
+    _call(f"kirai_paged_attention_plain_{_suffix(q.dtype)}", _ptr(q), _ptr(cache), _ptr(out), _ptr(block_table),
+          _ptr(request_of_token), _ptr(positions), _i(rows), _i(q_heads), _i(kv_heads), _i(head_dim), _l(q_stride),
+          _i(page_size), _i(block_table.shape[1]), _i(num_pages), _i(window or 0), _f(scale),
+          _ptr(error_flag(q.device)), _stream())
+    return out
+
+
+def paged_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, batch, window: Optional[int],
+                    scale: float) -> torch.Tensor:
+    """Attention of the product path over the paged cache for the tokens of ``batch``
+    (a kirai_b200.engine.batch.StepBatch): picks the kernel by dtype and by what the batch holds."""
+    return paged_attention_plain(q, cache, block_table, batch.request_of_token, batch.positions, window, scale)
+
+
+# ------------------------------------------------------------------------ linear
+def linear_plain(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``x`` [M, K] times ``weight`` [N, K] transposed on the CUDA cores with 32-bit FMAs."""
+    _need_cuda(x, weight)
+    assert x.dim() == 2 and x.stride(1) == 1 and weight.dim() == 2 and weight.is_contiguous()
+    assert x.shape[1] == weight.shape[1] and x.dtype == weight.dtype
+    out_dtype = out_dtype or x.dtype
+    m, k, n = x.shape[0], x.shape[1], weight.shape[0]
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    if x.dtype == torch.float32:
+        assert out_dtype == torch.float32
+        name = "kirai_gemm_simt_f32"
+    else:
+        name = "kirai_gemm_simt_bf16" if out_dtype == torch.bfloat16 else "kirai_gemm_simt_bf16_out_f32"
+    _call(name, _ptr(x), _ptr(weight), _ptr(out), _i(m), _i(n), _i(k), _l(x.stride(0)), _l(n), _stream())
+    return out
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """The linear layer of the product path: 32-bit FMAs for float32, tensor cores for bfloat16."""
+    return linear_plain(x, weight, out_dtype)
+
+
+# ------------------------------------------------------------------------ SwiGLU
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up for ``gate_up`` [T, 2 I] (gate half first); returns [T, I]."""
+    _need_cuda(gate_up)
+    assert gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0
+    rows, inter = gate_up.shape[0], gate_up.shape[1] // 2
+    out = torch.empty((rows, inter), dtype=gate_up.dtype, device=gate_up.device)
+    _call(f"kirai_swiglu_{_suffix(gate_up.dtype)}", _ptr(gate_up), _ptr(out), _i(rows), _i(inter), _stream())
+    return out
+
+
+# ---------------------------------------------------------------------- sampling
+def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
+    """Index of the greatest logit of each row, the lowest index on ties."""
+    _need_cuda(logits)
+    assert logits.dim() == 2 and logits.dtype == torch.float32 and logits.is_contiguous()
+    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    _call("kirai_argmax_rows", _ptr(logits), _ptr(out), _i(logits.shape[0]), _i(logits.shape[1]), _stream())
+    return out
+
+
+def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, draw: torch.Tensor) -> torch.Tensor:
+    """One token per row: greedy where temperature is 0, else nucleus sampling with the row's draw."""
+    _need_cuda(logits, temperature, top_p, draw)
+    assert logits.dim() == 2 and logits.dtype == torch.float32 and logits.is_contiguous()
+    rows = logits.shape[0]
+    for t in (temperature, top_p, draw):
+        assert t.dtype == torch.float32 and t.numel() == rows and t.is_contiguous()
+    scratch = torch.empty_like(logits)
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _call("kirai_sample_rows", _ptr(logits), _ptr(scratch), _ptr(temperature), _ptr(top_p), _ptr(draw), _ptr(out),
+          _i(rows), _i(logits.shape[1]), _stream())
+    return out

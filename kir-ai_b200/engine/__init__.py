@@ -1,0 +1,5 @@
+"""Step function, scheduler and the generation engine."""
+from .batch import StepBatch, StepEntry, build_batch
+from .step import OutOfPages, StepError, run_step
+
+__all__ = ["StepBatch", "StepEntry", "build_batch", "OutOfPages", "StepError", "run_step"]

@@ -1,0 +1,126 @@
+"""Interfaces of the parts a model is put together from.
+
+A model is an embedding, a list of blocks, an order in which the blocks run, a
+final norm and an output head.  A block arranges two norms, a mixer (attention
+here) and a feed-forward.  Every part takes its sizes and constants as
+constructor arguments, names the tensors it wants in ``weight_specs`` and picks
+them up in ``load``; no part knows which model it sits in.  ``forward`` methods
+work on a flat batch of tokens described by a ``StepBatch``
+(kirai_b200.engine.batch).
+
+The reference reaches the same separation with functions that take a spec and
+flags (crates/llm-backend/src/core/native_attention.rs:11-17,109-116 generic
+attention dims, crates/llm-backend/src/core/qwen/ops/attention_full.rs:41-48
+per-variant flags).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Optional, Tuple
+
+import torch
+
+
+@dataclass(frozen=True)
+class WeightSpec:
+    """Shape and role of one named tensor.  The role tells the random-weights
+    mode how to fill it and the loader which dtype family it must have:
+    ``linear`` and ``embedding`` are floating matrices, ``norm`` a floating
+    vector, ``int_table`` an integer table (kept as int32)."""
+
+    shape: Tuple[int, ...]
+    role: str = "linear"
+
+
+@dataclass(frozen=True)
+class KVCacheNeed:
+    """A mixer that keeps keys and values of earlier tokens in pages.
+    ``window`` None keeps every token; a width W keeps the last W."""
+
+    kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A mixer that keeps a fixed-size state per request in a slot."""
+
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class Runtime:
+    """Where and in which precision a model runs: the device, the dtype of
+    weights and activations (``torch.float32`` for the true 32-bit path,
+    ``torch.bfloat16`` for serving), and the kernel namespace ``ops``."""
+
+    def __init__(self, device: torch.device | str, dtype: torch.dtype, ops=None):
+        self.device = torch.device(device)
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"runtime dtype must be float32 or bfloat16, got {dtype}")
+        self.dtype = dtype
+        if ops is None:
+            from ..csrc import ops as _ops
+
+            ops = _ops
+        self.ops = ops
+
+
+class Part:
+    """Base of every part: the tensors it wants, and how it takes them."""
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {}
+
+    def load(self, weights, rt: Runtime) -> None:  # weights: kirai_b200.weights.loader.WeightSource
+        self.rt = rt
+
+
+class Norm(Part):
+    """Normalisation over the last axis.
+
+    ``forward(x)`` returns the normed rows in the runtime dtype.
+    ``add_forward(resid, delta)`` first adds ``delta`` (runtime dtype, may be None)
+    into the 32-bit residual stream ``resid`` in place, then norms the sum.
+    """
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def add_forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Puts positions into queries and keys.  ``apply`` rewrites ``q`` [T, nq, d]
+    and ``k`` [T, nkv, d] (row-strided views allowed) in place for the absolute
+    ``positions`` [T] (int32, on the device)."""
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    """Mixes information between the tokens of a request.
+
+    ``cache_need`` says what it keeps between steps (None, KVCacheNeed or
+    StateNeed).  ``forward(x, batch, cache, write_cache)`` gets the normed
+    hidden rows [T, H], the batch description and a view of its cache layer
+    (kirai_b200.cache.manager.KVLayerView or StateLayerView); when
+    ``write_cache`` is false it reads a cache that another layer filled in this
+    step and must not write it.
+    """
+
+    def cache_need(self):
+        return None
+
+    def forward(self, x: torch.Tensor, batch, cache, write_cache: bool = True) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    """Token-wise transformation: ``forward(x, batch)`` maps [T, H] to [T, H]."""
+
+    def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
+        raise NotImplementedError
