@@ -26,8 +26,9 @@ SOURCES = [
     "gemm_simt.cu",
     "attention_plain.cu",
     "sampling.cu",
+    "gemm_tcgen05.cu",
 ]
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "sm100.cuh", "tensor_map.cuh"]
 
 NVCC_FLAGS = [
     "-gencode",
