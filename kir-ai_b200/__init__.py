@@ -6,7 +6,10 @@ step function, scheduler and engine (``engine``), sampling (``sampling``) and
 the CUDA kernels with their bindings (``csrc``).
 """
 from . import registry  # registers the built-in architectures
+from .engine.engine import Engine, GenerationOutput
 from .registry import load_config, register_architecture, registered_architectures
+from .sampling.params import SamplingParams
 
-__all__ = ["registry", "load_config", "register_architecture", "registered_architectures"]
+__all__ = ["registry", "load_config", "register_architecture", "registered_architectures", "Engine",
+           "GenerationOutput", "SamplingParams"]
 __version__ = "0.1.0"

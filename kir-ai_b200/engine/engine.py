@@ -1,0 +1,132 @@
+"""The Python entry point: ``Engine.generate`` (token ids in, token ids out).
+
+The engine owns a loaded model with its cache (``ModelRunner``), a scheduler and
+the sampler, and runs the loop: schedule, step, sample, update.  Option names
+and defaults follow the reference's command line where it has them
+(crates/llm-engine/src/main.rs:423-475: ``--snapshot``, ``--max-new-tokens`` 256,
+``--max-prefill-tokens`` 2048, ``--max-concurrent-requests`` 4); the reference
+ignores ``generation_config.json`` and so does this engine.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Union
+
+import torch
+
+from ..sampling import rng
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import sample
+from .batch import StepEntry
+from .runner import ModelRunner
+from .scheduler import Request, Scheduler
+
+MAX_NEW_TOKENS_CAP = 65_536       # crates/llm-engine/src/main.rs:25-29
+MAX_PREFILL_TOKENS_CAP = 262_144
+MAX_CONCURRENT_CAP = 256
+
+
+@dataclass
+class GenerationOutput:
+    token_ids: List[int]
+    finish_reason: str
+    prompt_tokens: int
+    completion_tokens: int
+    preemptions: int = 0
+
+
+class Engine:
+    def __init__(self, snapshot: Optional[str] = None, *, config=None, random_weights_seed: Optional[int] = None,
+                 dtype: str = "bfloat16", device: str = "cuda:0", max_new_tokens: int = 256,
+                 max_prefill_tokens: int = 2048, max_concurrent_requests: int = 4, page_size: int = 16,
+                 max_cache_tokens: Optional[int] = None, prefill_chunk: Optional[int] = None,
+                 runner: Optional[ModelRunner] = None):
+        if not 1 <= max_new_tokens <= MAX_NEW_TOKENS_CAP:
+            raise ValueError(f"--max-new-tokens must be within 1..{MAX_NEW_TOKENS_CAP}")
+        if not 1 <= max_prefill_tokens <= MAX_PREFILL_TOKENS_CAP:
+            raise ValueError(f"--max-prefill-tokens must be within 1..{MAX_PREFILL_TOKENS_CAP}")
+        if not 1 <= max_concurrent_requests <= MAX_CONCURRENT_CAP:
+            raise ValueError(f"--max-concurrent-requests must be within 1..{MAX_CONCURRENT_CAP}")
+        if runner is None:
+            if snapshot is not None and config is None:
+                from ..registry import load_config
+
+                config = load_config(snapshot)
+            if config is None:
+                raise ValueError("give a snapshot folder, or a configuration with random_weights_seed")
+            max_positions = getattr(config, "max_position_embeddings", None)
+            if max_cache_tokens is None:
+                per_request = max(max_prefill_tokens + max_new_tokens, 4096)
+                if max_positions:
+                    per_request = min(per_request, max_positions)
+                max_cache_tokens = max_concurrent_requests * per_request
+            common = dict(dtype=dtype, device=device, page_size=page_size, max_tokens=max_cache_tokens,
+                          num_slots=max_concurrent_requests)
+            if random_weights_seed is not None:
+                runner = ModelRunner.from_random(config, random_weights_seed, **common)
+            else:
+                runner = ModelRunner.from_folder(snapshot, **common)
+        self.runner = runner
+        self.max_new_tokens = max_new_tokens
+        self.scheduler = Scheduler(
+            runner.cache, max_batched_tokens=max_prefill_tokens, max_running=max_concurrent_requests,
+            prefill_chunk=prefill_chunk, max_positions=runner.model.plan.max_positions,
+            default_max_new_tokens=max_new_tokens,
+        )
+        self._next_id = 0
+        self.counters = {"steps": 0, "prompt_tokens": 0, "generated_tokens": 0}
+
+    # ------------------------------------------------------------------ generate
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> Request:
+        params = params or SamplingParams()
+        vocab = self.runner.model.plan.vocab_size
+        for token in prompt:
+            if not 0 <= int(token) < vocab:
+                raise ValueError(f"token id {token} outside vocab size {vocab}")
+        request = self.scheduler.add(self._next_id, prompt, params)
+        self._next_id += 1
+        return request
+
+    def step(self) -> List[Request]:
+        """One scheduler step; returns the requests that finished in it."""
+        scheduled = self.scheduler.schedule()
+        entries = []
+        for item in scheduled:
+            tokens = item.request.tokens[item.first : item.first + item.count]
+            entries.append(StepEntry(item.request.pages, tokens, [item.count - 1] if item.sample else []))
+        logits = self.runner.step(entries, check_errors=False)
+        sampled: List[Optional[int]] = [None] * len(scheduled)
+        if logits is not None:
+            rows = [i for i, item in enumerate(scheduled) if item.sample]
+            requests = [scheduled[i].request for i in rows]
+            tokens = sample(
+                self.runner.rt.ops, logits,
+                [r.params.temperature for r in requests], [r.params.top_p for r in requests],
+                [rng.draw(r.seed, r.draws_used) for r in requests],
+            ).cpu().tolist()
+            for i, token in zip(rows, tokens):
+                sampled[i] = token
+        self.runner.rt.ops.check_device_errors(self.runner.rt.device)
+        self.counters["steps"] += 1
+        return self.scheduler.update(scheduled, sampled)
+
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 params: Union[None, SamplingParams, Sequence[SamplingParams]] = None) -> List[GenerationOutput]:
+        """Generates a continuation for every prompt (lists of token ids); results in the prompts' order."""
+        if params is None or isinstance(params, SamplingParams):
+            params = [params or SamplingParams()] * len(prompts)
+        if len(params) != len(prompts):
+            raise ValueError("one SamplingParams per prompt, or one for all")
+        requests = [self.add_request(prompt, p) for prompt, p in zip(prompts, params)]
+        while self.scheduler.has_work():
+            self.step()
+        outputs = []
+        for request in requests:
+            self.counters["prompt_tokens"] += len(request.prompt)
+            self.counters["generated_tokens"] += len(request.output)
+            outputs.append(GenerationOutput(list(request.output), request.finish_reason or "length", len(request.prompt),
+                                            len(request.output), request.preemptions))
+        return outputs
+
+    def stats(self) -> dict:
+        return {**self.counters, "scheduler": dict(self.scheduler.stats), "cache": self.runner.cache.stats()}

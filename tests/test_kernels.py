@@ -1,0 +1,278 @@
+"""Each kernel alone against plain torch arithmetic, at sizes other than the engine's tiny models:
+head sizes in steps of 16, head counts and groups that are no power of two, widths and
+vocabularies that are no power of two."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import kirai_b200  # noqa: F401
+    from kirai_b200.csrc import ops as module
+
+    module.library()
+    return module
+
+
+def tol(dtype, scale=1.0):
+    return (2e-5 if dtype == torch.float32 else 1.6e-2) * scale
+
+
+def rand(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    generator = torch.Generator(device="cpu").manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=generator) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab,hidden", [(1000, 72), (257, 200)])
+def test_embedding(ops, dtype, vocab, hidden):
+    table = rand(vocab, hidden, dtype=dtype)
+    ids = torch.tensor([0, vocab - 1, 5, 5, 17], dtype=torch.int32, device=DEV)
+    out = ops.embedding(table, ids)
+    assert out.dtype == torch.float32 and torch.equal(out, table.float()[ids.long()])
+    ops.embedding(table, torch.tensor([vocab], dtype=torch.int32, device=DEV))
+    with pytest.raises(ops.KernelError):
+        ops.check_device_errors(torch.device(DEV))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,hidden,eps", [(7, 200, 1e-5), (33, 4104, 1e-6), (1, 48, 0.0)])
+def test_add_rmsnorm(ops, dtype, rows, hidden, eps):
+    resid = rand(rows, hidden, scale=2.0)
+    delta = rand(rows, hidden, dtype=dtype, seed=1)
+    weight = 1.0 + 0.1 * rand(hidden, seed=2)
+    expected_sum = resid + delta.float()
+    expected = expected_sum * torch.rsqrt((expected_sum ** 2).mean(-1, keepdim=True) + eps) * weight
+    stream = resid.clone()
+    out = ops.add_rmsnorm(stream, delta, weight, eps, dtype)
+    assert torch.allclose(stream, expected_sum, atol=1e-6)
+    assert float((out.float() - expected).abs().max()) <= tol(dtype, float(expected.abs().max()))
+    # chosen rows only: the stream stays as it is
+    index = torch.tensor([rows - 1, 0], dtype=torch.int32, device=DEV)
+    stream2 = resid.clone()
+    out_rows, summed = ops.add_rmsnorm(stream2, delta, weight, eps, dtype, row_index=index)
+    assert torch.equal(stream2, resid) and torch.allclose(summed, expected_sum[index.long()], atol=1e-6)
+    assert float((out_rows.float() - expected[index.long()]).abs().max()) <= tol(dtype, float(expected.abs().max()))
+    zero = ops.add_rmsnorm(torch.zeros(2, hidden, device=DEV), None, weight, 0.0, dtype)
+    assert torch.equal(zero.float(), torch.zeros(2, hidden, device=DEV))  # mean + eps == 0 gives scale 0
+
+
+def rope_reference(x, positions, inv_freq, rotary_dim):
+    half = rotary_dim // 2
+    angle = positions.float()[:, None] * inv_freq[None, :]
+    cos, sin = torch.cos(angle.double()).float()[:, None, :], torch.sin(angle.double()).float()[:, None, :]
+    out = x.clone().float()
+    first, second = x[..., :half].float(), x[..., half:rotary_dim].float()
+    out[..., :half] = first * cos - second * sin
+    out[..., half:rotary_dim] = second * cos + first * sin
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,width,rotary", [(3, 48, 48), (5, 80, 32), (2, 256, 256)])
+def test_rope_and_head_rmsnorm(ops, dtype, heads, width, rotary):
+    rows = 19
+    buffer = rand(rows, heads * width + 24, dtype=dtype)  # heads live inside a wider row
+    x = buffer[:, : heads * width].unflatten(1, (heads, width))
+    positions = torch.tensor([0, 1, 2, 3, 100, 4095, 40959, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16, 17, 31], dtype=torch.int32, device=DEV)
+    inv_freq = torch.pow(torch.tensor(1e6), -(2.0 * torch.arange(rotary // 2)) / rotary).to(DEV)
+    expected = rope_reference(x, positions, inv_freq, rotary)
+    before_tail = buffer[:, heads * width :].clone()
+    ops.rope_(x, positions, inv_freq, rotary)
+    assert float((x.float() - expected).abs().max()) <= tol(dtype, float(expected.abs().max()))
+    assert torch.equal(buffer[:, heads * width :], before_tail)
+    weight = 1.0 + 0.1 * rand(width, seed=5)
+    y = x.clone()
+    expected = y.float() * torch.rsqrt((y.float() ** 2).mean(-1, keepdim=True) + 1e-5) * weight
+    ops.head_rmsnorm_(y, weight, 1e-5)
+    assert float((y.float() - expected).abs().max()) <= tol(dtype, float(expected.abs().max()))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,inter", [(5, 200), (130, 1000)])
+def test_swiglu(ops, dtype, rows, inter):
+    gate_up = rand(rows, 2 * inter, dtype=dtype, scale=3.0)
+    g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+    expected = g / (1.0 + torch.exp(-g)) * u
+    out = ops.swiglu(gate_up)
+    assert float((out.float() - expected).abs().max()) <= tol(dtype, float(expected.abs().max()))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 40, 24), (7, 130, 200), (70, 257, 72), (129, 64, 1000)])
+def test_linear_plain_float32_is_exact_enough(ops, m, n, k):
+    x, w = rand(m, k), rand(n, k, seed=3)
+    expected = (x.double() @ w.double().T).float()
+    out = ops.linear_plain(x, w)
+    assert float((out - expected).abs().max()) <= 1e-5 * math.sqrt(k)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 128, 64), (3, 200, 136), (16, 1000, 512), (48, 520, 1032), (64, 4096, 264),
+                                   (65, 264, 192), (200, 96, 64), (300, 1000, 520), (1024, 768, 2048)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_linear_tcgen05_against_plain(ops, m, n, k, out_dtype):
+    x, w = rand(m, k, dtype=torch.bfloat16, scale=0.5), rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=3)
+    expected = x.float() @ w.float().T
+    out = ops.linear_tcgen05(x, w, out_dtype)
+    plain = ops.linear_plain(x, w, out_dtype)
+    ops.check_device_errors(torch.device(DEV))
+    bound = (2e-5 * math.sqrt(k) if out_dtype == torch.float32 else 1e-2) * float(expected.abs().max())
+    assert float((out.float() - expected).abs().max()) <= bound
+    assert float((out.float() - plain.float()).abs().max()) <= bound
+    if m <= 64:  # split along K through the workspace
+        split = ops.linear_tcgen05(x, w, out_dtype, splits=3)
+        assert float((split.float() - expected).abs().max()) <= bound
+    # a row-strided input (a slice of a wider buffer)
+    wide = torch.zeros(m, k + 16, dtype=torch.bfloat16, device=DEV)
+    wide[:, :k] = x
+    strided = ops.linear_tcgen05(wide[:, :k], w, out_dtype)
+    assert torch.equal(strided, out)
+
+
+def test_linear_refuses_rows_that_tma_cannot_read(ops):
+    x, w = rand(4, 70, dtype=torch.bfloat16), rand(32, 70, dtype=torch.bfloat16)
+    with pytest.raises(ops.KernelError):
+        ops.linear_tcgen05(x, w)
+    out = ops.linear(x, w)  # the product path takes the CUDA-core kernel for such a K
+    assert float((out.float() - x.float() @ w.float().T).abs().max()) <= 0.05
+
+
+def paged_setup(dtype, lengths, kv_heads, head_dim, page_size, seed=0):
+    """Random keys and values for requests of the given lengths, scattered over shuffled pages."""
+    generator = torch.Generator().manual_seed(seed)
+    pages_per = [-(-n // page_size) for n in lengths]
+    num_pages = sum(pages_per) + 3
+    order = torch.randperm(num_pages, generator=generator).tolist()
+    cache = torch.zeros(num_pages, 2, kv_heads, page_size, head_dim, dtype=dtype, device=DEV)
+    width = max(pages_per)
+    table = torch.full((len(lengths), width), -1, dtype=torch.int32)
+    keys, values = [], []
+    cursor = 0
+    for r, n in enumerate(lengths):
+        k = (torch.randn(n, kv_heads, head_dim, generator=generator)).to(dtype)
+        v = (torch.randn(n, kv_heads, head_dim, generator=generator)).to(dtype)
+        keys.append(k)
+        values.append(v)
+        for p in range(pages_per[r]):
+            table[r, p] = order[cursor]
+            cursor += 1
+    return cache, table.to(DEV), keys, values
+
+
+def attention_reference(q, k, v, positions, window, scale):
+    """q [T, nq, d] at absolute positions of one request; k, v [n, nkv, d] all its rows."""
+    nq, nkv = q.shape[1], k.shape[1]
+    out = torch.zeros(q.shape, dtype=torch.float32)
+    for t, pos in enumerate(positions):
+        lo = 0 if not window else max(0, pos - window + 1)
+        for h in range(nq):
+            kv = h // (nq // nkv)
+            s = (k[lo : pos + 1, kv].float() @ q[t, h].float()) * scale
+            p = torch.softmax(s, dim=0)
+            out[t, h] = p @ v[lo : pos + 1, kv].float()
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,window",
+                         [(6, 2, 48, 8, None), (5, 5, 16, 4, 7), (8, 1, 128, 16, 40), (3, 1, 80, 1, None)])
+def test_kv_write_and_paged_attention(ops, dtype, q_heads, kv_heads, head_dim, page_size, window):
+    lengths = [37, 5, 64]
+    cache, table, keys, values = paged_setup(dtype, lengths, kv_heads, head_dim, page_size)
+    # write every row through the kernel, in two uneven portions per request
+    for cut in (0, 1):
+        rows_k, rows_v, req, pos = [], [], [], []
+        for r, n in enumerate(lengths):
+            lo, hi = (0, n // 3) if cut == 0 else (n // 3, n)
+            rows_k.append(keys[r][lo:hi]); rows_v.append(values[r][lo:hi])
+            req += [r] * (hi - lo); pos += list(range(lo, hi))
+        k_rows, v_rows = torch.cat(rows_k).to(DEV).contiguous(), torch.cat(rows_v).to(DEV).contiguous()
+        ops.kv_write(k_rows, v_rows, cache, table, torch.tensor(req, dtype=torch.int32, device=DEV),
+                     torch.tensor(pos, dtype=torch.int32, device=DEV))
+    for r, n in enumerate(lengths):
+        for p in (0, n - 1):
+            page = int(table[r, p // page_size])
+            assert torch.equal(cache[page, 0, :, p % page_size].cpu(), keys[r][p])
+            assert torch.equal(cache[page, 1, :, p % page_size].cpu(), values[r][p])
+    # queries: the last 9 positions of request 0, one of request 1, the last 2 of request 2
+    spans = [(0, list(range(28, 37))), (1, [4]), (2, [62, 63])]
+    generator = torch.Generator().manual_seed(9)
+    q = torch.randn(sum(len(s[1]) for s in spans), q_heads, head_dim, generator=generator).to(dtype)
+    req = [r for r, ps in spans for _ in ps]
+    pos = [p for _, ps in spans for p in ps]
+    scale = head_dim ** -0.5
+    out = ops.paged_attention_plain(q.to(DEV), cache, table, torch.tensor(req, dtype=torch.int32, device=DEV),
+                                    torch.tensor(pos, dtype=torch.int32, device=DEV), window, scale)
+    ops.check_device_errors(torch.device(DEV))
+    row = 0
+    for r, ps in spans:
+        expected = attention_reference(q[row : row + len(ps)], keys[r], values[r], ps, window, scale)
+        got = out[row : row + len(ps)].float().cpu().unflatten(1, (q_heads, head_dim))
+        assert float((got - expected).abs().max()) <= tol(dtype, 4.0)
+        row += len(ps)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("q_heads,kv_heads,head_dim", [(6, 2, 48), (4, 4, 16), (8, 2, 128), (2, 1, 512)])
+def test_fused_norm_rope_cache_write_equals_the_separate_kernels(ops, dtype, q_heads, kv_heads, head_dim):
+    page_size, lengths = 8, [11, 30]
+    cache_a, table, _, _ = paged_setup(dtype, lengths, kv_heads, head_dim, page_size)
+    cache_b = cache_a.clone()
+    rows = sum(lengths)
+    qkv = rand(rows, (q_heads + 2 * kv_heads) * head_dim, dtype=dtype)
+    req = torch.tensor([0] * 11 + [1] * 30, dtype=torch.int32, device=DEV)
+    pos = torch.tensor(list(range(11)) + list(range(30)), dtype=torch.int32, device=DEV)
+    qw, kw = 1.0 + 0.1 * rand(head_dim, seed=1), 1.0 + 0.1 * rand(head_dim, seed=2)
+    inv_freq = torch.pow(torch.tensor(1e4), -(2.0 * torch.arange(head_dim // 2)) / head_dim).to(DEV)
+    fused = qkv.clone()
+    ops.qk_norm_rope_kv_write_(fused, q_heads, kv_heads, head_dim, qw, kw, inv_freq, 1e-6, cache_a, table, req, pos)
+    separate = qkv.clone()
+    nq, nkv, d = q_heads, kv_heads, head_dim
+    q = separate[:, : nq * d].unflatten(1, (nq, d))
+    k = separate[:, nq * d : (nq + nkv) * d].unflatten(1, (nkv, d))
+    v = separate[:, (nq + nkv) * d :].unflatten(1, (nkv, d))
+    ops.head_rmsnorm_(q, qw, 1e-6); ops.head_rmsnorm_(k, kw, 1e-6)
+    ops.rope_(q, pos, inv_freq, d); ops.rope_(k, pos, inv_freq, d)
+    ops.kv_write(k, v, cache_b, table, req, pos)
+    ops.check_device_errors(torch.device(DEV))
+    # the fused kernel keeps the normed value in 32-bit where the separate kernels round in between
+    bound = 0.0 if dtype == torch.float32 else 0.05
+    assert float((fused.float() - separate.float()).abs().max()) <= bound + 1e-6
+    assert float((cache_a.float() - cache_b.float()).abs().max()) <= bound + 1e-6
+    # against the formulas in 32-bit
+    x = qkv.float()[:, : nq * d].unflatten(1, (nq, d))
+    normed = x * torch.rsqrt((x ** 2).mean(-1, keepdim=True) + 1e-6) * qw
+    expected = rope_reference(normed, pos, inv_freq, d)
+    assert float((fused[:, : nq * d].float().unflatten(1, (nq, d)) - expected).abs().max()) <= tol(dtype, float(expected.abs().max()))
+
+
+@pytest.mark.parametrize("vocab", [257, 1000, 151936])
+def test_argmax_and_sampling(ops, vocab):
+    import plain_qwen3 as plain
+
+    generator = torch.Generator().manual_seed(vocab)
+    logits = torch.randn(6, vocab, generator=generator) * 3.0
+    logits[0, 5] = logits[0, 77] = 50.0        # a tie: the lower index wins
+    logits[1, vocab - 1] = 60.0                # the last entry
+    dev = logits.to(DEV)
+    assert ops.argmax_rows(dev).tolist() == [plain.argmax_first(row) for row in logits]
+    temperatures = torch.tensor([0.0, 0.7, 1.0, 1.3, 0.7, 2.0])
+    top_ps = torch.tensor([1.0, 1.0, 0.9, 0.5, 0.05, 1.0])
+    for draw in (0.0, 0.25, 0.5, 0.83, 0.999999):
+        draws = torch.full((6,), draw)
+        got = ops.sample_rows(dev, temperatures.to(DEV), top_ps.to(DEV), draws.to(DEV)).tolist()
+        for row in range(6):
+            if temperatures[row] == 0:
+                expected = plain.argmax_first(logits[row])
+            else:
+                expected = plain.sample_top_p(logits[row], float(temperatures[row]), float(top_ps[row]), draw)
+            if got[row] != expected:  # only a draw within rounding of a boundary may land on the neighbour
+                probs = torch.softmax(logits[row] / temperatures[row], 0)
+                order = sorted(range(vocab), key=lambda i: (-float(probs[i]), i))
+                assert abs(order.index(got[row]) - order.index(expected)) == 1, (row, draw, got[row], expected)
