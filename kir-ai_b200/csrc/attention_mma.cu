@@ -1,0 +1,551 @@
+// bf16 causal grouped-query attention over the paged cache on the tensor cores
+// (warp-level mma.m16n8k16, 32-bit accumulation, softmax in 32-bit registers).
+//
+// Two kernels share one warp-level routine that folds a tile of keys into a
+// running (max, sum, output) state, flash-attention style:
+//
+//  * the prompt kernel: one CTA per (request, kv head, tile of 64 query rows),
+//    where the query rows enumerate (token, head of the group) pairs, so that
+//    the heads of a group share each key/value tile; its 4 warps own 16 rows
+//    each and walk the key tiles together, loads double-buffered by cp.async;
+//  * the decode kernel, for batches in which every request brings one token:
+//    one CTA per (request, kv head, split of the context); the group's heads
+//    are the (few) query rows, each warp walks its own key tiles, the warps'
+//    states are merged in shared memory, and with several splits a second
+//    kernel merges the splits' partial states.
+//
+// Keys are visible to a row at position pos when lo <= j <= pos, lo = max(0,
+// pos - window + 1) with a window, else 0 (same rule as the plain kernel).
+// Key tiles start at absolute multiples of the tile size, so which keys share
+// a tile does not depend on how a prompt was cut.  head_dim: any multiple of 8
+// up to 256 (the tile is padded with zeros to 64, 128 or 256 columns).
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// A tile in shared memory is [rows][D] bf16; the 16-byte chunk c of row r sits at chunk c ^ (r & 7),
+// which keeps the 8 rows of an ldmatrix on different banks.
+template <int D>
+__device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
+    return (uint32_t)(row * D * 2 + ((chunk ^ (row & 7)) << 4));
+}
+
+struct PagedKV {
+    const bf16* cache;        // [num_pages, 2, kv_heads, page_size, head_dim]
+    const int* table;         // this request's block table row
+    int table_width, num_pages, kv_heads, page_size, head_dim, kv_head;
+};
+
+// Loads `ROWS` key rows and value rows starting at key j0 into shared tiles (zero where the key is
+// outside [j_lo, j_hi], the column is beyond head_dim, or the page is missing).
+template <int D, int ROWS, int THREADS>
+__device__ __forceinline__ void load_kv_tile(const PagedKV& kv, int j0, int j_lo, int j_hi, uint32_t k_smem,
+                                             uint32_t v_smem, int tid, int* error_flag) {
+    constexpr int CH = D / 8;
+    const int chunks_used = kv.head_dim / 8;
+    for (int id = tid; id < ROWS * CH; id += THREADS) {
+        const int row = id / CH, chunk = id % CH;
+        const int j = j0 + row;
+        bool valid = j >= j_lo && j <= j_hi && chunk < chunks_used;
+        const bf16* k_src = kv.cache;
+        const bf16* v_src = kv.cache;
+        if (valid) {
+            const int logical = j / kv.page_size;
+            const int page = logical < kv.table_width ? kv.table[logical] : -1;
+            if (page < 0 || page >= kv.num_pages) {
+                atomicExch(error_flag, 3);
+                valid = false;
+            } else {
+                const long base = ((((long)page * 2) * kv.kv_heads + kv.kv_head) * kv.page_size + (j % kv.page_size)) *
+                                      (long)kv.head_dim + chunk * 8;
+                k_src = kv.cache + base;
+                v_src = kv.cache + base + (long)kv.kv_heads * kv.page_size * kv.head_dim;
+            }
+        }
+        cp_async_16(k_smem + tile_offset<D>(row, chunk), k_src, valid);
+        cp_async_16(v_smem + tile_offset<D>(row, chunk), v_src, valid);
+    }
+}
+
+// Running softmax state of the two rows (g and g + 8) that a thread of an m16 tile holds.
+template <int D>
+struct WarpState {
+    float m[2], l[2];
+    float o[D / 8][4];
+    __device__ __forceinline__ void init() {
+        m[0] = m[1] = -INFINITY;
+        l[0] = l[1] = 0.0f;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+    }
+};
+
+// Folds BN keys (tile at k_smem / v_smem, first key j0) into the state of this warp's 16 query
+// rows, whose A-operand tile is at q_smem rows [q_row0, q_row0 + 16).  Row r (0..15) sees key j
+// when lo[r] <= j <= hi[r]; the thread holds rows g = lane / 4 (index 0) and g + 8 (index 1).
+template <int D, int BN>
+__device__ __forceinline__ void warp_attend(WarpState<D>& st, uint32_t q_smem, int q_row0, uint32_t k_smem,
+                                            uint32_t v_smem, int j0, const int (&lo)[2], const int (&hi)[2],
+                                            float scale_log2, int lane) {
+    float s[BN / 8][4];
+#pragma unroll
+    for (int n = 0; n < BN / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
+    // S = Q K^T
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t a[4];
+        {
+            const int row = q_row0 + (lane & 15);
+            const int chunk = kk * 2 + (lane >> 4);
+            ldmatrix_x4(q_smem + tile_offset<D>(row, chunk), a[0], a[1], a[2], a[3]);
+        }
+#pragma unroll
+        for (int n2 = 0; n2 < BN / 16; ++n2) {
+            // two n-tiles (16 keys) per ldmatrix.x4: matrices (keys 0-7, k lo), (keys 0-7, k hi), (keys 8-15, k lo), (keys 8-15, k hi)
+            uint32_t b0, b1, b2, b3;
+            const int row = n2 * 16 + (lane & 7) + ((lane >> 4) << 3);
+            const int chunk = kk * 2 + ((lane >> 3) & 1);
+            ldmatrix_x4(k_smem + tile_offset<D>(row, chunk), b0, b1, b2, b3);
+            mma_bf16_16816(s[2 * n2], a, b0, b1);
+            mma_bf16_16816(s[2 * n2 + 1], a, b2, b3);
+        }
+    }
+    // mask, running maximum
+    const int col0 = j0 + 2 * (lane & 3);
+    float m_new[2] = {st.m[0], st.m[1]};
+#pragma unroll
+    for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const int j = col0 + n * 8 + (e & 1);
+            const bool visible = j >= lo[r] && j <= hi[r];
+            s[n][e] = visible ? s[n][e] * scale_log2 : -INFINITY;
+            m_new[r] = fmaxf(m_new[r], s[n][e]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 1));
+        m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 2));
+    }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        m_use[r] = m_new[r] == -INFINITY ? 0.0f : m_new[r];  // a row that has seen no key yet
+        corr[r] = exp2f(st.m[r] - m_use[r]);                  // exp2(-inf) = 0 on first contact
+        st.m[r] = m_new[r];
+    }
+    float row_sum[2] = {0.0f, 0.0f};
+    uint32_t p[BN / 16][4];  // P as A-operand tiles of 16 keys
+#pragma unroll
+    for (int n = 0; n < BN / 8; ++n) {
+        const float p0 = exp2f(s[n][0] - m_use[0]), p1 = exp2f(s[n][1] - m_use[0]);
+        const float p2 = exp2f(s[n][2] - m_use[1]), p3 = exp2f(s[n][3] - m_use[1]);
+        row_sum[0] += p0 + p1;
+        row_sum[1] += p2 + p3;
+        // accumulator layout of two neighbouring n-tiles is the A layout of one k16 tile
+        p[n >> 1][(n & 1) * 2 + 0] = pack_bf16(p0, p1);
+        p[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) st.l[r] = st.l[r] * corr[r] + row_sum[r];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+        st.o[n][0] *= corr[0];
+        st.o[n][1] *= corr[0];
+        st.o[n][2] *= corr[1];
+        st.o[n][3] *= corr[1];
+    }
+    // O += P V
+#pragma unroll
+    for (int kk = 0; kk < BN / 16; ++kk) {
+#pragma unroll
+        for (int n2 = 0; n2 < D / 16; ++n2) {
+            // V rows are keys (k), columns head dims (n): transposed 8x8 loads give the col-major B operand
+            uint32_t b0, b1, b2, b3;
+            const int row = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+            const int chunk = n2 * 2 + (lane >> 4);
+            ldmatrix_x4_trans(v_smem + tile_offset<D>(row, chunk), b0, b1, b2, b3);
+            mma_bf16_16816(st.o[2 * n2], p[kk], b0, b1);
+            mma_bf16_16816(st.o[2 * n2 + 1], p[kk], b2, b3);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ prompt kernel
+#define PF_WARPS 4
+#define PF_ROWS 64
+#define PF_BN 64
+
+template <int D>
+__global__ void __launch_bounds__(PF_WARPS * 32)
+attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, bf16* __restrict__ out,
+                         const int* __restrict__ block_table, const int* __restrict__ query_start,
+                         const int* __restrict__ context_len, int q_heads, int kv_heads, int head_dim,
+                         long q_row_stride, int page_size, int table_width, int num_pages, int window, float scale_log2,
+                         int* __restrict__ error_flag) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int tile = blockIdx.x, kv_head = blockIdx.y, req = blockIdx.z;
+    const int group = q_heads / kv_heads;
+    const int q_begin = query_start[req];
+    const int q_len = query_start[req + 1] - q_begin;
+    const int rows_total = q_len * group;
+    const int row0 = tile * PF_ROWS;
+    if (row0 >= rows_total) return;
+    const int ctx = context_len[req];
+    const int start_pos = ctx - q_len;  // position of the request's first new token
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    const uint32_t q_smem = smem_u32(smem);
+    const uint32_t kv_smem = q_smem + PF_ROWS * D * 2;  // [2 stages][K tile, V tile]
+    constexpr uint32_t TILE_BYTES = PF_BN * D * 2;
+
+    // Q tile: row r is token (row0 + r) / group, head kv_head * group + (row0 + r) % group
+    {
+        constexpr int CH = D / 8;
+        const int chunks_used = head_dim / 8;
+        for (int id = tid; id < PF_ROWS * CH; id += PF_WARPS * 32) {
+            const int r = id / CH, chunk = id % CH;
+            const int row = row0 + r;
+            const bool valid = row < rows_total && chunk < chunks_used;
+            const bf16* src = q;
+            if (valid) {
+                const int token = row / group, head = kv_head * group + row % group;
+                src = q + (size_t)(q_begin + token) * q_row_stride + (size_t)head * head_dim + chunk * 8;
+            }
+            cp_async_16(q_smem + tile_offset<D>(r, chunk), src, valid);
+        }
+    }
+    PagedKV kv{cache, block_table + (long)req * table_width, table_width, num_pages, kv_heads, page_size, head_dim, kv_head};
+
+    const int last_row = min(rows_total, row0 + PF_ROWS) - 1;
+    const int pos_first = start_pos + row0 / group;
+    const int pos_last = start_pos + last_row / group;
+    const int key_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+    const int first_tile = key_lo / PF_BN, last_tile = pos_last / PF_BN;
+
+    // per-thread rows g and g + 8 of this warp's 16
+    int lo[2], hi[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = row0 + warp * 16 + (lane >> 2) + r * 8;
+        if (row < rows_total) {
+            const int pos = start_pos + row / group;
+            hi[r] = pos;
+            lo[r] = window > 0 ? max(0, pos - window + 1) : 0;
+        } else {
+            hi[r] = -1;
+            lo[r] = 0;  // sees nothing
+        }
+    }
+    WarpState<D> st;
+    st.init();
+
+    load_kv_tile<D, PF_BN, PF_WARPS * 32>(kv, first_tile * PF_BN, key_lo, pos_last, kv_smem, kv_smem + TILE_BYTES, tid,
+                                          error_flag);
+    cp_async_commit();
+    for (int t = first_tile; t <= last_tile; ++t) {
+        const int stage = (t - first_tile) & 1;
+        if (t + 1 <= last_tile) {
+            const uint32_t next = kv_smem + (stage ^ 1) * 2 * TILE_BYTES;
+            load_kv_tile<D, PF_BN, PF_WARPS * 32>(kv, (t + 1) * PF_BN, key_lo, pos_last, next, next + TILE_BYTES, tid,
+                                                  error_flag);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const uint32_t k_s = kv_smem + stage * 2 * TILE_BYTES;
+        // a warp whose rows all end before this tile has nothing to add (uniform per warp)
+        const int warp_last_row = min(rows_total - 1, row0 + warp * 16 + 15);
+        const bool warp_active = row0 + warp * 16 < rows_total && (start_pos + warp_last_row / group) >= t * PF_BN;
+        if (warp_active)
+            warp_attend<D, PF_BN>(st, q_smem, warp * 16, k_s, k_s + TILE_BYTES, t * PF_BN, lo, hi, scale_log2, lane);
+        __syncthreads();  // the stage is free for the load after next
+    }
+    // normalise and store
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float l = st.l[r];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const int row = row0 + warp * 16 + (lane >> 2) + r * 8;
+        if (row >= rows_total) continue;
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        const int token = row / group, head = kv_head * group + row % group;
+        bf16* dst = out + ((size_t)(q_begin + token) * q_heads + head) * head_dim;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            const int col = n * 8 + 2 * (lane & 3);
+            if (col < head_dim)
+                *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(st.o[n][2 * r] * inv, st.o[n][2 * r + 1] * inv);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ decode kernel
+#define DC_WARPS 4
+// keys per warp tile: 32, or 16 for the widest heads so that the warps' double buffers fit shared memory
+template <int D>
+struct DecodeTile { static constexpr int BN = D > 128 ? 16 : 32; };
+
+// partial: [requests, q_heads, splits, head_dim + 2] floats: unnormalised output, then max (log2 domain), then sum.
+template <int D>
+__global__ void __launch_bounds__(DC_WARPS * 32)
+attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, bf16* __restrict__ out,
+                        float* __restrict__ partial, const int* __restrict__ block_table,
+                        const int* __restrict__ context_len, int q_heads, int kv_heads, int head_dim, long q_row_stride,
+                        int page_size, int table_width, int num_pages, int window, float scale_log2, int num_splits,
+                        int* __restrict__ error_flag) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int DC_BN = DecodeTile<D>::BN;
+    const int split = blockIdx.x, kv_head = blockIdx.y, req = blockIdx.z;
+    const int group = q_heads / kv_heads;  // <= 16 rows
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int ctx = context_len[req];
+    const int pos = ctx - 1;
+    const int key_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int first_tile = key_lo / DC_BN, last_tile = pos / DC_BN;
+    const int tiles = last_tile - first_tile + 1;
+    const int per_split = (tiles + num_splits - 1) / num_splits;
+    const int t_begin = first_tile + split * per_split;
+    const int t_end = min(last_tile + 1, t_begin + per_split);
+
+    const uint32_t q_smem = smem_u32(smem);                // [16][D]
+    const uint32_t kv_smem = q_smem + 16 * D * 2;          // [warps][2 stages][K tile, V tile]
+    constexpr uint32_t TILE_BYTES = DC_BN * D * 2;
+    float* merge = reinterpret_cast<float*>(smem + 16 * D * 2 + DC_WARPS * 4 * TILE_BYTES);  // [warps][16][D + 2]
+
+    {
+        constexpr int CH = D / 8;
+        const int chunks_used = head_dim / 8;
+        for (int id = tid; id < 16 * CH; id += DC_WARPS * 32) {
+            const int r = id / CH, chunk = id % CH;
+            const bool valid = r < group && chunk < chunks_used;
+            const bf16* src = valid ? q + (size_t)req * q_row_stride + (size_t)(kv_head * group + r) * head_dim + chunk * 8 : q;
+            cp_async_16(q_smem + tile_offset<D>(r, chunk), src, valid);
+        }
+        cp_async_commit();
+    }
+    PagedKV kv{cache, block_table + (long)req * table_width, table_width, num_pages, kv_heads, page_size, head_dim, kv_head};
+    int lo[2], hi[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = (lane >> 2) + r * 8;
+        hi[r] = row < group ? pos : -1;
+        lo[r] = key_lo;
+    }
+    WarpState<D> st;
+    st.init();
+    const uint32_t my_smem = kv_smem + warp * 4 * TILE_BYTES;
+    // each warp walks tiles t_begin + warp, + DC_WARPS, ... with its own double buffer
+    int t = t_begin + warp;
+    if (t < t_end) load_kv_tile<D, DC_BN, 32>(kv, t * DC_BN, key_lo, pos, my_smem, my_smem + TILE_BYTES, lane, error_flag);
+    cp_async_commit();
+    cp_async_wait<0>();  // the Q tile and the warps' first tiles
+    __syncthreads();
+    int stage = 0;
+    for (; t < t_end; t += DC_WARPS) {
+        const int next_t = t + DC_WARPS;
+        if (next_t < t_end) {
+            const uint32_t next = my_smem + (stage ^ 1) * 2 * TILE_BYTES;
+            load_kv_tile<D, DC_BN, 32>(kv, next_t * DC_BN, key_lo, pos, next, next + TILE_BYTES, lane, error_flag);
+        }
+        cp_async_commit();
+        const uint32_t k_s = my_smem + stage * 2 * TILE_BYTES;
+        warp_attend<D, DC_BN>(st, q_smem, 0, k_s, k_s + TILE_BYTES, t * DC_BN, lo, hi, scale_log2, lane);
+        cp_async_wait<0>();
+        __syncwarp();
+        stage ^= 1;
+    }
+    // merge the warps' states: every warp writes (o, m, l) of its rows, then 128 threads combine
+    constexpr int MS = D + 2;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float l = st.l[r];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const int row = (lane >> 2) + r * 8;
+        float* dst = merge + ((size_t)warp * 16 + row) * MS;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            const int col = n * 8 + 2 * (lane & 3);
+            dst[col] = st.o[n][2 * r];
+            dst[col + 1] = st.o[n][2 * r + 1];
+        }
+        if ((lane & 3) == 0) {
+            dst[D] = st.m[r];
+            dst[D + 1] = l;
+        }
+    }
+    __syncthreads();
+    for (int id = tid; id < group * head_dim; id += DC_WARPS * 32) {
+        const int row = id / head_dim, col = id % head_dim;
+        float m_all = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DC_WARPS; ++w) m_all = fmaxf(m_all, merge[((size_t)w * 16 + row) * MS + D]);
+        float acc = 0.0f, l_all = 0.0f;
+#pragma unroll
+        for (int w = 0; w < DC_WARPS; ++w) {
+            const float* src = merge + ((size_t)w * 16 + row) * MS;
+            const float weight = src[D] == -INFINITY ? 0.0f : exp2f(src[D] - m_all);
+            acc += src[col] * weight;
+            l_all += src[D + 1] * weight;
+        }
+        const int head = kv_head * group + row;
+        if (num_splits == 1) {
+            out[((size_t)req * q_heads + head) * head_dim + col] = from_f32<bf16>(l_all > 0.0f ? acc / l_all : 0.0f);
+        } else {
+            float* dst = partial + (((size_t)req * q_heads + head) * num_splits + split) * (head_dim + 2);
+            dst[col] = acc;
+            if (col == 0) {
+                dst[head_dim] = m_all;
+                dst[head_dim + 1] = l_all;
+            }
+        }
+    }
+}
+
+__global__ void attention_merge_splits_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int head_dim,
+                                              int num_splits) {
+    // one block per (request, head)
+    const size_t rh = blockIdx.x;
+    const float* base = partial + rh * num_splits * (head_dim + 2);
+    float m_all = -INFINITY;
+    for (int s = 0; s < num_splits; ++s) m_all = fmaxf(m_all, base[(size_t)s * (head_dim + 2) + head_dim]);
+    for (int col = threadIdx.x; col < head_dim; col += blockDim.x) {
+        float acc = 0.0f, l_all = 0.0f;
+        for (int s = 0; s < num_splits; ++s) {
+            const float* src = base + (size_t)s * (head_dim + 2);
+            const float weight = src[head_dim] == -INFINITY ? 0.0f : exp2f(src[head_dim] - m_all);
+            acc += src[col] * weight;
+            l_all += src[head_dim + 1] * weight;
+        }
+        out[rh * head_dim + col] = from_f32<bf16>(l_all > 0.0f ? acc / l_all : 0.0f);
+    }
+}
+
+template <int D>
+int prefill_launch(const void* q, const void* cache, void* out, const int* block_table, const int* query_start,
+                   const int* context_len, int requests, int max_query_len, int q_heads, int kv_heads, int head_dim,
+                   long q_row_stride, int page_size, int table_width, int num_pages, int window, float scale,
+                   int* error_flag, cudaStream_t stream) {
+    const int group = q_heads / kv_heads;
+    const size_t smem = (size_t)PF_ROWS * D * 2 + 4 * (size_t)PF_BN * D * 2;
+    auto kernel = attention_prefill_kernel<D>;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return (int)err;
+    dim3 grid((unsigned)(((long)max_query_len * group + PF_ROWS - 1) / PF_ROWS), kv_heads, requests);
+    kernel<<<grid, PF_WARPS * 32, smem, stream>>>((const bf16*)q, (const bf16*)cache, (bf16*)out, block_table,
+                                                 query_start, context_len, q_heads, kv_heads, head_dim, q_row_stride,
+                                                 page_size, table_width, num_pages, window,
+                                                 scale * 1.4426950408889634f, error_flag);
+    return launch_status();
+}
+
+template <int D>
+int decode_launch(const void* q, const void* cache, void* out, float* partial, const int* block_table,
+                  const int* context_len, int requests, int q_heads, int kv_heads, int head_dim, long q_row_stride,
+                  int page_size, int table_width, int num_pages, int window, float scale, int num_splits,
+                  int* error_flag, cudaStream_t stream) {
+    constexpr int DC_BN = DecodeTile<D>::BN;
+    const size_t smem = (size_t)16 * D * 2 + (size_t)DC_WARPS * 4 * DC_BN * D * 2 + (size_t)DC_WARPS * 16 * (D + 2) * 4;
+    auto kernel = attention_decode_kernel<D>;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return (int)err;
+    dim3 grid(num_splits, kv_heads, requests);
+    kernel<<<grid, DC_WARPS * 32, smem, stream>>>((const bf16*)q, (const bf16*)cache, (bf16*)out, partial, block_table,
+                                                 context_len, q_heads, kv_heads, head_dim, q_row_stride, page_size,
+                                                 table_width, num_pages, window, scale * 1.4426950408889634f,
+                                                 num_splits, error_flag);
+    int status = launch_status();
+    if (status || num_splits == 1) return status;
+    attention_merge_splits_kernel<<<requests * q_heads, 128, 0, stream>>>(partial, (bf16*)out, head_dim, num_splits);
+    return launch_status();
+}
+
+int check_common(int q_heads, int kv_heads, int head_dim, long q_row_stride, const void* q) {
+    if (kv_heads <= 0 || q_heads % kv_heads != 0) return KIRAI_ERR_BAD_SIZE;
+    if (head_dim <= 0 || head_dim > 256 || head_dim % 8 != 0) return KIRAI_ERR_BAD_SIZE;
+    if (q_row_stride % 8 != 0 || ((uintptr_t)q & 15)) return KIRAI_ERR_BAD_ALIGN;  // 16-byte row chunks
+    if (kv_heads > 65535) return KIRAI_ERR_BAD_SIZE;
+    return 0;
+}
+
+}  // namespace
+
+// Attention for the new tokens of a step: q [tokens, q_heads, head_dim] (row stride in elements),
+// requests described by query_start [requests + 1] and context_len [requests] (tokens in the cache
+// after this step, the new ones included).  out [tokens, q_heads * head_dim].
+KIRAI_EXPORT int kirai_attention_prefill_bf16(const void* q, const void* cache, void* out, const int* block_table,
+                                              const int* query_start, const int* context_len, int requests,
+                                              int max_query_len, int q_heads, int kv_heads, int head_dim,
+                                              long q_row_stride, int page_size, int table_width, int num_pages,
+                                              int window, float scale, int* error_flag, cudaStream_t stream) {
+    if (requests <= 0 || max_query_len <= 0) return 0;
+    int bad = check_common(q_heads, kv_heads, head_dim, q_row_stride, q);
+    if (bad) return bad;
+    if (requests > 65535) return KIRAI_ERR_BAD_SIZE;
+#define KIRAI_PF(D) \
+    return prefill_launch<D>(q, cache, out, block_table, query_start, context_len, requests, max_query_len, q_heads, \
+                             kv_heads, head_dim, q_row_stride, page_size, table_width, num_pages, window, scale, \
+                             error_flag, stream)
+    if (head_dim <= 64) KIRAI_PF(64);
+    if (head_dim <= 128) KIRAI_PF(128);
+    KIRAI_PF(256);
+#undef KIRAI_PF
+}
+
+// Attention for a batch in which every request brings exactly one token (token r belongs to request r).
+// With num_splits > 1, partial must hold requests * q_heads * num_splits * (head_dim + 2) floats.
+KIRAI_EXPORT int kirai_attention_decode_bf16(const void* q, const void* cache, void* out, float* partial,
+                                             const int* block_table, const int* context_len, int requests,
+                                             int q_heads, int kv_heads, int head_dim, long q_row_stride, int page_size,
+                                             int table_width, int num_pages, int window, float scale, int num_splits,
+                                             int* error_flag, cudaStream_t stream) {
+    if (requests <= 0) return 0;
+    int bad = check_common(q_heads, kv_heads, head_dim, q_row_stride, q);
+    if (bad) return bad;
+    if (q_heads / kv_heads > 16) return KIRAI_ERR_UNSUPPORTED;  // the group's heads are the rows of one m16 tile
+    if (num_splits < 1 || num_splits > 65535 || requests > 65535) return KIRAI_ERR_BAD_SIZE;
+    if (num_splits > 1 && !partial) return KIRAI_ERR_BAD_SIZE;
+#define KIRAI_DC(D) \
+    return decode_launch<D>(q, cache, out, partial, block_table, context_len, requests, q_heads, kv_heads, head_dim, \
+                            q_row_stride, page_size, table_width, num_pages, window, scale, num_splits, error_flag, \
+                            stream)
+    if (head_dim <= 64) KIRAI_DC(64);
+    if (head_dim <= 128) KIRAI_DC(128);
+    KIRAI_DC(256);
+#undef KIRAI_DC
+}

@@ -27,6 +27,7 @@ SOURCES = [
     "attention_plain.cu",
     "sampling.cu",
     "gemm_tcgen05.cu",
+    "attention_mma.cu",
 ]
 HEADERS = ["common.cuh", "sm100.cuh", "tensor_map.cuh"]
 

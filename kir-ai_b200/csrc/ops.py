@@ -244,11 +244,66 @@ def paged_attention_plain(q: torch.Tensor, cache: torch.Tensor, block_table: tor
     return out
 
 
+def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, query_start: torch.Tensor,
+                      context_len: torch.Tensor, max_query_len: int, window: Optional[int], scale: float) -> torch.Tensor:
+    """bf16 tensor-core attention for runs of new tokens (prompt portions, or any mix): q [T, nq, d]."""
+    _need_cuda(q, cache, block_table, query_start, context_len)
+    num_pages, kv_heads, page_size, head_dim = _cache_dims(cache)
+    rows, q_heads, qd, q_stride = _head_view(q)
+    assert qd == head_dim and q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
+    requests = context_len.numel()
+    assert query_start.numel() == requests + 1 and query_start.dtype == torch.int32 and context_len.dtype == torch.int32
+    out = torch.empty((rows, q_heads * head_dim), dtype=q.dtype, device=q.device)
+    _call("kirai_attention_prefill_bf16", _ptr(q), _ptr(cache), _ptr(out), _ptr(block_table), _ptr(query_start),
+          _ptr(context_len), _i(requests), _i(max_query_len), _i(q_heads), _i(kv_heads), _i(head_dim), _l(q_stride),
+          _i(page_size), _i(block_table.shape[1]), _i(num_pages), _i(window or 0), _f(scale),
+          _ptr(error_flag(q.device)), _stream())
+    return out
+
+
+def decode_splits(requests: int, kv_heads: int, max_context_len: int) -> int:
+    """How many CTAs share one (request, kv head) in the decode kernel: enough to fill the 148 SMs
+    about twice over, each split at least 256 keys long."""
+    ctas = max(1, requests * kv_heads)
+    by_fill = -(-296 // ctas)
+    by_length = max(1, max_context_len // 256)
+    return max(1, min(by_fill, by_length, 64))
+
+
+def attention_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, context_len: torch.Tensor,
+                     window: Optional[int], scale: float, num_splits: int = 1) -> torch.Tensor:
+    """bf16 tensor-core attention for a batch in which every request brings one token: q [R, nq, d]."""
+    _need_cuda(q, cache, block_table, context_len)
+    num_pages, kv_heads, page_size, head_dim = _cache_dims(cache)
+    rows, q_heads, qd, q_stride = _head_view(q)
+    assert qd == head_dim and q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
+    assert context_len.numel() == rows and context_len.dtype == torch.int32
+    out = torch.empty((rows, q_heads * head_dim), dtype=q.dtype, device=q.device)
+    partial = None
+    if num_splits > 1:
+        partial = torch.empty((rows, q_heads, num_splits, head_dim + 2), dtype=torch.float32, device=q.device)
+    _call("kirai_attention_decode_bf16", _ptr(q), _ptr(cache), _ptr(out), _ptr(partial), _ptr(block_table),
+          _ptr(context_len), _i(rows), _i(q_heads), _i(kv_heads), _i(head_dim), _l(q_stride), _i(page_size),
+          _i(block_table.shape[1]), _i(num_pages), _i(window or 0), _f(scale), _i(num_splits),
+          _ptr(error_flag(q.device)), _stream())
+    return out
+
+
 def paged_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, batch, window: Optional[int],
                     scale: float) -> torch.Tensor:
     """Attention of the product path over the paged cache for the tokens of ``batch``
-    (a kirai_b200.engine.batch.StepBatch): picks the kernel by dtype and by what the batch holds."""
-    return paged_attention_plain(q, cache, block_table, batch.request_of_token, batch.positions, window, scale)
+    (a kirai_b200.engine.batch.StepBatch).  float32 takes the plain kernel; bfloat16 takes the
+    tensor-core kernels (the decode kernel when every request brings one token), or the plain
+    kernel for head sizes they do not take (not a multiple of 8, or above 256)."""
+    head_dim, q_heads, kv_heads = q.shape[2], q.shape[1], cache.shape[2]
+    fast = (q.dtype == torch.bfloat16 and head_dim % 8 == 0 and head_dim <= 256 and q.stride(0) % 8 == 0
+            and q.data_ptr() % 16 == 0)
+    if not fast:
+        return paged_attention_plain(q, cache, block_table, batch.request_of_token, batch.positions, window, scale)
+    if batch.decode_only and q_heads // kv_heads <= 16:
+        splits = decode_splits(batch.num_requests, kv_heads, min(batch.max_context_len, window or batch.max_context_len))
+        return attention_decode(q, cache, block_table, batch.context_len, window, scale, splits)
+    return attention_prefill(q, cache, block_table, batch.query_start, batch.context_len, batch.max_query_len, window, scale)
 
 
 # ------------------------------------------------------------------------ linear

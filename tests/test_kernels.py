@@ -292,3 +292,77 @@ def test_argmax_and_sampling(ops, vocab):
             if vocab <= 1000:  # small enough that the sequential 32-bit walk of the plain implementation is exact too
                 expected = plain.sample_top_p(logits[row], float(temperatures[row]), float(top_ps[row]), draw)
                 assert abs(place - int(rank[expected])) <= 1, (row, draw, got[row], expected)
+
+
+@pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,window",
+                         [(6, 2, 48, 8, None), (5, 5, 16, 4, 7), (8, 2, 128, 16, 40), (32, 8, 128, 16, None),
+                          (3, 1, 80, 1, None), (4, 2, 256, 64, 33), (16, 1, 64, 16, None)])
+def test_tensor_core_attention_against_plain(ops, q_heads, kv_heads, head_dim, page_size, window):
+    """Prompt portions that start in the middle of a context, and single decoded tokens, through the
+    tensor-core kernels and through the plain kernel, against 32-bit arithmetic."""
+    dtype = torch.bfloat16
+    lengths = [150, 5, 64, 300]
+    cache, table, keys, values = paged_setup(dtype, lengths, kv_heads, head_dim, page_size, seed=3)
+    for r, n in enumerate(lengths):
+        pos = torch.arange(n, dtype=torch.int32, device=DEV)
+        ops.kv_write(keys[r].to(DEV).contiguous(), values[r].to(DEV).contiguous(), cache, table,
+                     torch.full((n,), r, dtype=torch.int32, device=DEV), pos)
+    scale = head_dim ** -0.5
+    generator = torch.Generator().manual_seed(4)
+    # mixed: the last 71 tokens of request 0, the whole of 1, one token of 2, the last 130 of 3
+    spans = [(0, 150 - 71, 71), (1, 0, 5), (2, 63, 1), (3, 170, 130)]
+    total = sum(s[2] for s in spans)
+    q = (torch.randn(total, q_heads, head_dim, generator=generator) * 2.0).to(dtype).to(DEV)
+    query_start = torch.tensor([0] + list(torch.tensor([s[2] for s in spans]).cumsum(0)), dtype=torch.int32, device=DEV)
+    context_len = torch.tensor([s[1] + s[2] for s in spans], dtype=torch.int32, device=DEV)
+    req = torch.tensor([i for i, s in enumerate(spans) for _ in range(s[2])], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([p for s in spans for p in range(s[1], s[1] + s[2])], dtype=torch.int32, device=DEV)
+    # only the keys up to each request's context length count: later rows are in the pages but masked
+    fast = ops.attention_prefill(q, cache, table, query_start, context_len, max(s[2] for s in spans), window, scale)
+    plain = ops.paged_attention_plain(q, cache, table, req, pos, window, scale)
+    ops.check_device_errors(torch.device(DEV))
+    row = 0
+    for r, first, count in spans:
+        expected = attention_reference(q[row : row + count].cpu(), keys[r], values[r], list(range(first, first + count)), window, scale)
+        got = fast[row : row + count].float().cpu().unflatten(1, (q_heads, head_dim))
+        assert float((got - expected).abs().max()) <= 2.5e-2, (r, first, count)
+        row += count
+    assert float((fast.float() - plain.float()).abs().max()) <= 2.5e-2
+    # decode: one token per request at the end of each context, with 1, 2 and 5 splits
+    if q_heads // kv_heads <= 16:
+        ends = [n - 1 for n in lengths]
+        qd = (torch.randn(len(lengths), q_heads, head_dim, generator=generator) * 2.0).to(dtype).to(DEV)
+        ctx = torch.tensor(lengths, dtype=torch.int32, device=DEV)
+        for splits in (1, 2, 5):
+            got = ops.attention_decode(qd, cache, table, ctx, window, scale, splits).float().cpu().unflatten(1, (q_heads, head_dim))
+            ops.check_device_errors(torch.device(DEV))
+            for r, end in enumerate(ends):
+                expected = attention_reference(qd[r : r + 1].cpu(), keys[r], values[r], [end], window, scale)
+                assert float((got[r : r + 1] - expected).abs().max()) <= 2.5e-2, (r, splits)
+
+
+def test_tensor_core_attention_finds_a_far_key(ops):
+    """One key among hundreds, far back and on a page edge, is made to dominate: the output must be its value."""
+    dtype, q_heads, kv_heads, head_dim, page_size = torch.bfloat16, 8, 2, 128, 16
+    lengths = [777]
+    cache, table, keys, values = paged_setup(dtype, lengths, kv_heads, head_dim, page_size, seed=8)
+    far = 16 * 3  # first row of the fourth page
+    direction = torch.randn(head_dim, generator=torch.Generator().manual_seed(1))
+    direction = direction / direction.norm()
+    keys[0][far] = (direction * 30.0).to(dtype)
+    ops.kv_write(keys[0].to(DEV).contiguous(), values[0].to(DEV).contiguous(), cache, table,
+                 torch.zeros(777, dtype=torch.int32, device=DEV), torch.arange(777, dtype=torch.int32, device=DEV))
+    q = (direction * 30.0).to(dtype).repeat(1, q_heads, 1).to(DEV)
+    ctx = torch.tensor([777], dtype=torch.int32, device=DEV)
+    for splits in (1, 4):
+        out = ops.attention_decode(q, cache, table, ctx, None, head_dim ** -0.5, splits).float().cpu().unflatten(1, (q_heads, head_dim))
+        for head in range(q_heads):
+            assert float((out[0, head] - values[0][far, head // 4].float()).abs().max()) <= 2e-2
+    qs = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    out = ops.attention_prefill(q, cache, table, qs, ctx, 1, None, head_dim ** -0.5).float().cpu().unflatten(1, (q_heads, head_dim))
+    assert float((out[0, 0] - values[0][far, 0].float()).abs().max()) <= 2e-2
+    # with a window that ends one short of the far key it must vanish from the result
+    out = ops.attention_decode(q, cache, table, ctx, 777 - far - 1, head_dim ** -0.5, 2).float().cpu().unflatten(1, (q_heads, head_dim))
+    assert float((out[0, 0] - values[0][far, 0].float()).abs().max()) > 0.5
+    out = ops.attention_decode(q, cache, table, ctx, 777 - far, head_dim ** -0.5, 2).float().cpu().unflatten(1, (q_heads, head_dim))
+    assert float((out[0, 0] - values[0][far, 0].float()).abs().max()) <= 2e-2
