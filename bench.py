@@ -1,0 +1,267 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200, Qwen3-8B shape, random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers 36]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second at the default batch with the
+requests' caches filled to the context length: K decode steps (forward pass, logits, sampling)
+replayed back to back on the device, timed with CUDA events.  ``e2e`` is the same through the
+Python entry point (``Engine.step``): every step copies its inputs from pinned host memory and
+reads the sampled tokens back to the host.  ``prefill`` is one 2,048-token prompt through the
+step function; ``points`` holds decode at batch 1 and 64.  The engine runs on one GPU; for
+--gpus > 1 one line says so and the exit code is 2.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=4096, intermediate_size=12288,
+    num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128, vocab_size=151936,
+    max_position_embeddings=40960, rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False,
+)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as handle:
+                raw = json.load(handle)
+            peaks = dict(FALLBACK_PEAKS)
+            for key in peaks:
+                if isinstance(raw.get(key), (int, float)):
+                    peaks[key] = float(raw[key])
+            return peaks, "measured"
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed regions run."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.process, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", "--id=0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.process.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.process is not None:
+            self.process.terminate()
+            try:
+                self.process.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.process.kill()
+        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "", 1).isdigit()]
+        sm_max = [float(s[1]) for s in self.samples if s[1].replace(".", "", 1).isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [name for i, name in enumerate(names) if any(s[3 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(sm_max) if sm_max else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def model_numbers(cfg, layers):
+    h, i, nq, nkv, d, v = (cfg["hidden_size"], cfg["intermediate_size"], cfg["num_attention_heads"],
+                           cfg["num_key_value_heads"], cfg["head_dim"], cfg["vocab_size"])
+    per_layer_weights = (nq + 2 * nkv) * d * h + h * nq * d + 2 * i * h + h * i
+    return dict(
+        layer_weight_elems=per_layer_weights, head_elems=v * h,
+        weight_bytes=2 * (layers * per_layer_weights + v * h),      # every weight a decode step uses, once (bf16)
+        kv_bytes_per_token=layers * 2 * nkv * d * 2,
+        linear_flops_per_token=2 * layers * per_layer_weights,
+        attention_flops=lambda tokens: layers * 2 * nq * d * tokens * tokens,  # causal: 2 products over T^2 / 2 pairs
+    )
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=32)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--context", type=int, default=4096)
+    parser.add_argument("--prefill-tokens", type=int, default=2048)
+    parser.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
+    parser.add_argument("--points", default="1,64", help="other decode batches to measure (comma separated, '' for none)")
+    args = parser.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "michaelasper/kir-ai is a Rust workspace (no setup.py or pyproject.toml, "
+                          "pip install refuses it) and its GPU path is Apple Metal; no Rust toolchain or Metal device here"}))
+        return 0
+    if args.gpus != 1:
+        print("bench.py measures one GPU: the engine is a single-GPU engine by design (--gpus 1)")
+        return 2
+    warmup = max(3, args.warmup)
+    steps = max(1, args.steps)
+
+    import torch
+
+    import kirai_b200
+    from kirai_b200 import Engine, SamplingParams
+    from kirai_b200.csrc import ops
+    from kirai_b200.engine.batch import StepEntry
+    from kirai_b200.registry import config_from_dict
+
+    raw = dict(QWEN3_8B)
+    raw["num_hidden_layers"] = args.layers
+    config = config_from_dict(raw)
+    numbers = model_numbers(raw, args.layers)
+    peaks, peak_source = load_peaks()
+    batches = [args.batch] + [int(b) for b in args.points.split(",") if b.strip()]
+    max_batch = max(batches)
+    page_size = 16
+    context = args.context
+    torch.cuda.set_device(0)
+    engine = Engine(config=config, random_weights_seed=2, dtype="bfloat16", page_size=page_size,
+                    max_new_tokens=4096, max_prefill_tokens=args.prefill_tokens, max_concurrent_requests=max_batch,
+                    max_cache_tokens=max_batch * (context + 256))
+    runner = engine.runner
+    generator = torch.Generator().manual_seed(1234)
+
+    def random_prompt(n):
+        return torch.randint(0, raw["vocab_size"], (n,), generator=generator).tolist()
+
+    clocks = ClockSampler()
+    clocks.start()
+
+    # ------------------------------------------------------------------ prefill: one prompt through the step function
+    T = args.prefill_tokens
+    prefill_times = []
+    for it in range(warmup + 5):
+        pages = runner.cache.open(("prefill", it))
+        prompt = random_prompt(T)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        runner.step([StepEntry(pages, prompt, [T - 1])], check_errors=False)
+        stop.record()
+        torch.cuda.synchronize()
+        if it >= warmup:
+            prefill_times.append(start.elapsed_time(stop))
+        runner.cache.close(pages)
+    ops.check_device_errors(runner.rt.device)
+    prefill_ms = statistics.median(prefill_times)
+    prefill_flops = numbers["linear_flops_per_token"] * T + numbers["attention_flops"](T) + 2 * numbers["head_elems"]
+    prefill = {"value": T / (prefill_ms / 1e3), "tokens": T, "ms": prefill_ms,
+               "frac": prefill_flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), "flops": prefill_flops}
+
+    # ------------------------------------------------------------------ decode
+    def measure_decode(batch):
+        """Fills `batch` requests' caches through the engine, then times decode steps two ways."""
+        # Requests that finish their prompt early decode while the others are still being filled, one
+        # token per fill step; start them that much lower so that all end near the context length.
+        budget = args.prefill_tokens
+        fill_steps = batch * -(-context // budget)
+        filled = max(16, context - (2 * (warmup + steps) + 4) - fill_steps)
+        params = SamplingParams(temperature=0.0, max_new_tokens=4096, ignore_eos=True)
+        requests = [engine.add_request(random_prompt(filled), params) for _ in range(batch)]
+        while any(r.pending > 1 or not r.output for r in requests):
+            engine.step()  # prompt portions under the token budget, then the first sampled tokens
+        # (a) through the Python entry point: host tokens in and out every step
+        for _ in range(warmup):
+            engine.step()
+        torch.cuda.synchronize()
+        launches_before = engine.counters["graph_steps"]
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            engine.step()
+        torch.cuda.synchronize()
+        e2e_seconds = time.perf_counter() - t0
+        assert engine.counters["graph_steps"] - launches_before == steps
+        # (b) on the device: the captured step feeds itself; pages for the steps ahead are reserved first
+        ahead = warmup + steps
+        for r in requests:
+            assert runner.cache.reserve(r.pages, ahead + 1)
+        cache = runner.cache
+        tables = [cache.block_table_array([r.pages for r in requests], g) for g in range(len(cache.groups))]
+        graph, fresh = engine.graphs.get(batch, max(t.shape[1] for t in tables))
+        graph.load_inputs([r.token_at(r.computed) for r in requests], [r.pages.length for r in requests],
+                          [r.pages.slot for r in requests], tables, [0.0] * batch, [1.0] * batch, [0.0] * batch)
+        if fresh:
+            graph.capture()
+        lengths_before = sum(r.pages.length for r in requests) / batch
+        for _ in range(warmup):
+            graph.replay()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        device_ms = start.elapsed_time(stop) / steps
+        ops.check_device_errors(runner.rt.device)
+        mean_context = lengths_before + warmup + steps / 2.0
+        step_bytes = numbers["weight_bytes"] + batch * mean_context * numbers["kv_bytes_per_token"]
+        result = dict(batch=batch, device_ms=device_ms, tokens_per_s=batch / (device_ms / 1e3),
+                      e2e_tokens_per_s=batch * steps / e2e_seconds, e2e_ms=e2e_seconds / steps * 1e3,
+                      bytes=step_bytes, gbs=step_bytes / (device_ms / 1e3) / 1e9, context=mean_context,
+                      kernels=graph.kernels_per_replay, h2d=graph.input_bytes, d2h=4 * batch)
+        for r in requests:
+            engine.scheduler.abort(r)
+        return result
+
+    results = {b: measure_decode(b) for b in batches}
+    clock_record = clocks.stop()
+    main_result = results[args.batch]
+    roofline = {"bound": "hbm", "achieved": main_result["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": main_result["gbs"] / peaks["hbm_gbs"], "of": peak_source}
+    line = {
+        "metric": "decode tok/s at batch 8 (points: batch 1 and 64); prefill tok/s at 2,048 tokens (Qwen3-8B)",
+        "value": main_result["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": main_result["device_ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: uniform-random token ids, random weights (seed 2)",
+        "config": {
+            "model": "Qwen3-8B shape", "layers": args.layers, "layers_of_config": QWEN3_8B["num_hidden_layers"],
+            "hidden": raw["hidden_size"], "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
+            "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"],
+            "global_batch": args.batch, "seq_len": context, "context_at_timing": round(main_result["context"]),
+            "page_size": page_size, "prefill_tokens": T, "parallelism": "single GPU",
+            "l2": "weights (16 GB) and cache exceed L2; no flush needed", "peaks": peak_source,
+        },
+        "prefill": {k: prefill[k] for k in ("value", "tokens", "ms", "frac")},
+        "roofline": roofline,
+        "points": {f"decode_b{b}": results[b]["tokens_per_s"] for b in batches if b != args.batch},
+        "points_detail": {f"decode_b{b}": {"ms": results[b]["device_ms"], "gbs": results[b]["gbs"],
+                                           "frac": results[b]["gbs"] / peaks["hbm_gbs"],
+                                           "e2e": results[b]["e2e_tokens_per_s"]} for b in batches},
+        "e2e": {"value": main_result["e2e_tokens_per_s"], "unit": "tokens/s", "ms_per_step": main_result["e2e_ms"],
+                "h2d_bytes_per_step": main_result["h2d"], "d2h_bytes_per_step": main_result["d2h"]},
+        "gpu_launches": main_result["kernels"] * steps,
+        "clocks": clock_record,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

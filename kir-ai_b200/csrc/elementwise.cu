@@ -436,3 +436,22 @@ KIRAI_EXPORT int kirai_add_residual_f32(float* resid, const void* delta, long co
 KIRAI_EXPORT int kirai_add_residual_bf16(float* resid, const void* delta, long count, cudaStream_t stream) {
     return add_residual_launch<bf16>(resid, delta, count, stream);
 }
+
+// ------------------------------------------------------------- decode advance
+// After a captured decode step: the sampled tokens become the next step's input
+// and every request moves one position on, so the same graph can be replayed
+// without the host in between.
+__global__ void decode_advance_kernel(int* __restrict__ token_ids, const int* __restrict__ sampled,
+                                      int* __restrict__ positions, int* __restrict__ context_len, int count) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    token_ids[i] = sampled[i];
+    positions[i] += 1;
+    context_len[i] += 1;
+}
+KIRAI_EXPORT int kirai_decode_advance(int* token_ids, const int* sampled, int* positions, int* context_len, int count,
+                                      cudaStream_t stream) {
+    if (count <= 0) return 0;
+    decode_advance_kernel<<<(count + 127) / 128, 128, 0, stream>>>(token_ids, sampled, positions, context_len, count);
+    return launch_status();
+}

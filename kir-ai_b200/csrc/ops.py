@@ -78,10 +78,15 @@ def _suffix(dtype: torch.dtype) -> str:
     raise KernelError(f"kernels take float32 or bfloat16 activations, got {dtype}")
 
 
+launch_count = 0  # entry points called so far (each launches one to three kernels); read by measurements
+
+
 def _call(name: str, *args) -> None:
+    global launch_count
     fn = getattr(library(), name)
     fn.restype = ctypes.c_int
     _check(fn(*args), name)
+    launch_count += 1
 
 
 _i = ctypes.c_int
@@ -365,6 +370,15 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     out = torch.empty((rows, inter), dtype=gate_up.dtype, device=gate_up.device)
     _call(f"kirai_swiglu_{_suffix(gate_up.dtype)}", _ptr(gate_up), _ptr(out), _i(rows), _i(inter), _stream())
     return out
+
+
+def decode_advance(token_ids: torch.Tensor, sampled: torch.Tensor, positions: torch.Tensor, context_len: torch.Tensor) -> None:
+    """token_ids <- sampled; positions += 1; context_len += 1 (all int32 [R], on the device)."""
+    _need_cuda(token_ids, sampled, positions, context_len)
+    for t in (token_ids, sampled, positions, context_len):
+        assert t.dtype == torch.int32 and t.is_contiguous() and t.numel() == token_ids.numel()
+    _call("kirai_decode_advance", _ptr(token_ids), _ptr(sampled), _ptr(positions), _ptr(context_len),
+          _i(token_ids.numel()), _stream())
 
 
 # ---------------------------------------------------------------------- sampling

@@ -18,6 +18,7 @@ from ..sampling import rng
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import sample
 from .batch import StepEntry
+from .graphs import DecodeGraphs
 from .runner import ModelRunner
 from .scheduler import Request, Scheduler
 
@@ -40,7 +41,7 @@ class Engine:
                  dtype: str = "bfloat16", device: str = "cuda:0", max_new_tokens: int = 256,
                  max_prefill_tokens: int = 2048, max_concurrent_requests: int = 4, page_size: int = 16,
                  max_cache_tokens: Optional[int] = None, prefill_chunk: Optional[int] = None,
-                 runner: Optional[ModelRunner] = None):
+                 runner: Optional[ModelRunner] = None, cuda_graphs: bool = True):
         if not 1 <= max_new_tokens <= MAX_NEW_TOKENS_CAP:
             raise ValueError(f"--max-new-tokens must be within 1..{MAX_NEW_TOKENS_CAP}")
         if not 1 <= max_prefill_tokens <= MAX_PREFILL_TOKENS_CAP:
@@ -74,7 +75,8 @@ class Engine:
             default_max_new_tokens=max_new_tokens,
         )
         self._next_id = 0
-        self.counters = {"steps": 0, "prompt_tokens": 0, "generated_tokens": 0}
+        self.counters = {"steps": 0, "graph_steps": 0, "prompt_tokens": 0, "generated_tokens": 0}
+        self.graphs = DecodeGraphs(runner) if cuda_graphs else None
 
     # ------------------------------------------------------------------ generate
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> Request:
@@ -90,9 +92,18 @@ class Engine:
     def step(self) -> List[Request]:
         """One scheduler step; returns the requests that finished in it."""
         scheduled = self.scheduler.schedule()
+        if self.graphs is not None and scheduled and all(item.count == 1 for item in scheduled):
+            sampled = self._decode_step_with_graph(scheduled)
+        else:
+            sampled = self._general_step(scheduled)
+        self.runner.rt.ops.check_device_errors(self.runner.rt.device)
+        self.counters["steps"] += 1
+        return self.scheduler.update(scheduled, sampled)
+
+    def _general_step(self, scheduled) -> List[Optional[int]]:
         entries = []
         for item in scheduled:
-            tokens = item.request.tokens[item.first : item.first + item.count]
+            tokens = item.request.token_slice(item.first, item.count)
             entries.append(StepEntry(item.request.pages, tokens, [item.count - 1] if item.sample else []))
         logits = self.runner.step(entries, check_errors=False)
         sampled: List[Optional[int]] = [None] * len(scheduled)
@@ -106,9 +117,29 @@ class Engine:
             ).cpu().tolist()
             for i, token in zip(rows, tokens):
                 sampled[i] = token
-        self.runner.rt.ops.check_device_errors(self.runner.rt.device)
-        self.counters["steps"] += 1
-        return self.scheduler.update(scheduled, sampled)
+        return sampled
+
+    def _decode_step_with_graph(self, scheduled) -> List[Optional[int]]:
+        """Every request brings one token: replay the captured step for this many requests.
+        The scheduler has reserved the pages; the inputs go to the graph's fixed buffers."""
+        cache = self.runner.cache
+        requests = [item.request for item in scheduled]
+        pages = [r.pages for r in requests]
+        tables = [cache.block_table_array(pages, g) for g in range(len(cache.groups))]
+        width = max([1] + [t.shape[1] for t in tables])
+        graph, fresh = self.graphs.get(len(requests), width)
+        graph.load_inputs(
+            [r.token_at(item.first) for r, item in zip(requests, scheduled)], [p.length for p in pages],
+            [p.slot for p in pages], tables, [r.params.temperature for r in requests],
+            [r.params.top_p for r in requests], [rng.draw(r.seed, r.draws_used) for r in requests],
+        )
+        if fresh:
+            graph.capture()
+        tokens = graph.replay().cpu().tolist()
+        for p in pages:
+            cache.commit(p, 1)
+        self.counters["graph_steps"] += 1
+        return list(tokens)
 
     def generate(self, prompts: Sequence[Sequence[int]],
                  params: Union[None, SamplingParams, Sequence[SamplingParams]] = None) -> List[GenerationOutput]:

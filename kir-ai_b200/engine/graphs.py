@@ -1,0 +1,140 @@
+"""CUDA graphs for decode steps.
+
+A step in which every request brings one token has the same kernel sequence
+whenever the number of requests and the width of the block tables are the same,
+so it is captured once per (requests, table width) and replayed.  The captured
+step reads its inputs from fixed device buffers (token ids, positions, context
+lengths, slots, block tables, sampling options and draws), runs the model's own
+forward pass, samples, and then feeds itself: the sampled tokens become the next
+input and positions move on by one, so a replay needs the host only when a
+request's pages, options or membership change.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .batch import StepBatch
+
+
+class DecodeGraph:
+    def __init__(self, runner, num_requests: int, table_width: int):
+        self.runner = runner
+        self.num_requests = B = num_requests
+        self.table_width = table_width
+        device = runner.rt.device
+        groups = len(runner.cache.groups)
+        # packed int32 inputs: token_ids, positions, context_len, slots, then one table per group
+        self.sections = [B, B, B, B] + [B * table_width] * groups
+        offsets, cursor = [], 0
+        for size in self.sections:
+            offsets.append(cursor)
+            cursor += -(-size // 4) * 4
+        self.offsets = offsets
+        self.host_ints = torch.zeros(cursor, dtype=torch.int32).pin_memory()
+        self.dev_ints = torch.zeros(cursor, dtype=torch.int32, device=device)
+        self.host_floats = torch.zeros(3 * B, dtype=torch.float32).pin_memory()
+        self.dev_floats = torch.zeros(3 * B, dtype=torch.float32, device=device)
+        self.fixed = torch.arange(B + 1, dtype=torch.int32, device=device)
+
+        def section(i, source):
+            return source[offsets[i] : offsets[i] + self.sections[i]]
+
+        self.token_ids, self.positions = section(0, self.dev_ints), section(1, self.dev_ints)
+        self.context_len, self.slots = section(2, self.dev_ints), section(3, self.dev_ints)
+        self.tables = [section(4 + g, self.dev_ints).view(B, table_width) for g in range(groups)]
+        self._host = [section(i, self.host_ints) for i in range(len(self.sections))]
+        self.batch = StepBatch(
+            num_tokens=B, num_requests=B, token_ids=self.token_ids, positions=self.positions,
+            request_of_token=self.fixed[:B], query_start=self.fixed, context_len=self.context_len, slots=self.slots,
+            block_tables=self.tables, want_rows=self.fixed[:B], query_lens=[1] * B, start_positions=[0] * B,
+            slot_ids=[0] * B, max_query_len=1, max_context_len=table_width * runner.cache.page_size, num_want=B,
+        )
+        self.tokens_out: Optional[torch.Tensor] = None
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.kernels_per_replay = 0
+
+    def _body(self) -> None:
+        ops = self.runner.rt.ops
+        model = self.runner.model
+        resid, delta = model.forward(self.batch, self.runner.cache)
+        logits = model.logits(resid, delta, self.batch.want_rows)
+        B = self.num_requests
+        floats = self.dev_floats
+        self.tokens_out = ops.sample_rows(logits, floats[:B], floats[B : 2 * B], floats[2 * B :])
+        ops.decode_advance(self.token_ids, self.tokens_out, self.positions, self.context_len)
+
+    def load_inputs(self, token_ids: Sequence[int], positions: Sequence[int], slots: Sequence[int],
+                    tables: Sequence[np.ndarray], temperatures: Sequence[float], top_ps: Sequence[float],
+                    draws: Sequence[float]) -> None:
+        """Copies a step's inputs from pinned host memory to the fixed device buffers (two copies)."""
+        B = self.num_requests
+        self._host[0].copy_(torch.as_tensor(token_ids, dtype=torch.int32))
+        position_tensor = torch.as_tensor(positions, dtype=torch.int32)
+        self._host[1].copy_(position_tensor)
+        self._host[2].copy_(position_tensor + 1)
+        self._host[3].copy_(torch.as_tensor(slots, dtype=torch.int32))
+        for g, table in enumerate(tables):
+            padded = np.full((B, self.table_width), -1, dtype=np.int32)
+            padded[:, : table.shape[1]] = table
+            self._host[4 + g].copy_(torch.from_numpy(padded.reshape(-1)))
+        self.host_floats[:B] = torch.as_tensor(temperatures, dtype=torch.float32)
+        self.host_floats[B : 2 * B] = torch.as_tensor(top_ps, dtype=torch.float32)
+        self.host_floats[2 * B :] = torch.as_tensor(draws, dtype=torch.float32)
+        self.dev_ints.copy_(self.host_ints, non_blocking=True)
+        self.dev_floats.copy_(self.host_floats, non_blocking=True)
+
+    @property
+    def input_bytes(self) -> int:
+        return self.host_ints.numel() * 4 + self.host_floats.numel() * 4
+
+    def capture(self) -> None:
+        """Runs the step once eagerly (so that everything lazy has happened), then captures it.
+        The inputs must describe a valid step; what the eager run writes to the cache is written
+        again, identically, by the first replay."""
+        ops = self.runner.rt.ops
+        saved = self.dev_ints.clone()
+        stream = torch.cuda.Stream(device=self.runner.rt.device)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            self._body()
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize()
+        self.dev_ints.copy_(saved)  # undo the eager run's advance
+        before = ops.launch_count
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._body()
+        self.kernels_per_replay = ops.launch_count - before
+        self.dev_ints.copy_(saved)  # capture does not run the kernels, but keep the inputs as the caller set them
+
+    def replay(self) -> torch.Tensor:
+        self.graph.replay()
+        return self.tokens_out
+
+
+class DecodeGraphs:
+    """The captured decode steps of a runner, by (requests, table width bucket)."""
+
+    def __init__(self, runner):
+        self.runner = runner
+        self.graphs: Dict[Tuple[int, int], DecodeGraph] = {}
+
+    @staticmethod
+    def width_bucket(width: int) -> int:
+        bucket = 16
+        while bucket < width:
+            bucket *= 2
+        return bucket
+
+    def get(self, num_requests: int, table_width: int) -> Tuple[DecodeGraph, bool]:
+        """The graph for this shape and whether it still has to be captured."""
+        key = (num_requests, self.width_bucket(table_width))
+        graph = self.graphs.get(key)
+        if graph is None:
+            graph = DecodeGraph(self.runner, key[0], key[1])
+            self.graphs[key] = graph
+            return graph, True
+        return graph, False

@@ -54,6 +54,16 @@ class Request:
     def tokens(self) -> List[int]:
         return self.prompt + self.output
 
+    def token_at(self, index: int) -> int:
+        n = len(self.prompt)
+        return self.prompt[index] if index < n else self.output[index - n]
+
+    def token_slice(self, first: int, count: int) -> List[int]:
+        n = len(self.prompt)
+        if first + count <= n:
+            return self.prompt[first : first + count]
+        return [self.token_at(i) for i in range(first, first + count)]
+
     @property
     def pending(self) -> int:
         """Tokens not yet run: the rest of the prompt, or the one token sampled last."""
