@@ -549,3 +549,61 @@ KIRAI_EXPORT int kirai_attention_decode_bf16(const void* q, const void* cache, v
     KIRAI_DC(256);
 #undef KIRAI_DC
 }
+
+// ----------------------------------------------------- decode without allocation
+// The same decode kernels, with the splits' partial results in a file-scope device array
+// instead of a buffer from the caller; see no_alloc.h for who needs this and for the rules.
+#include "no_alloc.h"
+
+#include <mutex>
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) float kirai_static_scratch[KIRAI_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* static_scratch_address[kMaxDevices];  // per device, found on the first call there
+std::mutex static_scratch_mutex;
+
+// The device address of the array on the current device (looked up once per device).
+int static_scratch_for_current_device(float** address) {
+    int device = -1;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) return (int)err;
+    if (device < 0 || device >= kMaxDevices) return KIRAI_ERR_STATIC_SCRATCH_SETUP;
+    std::lock_guard<std::mutex> lock(static_scratch_mutex);
+    if (static_scratch_address[device] == nullptr) {
+        float* found = nullptr;
+        err = cudaGetSymbolAddress((void**)&found, kirai_static_scratch);
+        if (err != cudaSuccess) return (int)err;
+        if (found == nullptr) return KIRAI_ERR_STATIC_SCRATCH_SETUP;
+        static_scratch_address[device] = found;
+    }
+    *address = static_scratch_address[device];
+    return 0;
+}
+}  // namespace
+
+KIRAI_EXPORT unsigned kirai_static_scratch_capacity_floats(void) { return KIRAI_STATIC_SCRATCH_FLOATS; }
+
+KIRAI_EXPORT int kirai_attention_decode_bf16_static_scratch(const void* q, const void* cache, void* out,
+                                                            const int* block_table, const int* context_len,
+                                                            int requests, int q_heads, int kv_heads, int head_dim,
+                                                            long q_row_stride, int page_size, int table_width,
+                                                            int num_pages, int window, float scale, int num_splits,
+                                                            int* error_flag, cudaStream_t stream) {
+    if (requests <= 0) return 0;
+    if (num_splits < 1 || q_heads <= 0 || head_dim <= 0) return KIRAI_ERR_BAD_SIZE;
+    float* scratch = nullptr;
+    if (num_splits > 1) {
+        const unsigned long long need =
+            (unsigned long long)requests * (unsigned long long)q_heads * (unsigned long long)num_splits *
+            (unsigned long long)(head_dim + 2);
+        if (need > KIRAI_STATIC_SCRATCH_FLOATS) return KIRAI_ERR_STATIC_SCRATCH_TOO_SMALL;
+        const int status = static_scratch_for_current_device(&scratch);
+        if (status) return status;
+    }
+    return kirai_attention_decode_bf16(q, cache, out, scratch, block_table, context_len, requests, q_heads, kv_heads,
+                                       head_dim, q_row_stride, page_size, table_width, num_pages, window, scale,
+                                       num_splits, error_flag, stream);
+}

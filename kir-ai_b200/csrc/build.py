@@ -29,7 +29,7 @@ SOURCES = [
     "gemm_tcgen05.cu",
     "attention_mma.cu",
 ]
-HEADERS = ["common.cuh", "sm100.cuh", "tensor_map.cuh"]
+HEADERS = ["common.cuh", "sm100.cuh", "tensor_map.cuh", "no_alloc.h"]
 
 NVCC_FLAGS = [
     "-gencode",
