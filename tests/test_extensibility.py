@@ -65,9 +65,10 @@ def define_toys():
             angle = positions.float()[:, None, None] * self.freq[None, None, :]
             cos, sin = torch.cos(angle), torch.sin(angle)
             for x in (q, k):
-                even, odd = x[..., 0::2].float(), x[..., 1::2].float()
-                x[..., 0::2] = (even * cos - odd * sin).to(x.dtype)
-                x[..., 1::2] = (odd * cos + even * sin).to(x.dtype)
+                even, odd = x[..., 0::2].float(), x[..., 1::2].float()  # views of x when x is 32-bit
+                new_even, new_odd = even * cos - odd * sin, odd * cos + even * sin
+                x[..., 0::2] = new_even.to(x.dtype)
+                x[..., 1::2] = new_odd.to(x.dtype)
 
     class TopOneOfTwo(FeedForward):
         """A router picks one of two SwiGLU experts per token (router logits in 32-bit)."""
