@@ -19,7 +19,8 @@
 // Key tiles start at absolute multiples of the tile size, so which keys share
 // a tile does not depend on how a prompt was cut.  head_dim: any multiple of 8
 // up to 256 (the tile is padded with zeros to 64, 128 or 256 columns).
-#include "common.cuh"
+#include "sm100.cuh"
+#include "tensor_map.cuh"
 
 namespace {
 
@@ -52,11 +53,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// A tile in shared memory is [rows][D] bf16; the 16-byte chunk c of row r sits at chunk c ^ (r & 7),
-// which keeps the 8 rows of an ldmatrix on different banks.
-template <int D>
+// A tile in shared memory holds ROWS rows of D bf16 as D / 64 panels of [ROWS][64] (128-byte rows);
+// inside a panel the 16-byte chunk c of row r sits at chunk c ^ (r & 7).  This is the layout that a
+// TMA box of 64 columns with the 128-byte swizzle produces (panels based at multiples of 1024 bytes),
+// and it keeps the 8 rows of an ldmatrix on different banks.
+template <int ROWS>
 __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
-    return (uint32_t)(row * D * 2 + ((chunk ^ (row & 7)) << 4));
+    return (uint32_t)((chunk >> 3) * (ROWS * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
 struct PagedKV {
@@ -91,8 +94,8 @@ __device__ __forceinline__ void load_kv_tile(const PagedKV& kv, int j0, int j_lo
                 v_src = kv.cache + base + (long)kv.kv_heads * kv.page_size * kv.head_dim;
             }
         }
-        cp_async_16(k_smem + tile_offset<D>(row, chunk), k_src, valid);
-        cp_async_16(v_smem + tile_offset<D>(row, chunk), v_src, valid);
+        cp_async_16(k_smem + tile_offset<ROWS>(row, chunk), k_src, valid);
+        cp_async_16(v_smem + tile_offset<ROWS>(row, chunk), v_src, valid);
     }
 }
 
@@ -112,8 +115,8 @@ struct WarpState {
 // Folds BN keys (tile at k_smem / v_smem, first key j0) into the state of this warp's 16 query
 // rows, whose A-operand tile is at q_smem rows [q_row0, q_row0 + 16).  Row r (0..15) sees key j
 // when lo[r] <= j <= hi[r]; the thread holds rows g = lane / 4 (index 0) and g + 8 (index 1).
-template <int D, int BN>
-__device__ __forceinline__ void warp_attend(WarpState<D>& st, uint32_t q_smem, int q_row0, uint32_t k_smem,
+template <int D, int BN, int QROWS, bool Q_IN_REGS>
+__device__ __forceinline__ void warp_attend(WarpState<D>& st, uint32_t q_smem, int q_row0, const uint32_t (*q_regs)[4], uint32_t k_smem,
                                             uint32_t v_smem, int j0, const int (&lo)[2], const int (&hi)[2],
                                             float scale_log2, int lane) {
     float s[BN / 8][4];
@@ -123,10 +126,12 @@ __device__ __forceinline__ void warp_attend(WarpState<D>& st, uint32_t q_smem, i
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
         uint32_t a[4];
-        {
+        if (Q_IN_REGS) {
+            a[0] = q_regs[kk][0]; a[1] = q_regs[kk][1]; a[2] = q_regs[kk][2]; a[3] = q_regs[kk][3];
+        } else {
             const int row = q_row0 + (lane & 15);
             const int chunk = kk * 2 + (lane >> 4);
-            ldmatrix_x4(q_smem + tile_offset<D>(row, chunk), a[0], a[1], a[2], a[3]);
+            ldmatrix_x4(q_smem + tile_offset<QROWS>(row, chunk), a[0], a[1], a[2], a[3]);
         }
 #pragma unroll
         for (int n2 = 0; n2 < BN / 16; ++n2) {
@@ -134,7 +139,7 @@ __device__ __forceinline__ void warp_attend(WarpState<D>& st, uint32_t q_smem, i
             uint32_t b0, b1, b2, b3;
             const int row = n2 * 16 + (lane & 7) + ((lane >> 4) << 3);
             const int chunk = kk * 2 + ((lane >> 3) & 1);
-            ldmatrix_x4(k_smem + tile_offset<D>(row, chunk), b0, b1, b2, b3);
+            ldmatrix_x4(k_smem + tile_offset<BN>(row, chunk), b0, b1, b2, b3);
             mma_bf16_16816(s[2 * n2], a, b0, b1);
             mma_bf16_16816(s[2 * n2 + 1], a, b2, b3);
         }
@@ -195,7 +200,7 @@ __device__ __forceinline__ void warp_attend(WarpState<D>& st, uint32_t q_smem, i
             uint32_t b0, b1, b2, b3;
             const int row = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
             const int chunk = n2 * 2 + (lane >> 4);
-            ldmatrix_x4_trans(v_smem + tile_offset<D>(row, chunk), b0, b1, b2, b3);
+            ldmatrix_x4_trans(v_smem + tile_offset<BN>(row, chunk), b0, b1, b2, b3);
             mma_bf16_16816(st.o[2 * n2], p[kk], b0, b1);
             mma_bf16_16816(st.o[2 * n2 + 1], p[kk], b2, b3);
         }
@@ -243,7 +248,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ ca
                 const int token = row / group, head = kv_head * group + row % group;
                 src = q + (size_t)(q_begin + token) * q_row_stride + (size_t)head * head_dim + chunk * 8;
             }
-            cp_async_16(q_smem + tile_offset<D>(r, chunk), src, valid);
+            cp_async_16(q_smem + tile_offset<PF_ROWS>(r, chunk), src, valid);
         }
     }
     PagedKV kv{cache, block_table + (long)req * table_width, table_width, num_pages, kv_heads, page_size, head_dim, kv_head};
@@ -291,7 +296,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ ca
         const int warp_last_row = min(rows_total - 1, row0 + warp * 16 + 15);
         const bool warp_active = row0 + warp * 16 < rows_total && (start_pos + warp_last_row / group) >= t * PF_BN;
         if (warp_active)
-            warp_attend<D, PF_BN>(st, q_smem, warp * 16, k_s, k_s + TILE_BYTES, t * PF_BN, lo, hi, scale_log2, lane);
+            warp_attend<D, PF_BN, PF_ROWS, false>(st, q_smem, warp * 16, nullptr, k_s, k_s + TILE_BYTES, t * PF_BN, lo, hi, scale_log2, lane);
         __syncthreads();  // the stage is free for the load after next
     }
     // normalise and store
@@ -316,49 +321,126 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ ca
 
 // ------------------------------------------------------------------ decode kernel
 #define DC_WARPS 4
-// keys per warp tile: 32, or 16 for the widest heads so that the warps' double buffers fit shared memory
+#define DC_STAGES 3
+// keys per warp tile: 32, or 16 for the widest heads so that the warps' rings fit shared memory
 template <int D>
 struct DecodeTile { static constexpr int BN = D > 128 ? 16 : 32; };
 
+// Shared memory of the decode kernel: the query tile, per warp a ring of DC_STAGES (K tile, V tile)
+// filled by TMA, one mbarrier per ring slot; after the key loop the ring is reused to merge the warps.
+template <int D>
+struct DecodeSmem {
+    static constexpr int BN = DecodeTile<D>::BN;
+    static constexpr int q_bytes = 16 * D * 2;
+    static constexpr int tile_bytes = BN * D * 2;
+    static constexpr int ring_bytes = DC_WARPS * DC_STAGES * 2 * tile_bytes;
+    static constexpr int merge_bytes = DC_WARPS * 16 * (D + 2) * 4;
+    static constexpr int body = q_bytes + (ring_bytes > merge_bytes ? ring_bytes : merge_bytes);
+    static constexpr int total = body + DC_WARPS * DC_STAGES * 8 + 1024;  // barriers, and slack to align to 1024
+};
+
 // partial: [requests, q_heads, splits, head_dim + 2] floats: unnormalised output, then max (log2 domain), then sum.
+// kv_map: the cache layer as a 2-D bf16 matrix [num_pages * 2 * kv_heads * page_size, head_dim], boxes of
+// [box_rows, 64] with the 128-byte swizzle; box_rows = min(page_size, BN) and divides BN.
 template <int D>
 __global__ void __launch_bounds__(DC_WARPS * 32)
-attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, bf16* __restrict__ out,
+attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ q, bf16* __restrict__ out,
                         float* __restrict__ partial, const int* __restrict__ block_table,
                         const int* __restrict__ context_len, int q_heads, int kv_heads, int head_dim, long q_row_stride,
-                        int page_size, int table_width, int num_pages, int window, float scale_log2, int num_splits,
-                        int* __restrict__ error_flag) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int DC_BN = DecodeTile<D>::BN;
+                        int page_size, int box_rows, int table_width, int num_pages, int window, float scale_log2,
+                        int num_splits, int* __restrict__ error_flag) {
+    using Smem = DecodeSmem<D>;
+    constexpr int BN = Smem::BN;
+    constexpr int PANELS = D / 64;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int split = blockIdx.x, kv_head = blockIdx.y, req = blockIdx.z;
     const int group = q_heads / kv_heads;  // <= 16 rows
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int ctx = context_len[req];
     const int pos = ctx - 1;
     const int key_lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int first_tile = key_lo / DC_BN, last_tile = pos / DC_BN;
+    const int first_tile = key_lo / BN, last_tile = pos / BN;
     const int tiles = last_tile - first_tile + 1;
     const int per_split = (tiles + num_splits - 1) / num_splits;
     const int t_begin = first_tile + split * per_split;
     const int t_end = min(last_tile + 1, t_begin + per_split);
 
-    const uint32_t q_smem = smem_u32(smem);                // [16][D]
-    const uint32_t kv_smem = q_smem + 16 * D * 2;          // [warps][2 stages][K tile, V tile]
-    constexpr uint32_t TILE_BYTES = DC_BN * D * 2;
-    float* merge = reinterpret_cast<float*>(smem + 16 * D * 2 + DC_WARPS * 4 * TILE_BYTES);  // [warps][16][D + 2]
+    const uint32_t q_smem = sm100::smem_addr(smem);
+    const uint32_t ring = q_smem + Smem::q_bytes + warp * DC_STAGES * 2 * Smem::tile_bytes;
+    uint64_t* bars = (uint64_t*)(smem + Smem::body) + warp * DC_STAGES;
+    float* merge = reinterpret_cast<float*>(smem + Smem::q_bytes);  // [warps][16][D + 2], over the ring
 
+    if (tid == 0) sm100::tma_prefetch_descriptor(&kv_map);
+    if (lane == 0) {
+        for (int s = 0; s < DC_STAGES; ++s) sm100::mbar_init(sm100::smem_addr(&bars[s]), 1);
+        sm100::mbar_fence_init();
+    }
+    // the query rows (the group's heads), zero beyond the group and beyond head_dim
     {
         constexpr int CH = D / 8;
         const int chunks_used = head_dim / 8;
         for (int id = tid; id < 16 * CH; id += DC_WARPS * 32) {
             const int r = id / CH, chunk = id % CH;
-            const bool valid = r < group && chunk < chunks_used;
-            const bf16* src = valid ? q + (size_t)req * q_row_stride + (size_t)(kv_head * group + r) * head_dim + chunk * 8 : q;
-            cp_async_16(q_smem + tile_offset<D>(r, chunk), src, valid);
+            uint4 value = make_uint4(0u, 0u, 0u, 0u);
+            if (r < group && chunk < chunks_used)
+                value = *reinterpret_cast<const uint4*>(q + (size_t)req * q_row_stride + (size_t)(kv_head * group + r) * head_dim + chunk * 8);
+            *reinterpret_cast<uint4*>(smem + tile_offset<16>(r, chunk)) = value;
         }
-        cp_async_commit();
     }
-    PagedKV kv{cache, block_table + (long)req * table_width, table_width, num_pages, kv_heads, page_size, head_dim, kv_head};
+    __syncthreads();
+
+    const int* table = block_table + (long)req * table_width;
+    const int boxes = BN / box_rows;  // <= 32: one lane per box
+    const uint32_t box_bytes = (uint32_t)box_rows * 128u * PANELS;  // of K, and as much of V
+    bool ok = true;
+
+    // Fills ring slot `slot` with key tile `t`: every lane looks after one box (one page, or a part of one).
+    auto issue = [&](int t, int slot) {
+        const uint32_t bar = sm100::smem_addr(&bars[slot]);
+        const uint32_t k_dst = ring + slot * 2 * Smem::tile_bytes, v_dst = k_dst + Smem::tile_bytes;
+        int page = -1, j = 0;
+        if (lane < boxes) {
+            j = t * BN + lane * box_rows;
+            const int logical = j / page_size;
+            if (j <= pos && logical < table_width) page = table[logical];
+            if (page >= num_pages) page = -1;
+        }
+        const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
+        if (lane == 0) {
+            if (valid) sm100::mbar_expect_tx(bar, 2u * box_bytes * __popc(valid));
+            else sm100::mbar_arrive(bar);
+        }
+        __syncwarp();
+        if (page >= 0) {
+            const int row_k = ((page * 2) * kv_heads + kv_head) * page_size + (j % page_size);
+            const int row_v = row_k + kv_heads * page_size;
+#pragma unroll
+            for (int h = 0; h < PANELS; ++h) {
+                const uint32_t off = (uint32_t)(h * (BN * 128) + lane * box_rows * 128);
+                sm100::tma_load_2d(k_dst + off, &kv_map, bar, h * 64, row_k);
+                sm100::tma_load_2d(v_dst + off, &kv_map, bar, h * 64, row_v);
+            }
+        }
+        // boxes without a page (past the context, or given back by the window) hold masked keys only;
+        // their value rows must still be finite, so they are cleared
+        unsigned missing = ~valid & (boxes >= 32 ? 0xffffffffu : ((1u << boxes) - 1u));
+        while (missing) {
+            const int b = __ffs(missing) - 1;
+            missing &= missing - 1;
+            for (int h = 0; h < PANELS; ++h) {
+                const uint32_t off = (uint32_t)(h * (BN * 128) + b * box_rows * 128);
+                for (int i = lane; i < box_rows * 8; i += 32) {
+                    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(k_dst + off + i * 16), "r"(zero.x), "r"(zero.y), "r"(zero.z), "r"(zero.w) : "memory");
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(v_dst + off + i * 16), "r"(zero.x), "r"(zero.y), "r"(zero.z), "r"(zero.w) : "memory");
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __syncwarp();
+    };
+
     int lo[2], hi[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -366,30 +448,35 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
         hi[r] = row < group ? pos : -1;
         lo[r] = key_lo;
     }
+    // query fragments stay in registers for the narrower heads
+    constexpr bool Q_IN_REGS = D <= 128;
+    uint32_t q_regs[Q_IN_REGS ? D / 16 : 1][4];
+    if (Q_IN_REGS) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+            ldmatrix_x4(q_smem + tile_offset<16>(lane & 15, kk * 2 + (lane >> 4)), q_regs[kk][0], q_regs[kk][1], q_regs[kk][2], q_regs[kk][3]);
+    }
     WarpState<D> st;
     st.init();
-    const uint32_t my_smem = kv_smem + warp * 4 * TILE_BYTES;
-    // each warp walks tiles t_begin + warp, + DC_WARPS, ... with its own double buffer
-    int t = t_begin + warp;
-    if (t < t_end) load_kv_tile<D, DC_BN, 32>(kv, t * DC_BN, key_lo, pos, my_smem, my_smem + TILE_BYTES, lane, error_flag);
-    cp_async_commit();
-    cp_async_wait<0>();  // the Q tile and the warps' first tiles
-    __syncthreads();
-    int stage = 0;
-    for (; t < t_end; t += DC_WARPS) {
-        const int next_t = t + DC_WARPS;
-        if (next_t < t_end) {
-            const uint32_t next = my_smem + (stage ^ 1) * 2 * TILE_BYTES;
-            load_kv_tile<D, DC_BN, 32>(kv, next_t * DC_BN, key_lo, pos, next, next + TILE_BYTES, lane, error_flag);
+    // this warp's tiles: t_begin + warp, + DC_WARPS, ...; the ring runs DC_STAGES - 1 tiles ahead
+    const int my_first = t_begin + warp;
+    const int my_count = my_first < t_end ? (t_end - my_first + DC_WARPS - 1) / DC_WARPS : 0;
+    for (int k = 0; k < DC_STAGES - 1 && k < my_count; ++k) issue(my_first + k * DC_WARPS, k);
+    for (int k = 0; k < my_count; ++k) {
+        const int ahead = k + DC_STAGES - 1;
+        if (ahead < my_count) issue(my_first + ahead * DC_WARPS, ahead % DC_STAGES);
+        const int slot = k % DC_STAGES;
+        if (!sm100::mbar_wait(sm100::smem_addr(&bars[slot]), (uint32_t)(k / DC_STAGES) & 1u)) {
+            ok = false;
+            break;
         }
-        cp_async_commit();
-        const uint32_t k_s = my_smem + stage * 2 * TILE_BYTES;
-        warp_attend<D, DC_BN>(st, q_smem, 0, k_s, k_s + TILE_BYTES, t * DC_BN, lo, hi, scale_log2, lane);
-        cp_async_wait<0>();
+        const uint32_t k_s = ring + slot * 2 * Smem::tile_bytes;
+        warp_attend<D, BN, 16, Q_IN_REGS>(st, q_smem, 0, q_regs, k_s, k_s + Smem::tile_bytes, (my_first + k * DC_WARPS) * BN, lo, hi,
+                                          scale_log2, lane);
         __syncwarp();
-        stage ^= 1;
     }
-    // merge the warps' states: every warp writes (o, m, l) of its rows, then 128 threads combine
+    if (!ok && lane == 0) atomicExch(error_flag, 4);
+    __syncthreads();  // every warp is done with its ring: it becomes the merge buffer
     constexpr int MS = D + 2;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -479,16 +566,20 @@ int decode_launch(const void* q, const void* cache, void* out, float* partial, c
                   const int* context_len, int requests, int q_heads, int kv_heads, int head_dim, long q_row_stride,
                   int page_size, int table_width, int num_pages, int window, float scale, int num_splits,
                   int* error_flag, cudaStream_t stream) {
-    constexpr int DC_BN = DecodeTile<D>::BN;
-    const size_t smem = (size_t)16 * D * 2 + (size_t)DC_WARPS * 4 * DC_BN * D * 2 + (size_t)DC_WARPS * 16 * (D + 2) * 4;
+    using Smem = DecodeSmem<D>;
+    const int box_rows = page_size < Smem::BN ? page_size : Smem::BN;
+    if (Smem::BN % box_rows != 0 || page_size % box_rows != 0) return KIRAI_ERR_UNSUPPORTED;  // page sizes: powers of two
+    CUtensorMap kv_map;
+    const uint64_t rows = (uint64_t)num_pages * 2 * kv_heads * page_size;
+    if (!tmap::bf16_2d_sw128(&kv_map, cache, rows, head_dim, head_dim, box_rows, 64)) return KIRAI_ERR_BAD_ALIGN;
     auto kernel = attention_decode_kernel<D>;
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total);
     if (err != cudaSuccess) return (int)err;
     dim3 grid(num_splits, kv_heads, requests);
-    kernel<<<grid, DC_WARPS * 32, smem, stream>>>((const bf16*)q, (const bf16*)cache, (bf16*)out, partial, block_table,
-                                                 context_len, q_heads, kv_heads, head_dim, q_row_stride, page_size,
-                                                 table_width, num_pages, window, scale * 1.4426950408889634f,
-                                                 num_splits, error_flag);
+    kernel<<<grid, DC_WARPS * 32, Smem::total, stream>>>(kv_map, (const bf16*)q, (bf16*)out, partial, block_table,
+                                                        context_len, q_heads, kv_heads, head_dim, q_row_stride,
+                                                        page_size, box_rows, table_width, num_pages, window,
+                                                        scale * 1.4426950408889634f, num_splits, error_flag);
     int status = launch_status();
     if (status || num_splits == 1) return status;
     attention_merge_splits_kernel<<<requests * q_heads, 128, 0, stream>>>(partial, (bf16*)out, head_dim, num_splits);
