@@ -11,10 +11,12 @@
 //
 // Warp roles: warp 0 issues TMA loads into a ring of STAGES buffers, one thread
 // of warp 1 issues the MMAs and owns the tensor-memory allocation, warps 2-5
-// read the accumulator back (tcgen05.ld) and store the tile.  With split-K each
-// CTA of a tile covers a range of K and stores 32-bit partial sums that a
-// second kernel adds in a fixed order.  Every barrier wait is bounded; a wait
-// that runs out sets the device error flag and the CTA winds down.
+// read the accumulator back (tcgen05.ld) and store the tile.  With split-K the
+// CTAs of a thread-block cluster cover ranges of K of one tile and the partial
+// tiles are added through distributed shared memory, in rank order.  An
+// epilogue variant applies SwiGLU to interleaved gate and up rows.  Every
+// barrier wait is bounded; a wait that runs out sets the device error flag and
+// the CTA winds down.
 #include "sm100.cuh"
 #include "tensor_map.cuh"
 
@@ -24,32 +26,60 @@ using namespace sm100;
 #define GEMM_BK 64
 #define GEMM_THREADS 192
 
+// Shared memory of one CTA.  The swapped, weight-streaming case (BN <= 32) keeps the CTA small
+// enough for two CTAs per SM, so that every SM streams weights even when there are fewer tiles
+// than two waves; it also holds the slots in which the cluster's CTAs leave their partial tiles.
+// The many-token case takes as many stages as fit one CTA per SM.
 template <int BN>
 struct GemmSmem {
+    static constexpr bool streaming = BN <= 32;
     static constexpr int x_bytes = GEMM_BM * GEMM_BK * 2;
     static constexpr int y_bytes = BN * GEMM_BK * 2;
     static constexpr int stage_bytes = x_bytes + y_bytes;
-    static constexpr int max_bytes = 200 * 1024;
-    static constexpr int stages = (max_bytes / stage_bytes) > 10 ? 10 : (max_bytes / stage_bytes);
+    static constexpr int max_splits = streaming ? 64 / BN : 1;                        // 4 for BN 16, 2 for BN 32
+    static constexpr int slot_bytes = BN * GEMM_BM * 4;                               // one 32-bit partial tile
+    static constexpr int slots_bytes = streaming ? max_splits * slot_bytes : 0;       // 32 KB
+    static constexpr int stages = streaming ? (BN == 16 ? 4 : 3) : (200 * 1024 / stage_bytes);
     static constexpr int barrier_bytes = 256;
-    static constexpr int total = stages * stage_bytes + barrier_bytes + 1024;  // + slack for the 1024-byte alignment
+    static constexpr int total = stages * stage_bytes + slots_bytes + barrier_bytes + 1024;  // + slack to align to 1024
+    static constexpr int ctas_per_sm = streaming ? 2 : 1;
 };
 
 template <int BN>
 __host__ __device__ constexpr int tmem_columns() { return BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256)); }
 
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The address, in the cluster's shared window, that `local` has in CTA `rank`; and a store to it.
+__device__ __forceinline__ uint32_t cluster_address(uint32_t local, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t address, float value) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(address), "f"(value) : "memory");
+}
+
+__device__ __forceinline__ float silu_mul(float gate, float up) { return gate / (1.0f + expf(-gate)) * up; }
+
 // SWAP false: X = A (rows m), Y = W (rows n), C[m, n].  SWAP true: X = W, Y = A.
-// PARTIAL: store 32-bit sums to partial[split][M][N] instead of C.
-template <int BN, bool SWAP, typename OutT, bool PARTIAL>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+// Split-K: the CTAs of a cluster (1, 1, splits) cover one tile; each stores its 32-bit partial
+// tile into its slot in the shared memory of the cluster's first CTA (distributed shared memory),
+// which adds the slots in rank order and stores the result: no partial sum goes to global memory.
+// EPI 0 stores C.  EPI 1 expects W's rows interleaved in eights (8 gate rows, the 8 matching up
+// rows, ...) and stores silu(gate) * up, [M, N / 2].
+template <int BN, bool SWAP, typename OutT, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, GemmSmem<BN>::ctas_per_sm)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
-                    OutT* __restrict__ C, float* __restrict__ partial, int M, int N, int K, long ldc,
-                    int k_blocks_per_split, int* __restrict__ error_flag) {
+                    OutT* __restrict__ C, int M, int N, int K, long ldc, int k_blocks_per_split, int splits,
+                    int* __restrict__ error_flag) {
     using Smem = GemmSmem<BN>;
     constexpr int STAGES = Smem::stages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = (uint64_t*)(smem + STAGES * Smem::stage_bytes);
+    float* slots = reinterpret_cast<float*>(smem + STAGES * Smem::stage_bytes);  // [splits][BN][128], used in the first CTA
+    uint64_t* bars = (uint64_t*)(smem + STAGES * Smem::stage_bytes + Smem::slots_bytes);
     uint64_t* full_bar = bars;                 // [STAGES] TMA -> MMA
     uint64_t* empty_bar = bars + STAGES;       // [STAGES] MMA -> TMA
     uint64_t* done_bar = bars + 2 * STAGES;    // accumulator complete
@@ -61,7 +91,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const int total_k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
     const int kb_begin = blockIdx.z * k_blocks_per_split;
     const int kb_end = min(total_k_blocks, kb_begin + k_blocks_per_split);
-    const int num_kb = kb_end - kb_begin;
+    const int num_kb = max(0, kb_end - kb_begin);
+    const uint32_t rank = blockIdx.z;  // the cluster is (1, 1, splits) and the grid's z extent is splits
 
     if (threadIdx.x == 0) {
         tma_prefetch_descriptor(&map_x);
@@ -82,6 +113,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
+    const int lane_group = warp & 3;           // epilogue warps: tensor-memory lanes 32 (warp % 4) ..
+    const int tile_row = lane_group * 32 + lane;
 
     if (warp == 0) {
         if (elect_one()) {
@@ -119,64 +152,112 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             mma_commit(smem_addr(done_bar));
         }
     } else {
-        // Epilogue: warp w reads tensor-memory lanes 32 (w % 4) .. +31, one lane per thread.
-        const int lane_group = warp & 3;
-        const int x_row = x0 + lane_group * 32 + lane;  // row of X that this thread holds
-        const int x_rows = SWAP ? N : M;
-        const int y_rows = SWAP ? M : N;
         if (num_kb > 0) ok = mbar_wait(smem_addr(done_bar), 0);
         tc_fence_after();
-        if (ok) {
+        if (splits > 1) {
+            // store this CTA's partial tile into its slot in the first CTA (column-major: lanes side by side)
+            const uint32_t slot = cluster_address(smem_addr(slots) + rank * (uint32_t)Smem::slot_bytes, 0);
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
-                if (y0 + c0 >= y_rows) break;  // uniform across the warp
                 uint32_t r[16];
-                if (num_kb > 0) {
+                if (num_kb > 0 && ok) {
                     tmem_load_32x16(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)c0, r);
                     tmem_load_wait();
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) r[j] = 0u;
                 }
-                if (x_row >= x_rows) continue;
-                if (PARTIAL) {
-                    float* base = partial + (size_t)blockIdx.z * M * N;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int y = y0 + c0 + j;
-                        if (y < y_rows) {
-                            if (SWAP) base[(size_t)y * N + x_row] = __uint_as_float(r[j]);
-                            else base[(size_t)x_row * N + y] = __uint_as_float(r[j]);
-                        }
-                    }
-                } else if (SWAP) {
+                for (int j = 0; j < 16; ++j)
+                    st_cluster_f32(slot + (uint32_t)(((c0 + j) * GEMM_BM + tile_row) * 4), __uint_as_float(r[j]));
+            }
+        }
+    }
+    if (splits > 1) cluster_sync_all();  // every partial tile has arrived in the first CTA
+
+    if (warp >= 2 && rank == 0) {
+        const int x_row = x0 + tile_row;  // row of X that this thread holds
+        const int x_rows = SWAP ? N : M;
+        const int y_rows = SWAP ? M : N;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+            if (y0 + c0 >= y_rows) break;  // uniform across the warp
+            float v[16];
+            if (splits > 1) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int y = y0 + c0 + j;
-                        if (y < y_rows) C[(size_t)y * ldc + x_row] = from_f32<OutT>(__uint_as_float(r[j]));
-                    }
+                for (int j = 0; j < 16; ++j) v[j] = slots[(c0 + j) * GEMM_BM + tile_row];
+                for (int other = 1; other < splits; ++other) {
+                    const float* slot = slots + (size_t)other * (BN * GEMM_BM);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] += slot[(c0 + j) * GEMM_BM + tile_row];
+                }
+            } else {
+                uint32_t r[16];
+                if (num_kb > 0 && ok) {
+                    tmem_load_32x16(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)c0, r);
+                    tmem_load_wait();
                 } else {
-                    OutT* dst = C + (size_t)x_row * ldc + y0 + c0;
-                    const bool full = (y0 + c0 + 16 <= y_rows) && (((uintptr_t)dst & 15) == 0);
-                    if (full && sizeof(OutT) == 2) {
-                        uint32_t packed[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-                            packed[j] = *reinterpret_cast<uint32_t*>(&pair);
-                        }
-                        uint4* out = reinterpret_cast<uint4*>(dst);
-                        out[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                        out[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                    } else if (full && sizeof(OutT) == 4) {
-                        uint4* out = reinterpret_cast<uint4*>(dst);
+                    for (int j = 0; j < 16; ++j) r[j] = 0u;
+                }
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) out[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-                    } else {
+                for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+            }
+            if (EPI == 1 && SWAP) {
+                // this lane holds weight row x_row: rows 16k..16k+7 are gate rows, 16k+8..16k+15 their up rows
 #pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (y0 + c0 + j < y_rows) dst[j] = from_f32<OutT>(__uint_as_float(r[j]));
+                for (int j = 0; j < 16; ++j) {
+                    const float partner = __shfl_xor_sync(0xffffffffu, v[j], 8);
+                    const int y = y0 + c0 + j;
+                    if ((lane & 8) == 0 && x_row < x_rows && y < y_rows)
+                        C[(size_t)y * ldc + (x_row >> 4) * 8 + (x_row & 7)] = from_f32<OutT>(silu_mul(v[j], partner));
+                }
+                continue;
+            }
+            if (x_row >= x_rows) continue;
+            if (EPI == 1) {
+                // columns y0 + c0 .. + 15 are 8 gate rows then their 8 up rows: 8 outputs at (y0 + c0) / 2
+                OutT* dst = C + (size_t)x_row * ldc + ((y0 + c0) >> 1);
+                if (y0 + c0 + 16 <= y_rows && sizeof(OutT) == 2 && (((uintptr_t)dst & 15) == 0)) {
+                    uint32_t packed[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        __nv_bfloat162 pair = __floats2bfloat162_rn(silu_mul(v[2 * j], v[2 * j + 8]), silu_mul(v[2 * j + 1], v[2 * j + 9]));
+                        packed[j] = *reinterpret_cast<uint32_t*>(&pair);
                     }
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (y0 + c0 + j + 8 < y_rows) dst[j] = from_f32<OutT>(silu_mul(v[j], v[j + 8]));
+                }
+            } else if (SWAP) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int y = y0 + c0 + j;
+                    if (y < y_rows) C[(size_t)y * ldc + x_row] = from_f32<OutT>(v[j]);
+                }
+            } else {
+                OutT* dst = C + (size_t)x_row * ldc + y0 + c0;
+                const bool full = (y0 + c0 + 16 <= y_rows) && (((uintptr_t)dst & 15) == 0);
+                if (full && sizeof(OutT) == 2) {
+                    uint32_t packed[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        __nv_bfloat162 pair = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                        packed[j] = *reinterpret_cast<uint32_t*>(&pair);
+                    }
+                    uint4* out = reinterpret_cast<uint4*>(dst);
+                    out[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    out[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                } else if (full && sizeof(OutT) == 4) {
+                    float4* out = reinterpret_cast<float4*>(dst);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) out[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (y0 + c0 + j < y_rows) dst[j] = from_f32<OutT>(v[j]);
                 }
             }
         }
@@ -190,20 +271,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
 }
 
-// Adds the split-K partial sums in split order and converts.
-template <typename OutT>
-__global__ void splitk_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ C, int splits, int M, int N,
-                                     long ldc) {
-    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (long)M * N) return;
-    float acc = 0.0f;
-    for (int s = 0; s < splits; ++s) acc += partial[(size_t)s * M * N + idx];
-    C[(size_t)(idx / N) * ldc + (idx % N)] = from_f32<OutT>(acc);
-}
-
-template <int BN, bool SWAP, typename OutT>
-static int launch_config(const void* A, const void* W, void* C, float* workspace, size_t workspace_bytes, int M, int N,
-                         int K, long lda, long ldc, int splits, int* error_flag, cudaStream_t stream) {
+template <int BN, bool SWAP, typename OutT, int EPI>
+static int launch_config(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc, int splits,
+                         int* error_flag, cudaStream_t stream) {
     using Smem = GemmSmem<BN>;
     CUtensorMap map_a, map_w;
     const void* x_ptr = SWAP ? W : A;
@@ -214,85 +284,78 @@ static int launch_config(const void* A, const void* W, void* C, float* workspace
     if (!tmap::bf16_2d_sw128(&map_w, y_ptr, y_rows, K, y_stride, BN, GEMM_BK)) return KIRAI_ERR_BAD_ALIGN;
     const int total_k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
     if (splits < 1) splits = 1;
+    if (splits > Smem::max_splits) splits = Smem::max_splits;  // slots in the first CTA's shared memory
     if (splits > total_k_blocks) splits = total_k_blocks;
     const int per_split = (total_k_blocks + splits - 1) / splits;
     splits = (total_k_blocks + per_split - 1) / per_split;
     dim3 grid((unsigned)((x_rows + GEMM_BM - 1) / GEMM_BM), (unsigned)((y_rows + BN - 1) / BN), (unsigned)splits);
-    if (grid.y > 65535 || grid.z > 65535) return KIRAI_ERR_BAD_SIZE;
-    cudaError_t err;
-    if (splits == 1) {
-        auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT, false>;
-        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total);
-        if (err != cudaSuccess) return (int)err;
-        kernel<<<grid, GEMM_THREADS, Smem::total, stream>>>(map_a, map_w, (OutT*)C, nullptr, M, N, K, ldc, per_split,
-                                                           error_flag);
-        return launch_status();
-    }
-    if (!workspace || workspace_bytes < (size_t)splits * M * N * sizeof(float)) return KIRAI_ERR_BAD_SIZE;
-    auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT, true>;
-    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total);
+    if (grid.y > 65535) return KIRAI_ERR_BAD_SIZE;
+    auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT, EPI>;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total);
     if (err != cudaSuccess) return (int)err;
-    kernel<<<grid, GEMM_THREADS, Smem::total, stream>>>(map_a, map_w, (OutT*)C, workspace, M, N, K, ldc, per_split,
-                                                       error_flag);
-    int status = launch_status();
-    if (status) return status;
-    const long count = (long)M * N;
-    splitk_reduce_kernel<OutT><<<(unsigned)((count + 255) / 256), 256, 0, stream>>>(workspace, (OutT*)C, splits, M, N, ldc);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = dim3(GEMM_THREADS);
+    config.dynamicSmemBytes = Smem::total;
+    config.stream = stream;
+    cudaLaunchAttribute attrs[1];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = 1;
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = (unsigned)splits;
+    config.attrs = attrs;
+    config.numAttrs = 1;
+    err = cudaLaunchKernelEx(&config, kernel, map_a, map_w, (OutT*)C, M, N, K, ldc, per_split, splits, error_flag);
+    if (err != cudaSuccess) return (int)err;
     return launch_status();
 }
 
 // Split count for the swapped (few tokens) case, which is bound by the weight
-// stream: enough CTAs to fill the 148 SMs in whole waves, each split at least 8
-// k-blocks long, and no more partial-sum traffic than a fraction of the weights.
+// stream: enough CTAs that every SM streams (two of these CTAs fit an SM), each
+// split at least 8 k-blocks long, and no more splits than the first CTA has slots.
 static int choose_splits(int M, int N, int K) {
-    const int tiles = (N + GEMM_BM - 1) / GEMM_BM;
+    const int x_tiles = (N + GEMM_BM - 1) / GEMM_BM;
+    const int y_tiles = M <= 16 ? 1 : (M + 31) / 32;
+    const int max_splits = M <= 16 ? 4 : 2;
     const int k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
-    const int sms = 148;
-    int best = 1;
-    double best_score = 0.0;
-    for (int s = 1; s <= 16 && s * 8 <= k_blocks; ++s) {
-        const int ctas = tiles * s;
-        const int waves = (ctas + sms - 1) / sms;
-        double score = (double)ctas / ((double)waves * sms);
-        // partial sums are written and read once: 8 bytes per output per split, against 2 K bytes of weights per row
-        const double extra = s > 1 ? (8.0 * s * M) / (2.0 * K) : 0.0;
-        score /= (1.0 + extra);
-        if (score > best_score + 1e-9) {
-            best_score = score;
-            best = s;
-        }
-    }
-    return best;
+    const int base = x_tiles * y_tiles;
+    int splits = (120 + base - 1) / base;  // about one CTA per SM at least; two fit
+    if (splits > max_splits) splits = max_splits;
+    while (splits > 1 && k_blocks / splits < 8) --splits;
+    return splits < 1 ? 1 : splits;
 }
 
-template <typename OutT>
-static int gemm_dispatch(const void* A, const void* W, void* C, float* workspace, size_t workspace_bytes, int M, int N,
-                         int K, long lda, long ldc, int splits, int* error_flag, cudaStream_t stream) {
+template <typename OutT, int EPI>
+static int gemm_dispatch(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc, int splits,
+                         int* error_flag, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) return KIRAI_ERR_BAD_SIZE;
     if (K % 8 != 0 || lda % 8 != 0) return KIRAI_ERR_BAD_ALIGN;  // TMA needs 16-byte row strides
+    if (EPI == 1 && N % 16 != 0) return KIRAI_ERR_BAD_SIZE;      // whole groups of 8 gate + 8 up rows
     if (splits <= 0) splits = M <= 64 ? choose_splits(M, N, K) : 1;
 #define KIRAI_GEMM_CASE(BN, SWAP) \
-    return launch_config<BN, SWAP, OutT>(A, W, C, workspace, workspace_bytes, M, N, K, lda, ldc, splits, error_flag, stream)
+    return launch_config<BN, SWAP, OutT, EPI>(A, W, C, M, N, K, lda, ldc, splits, error_flag, stream)
     if (M <= 16) KIRAI_GEMM_CASE(16, true);
-    if (M <= 32) KIRAI_GEMM_CASE(32, true);
-    if (M <= 64) KIRAI_GEMM_CASE(64, true);
+    if (M <= 64) KIRAI_GEMM_CASE(32, true);  // 33..64 tokens: two column tiles of 32
     if (N <= 128) KIRAI_GEMM_CASE(128, false);
     KIRAI_GEMM_CASE(256, false);
 #undef KIRAI_GEMM_CASE
 }
 
-// Split count that kirai_gemm_bf16 picks for splits <= 0 (callers size the workspace with it).
+// Split count that the entry points pick for splits <= 0.
 KIRAI_EXPORT int kirai_gemm_bf16_auto_splits(int M, int N, int K) { return M <= 64 ? choose_splits(M, N, K) : 1; }
 
-// workspace: 32-bit scratch for split-K partial sums, at least splits * M * N floats when splits > 1.
-// splits <= 0 picks the count itself.
-KIRAI_EXPORT int kirai_gemm_bf16(const void* A, const void* W, void* C, float* workspace, size_t workspace_bytes, int M,
-                                 int N, int K, long lda, long ldc, int splits, int* error_flag, cudaStream_t stream) {
-    return gemm_dispatch<bf16>(A, W, C, workspace, workspace_bytes, M, N, K, lda, ldc, splits, error_flag, stream);
+// C[M, N] = A[M, K] W[N, K]^T.  splits <= 0 picks the split-K count itself (at most 4).
+KIRAI_EXPORT int kirai_gemm_bf16(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc,
+                                 int splits, int* error_flag, cudaStream_t stream) {
+    return gemm_dispatch<bf16, 0>(A, W, C, M, N, K, lda, ldc, splits, error_flag, stream);
 }
-KIRAI_EXPORT int kirai_gemm_bf16_out_f32(const void* A, const void* W, void* C, float* workspace,
-                                         size_t workspace_bytes, int M, int N, int K, long lda, long ldc, int splits,
-                                         int* error_flag, cudaStream_t stream) {
-    return gemm_dispatch<float>(A, W, C, workspace, workspace_bytes, M, N, K, lda, ldc, splits, error_flag, stream);
+KIRAI_EXPORT int kirai_gemm_bf16_out_f32(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc,
+                                         int splits, int* error_flag, cudaStream_t stream) {
+    return gemm_dispatch<float, 0>(A, W, C, M, N, K, lda, ldc, splits, error_flag, stream);
+}
+// C[M, N / 2] = silu(gate) * up, where W's N rows come in groups of 8 gate rows followed by their 8 up rows.
+KIRAI_EXPORT int kirai_gemm_bf16_swiglu(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc,
+                                        int splits, int* error_flag, cudaStream_t stream) {
+    return gemm_dispatch<bf16, 1>(A, W, C, M, N, K, lda, ldc, splits, error_flag, stream);
 }

@@ -337,33 +337,48 @@ def linear_plain(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torc
 
 
 def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-                   splits: int = 0) -> torch.Tensor:
+                   splits: int = 0, swiglu: bool = False) -> torch.Tensor:
     """bf16 ``x`` [M, K] times ``weight`` [N, K] transposed on the tcgen05 tensor cores (32-bit accumulation).
 
     K and the row stride of ``x`` must be multiples of 8 (TMA reads rows in 16-byte units).
-    ``splits`` > 1 cuts K between CTAs (0: chosen from the shape); the partial sums go through
-    a 32-bit workspace.
+    ``splits`` > 1 cuts K between the CTAs of a cluster (0: chosen from the shape, at most 8).
+    With ``swiglu`` the rows of ``weight`` are 8 gate rows, their 8 up rows, 8 gate rows, ... and
+    the result is silu(gate) * up, [M, N / 2].
     """
     _need_cuda(x, weight)
     assert x.dim() == 2 and x.stride(1) == 1 and weight.dim() == 2 and weight.is_contiguous()
     assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[1] == weight.shape[1]
     out_dtype = out_dtype or torch.bfloat16
     m, k, n = x.shape[0], x.shape[1], weight.shape[0]
-    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
-    if splits <= 0:
-        splits = library().kirai_gemm_bf16_auto_splits(_i(m), _i(n), _i(k))
-    workspace = torch.empty((splits, m, n), dtype=torch.float32, device=x.device) if splits > 1 else None
-    name = "kirai_gemm_bf16" if out_dtype == torch.bfloat16 else "kirai_gemm_bf16_out_f32"
-    _call(name, _ptr(x), _ptr(weight), _ptr(out), _ptr(workspace),
-          ctypes.c_size_t(0 if workspace is None else workspace.numel() * 4), _i(m), _i(n), _i(k), _l(x.stride(0)),
-          _l(n), _i(splits), _ptr(error_flag(x.device)), _stream())
+    if swiglu:
+        assert out_dtype == torch.bfloat16 and n % 16 == 0
+        name, width = "kirai_gemm_bf16_swiglu", n // 2
+    else:
+        name, width = ("kirai_gemm_bf16" if out_dtype == torch.bfloat16 else "kirai_gemm_bf16_out_f32"), n
+    out = torch.empty((m, width), dtype=out_dtype, device=x.device)
+    _call(name, _ptr(x), _ptr(weight), _ptr(out), _i(m), _i(n), _i(k), _l(x.stride(0)), _l(width), _i(splits),
+          _ptr(error_flag(x.device)), _stream())
     return out
+
+
+def tcgen05_takes(x: torch.Tensor) -> bool:
+    """Whether the tensor-core GEMM can read ``x`` [M, K] (bf16, 16-byte aligned rows)."""
+    return (x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) == 1
+            and x.data_ptr() % 16 == 0)
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Stacks gate [I, K] and up [I, K] as 8 gate rows, their 8 up rows, ... (I a multiple of 8),
+    the row order that the SwiGLU epilogue of the tensor-core GEMM reads."""
+    inter, k = gate.shape
+    assert up.shape == gate.shape and inter % 8 == 0
+    return torch.stack([gate.view(inter // 8, 8, k), up.view(inter // 8, 8, k)], dim=1).reshape(2 * inter, k).contiguous()
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """The linear layer of the product path: 32-bit FMAs for float32; for bfloat16 the tcgen05
     kernel, or the CUDA-core kernel when K is not a multiple of 8 (TMA cannot read such rows)."""
-    if x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
+    if tcgen05_takes(x):
         return linear_tcgen05(x, weight, out_dtype)
     return linear_plain(x, weight, out_dtype)
 

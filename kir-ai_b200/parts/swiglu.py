@@ -26,9 +26,23 @@ class SwiGLU(FeedForward):
 
     def load(self, weights, rt: Runtime) -> None:
         self.rt = rt
-        self.gate_up.load(weights, rt)
         self.down.load(weights, rt)
+        # On the tensor cores gate and up are one product whose epilogue applies silu(gate) * up:
+        # their rows are interleaved in eights at load, so that a thread's 16 outputs pair up.
+        self.fused_weight = None
+        if rt.dtype == torch.bfloat16 and self.intermediate_size % 8 == 0 and self.hidden_size % 8 == 0:
+            (gate_name, _), (up_name, _) = self.gate_up.sources
+            gate = weights.stored(gate_name).to(device=rt.device, dtype=rt.dtype)
+            up = weights.stored(up_name).to(device=rt.device, dtype=rt.dtype)
+            self.fused_weight = rt.ops.interleave_gate_up(gate, up)
+        else:
+            self.gate_up.load(weights, rt)
 
     def forward(self, x: torch.Tensor, batch=None) -> torch.Tensor:
+        ops = self.rt.ops
+        if self.fused_weight is not None and ops.tcgen05_takes(x):
+            return self.down.forward(ops.linear_tcgen05(x, self.fused_weight, swiglu=True))
+        if self.fused_weight is not None:
+            raise ValueError("SwiGLU input is not laid out for the tensor-core kernel (rows must be 16-byte aligned)")
         gate_up = self.gate_up.forward(x)
-        return self.down.forward(self.rt.ops.swiglu(gate_up))
+        return self.down.forward(ops.swiglu(gate_up))

@@ -128,6 +128,9 @@ def test_linear_tcgen05_against_plain(ops, m, n, k, out_dtype):
     if m <= 64:  # split along K through the workspace
         split = ops.linear_tcgen05(x, w, out_dtype, splits=3)
         assert float((split.float() - expected).abs().max()) <= bound
+    if m <= 64:
+        eight = ops.linear_tcgen05(x, w, out_dtype, splits=8)  # the largest cluster
+        assert float((eight.float() - expected).abs().max()) <= bound
     # a row-strided input (a slice of a wider buffer)
     wide = torch.zeros(m, k + 16, dtype=torch.bfloat16, device=DEV)
     wide[:, :k] = x
@@ -366,3 +369,20 @@ def test_tensor_core_attention_finds_a_far_key(ops):
     assert float((out[0, 0] - values[0][far, 0].float()).abs().max()) > 0.5
     out = ops.attention_decode(q, cache, table, ctx, 777 - far, head_dim ** -0.5, 2).float().cpu().unflatten(1, (q_heads, head_dim))
     assert float((out[0, 0] - values[0][far, 0].float()).abs().max()) <= 2e-2
+
+
+@pytest.mark.parametrize("m,inter,k,splits", [(1, 128, 64, 0), (5, 200, 136, 0), (16, 1000, 512, 3), (64, 1536, 1032, 8),
+                                              (65, 264, 192, 0), (300, 1000, 520, 0), (1024, 768, 256, 0)])
+def test_linear_swiglu_epilogue(ops, m, inter, k, splits):
+    x = rand(m, k, dtype=torch.bfloat16, scale=0.5)
+    gate, up = rand(inter, k, dtype=torch.bfloat16, scale=0.1, seed=3), rand(inter, k, dtype=torch.bfloat16, scale=0.1, seed=4)
+    weight = ops.interleave_gate_up(gate, up)
+    assert torch.equal(weight[:8], gate[:8]) and torch.equal(weight[8:16], up[:8]) and torch.equal(weight[16:24], gate[8:16])
+    g, u = x.float() @ gate.float().T, x.float() @ up.float().T
+    expected = g / (1.0 + torch.exp(-g)) * u
+    out = ops.linear_tcgen05(x, weight, splits=splits, swiglu=True)
+    ops.check_device_errors(torch.device(DEV))
+    assert out.shape == (m, inter)
+    assert float((out.float() - expected).abs().max()) <= 1e-2 * float(expected.abs().max())
+    separate = ops.swiglu(ops.linear_tcgen05(x, torch.cat([gate, up])))  # rounds gate and up to bf16 in between
+    assert float((out.float() - separate.float()).abs().max()) <= 2e-2 * float(expected.abs().max())

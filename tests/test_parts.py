@@ -58,7 +58,8 @@ def test_swiglu_and_linear_parts(dtype):
     out = ffn.forward(x.to(DEV))
     expected = plain.swiglu_mlp(x.float(), weights["mlp.gate_proj.weight"], weights["mlp.up_proj.weight"], weights["mlp.down_proj.weight"])
     assert out.shape == (11, 40) and float((out.float().cpu() - expected).abs().max()) <= tolerance(dtype, expected)
-    assert ffn.gate_up.weight.shape == (208, 40)  # gate and up stacked at load
+    stacked = ffn.fused_weight if dtype == torch.bfloat16 else ffn.gate_up.weight  # gate and up are one matrix after load
+    assert stacked.shape == (208, 40)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
