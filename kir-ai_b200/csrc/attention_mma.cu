@@ -6,13 +6,13 @@
 //
 //  * the prompt kernel: one CTA per (request, kv head, tile of 64 query rows),
 //    where the query rows enumerate (token, head of the group) pairs, so that
-//    the heads of a group share each key/value tile; its 4 warps own 16 rows
-//    each and walk the key tiles together, loads double-buffered by cp.async;
+//    the heads of a group share each key/value tile; 4 warps own 16 rows each
+//    and a fifth keeps a ring of 3 key/value tiles full by TMA from the pages;
 //  * the decode kernel, for batches in which every request brings one token:
 //    one CTA per (request, kv head, split of the context); the group's heads
-//    are the (few) query rows, each warp walks its own key tiles, the warps'
-//    states are merged in shared memory, and with several splits a second
-//    kernel merges the splits' partial states.
+//    are the (few) query rows, each warp walks its own key tiles through its
+//    own TMA ring, the warps' states are merged in shared memory, and with
+//    several splits a second kernel merges the splits' partial states.
 //
 // Keys are visible to a row at position pos when lo <= j <= pos, lo = max(0,
 // pos - window + 1) with a window, else 0 (same rule as the plain kernel).
@@ -23,16 +23,6 @@
 #include "tensor_map.cuh"
 
 namespace {
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
-    const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -60,43 +50,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int ROWS>
 __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
     return (uint32_t)((chunk >> 3) * (ROWS * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
-}
-
-struct PagedKV {
-    const bf16* cache;        // [num_pages, 2, kv_heads, page_size, head_dim]
-    const int* table;         // this request's block table row
-    int table_width, num_pages, kv_heads, page_size, head_dim, kv_head;
-};
-
-// Loads `ROWS` key rows and value rows starting at key j0 into shared tiles (zero where the key is
-// outside [j_lo, j_hi], the column is beyond head_dim, or the page is missing).
-template <int D, int ROWS, int THREADS>
-__device__ __forceinline__ void load_kv_tile(const PagedKV& kv, int j0, int j_lo, int j_hi, uint32_t k_smem,
-                                             uint32_t v_smem, int tid, int* error_flag) {
-    constexpr int CH = D / 8;
-    const int chunks_used = kv.head_dim / 8;
-    for (int id = tid; id < ROWS * CH; id += THREADS) {
-        const int row = id / CH, chunk = id % CH;
-        const int j = j0 + row;
-        bool valid = j >= j_lo && j <= j_hi && chunk < chunks_used;
-        const bf16* k_src = kv.cache;
-        const bf16* v_src = kv.cache;
-        if (valid) {
-            const int logical = j / kv.page_size;
-            const int page = logical < kv.table_width ? kv.table[logical] : -1;
-            if (page < 0 || page >= kv.num_pages) {
-                atomicExch(error_flag, 3);
-                valid = false;
-            } else {
-                const long base = ((((long)page * 2) * kv.kv_heads + kv.kv_head) * kv.page_size + (j % kv.page_size)) *
-                                      (long)kv.head_dim + chunk * 8;
-                k_src = kv.cache + base;
-                v_src = kv.cache + base + (long)kv.kv_heads * kv.page_size * kv.head_dim;
-            }
-        }
-        cp_async_16(k_smem + tile_offset<ROWS>(row, chunk), k_src, valid);
-        cp_async_16(v_smem + tile_offset<ROWS>(row, chunk), v_src, valid);
-    }
 }
 
 // Running softmax state of the two rows (g and g + 8) that a thread of an m16 tile holds.
@@ -207,59 +160,165 @@ __device__ __forceinline__ void warp_attend(WarpState<D>& st, uint32_t q_smem, i
     }
 }
 
+// Fills one ring slot (K tile at k_dst, V tile at v_dst, `BN` keys from key t * BN on) by TMA, one
+// box (a page, or part of one) per lane in turn; called by a whole warp.  Boxes without a page
+// (past the last key, or given back by the window) hold masked keys only.
+template <int BN, int PANELS>
+__device__ __forceinline__ void fill_kv_slot(const CUtensorMap* kv_map, uint32_t bar, uint32_t k_dst, uint32_t v_dst, int t,
+                                             int last_key, const int* table, int table_width, int num_pages,
+                                             int kv_heads, int kv_head, int page_size, int box_rows, int lane) {
+    const int boxes = BN / box_rows;
+    const uint32_t box_bytes = (uint32_t)box_rows * 128u * PANELS;  // of K, and as much of V
+    // first pass: how many boxes have a page (the barrier must know the byte count before any copy lands)
+    int count = 0;
+    for (int b = lane; b < boxes; b += 32) {
+        const int j = t * BN + b * box_rows;
+        const int logical = j / page_size;
+        const int page = (j <= last_key && logical < table_width) ? table[logical] : -1;
+        count += (page >= 0 && page < num_pages);
+    }
+    count = __reduce_add_sync(0xffffffffu, count);
+    // Boxes without a page: the warp clears their value rows together (their keys are masked by
+    // position whatever they hold, but a value row is multiplied by its zero weight and must be
+    // finite).  This happens before the barrier is armed, so that whoever passes the barrier
+    // (another warp, in the prompt kernel) sees the cleared rows.
+    if (count < boxes) {
+        for (int b = 0; b < boxes; ++b) {
+            const int j = t * BN + b * box_rows;
+            const int logical = j / page_size;
+            const int page = (j <= last_key && logical < table_width) ? table[logical] : -1;
+            if (page >= 0 && page < num_pages) continue;
+            for (int h = 0; h < PANELS; ++h) {
+                const uint32_t off = (uint32_t)(h * (BN * 128) + b * box_rows * 128);
+                for (int i = lane; i < box_rows * 8; i += 32)
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v_dst + off + i * 16), "r"(0u) : "memory");
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+    }
+    if (lane == 0) {
+        if (count) sm100::mbar_expect_tx(bar, 2u * box_bytes * (uint32_t)count);
+        else sm100::mbar_arrive(bar);
+    }
+    __syncwarp();
+    for (int b = lane; b < boxes; b += 32) {
+        const int j = t * BN + b * box_rows;
+        const int logical = j / page_size;
+        const int page = (j <= last_key && logical < table_width) ? table[logical] : -1;
+        if (page >= 0 && page < num_pages) {
+            const int row_k = ((page * 2) * kv_heads + kv_head) * page_size + (j % page_size);
+            const int row_v = row_k + kv_heads * page_size;
+#pragma unroll
+            for (int h = 0; h < PANELS; ++h) {
+                const uint32_t off = (uint32_t)(h * (BN * 128) + b * box_rows * 128);
+                sm100::tma_load_2d(k_dst + off, kv_map, bar, h * 64, row_k);
+                sm100::tma_load_2d(v_dst + off, kv_map, bar, h * 64, row_v);
+            }
+        }
+    }
+    __syncwarp();
+}
+
 // ------------------------------------------------------------------ prompt kernel
-#define PF_WARPS 4
+#define PF_WARPS 4      // consumer warps, 16 query rows each; one more warp feeds the ring
 #define PF_ROWS 64
 #define PF_BN 64
+#define PF_STAGES 3
 
 template <int D>
-__global__ void __launch_bounds__(PF_WARPS * 32)
-attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, bf16* __restrict__ out,
+struct PrefillSmem {
+    static constexpr int q_bytes = PF_ROWS * D * 2;
+    static constexpr int tile_bytes = PF_BN * D * 2;
+    static constexpr int ring_bytes = PF_STAGES * 2 * tile_bytes;
+    static constexpr int total = q_bytes + ring_bytes + 2 * PF_STAGES * 8;  // no slack: the base must be 1024-aligned
+    static constexpr int ctas_per_sm = (2 * (total + 1024) <= 227 * 1024) ? 2 : 1;
+};
+
+template <int D>
+__global__ void __launch_bounds__((PF_WARPS + 1) * 32, PrefillSmem<D>::ctas_per_sm)
+attention_prefill_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ q, bf16* __restrict__ out,
                          const int* __restrict__ block_table, const int* __restrict__ query_start,
                          const int* __restrict__ context_len, int q_heads, int kv_heads, int head_dim,
-                         long q_row_stride, int page_size, int table_width, int num_pages, int window, float scale_log2,
-                         int* __restrict__ error_flag) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    const int tile = blockIdx.x, kv_head = blockIdx.y, req = blockIdx.z;
+                         long q_row_stride, int page_size, int box_rows, int table_width, int num_pages, int window,
+                         float scale_log2, int* __restrict__ error_flag) {
+    pdl_launch_dependents();
+    pdl_wait();
+    using Smem = PrefillSmem<D>;
+    constexpr int PANELS = D / 64;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int tile = gridDim.x - 1 - blockIdx.x;  // late tiles see the most keys: start them first
+    const int kv_head = blockIdx.y, req = blockIdx.z;
     const int group = q_heads / kv_heads;
     const int q_begin = query_start[req];
     const int q_len = query_start[req + 1] - q_begin;
     const int rows_total = q_len * group;
     const int row0 = tile * PF_ROWS;
     if (row0 >= rows_total) return;
+    const uint32_t q_smem = sm100::smem_addr(smem);
+    if (q_smem & 1023u) {  // the swizzled tiles need a 1024-byte aligned base: refuse rather than compute nonsense
+        if (threadIdx.x == 0) atomicExch(error_flag, 5);
+        return;
+    }
     const int ctx = context_len[req];
     const int start_pos = ctx - q_len;  // position of the request's first new token
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t ring = q_smem + Smem::q_bytes;
+    uint64_t* full_bar = (uint64_t*)(smem + Smem::q_bytes + Smem::ring_bytes);
+    uint64_t* empty_bar = full_bar + PF_STAGES;
 
-    const uint32_t q_smem = smem_u32(smem);
-    const uint32_t kv_smem = q_smem + PF_ROWS * D * 2;  // [2 stages][K tile, V tile]
-    constexpr uint32_t TILE_BYTES = PF_BN * D * 2;
-
+    if (tid == 0) {
+        sm100::tma_prefetch_descriptor(&kv_map);
+        for (int s = 0; s < PF_STAGES; ++s) {
+            sm100::mbar_init(sm100::smem_addr(&full_bar[s]), 1);
+            sm100::mbar_init(sm100::smem_addr(&empty_bar[s]), PF_WARPS);
+        }
+        sm100::mbar_fence_init();
+    }
     // Q tile: row r is token (row0 + r) / group, head kv_head * group + (row0 + r) % group
     {
         constexpr int CH = D / 8;
         const int chunks_used = head_dim / 8;
-        for (int id = tid; id < PF_ROWS * CH; id += PF_WARPS * 32) {
+        for (int id = tid; id < PF_ROWS * CH; id += (PF_WARPS + 1) * 32) {
             const int r = id / CH, chunk = id % CH;
             const int row = row0 + r;
-            const bool valid = row < rows_total && chunk < chunks_used;
-            const bf16* src = q;
-            if (valid) {
+            uint4 value = make_uint4(0u, 0u, 0u, 0u);
+            if (row < rows_total && chunk < chunks_used) {
                 const int token = row / group, head = kv_head * group + row % group;
-                src = q + (size_t)(q_begin + token) * q_row_stride + (size_t)head * head_dim + chunk * 8;
+                value = *reinterpret_cast<const uint4*>(q + (size_t)(q_begin + token) * q_row_stride + (size_t)head * head_dim + chunk * 8);
             }
-            cp_async_16(q_smem + tile_offset<PF_ROWS>(r, chunk), src, valid);
+            *reinterpret_cast<uint4*>(smem + tile_offset<PF_ROWS>(r, chunk)) = value;
         }
     }
-    PagedKV kv{cache, block_table + (long)req * table_width, table_width, num_pages, kv_heads, page_size, head_dim, kv_head};
+    __syncthreads();
 
     const int last_row = min(rows_total, row0 + PF_ROWS) - 1;
     const int pos_first = start_pos + row0 / group;
     const int pos_last = start_pos + last_row / group;
     const int key_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
     const int first_tile = key_lo / PF_BN, last_tile = pos_last / PF_BN;
+    const int num_tiles = last_tile - first_tile + 1;
+    bool ok = true;
 
-    // per-thread rows g and g + 8 of this warp's 16
+    if (warp == PF_WARPS) {
+        // producer: keeps the ring full
+        const int* table = block_table + (long)req * table_width;
+        for (int it = 0; it < num_tiles; ++it) {
+            const int slot = it % PF_STAGES;
+            if (it >= PF_STAGES && !sm100::mbar_wait(sm100::smem_addr(&empty_bar[slot]), (uint32_t)(it / PF_STAGES - 1) & 1u)) {
+                ok = false;
+                break;
+            }
+            const uint32_t k_dst = ring + slot * 2 * Smem::tile_bytes;
+            fill_kv_slot<PF_BN, PANELS>(&kv_map, sm100::smem_addr(&full_bar[slot]), k_dst, k_dst + Smem::tile_bytes,
+                                        first_tile + it, pos_last, table, table_width, num_pages, kv_heads, kv_head,
+                                        page_size, box_rows, lane);
+        }
+        if (!ok && lane == 0) atomicExch(error_flag, 4);
+        return;
+    }
+
+    // consumers: per-thread rows g and g + 8 of this warp's 16
     int lo[2], hi[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -273,32 +332,38 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ ca
             lo[r] = 0;  // sees nothing
         }
     }
+    constexpr bool Q_IN_REGS = D <= 128;
+    uint32_t q_regs[Q_IN_REGS ? D / 16 : 1][4];
+    if (Q_IN_REGS) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+            ldmatrix_x4(q_smem + tile_offset<PF_ROWS>(warp * 16 + (lane & 15), kk * 2 + (lane >> 4)), q_regs[kk][0],
+                        q_regs[kk][1], q_regs[kk][2], q_regs[kk][3]);
+    }
     WarpState<D> st;
     st.init();
-
-    load_kv_tile<D, PF_BN, PF_WARPS * 32>(kv, first_tile * PF_BN, key_lo, pos_last, kv_smem, kv_smem + TILE_BYTES, tid,
-                                          error_flag);
-    cp_async_commit();
-    for (int t = first_tile; t <= last_tile; ++t) {
-        const int stage = (t - first_tile) & 1;
-        if (t + 1 <= last_tile) {
-            const uint32_t next = kv_smem + (stage ^ 1) * 2 * TILE_BYTES;
-            load_kv_tile<D, PF_BN, PF_WARPS * 32>(kv, (t + 1) * PF_BN, key_lo, pos_last, next, next + TILE_BYTES, tid,
-                                                  error_flag);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
+    const int warp_first_row = row0 + warp * 16;
+    const int warp_last_row = min(rows_total - 1, warp_first_row + 15);
+    const int warp_pos_last = warp_first_row < rows_total ? start_pos + warp_last_row / group : -1;
+    const int warp_key_lo = (window > 0 && warp_first_row < rows_total) ? max(0, start_pos + warp_first_row / group - window + 1) : 0;
+    for (int it = 0; it < num_tiles; ++it) {
+        const int slot = it % PF_STAGES;
+        const int t = first_tile + it;
+        if (!sm100::mbar_wait(sm100::smem_addr(&full_bar[slot]), (uint32_t)(it / PF_STAGES) & 1u)) {
+            ok = false;
+            break;
         }
-        __syncthreads();
-        const uint32_t k_s = kv_smem + stage * 2 * TILE_BYTES;
-        // a warp whose rows all end before this tile has nothing to add (uniform per warp)
-        const int warp_last_row = min(rows_total - 1, row0 + warp * 16 + 15);
-        const bool warp_active = row0 + warp * 16 < rows_total && (start_pos + warp_last_row / group) >= t * PF_BN;
-        if (warp_active)
-            warp_attend<D, PF_BN, PF_ROWS, false>(st, q_smem, warp * 16, nullptr, k_s, k_s + TILE_BYTES, t * PF_BN, lo, hi, scale_log2, lane);
-        __syncthreads();  // the stage is free for the load after next
+        // a warp whose rows all lie before this tile, or whose windows all start after it, adds nothing
+        const bool warp_active = warp_pos_last >= t * PF_BN && warp_key_lo < (t + 1) * PF_BN;
+        if (warp_active) {
+            const uint32_t k_s = ring + slot * 2 * Smem::tile_bytes;
+            warp_attend<D, PF_BN, PF_ROWS, Q_IN_REGS>(st, q_smem, warp * 16, q_regs, k_s, k_s + Smem::tile_bytes, t * PF_BN, lo, hi,
+                                                     scale_log2, lane);
+        }
+        __syncwarp();
+        if (lane == 0) sm100::mbar_arrive(sm100::smem_addr(&empty_bar[slot]));
     }
+    if (!ok && lane == 0) atomicExch(error_flag, 4);
     // normalise and store
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -349,6 +414,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
                         const int* __restrict__ context_len, int q_heads, int kv_heads, int head_dim, long q_row_stride,
                         int page_size, int box_rows, int table_width, int num_pages, int window, float scale_log2,
                         int num_splits, int* __restrict__ error_flag) {
+    pdl_launch_dependents();
+    pdl_wait();
     using Smem = DecodeSmem<D>;
     constexpr int BN = Smem::BN;
     constexpr int PANELS = D / 64;
@@ -391,54 +458,12 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
     __syncthreads();
 
     const int* table = block_table + (long)req * table_width;
-    const int boxes = BN / box_rows;  // <= 32: one lane per box
-    const uint32_t box_bytes = (uint32_t)box_rows * 128u * PANELS;  // of K, and as much of V
     bool ok = true;
-
-    // Fills ring slot `slot` with key tile `t`: every lane looks after one box (one page, or a part of one).
+    // Fills ring slot `slot` with key tile `t`.
     auto issue = [&](int t, int slot) {
-        const uint32_t bar = sm100::smem_addr(&bars[slot]);
-        const uint32_t k_dst = ring + slot * 2 * Smem::tile_bytes, v_dst = k_dst + Smem::tile_bytes;
-        int page = -1, j = 0;
-        if (lane < boxes) {
-            j = t * BN + lane * box_rows;
-            const int logical = j / page_size;
-            if (j <= pos && logical < table_width) page = table[logical];
-            if (page >= num_pages) page = -1;
-        }
-        const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
-        if (lane == 0) {
-            if (valid) sm100::mbar_expect_tx(bar, 2u * box_bytes * __popc(valid));
-            else sm100::mbar_arrive(bar);
-        }
-        __syncwarp();
-        if (page >= 0) {
-            const int row_k = ((page * 2) * kv_heads + kv_head) * page_size + (j % page_size);
-            const int row_v = row_k + kv_heads * page_size;
-#pragma unroll
-            for (int h = 0; h < PANELS; ++h) {
-                const uint32_t off = (uint32_t)(h * (BN * 128) + lane * box_rows * 128);
-                sm100::tma_load_2d(k_dst + off, &kv_map, bar, h * 64, row_k);
-                sm100::tma_load_2d(v_dst + off, &kv_map, bar, h * 64, row_v);
-            }
-        }
-        // boxes without a page (past the context, or given back by the window) hold masked keys only;
-        // their value rows must still be finite, so they are cleared
-        unsigned missing = ~valid & (boxes >= 32 ? 0xffffffffu : ((1u << boxes) - 1u));
-        while (missing) {
-            const int b = __ffs(missing) - 1;
-            missing &= missing - 1;
-            for (int h = 0; h < PANELS; ++h) {
-                const uint32_t off = (uint32_t)(h * (BN * 128) + b * box_rows * 128);
-                for (int i = lane; i < box_rows * 8; i += 32) {
-                    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(k_dst + off + i * 16), "r"(zero.x), "r"(zero.y), "r"(zero.z), "r"(zero.w) : "memory");
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(v_dst + off + i * 16), "r"(zero.x), "r"(zero.y), "r"(zero.z), "r"(zero.w) : "memory");
-                }
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        }
-        __syncwarp();
+        const uint32_t k_dst = ring + slot * 2 * Smem::tile_bytes;
+        fill_kv_slot<BN, PANELS>(&kv_map, sm100::smem_addr(&bars[slot]), k_dst, k_dst + Smem::tile_bytes, t, pos, table,
+                                 table_width, num_pages, kv_heads, kv_head, page_size, box_rows, lane);
     };
 
     int lo[2], hi[2];
@@ -526,6 +551,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
 
 __global__ void attention_merge_splits_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int head_dim,
                                               int num_splits) {
+    pdl_launch_dependents();
+    pdl_wait();
     // one block per (request, head)
     const size_t rh = blockIdx.x;
     const float* base = partial + rh * num_splits * (head_dim + 2);
@@ -548,17 +575,20 @@ int prefill_launch(const void* q, const void* cache, void* out, const int* block
                    const int* context_len, int requests, int max_query_len, int q_heads, int kv_heads, int head_dim,
                    long q_row_stride, int page_size, int table_width, int num_pages, int window, float scale,
                    int* error_flag, cudaStream_t stream) {
+    using Smem = PrefillSmem<D>;
     const int group = q_heads / kv_heads;
-    const size_t smem = (size_t)PF_ROWS * D * 2 + 4 * (size_t)PF_BN * D * 2;
+    const int box_rows = page_size < PF_BN ? page_size : PF_BN;
+    if (PF_BN % box_rows != 0 || page_size % box_rows != 0) return KIRAI_ERR_UNSUPPORTED;  // page sizes: powers of two
+    CUtensorMap kv_map;
+    const uint64_t rows = (uint64_t)num_pages * 2 * kv_heads * page_size;
+    if (!tmap::bf16_2d_sw128(&kv_map, cache, rows, head_dim, head_dim, box_rows, 64)) return KIRAI_ERR_BAD_ALIGN;
     auto kernel = attention_prefill_kernel<D>;
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total);
     if (err != cudaSuccess) return (int)err;
     dim3 grid((unsigned)(((long)max_query_len * group + PF_ROWS - 1) / PF_ROWS), kv_heads, requests);
-    kernel<<<grid, PF_WARPS * 32, smem, stream>>>((const bf16*)q, (const bf16*)cache, (bf16*)out, block_table,
-                                                 query_start, context_len, q_heads, kv_heads, head_dim, q_row_stride,
-                                                 page_size, table_width, num_pages, window,
-                                                 scale * 1.4426950408889634f, error_flag);
-    return launch_status();
+    return launch_pdl(kernel, grid, dim3((PF_WARPS + 1) * 32), (size_t)Smem::total, stream, 1u, kv_map, (const bf16*)q,
+                      (bf16*)out, block_table, query_start, context_len, q_heads, kv_heads, head_dim, q_row_stride,
+                      page_size, box_rows, table_width, num_pages, window, scale * 1.4426950408889634f, error_flag);
 }
 
 template <int D>
@@ -576,14 +606,13 @@ int decode_launch(const void* q, const void* cache, void* out, float* partial, c
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total);
     if (err != cudaSuccess) return (int)err;
     dim3 grid(num_splits, kv_heads, requests);
-    kernel<<<grid, DC_WARPS * 32, Smem::total, stream>>>(kv_map, (const bf16*)q, (bf16*)out, partial, block_table,
-                                                        context_len, q_heads, kv_heads, head_dim, q_row_stride,
-                                                        page_size, box_rows, table_width, num_pages, window,
-                                                        scale * 1.4426950408889634f, num_splits, error_flag);
-    int status = launch_status();
+    int status = launch_pdl(kernel, grid, dim3(DC_WARPS * 32), (size_t)Smem::total, stream, 1u, kv_map, (const bf16*)q,
+                            (bf16*)out, partial, block_table, context_len, q_heads, kv_heads, head_dim, q_row_stride,
+                            page_size, box_rows, table_width, num_pages, window, scale * 1.4426950408889634f,
+                            num_splits, error_flag);
     if (status || num_splits == 1) return status;
-    attention_merge_splits_kernel<<<requests * q_heads, 128, 0, stream>>>(partial, (bf16*)out, head_dim, num_splits);
-    return launch_status();
+    return launch_pdl(attention_merge_splits_kernel, dim3(requests * q_heads), dim3(128), 0, stream, 1u,
+                      (const float*)partial, (bf16*)out, head_dim, num_splits);
 }
 
 int check_common(int q_heads, int kv_heads, int head_dim, long q_row_stride, const void* q) {

@@ -73,3 +73,51 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
+
+// ---- programmatic dependent launch -----------------------------------------
+// Kernels of the forward pass are launched so that a kernel may begin (set up, prefetch what
+// does not depend on its predecessor) while the kernel before it in the stream drains.  A kernel
+// calls pdl_launch_dependents() as soon as its successor may start and pdl_wait() before it
+// touches anything its predecessor wrote; without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <cstdlib>
+static inline bool pdl_enabled() {
+    static const bool enabled = [] {
+        const char* value = std::getenv("KIRAI_PDL");
+        return !(value && value[0] == '0');
+    }();
+    return enabled;
+}
+
+// Launches `kernel` with programmatic stream serialization (and, if cluster_z > 1, as clusters of
+// (1, 1, cluster_z) CTAs).  Returns the launch status.
+template <typename... Params, typename... Args>
+static inline int launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             unsigned cluster_z, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    unsigned count = 0;
+    if (pdl_enabled()) {
+        attrs[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[count].val.programmaticStreamSerializationAllowed = 1;
+        ++count;
+    }
+    if (cluster_z > 1) {
+        attrs[count].id = cudaLaunchAttributeClusterDimension;
+        attrs[count].val.clusterDim.x = 1;
+        attrs[count].val.clusterDim.y = 1;
+        attrs[count].val.clusterDim.z = cluster_z;
+        ++count;
+    }
+    config.attrs = attrs;
+    config.numAttrs = count;
+    const cudaError_t err = cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+    if (err != cudaSuccess) return (int)err;
+    return (int)cudaGetLastError();
+}

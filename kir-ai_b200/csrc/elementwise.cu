@@ -11,6 +11,8 @@
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                                  int hidden, int vocab, int* __restrict__ error_flag) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int token = blockIdx.x;
     const int id = ids[token];
     if (id < 0 || id >= vocab) {
@@ -26,8 +28,8 @@ template <typename T>
 static int embedding_launch(const void* table, const int* ids, float* out, int tokens, int hidden, int vocab,
                             int* error_flag, cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    embedding_kernel<T><<<tokens, 256, 0, stream>>>((const T*)table, ids, out, hidden, vocab, error_flag);
-    return launch_status();
+    const int pdl_status = launch_pdl(embedding_kernel<T>, dim3(tokens), dim3(256), 0, stream, 1u, (const T*)table, ids, out, hidden, vocab, error_flag);
+    return pdl_status;
 }
 
 KIRAI_EXPORT int kirai_embedding_f32(const void* table, const int* ids, float* out, int tokens, int hidden, int vocab,
@@ -48,6 +50,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
                                    const float* __restrict__ weight, T* __restrict__ out,
                                    const int* __restrict__ row_index, float* __restrict__ resid_out, int hidden,
                                    float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[32];
     const int row = blockIdx.x;
     const int src = row_index ? row_index[row] : row;
@@ -81,9 +85,9 @@ static int add_rmsnorm_launch(float* resid, const void* delta, const float* weig
     if (rows <= 0) return 0;
     if (row_index && !resid_out) return KIRAI_ERR_BAD_SIZE;
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-    add_rmsnorm_kernel<T><<<rows, threads, 0, stream>>>(resid, (const T*)delta, weight, (T*)out, row_index, resid_out,
+    const int pdl_status = launch_pdl(add_rmsnorm_kernel<T>, dim3(rows), dim3(threads), 0, stream, 1u, resid, (const T*)delta, weight, (T*)out, row_index, resid_out,
                                                         hidden, eps);
-    return launch_status();
+    return pdl_status;
 }
 
 KIRAI_EXPORT int kirai_add_rmsnorm_f32(float* resid, const void* delta, const float* weight, void* out,
@@ -102,6 +106,8 @@ KIRAI_EXPORT int kirai_add_rmsnorm_bf16(float* resid, const void* delta, const f
 template <typename T>
 __global__ void head_rmsnorm_kernel(T* __restrict__ x, const float* __restrict__ weight, int rows, int heads, int width,
                                     long row_stride, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (warp >= rows * heads) return;
@@ -124,8 +130,8 @@ static int head_rmsnorm_launch(void* x, const float* weight, int rows, int heads
     if (warps <= 0) return 0;
     const int threads = 128;
     const long blocks = (warps * 32 + threads - 1) / threads;
-    head_rmsnorm_kernel<T><<<(unsigned)blocks, threads, 0, stream>>>((T*)x, weight, rows, heads, width, row_stride, eps);
-    return launch_status();
+    const int pdl_status = launch_pdl(head_rmsnorm_kernel<T>, dim3((unsigned)blocks), dim3(threads), 0, stream, 1u, (T*)x, weight, rows, heads, width, row_stride, eps);
+    return pdl_status;
 }
 KIRAI_EXPORT int kirai_head_rmsnorm_f32(void* x, const float* weight, int rows, int heads, int width, long row_stride,
                                         float eps, cudaStream_t stream) {
@@ -142,6 +148,8 @@ KIRAI_EXPORT int kirai_head_rmsnorm_bf16(void* x, const float* weight, int rows,
 template <typename T>
 __global__ void rope_kernel(T* __restrict__ x, const int* __restrict__ positions, const float* __restrict__ inv_freq,
                             int rows, int heads, int width, int rotary_dim, long row_stride) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int half = rotary_dim >> 1;
     const long total = (long)rows * heads * half;
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -166,10 +174,10 @@ static int rope_launch(void* x, const int* positions, const float* inv_freq, int
     const long total = (long)rows * heads * (rotary_dim / 2);
     if (total <= 0) return 0;
     const int threads = 256;
-    rope_kernel<T><<<(unsigned)((total + threads - 1) / threads), threads, 0, stream>>>((T*)x, positions, inv_freq, rows,
+    const int pdl_status = launch_pdl(rope_kernel<T>, dim3((unsigned)((total + threads - 1) / threads)), dim3(threads), 0, stream, 1u, (T*)x, positions, inv_freq, rows,
                                                                                       heads, width, rotary_dim,
                                                                                       row_stride);
-    return launch_status();
+    return pdl_status;
 }
 KIRAI_EXPORT int kirai_rope_f32(void* x, const int* positions, const float* inv_freq, int rows, int heads, int width,
                                 int rotary_dim, long row_stride, cudaStream_t stream) {
@@ -195,6 +203,8 @@ __global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v
                                 const int* __restrict__ positions, int rows, int kv_heads, int head_dim,
                                 long k_row_stride, long v_row_stride, int page_size, int table_width, int num_pages,
                                 int* __restrict__ error_flag) {
+    pdl_launch_dependents();
+    pdl_wait();
     const long total = (long)rows * kv_heads * head_dim;
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
@@ -223,10 +233,10 @@ static int kv_write_launch(const void* k, const void* v, void* cache, const int*
     const long total = (long)rows * kv_heads * head_dim;
     if (total <= 0) return 0;
     const int threads = 256;
-    kv_write_kernel<T><<<(unsigned)((total + threads - 1) / threads), threads, 0, stream>>>(
+    const int pdl_status = launch_pdl(kv_write_kernel<T>, dim3((unsigned)((total + threads - 1) / threads)), dim3(threads), 0, stream, 1u, 
         (const T*)k, (const T*)v, (T*)cache, block_table, request_of_token, positions, rows, kv_heads, head_dim,
         k_row_stride, v_row_stride, page_size, table_width, num_pages, error_flag);
-    return launch_status();
+    return pdl_status;
 }
 KIRAI_EXPORT int kirai_kv_write_f32(const void* k, const void* v, void* cache, const int* block_table,
                                     const int* request_of_token, const int* positions, int rows, int kv_heads,
@@ -259,6 +269,8 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const float* _
                                              const int* __restrict__ positions, int rows, int q_heads, int kv_heads,
                                              int head_dim, int rotary_dim, float eps, int page_size, int table_width,
                                              int num_pages, int write_cache, int* __restrict__ error_flag) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int heads_total = q_heads + 2 * kv_heads;
     const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -362,10 +374,10 @@ static int qk_norm_rope_kv_write_launch(void* qkv, const float* q_weight, const 
     const long warps = (long)rows * (q_heads + 2 * kv_heads);
     if (warps <= 0) return 0;
     const int threads = 128;
-    qk_norm_rope_kv_write_kernel<T><<<(unsigned)((warps * 32 + threads - 1) / threads), threads, 0, stream>>>(
+    const int pdl_status = launch_pdl(qk_norm_rope_kv_write_kernel<T>, dim3((unsigned)((warps * 32 + threads - 1) / threads)), dim3(threads), 0, stream, 1u, 
         (T*)qkv, q_weight, k_weight, inv_freq, (T*)cache, block_table, request_of_token, positions, rows, q_heads,
         kv_heads, head_dim, rotary_dim, eps, page_size, table_width, num_pages, write_cache, error_flag);
-    return launch_status();
+    return pdl_status;
 }
 KIRAI_EXPORT int kirai_qk_norm_rope_kv_write_f32(void* qkv, const float* q_weight, const float* k_weight,
                                                  const float* inv_freq, void* cache, const int* block_table,
@@ -392,6 +404,8 @@ KIRAI_EXPORT int kirai_qk_norm_rope_kv_write_bf16(void* qkv, const float* q_weig
 // gate_up is [rows, 2 * inter]: the gate half, then the up half.  out = silu(gate) * up.
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long rows, int inter) {
+    pdl_launch_dependents();
+    pdl_wait();
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * inter) return;
     const long row = idx / inter;
@@ -405,9 +419,9 @@ static int swiglu_launch(const void* gate_up, void* out, int rows, int inter, cu
     const long total = (long)rows * inter;
     if (total <= 0) return 0;
     const int threads = 256;
-    swiglu_kernel<T><<<(unsigned)((total + threads - 1) / threads), threads, 0, stream>>>((const T*)gate_up, (T*)out,
+    const int pdl_status = launch_pdl(swiglu_kernel<T>, dim3((unsigned)((total + threads - 1) / threads)), dim3(threads), 0, stream, 1u, (const T*)gate_up, (T*)out,
                                                                                         rows, inter);
-    return launch_status();
+    return pdl_status;
 }
 KIRAI_EXPORT int kirai_swiglu_f32(const void* gate_up, void* out, int rows, int inter, cudaStream_t stream) {
     return swiglu_launch<float>(gate_up, out, rows, inter, stream);
@@ -421,14 +435,16 @@ KIRAI_EXPORT int kirai_swiglu_bf16(const void* gate_up, void* out, int rows, int
 // followed by a norm that could fold the add in.
 template <typename T>
 __global__ void add_residual_kernel(float* __restrict__ resid, const T* __restrict__ delta, long count) {
+    pdl_launch_dependents();
+    pdl_wait();
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx < count) resid[idx] += to_f32<T>(delta[idx]);
 }
 template <typename T>
 static int add_residual_launch(float* resid, const void* delta, long count, cudaStream_t stream) {
     if (count <= 0) return 0;
-    add_residual_kernel<T><<<(unsigned)((count + 255) / 256), 256, 0, stream>>>(resid, (const T*)delta, count);
-    return launch_status();
+    const int pdl_status = launch_pdl(add_residual_kernel<T>, dim3((unsigned)((count + 255) / 256)), dim3(256), 0, stream, 1u, resid, (const T*)delta, count);
+    return pdl_status;
 }
 KIRAI_EXPORT int kirai_add_residual_f32(float* resid, const void* delta, long count, cudaStream_t stream) {
     return add_residual_launch<float>(resid, delta, count, stream);
@@ -443,6 +459,8 @@ KIRAI_EXPORT int kirai_add_residual_bf16(float* resid, const void* delta, long c
 // without the host in between.
 __global__ void decode_advance_kernel(int* __restrict__ token_ids, const int* __restrict__ sampled,
                                       int* __restrict__ positions, int* __restrict__ context_len, int count) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= count) return;
     token_ids[i] = sampled[i];
@@ -452,6 +470,6 @@ __global__ void decode_advance_kernel(int* __restrict__ token_ids, const int* __
 KIRAI_EXPORT int kirai_decode_advance(int* token_ids, const int* sampled, int* positions, int* context_len, int count,
                                       cudaStream_t stream) {
     if (count <= 0) return 0;
-    decode_advance_kernel<<<(count + 127) / 128, 128, 0, stream>>>(token_ids, sampled, positions, context_len, count);
-    return launch_status();
+    const int pdl_status = launch_pdl(decode_advance_kernel, dim3((count + 127) / 128), dim3(128), 0, stream, 1u, token_ids, sampled, positions, context_len, count);
+    return pdl_status;
 }

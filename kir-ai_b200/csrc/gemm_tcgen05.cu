@@ -17,6 +17,12 @@
 // epilogue variant applies SwiGLU to interleaved gate and up rows.  Every
 // barrier wait is bounded; a wait that runs out sets the device error flag and
 // the CTA winds down.
+//
+// The kernel is launched with programmatic stream serialization and starts
+// fetching W before the kernel before it in the stream has finished; it waits
+// for that kernel only before it reads A or writes C.  W must therefore not be
+// written by the kernel that directly precedes a product in the same stream
+// (weights are constants of a loaded model).
 #include "sm100.cuh"
 #include "tensor_map.cuh"
 
@@ -26,23 +32,24 @@ using namespace sm100;
 #define GEMM_BK 64
 #define GEMM_THREADS 192
 
-// Shared memory of one CTA.  The swapped, weight-streaming case (BN <= 32) keeps the CTA small
-// enough for two CTAs per SM, so that every SM streams weights even when there are fewer tiles
-// than two waves; it also holds the slots in which the cluster's CTAs leave their partial tiles.
-// The many-token case takes as many stages as fit one CTA per SM.
+// Shared memory of one CTA: the ring of stages, the barriers, then (only with split-K) one slot
+// per CTA of the cluster for the partial tiles.  The swapped, weight-streaming case (BN <= 64)
+// keeps the ring small enough for two CTAs per SM, so that every SM streams weights even when
+// there are fewer tiles than two waves; the many-token case takes as many stages as fit.
 template <int BN>
 struct GemmSmem {
-    static constexpr bool streaming = BN <= 32;
+    static constexpr bool streaming = BN <= 64;
     static constexpr int x_bytes = GEMM_BM * GEMM_BK * 2;
     static constexpr int y_bytes = BN * GEMM_BK * 2;
     static constexpr int stage_bytes = x_bytes + y_bytes;
-    static constexpr int max_splits = streaming ? 64 / BN : 1;                        // 4 for BN 16, 2 for BN 32
-    static constexpr int slot_bytes = BN * GEMM_BM * 4;                               // one 32-bit partial tile
-    static constexpr int slots_bytes = streaming ? max_splits * slot_bytes : 0;       // 32 KB
-    static constexpr int stages = streaming ? (BN == 16 ? 4 : 3) : (200 * 1024 / stage_bytes);
+    static constexpr int max_splits = BN == 16 ? 4 : (BN <= 64 ? 2 : 1);
+    static constexpr int slot_bytes = BN * GEMM_BM * 4;  // one 32-bit partial tile
+    static constexpr int stages = streaming ? 4 : (200 * 1024 / stage_bytes);
     static constexpr int barrier_bytes = 256;
-    static constexpr int total = stages * stage_bytes + slots_bytes + barrier_bytes + 1024;  // + slack to align to 1024
     static constexpr int ctas_per_sm = streaming ? 2 : 1;
+    static constexpr int total(int splits) {  // + slack to align the base to 1024 bytes
+        return stages * stage_bytes + barrier_bytes + (splits > 1 ? splits * slot_bytes : 0) + 1024;
+    }
 };
 
 template <int BN>
@@ -78,8 +85,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     constexpr int STAGES = Smem::stages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    float* slots = reinterpret_cast<float*>(smem + STAGES * Smem::stage_bytes);  // [splits][BN][128], used in the first CTA
-    uint64_t* bars = (uint64_t*)(smem + STAGES * Smem::stage_bytes + Smem::slots_bytes);
+    uint64_t* bars = (uint64_t*)(smem + STAGES * Smem::stage_bytes);
+    float* slots = reinterpret_cast<float*>(smem + STAGES * Smem::stage_bytes + Smem::barrier_bytes);  // [splits][BN][128], used in the first CTA
     uint64_t* full_bar = bars;                 // [STAGES] TMA -> MMA
     uint64_t* empty_bar = bars + STAGES;       // [STAGES] MMA -> TMA
     uint64_t* done_bar = bars + 2 * STAGES;    // accumulator complete
@@ -93,6 +100,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const int kb_end = min(total_k_blocks, kb_begin + k_blocks_per_split);
     const int num_kb = max(0, kb_end - kb_begin);
     const uint32_t rank = blockIdx.z;  // the cluster is (1, 1, splits) and the grid's z extent is splits
+    pdl_launch_dependents();  // the next kernel may set itself up while this one streams
 
     if (threadIdx.x == 0) {
         tma_prefetch_descriptor(&map_x);
@@ -118,7 +126,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 
     if (warp == 0) {
         if (elect_one()) {
-            for (int i = 0; i < num_kb; ++i) {
+            // The weights do not depend on the kernel before this one: with SWAP the X operand (weights)
+            // of the first ring of stages is fetched at once, and only the activations wait for it.
+            const int x_first = SWAP ? 0 : 1, y_first = SWAP ? 1 : 0;  // which operand is the weights
+            const int head = num_kb < STAGES ? num_kb : STAGES;
+            for (int i = 0; i < head; ++i) {
+                const uint32_t full = smem_addr(&full_bar[i]);
+                mbar_expect_tx(full, Smem::stage_bytes);
+                const uint32_t dst = smem_addr(smem + i * Smem::stage_bytes);
+                const int k = (kb_begin + i) * GEMM_BK;
+                if (x_first == 0) tma_load_2d(dst, &map_x, full, k, x0);
+                if (y_first == 0) tma_load_2d(dst + Smem::x_bytes, &map_y, full, k, y0);
+            }
+            pdl_wait();  // what the kernel before wrote (the activations) is complete and visible
+            for (int i = 0; i < head; ++i) {
+                const uint32_t full = smem_addr(&full_bar[i]);
+                const uint32_t dst = smem_addr(smem + i * Smem::stage_bytes);
+                const int k = (kb_begin + i) * GEMM_BK;
+                if (x_first == 1) tma_load_2d(dst, &map_x, full, k, x0);
+                if (y_first == 1) tma_load_2d(dst + Smem::x_bytes, &map_y, full, k, y0);
+            }
+            for (int i = head; i < num_kb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
                 if (!mbar_wait(smem_addr(&empty_bar[s]), phase ^ 1u)) { ok = false; break; }
@@ -152,6 +180,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             mma_commit(smem_addr(done_bar));
         }
     } else {
+        pdl_wait();  // the output buffer may still be read by the kernel before this one
         if (num_kb > 0) ok = mbar_wait(smem_addr(done_bar), 0);
         tc_fence_after();
         if (splits > 1) {
@@ -291,23 +320,10 @@ static int launch_config(const void* A, const void* W, void* C, int M, int N, in
     dim3 grid((unsigned)((x_rows + GEMM_BM - 1) / GEMM_BM), (unsigned)((y_rows + BN - 1) / BN), (unsigned)splits);
     if (grid.y > 65535) return KIRAI_ERR_BAD_SIZE;
     auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT, EPI>;
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total);
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total(Smem::max_splits));
     if (err != cudaSuccess) return (int)err;
-    cudaLaunchConfig_t config = {};
-    config.gridDim = grid;
-    config.blockDim = dim3(GEMM_THREADS);
-    config.dynamicSmemBytes = Smem::total;
-    config.stream = stream;
-    cudaLaunchAttribute attrs[1];
-    attrs[0].id = cudaLaunchAttributeClusterDimension;
-    attrs[0].val.clusterDim.x = 1;
-    attrs[0].val.clusterDim.y = 1;
-    attrs[0].val.clusterDim.z = (unsigned)splits;
-    config.attrs = attrs;
-    config.numAttrs = 1;
-    err = cudaLaunchKernelEx(&config, kernel, map_a, map_w, (OutT*)C, M, N, K, ldc, per_split, splits, error_flag);
-    if (err != cudaSuccess) return (int)err;
-    return launch_status();
+    return launch_pdl(kernel, grid, dim3(GEMM_THREADS), (size_t)Smem::total(splits), stream, (unsigned)splits, map_a, map_w,
+                      (OutT*)C, M, N, K, ldc, per_split, splits, error_flag);
 }
 
 // Split count for the swapped (few tokens) case, which is bound by the weight
@@ -315,11 +331,9 @@ static int launch_config(const void* A, const void* W, void* C, int M, int N, in
 // split at least 8 k-blocks long, and no more splits than the first CTA has slots.
 static int choose_splits(int M, int N, int K) {
     const int x_tiles = (N + GEMM_BM - 1) / GEMM_BM;
-    const int y_tiles = M <= 16 ? 1 : (M + 31) / 32;
     const int max_splits = M <= 16 ? 4 : 2;
     const int k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
-    const int base = x_tiles * y_tiles;
-    int splits = (120 + base - 1) / base;  // about one CTA per SM at least; two fit
+    int splits = (120 + x_tiles - 1) / x_tiles;  // about one CTA per SM at least; two fit
     if (splits > max_splits) splits = max_splits;
     while (splits > 1 && k_blocks / splits < 8) --splits;
     return splits < 1 ? 1 : splits;
@@ -336,7 +350,8 @@ static int gemm_dispatch(const void* A, const void* W, void* C, int M, int N, in
 #define KIRAI_GEMM_CASE(BN, SWAP) \
     return launch_config<BN, SWAP, OutT, EPI>(A, W, C, M, N, K, lda, ldc, splits, error_flag, stream)
     if (M <= 16) KIRAI_GEMM_CASE(16, true);
-    if (M <= 64) KIRAI_GEMM_CASE(32, true);  // 33..64 tokens: two column tiles of 32
+    if (M <= 32) KIRAI_GEMM_CASE(32, true);
+    if (M <= 64) KIRAI_GEMM_CASE(64, true);
     if (N <= 128) KIRAI_GEMM_CASE(128, false);
     KIRAI_GEMM_CASE(256, false);
 #undef KIRAI_GEMM_CASE

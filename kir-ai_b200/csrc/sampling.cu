@@ -30,11 +30,19 @@ __device__ int block_argmax(const float* __restrict__ row, int vocab, float inv_
     __shared__ int s_idx[32];
     float best = -INFINITY;
     int best_index = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = row[i] * inv_temperature;
-        if (v > best) {  // indices ascend within a thread, so strict > keeps the lowest
-            best = v;
-            best_index = i;
+    // four loads in flight per thread; they are compared in ascending index order, so strict >
+    // keeps the lowest index among equal values
+    const int stride = blockDim.x;
+    for (int i = threadIdx.x; i < vocab; i += 4 * stride) {
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = (i + u * stride < vocab) ? row[i + u * stride] * inv_temperature : -INFINITY;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (v[u] > best) {
+                best = v[u];
+                best_index = i + u * stride;
+            }
         }
     }
 #pragma unroll
@@ -64,6 +72,8 @@ __device__ int block_argmax(const float* __restrict__ row, int vocab, float inv_
 }
 
 __global__ void __launch_bounds__(SAMPLE_THREADS) argmax_rows_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * vocab;
     const int best = block_argmax(row, vocab, 1.0f, nullptr);
     if (threadIdx.x == 0) out[blockIdx.x] = best;
@@ -72,8 +82,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) argmax_rows_kernel(const float
 KIRAI_EXPORT int kirai_argmax_rows(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return KIRAI_ERR_BAD_SIZE;
-    argmax_rows_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, out, vocab);
-    return launch_status();
+    const int pdl_status = launch_pdl(argmax_rows_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, 1u, logits, out, vocab);
+    return pdl_status;
 }
 
 // Sum of the probabilities greater than `value` (and how many equal it).
@@ -146,6 +156,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const float* __restrict__ logits, float* __restrict__ probs_scratch,
                    const float* __restrict__ temperature, const float* __restrict__ top_p,
                    const float* __restrict__ draw, int* __restrict__ out, int vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[32];
     __shared__ int s_counts[SAMPLE_THREADS];
     const int r = blockIdx.x;
@@ -240,6 +252,6 @@ KIRAI_EXPORT int kirai_sample_rows(const float* logits, float* probs_scratch, co
                                    cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return KIRAI_ERR_BAD_SIZE;
-    sample_rows_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, probs_scratch, temperature, top_p, draw, out, vocab);
-    return launch_status();
+    const int pdl_status = launch_pdl(sample_rows_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, 1u, logits, probs_scratch, temperature, top_p, draw, out, vocab);
+    return pdl_status;
 }
