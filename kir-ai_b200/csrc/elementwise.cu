@@ -79,11 +79,92 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
     }
 }
 
+// The same, for rows whose width is a multiple of 4 and fits 4 * VEC * blockDim values: 16-byte
+// loads, and the summed row stays in registers between the statistics and the scaling.
+template <typename T>
+struct Vec4 {};
+template <>
+struct Vec4<float> {
+    typedef float4 type;
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <>
+struct Vec4<bf16> {
+    typedef uint2 type;
+    static __device__ __forceinline__ float4 load(const bf16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+    }
+    static __device__ __forceinline__ void store(bf16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<uint32_t*>(&a);
+        raw.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+template <typename T, int VEC>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                       const float* __restrict__ weight, T* __restrict__ out,
+                                       const int* __restrict__ row_index, float* __restrict__ resid_out, int hidden,
+                                       float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const int row = blockIdx.x;
+    const int src = row_index ? row_index[row] : row;
+    const float* x = resid + (size_t)src * hidden;
+    const T* d = delta ? delta + (size_t)src * hidden : nullptr;
+    float* sum_dst = row_index ? resid_out + (size_t)row * hidden : resid + (size_t)src * hidden;
+    float4 v[VEC];
+    float acc = 0.0f;
+#pragma unroll
+    for (int n = 0; n < VEC; ++n) {
+        const int i = (n * blockDim.x + threadIdx.x) * 4;
+        v[n] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (i < hidden) {
+            v[n] = Vec4<float>::load(x + i);
+            if (d) {
+                const float4 dv = Vec4<T>::load(d + i);
+                v[n].x += dv.x; v[n].y += dv.y; v[n].z += dv.z; v[n].w += dv.w;
+            }
+            if (d || row_index) Vec4<float>::store(sum_dst + i, v[n]);
+            acc = fmaf(v[n].x, v[n].x, acc);
+            acc = fmaf(v[n].y, v[n].y, acc);
+            acc = fmaf(v[n].z, v[n].z, acc);
+            acc = fmaf(v[n].w, v[n].w, acc);
+        }
+    }
+    const float total = block_sum(acc, scratch);
+    const float variance = total / (float)hidden + eps;
+    const float scale = variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
+    T* y = out + (size_t)row * hidden;
+#pragma unroll
+    for (int n = 0; n < VEC; ++n) {
+        const int i = (n * blockDim.x + threadIdx.x) * 4;
+        if (i < hidden) {
+            const float4 w = Vec4<float>::load(weight + i);
+            Vec4<T>::store(y + i, make_float4(v[n].x * scale * w.x, v[n].y * scale * w.y, v[n].z * scale * w.z, v[n].w * scale * w.w));
+        }
+    }
+}
+
 template <typename T>
 static int add_rmsnorm_launch(float* resid, const void* delta, const float* weight, void* out, const int* row_index,
                               float* resid_out, int rows, int hidden, float eps, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (row_index && !resid_out) return KIRAI_ERR_BAD_SIZE;
+    const bool aligned = hidden % 4 == 0 && (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out |
+                                              (uintptr_t)resid_out) & 15) == 0;
+    if (aligned && hidden <= 4 * 4 * 512) {
+        const int threads = hidden <= 4 * 4 * 128 ? 128 : (hidden <= 4 * 4 * 256 ? 256 : 512);
+        return launch_pdl(add_rmsnorm_vec_kernel<T, 4>, dim3(rows), dim3(threads), 0, stream, 1u, resid, (const T*)delta,
+                          weight, (T*)out, row_index, resid_out, hidden, eps);
+    }
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     const int pdl_status = launch_pdl(add_rmsnorm_kernel<T>, dim3(rows), dim3(threads), 0, stream, 1u, resid, (const T*)delta, weight, (T*)out, row_index, resid_out,
                                                         hidden, eps);
@@ -261,8 +342,13 @@ KIRAI_EXPORT int kirai_kv_write_bf16(const void* k, const void* v, void* cache, 
 // absent (nullptr) the norm is skipped; with inv_freq absent the rotation is.
 // head_dim <= 512 (16 values per lane).
 #define FUSED_MAX_PAIRS 8
+#define FUSED_WARPS 8
+// One block per token: the rotation's sines and cosines depend on the token's position only, so
+// they are computed once into shared memory; then the block's warps take the token's heads in
+// turn, one warp per head, each lane holding pairs (i, i + head_dim / 2).
 template <typename T>
-__global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_weight,
+__global__ void __launch_bounds__(FUSED_WARPS * 32)
+qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_weight,
                                              const float* __restrict__ k_weight, const float* __restrict__ inv_freq,
                                              T* __restrict__ cache, const int* __restrict__ block_table,
                                              const int* __restrict__ request_of_token,
@@ -271,93 +357,82 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const float* _
                                              int num_pages, int write_cache, int* __restrict__ error_flag) {
     pdl_launch_dependents();
     pdl_wait();
+    __shared__ float cos_s[32 * FUSED_MAX_PAIRS], sin_s[32 * FUSED_MAX_PAIRS];
     const int heads_total = q_heads + 2 * kv_heads;
-    const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (warp >= (long)rows * heads_total) return;
-    const int row = (int)(warp / heads_total);
-    const int head = (int)(warp % heads_total);
-    T* x = qkv + (size_t)row * heads_total * head_dim + (size_t)head * head_dim;
+    const int row = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int pos = positions[row];
-    const bool is_q = head < q_heads;
-    const bool is_k = !is_q && head < q_heads + kv_heads;
-    const int kv_head = is_q ? 0 : (is_k ? head - q_heads : head - q_heads - kv_heads);
-
-    T* dst = nullptr;
-    if (!is_q && write_cache) {
-        const int logical = pos / page_size;
-        const int page =
-            logical < table_width ? block_table[(long)request_of_token[row] * table_width + logical] : -1;
-        if (page < 0 || page >= num_pages) {
-            if (lane == 0) atomicExch(error_flag, 2);
-            return;
-        }
-        dst = cache + kv_row_offset(page, is_k ? 0 : 1, kv_head, pos % page_size, kv_heads, page_size, head_dim);
-    }
-    if (!is_q && !is_k) {  // value head: plain copy
-        if (dst)
-            for (int i = lane; i < head_dim; i += 32) dst[i] = x[i];
-        return;
-    }
     const int half_dim = head_dim >> 1;  // values are held as (i, i + head_dim/2) so that the norm sees all of them
-    float lo[FUSED_MAX_PAIRS], hi[FUSED_MAX_PAIRS];
-    float acc = 0.0f;
-#pragma unroll
-    for (int j = 0; j < FUSED_MAX_PAIRS; ++j) {
-        const int i = lane + 32 * j;
-        lo[j] = hi[j] = 0.0f;
-        if (i < half_dim) {
-            lo[j] = to_f32<T>(x[i]);
-            hi[j] = to_f32<T>(x[i + half_dim]);
-            acc = fmaf(lo[j], lo[j], acc);
-            acc = fmaf(hi[j], hi[j], acc);
+    if (inv_freq) {
+        for (int i = threadIdx.x; i < half_dim; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sin_s[i], &cos_s[i]);
+        __syncthreads();
+    }
+    int page = -1;
+    if (write_cache) {
+        const int logical = pos / page_size;
+        page = logical < table_width ? block_table[(long)request_of_token[row] * table_width + logical] : -1;
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicExch(error_flag, 2);
+            page = -1;
         }
     }
-    const float* weight = is_q ? q_weight : k_weight;
-    float scale = 1.0f;
-    if (weight) {
-        acc = warp_sum(acc);
-        const float variance = acc / (float)head_dim + eps;
-        scale = variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
-    }
-    const int half_rot = rotary_dim >> 1;
-#pragma unroll
-    for (int j = 0; j < FUSED_MAX_PAIRS; ++j) {
-        const int i = lane + 32 * j;
-        if (i < half_dim) {
-            float a = lo[j], b = hi[j];
-            if (weight) {
-                a = a * scale * weight[i];
-                b = b * scale * weight[i + half_dim];
-            }
-            lo[j] = a;
-            hi[j] = b;
+    for (int head = warp; head < heads_total; head += FUSED_WARPS) {
+        T* x = qkv + (size_t)row * heads_total * head_dim + (size_t)head * head_dim;
+        const bool is_q = head < q_heads;
+        const bool is_k = !is_q && head < q_heads + kv_heads;
+        const int kv_head = is_q ? 0 : (is_k ? head - q_heads : head - q_heads - kv_heads);
+        T* dst = nullptr;
+        if (!is_q && write_cache) {
+            if (page < 0) continue;
+            dst = cache + kv_row_offset(page, is_k ? 0 : 1, kv_head, pos % page_size, kv_heads, page_size, head_dim);
         }
-    }
-    // Rotation pairs are (i, i + rotary_dim/2); with rotary_dim == head_dim they are the (lo, hi) held above.
-    if (inv_freq && rotary_dim == head_dim) {
+        if (!is_q && !is_k) {  // value head: plain copy
+            if (dst)
+                for (int i = lane; i < head_dim; i += 32) dst[i] = x[i];
+            continue;
+        }
+        float lo[FUSED_MAX_PAIRS], hi[FUSED_MAX_PAIRS];
+        float acc = 0.0f;
 #pragma unroll
         for (int j = 0; j < FUSED_MAX_PAIRS; ++j) {
             const int i = lane + 32 * j;
-            if (i < half_rot) {
-                float s, c;
-                sincosf((float)pos * inv_freq[i], &s, &c);
-                const float a = lo[j], b = hi[j];
-                lo[j] = a * c - b * s;
-                hi[j] = b * c + a * s;
+            lo[j] = hi[j] = 0.0f;
+            if (i < half_dim) {
+                lo[j] = to_f32<T>(x[i]);
+                hi[j] = to_f32<T>(x[i + half_dim]);
+                acc = fmaf(lo[j], lo[j], acc);
+                acc = fmaf(hi[j], hi[j], acc);
             }
         }
-    }
+        const float* weight = is_q ? q_weight : k_weight;
+        float scale = 1.0f;
+        if (weight) {
+            acc = warp_sum(acc);
+            const float variance = acc / (float)head_dim + eps;
+            scale = variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
+        }
 #pragma unroll
-    for (int j = 0; j < FUSED_MAX_PAIRS; ++j) {
-        const int i = lane + 32 * j;
-        if (i < half_dim) {
-            const T a = from_f32<T>(lo[j]), b = from_f32<T>(hi[j]);
-            x[i] = a;
-            x[i + half_dim] = b;
-            if (dst) {
-                dst[i] = a;
-                dst[i + half_dim] = b;
+        for (int j = 0; j < FUSED_MAX_PAIRS; ++j) {
+            const int i = lane + 32 * j;
+            if (i < half_dim) {
+                float a = lo[j], b = hi[j];
+                if (weight) {
+                    a = a * scale * weight[i];
+                    b = b * scale * weight[i + half_dim];
+                }
+                if (inv_freq) {  // rotary_dim == head_dim: the pairs are the (lo, hi) held here
+                    const float c = cos_s[i], sn = sin_s[i];
+                    const float ra = a * c - b * sn, rb = b * c + a * sn;
+                    a = ra;
+                    b = rb;
+                }
+                const T ta = from_f32<T>(a), tb = from_f32<T>(b);
+                x[i] = ta;
+                x[i + half_dim] = tb;
+                if (dst) {
+                    dst[i] = ta;
+                    dst[i + half_dim] = tb;
+                }
             }
         }
     }
@@ -371,13 +446,10 @@ static int qk_norm_rope_kv_write_launch(void* qkv, const float* q_weight, const 
                                         int write_cache, int* error_flag, cudaStream_t stream) {
     if (head_dim > 64 * FUSED_MAX_PAIRS || (head_dim & 1)) return KIRAI_ERR_BAD_SIZE;
     if (inv_freq && rotary_dim != head_dim) return KIRAI_ERR_UNSUPPORTED;  // partial rotation goes through rope_kernel
-    const long warps = (long)rows * (q_heads + 2 * kv_heads);
-    if (warps <= 0) return 0;
-    const int threads = 128;
-    const int pdl_status = launch_pdl(qk_norm_rope_kv_write_kernel<T>, dim3((unsigned)((warps * 32 + threads - 1) / threads)), dim3(threads), 0, stream, 1u, 
-        (T*)qkv, q_weight, k_weight, inv_freq, (T*)cache, block_table, request_of_token, positions, rows, q_heads,
-        kv_heads, head_dim, rotary_dim, eps, page_size, table_width, num_pages, write_cache, error_flag);
-    return pdl_status;
+    if (rows <= 0 || q_heads + 2 * kv_heads <= 0) return 0;
+    return launch_pdl(qk_norm_rope_kv_write_kernel<T>, dim3(rows), dim3(FUSED_WARPS * 32), 0, stream, 1u, (T*)qkv, q_weight,
+                      k_weight, inv_freq, (T*)cache, block_table, request_of_token, positions, rows, q_heads, kv_heads,
+                      head_dim, rotary_dim, eps, page_size, table_width, num_pages, write_cache, error_flag);
 }
 KIRAI_EXPORT int kirai_qk_norm_rope_kv_write_f32(void* qkv, const float* q_weight, const float* k_weight,
                                                  const float* inv_freq, void* cache, const int* block_table,
