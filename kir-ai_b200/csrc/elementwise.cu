@@ -342,7 +342,7 @@ KIRAI_EXPORT int kirai_kv_write_bf16(const void* k, const void* v, void* cache, 
 // absent (nullptr) the norm is skipped; with inv_freq absent the rotation is.
 // head_dim <= 512 (16 values per lane).
 #define FUSED_MAX_PAIRS 8
-#define FUSED_WARPS 8
+#define FUSED_WARPS 4
 // One block per token: the rotation's sines and cosines depend on the token's position only, so
 // they are computed once into shared memory; then the block's warps take the token's heads in
 // turn, one warp per head, each lane holding pairs (i, i + head_dim / 2).
@@ -376,7 +376,8 @@ qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_we
             page = -1;
         }
     }
-    for (int head = warp; head < heads_total; head += FUSED_WARPS) {
+    // with few tokens the heads are spread over gridDim.y blocks, so that enough blocks run at once
+    for (int head = blockIdx.y * FUSED_WARPS + warp; head < heads_total; head += gridDim.y * FUSED_WARPS) {
         T* x = qkv + (size_t)row * heads_total * head_dim + (size_t)head * head_dim;
         const bool is_q = head < q_heads;
         const bool is_k = !is_q && head < q_heads + kv_heads;
@@ -447,7 +448,10 @@ static int qk_norm_rope_kv_write_launch(void* qkv, const float* q_weight, const 
     if (head_dim > 64 * FUSED_MAX_PAIRS || (head_dim & 1)) return KIRAI_ERR_BAD_SIZE;
     if (inv_freq && rotary_dim != head_dim) return KIRAI_ERR_UNSUPPORTED;  // partial rotation goes through rope_kernel
     if (rows <= 0 || q_heads + 2 * kv_heads <= 0) return 0;
-    return launch_pdl(qk_norm_rope_kv_write_kernel<T>, dim3(rows), dim3(FUSED_WARPS * 32), 0, stream, 1u, (T*)qkv, q_weight,
+    if (rows > 65535 * 1024) return KIRAI_ERR_BAD_SIZE;
+    const int heads_total = q_heads + 2 * kv_heads;
+    const int head_blocks = rows >= 1024 ? 1 : (heads_total + FUSED_WARPS - 1) / FUSED_WARPS;
+    return launch_pdl(qk_norm_rope_kv_write_kernel<T>, dim3(rows, head_blocks), dim3(FUSED_WARPS * 32), 0, stream, 1u, (T*)qkv, q_weight,
                       k_weight, inv_freq, (T*)cache, block_table, request_of_token, positions, rows, q_heads, kv_heads,
                       head_dim, rotary_dim, eps, page_size, table_width, num_pages, write_cache, error_flag);
 }

@@ -42,7 +42,7 @@ struct GemmSmem {
     static constexpr int x_bytes = GEMM_BM * GEMM_BK * 2;
     static constexpr int y_bytes = BN * GEMM_BK * 2;
     static constexpr int stage_bytes = x_bytes + y_bytes;
-    static constexpr int max_splits = BN == 16 ? 4 : (BN <= 64 ? 2 : 1);
+    static constexpr int max_splits = BN <= 64 ? 4 : 1;  // up to 128 KB of slots beside the 96 KB ring
     static constexpr int slot_bytes = BN * GEMM_BM * 4;  // one 32-bit partial tile
     static constexpr int stages = streaming ? 4 : (200 * 1024 / stage_bytes);
     static constexpr int barrier_bytes = 256;
@@ -331,7 +331,7 @@ static int launch_config(const void* A, const void* W, void* C, int M, int N, in
 // split at least 8 k-blocks long, and no more splits than the first CTA has slots.
 static int choose_splits(int M, int N, int K) {
     const int x_tiles = (N + GEMM_BM - 1) / GEMM_BM;
-    const int max_splits = M <= 16 ? 4 : 2;
+    const int max_splits = 4;
     const int k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
     int splits = (120 + x_tiles - 1) / x_tiles;  // about one CTA per SM at least; two fit
     if (splits > max_splits) splits = max_splits;
