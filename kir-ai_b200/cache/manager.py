@@ -122,11 +122,17 @@ class CacheManager:
 
     def block_table_array(self, requests: Sequence[RequestPages], group: int, min_width: int = 1) -> np.ndarray:
         """int32 [len(requests), width] of page ids, NO_PAGE where a request holds none."""
-        width = max([min_width] + [len(r.tables[group]) for r in requests])
+        rows = []
+        for request in requests:
+            cached = getattr(request, "_table_arrays", None)
+            if cached is None or cached[0] != request.version:
+                cached = (request.version, [np.asarray(t, dtype=np.int32) for t in request.tables])
+                request._table_arrays = cached
+            rows.append(cached[1][group])
+        width = max(min_width, max((r.size for r in rows), default=0))
         array = np.full((len(requests), width), NO_PAGE, dtype=np.int32)
-        for row, request in enumerate(requests):
-            table = request.tables[group]
-            array[row, : len(table)] = table
+        for index, row in enumerate(rows):
+            array[index, : row.size] = row
         return array
 
     def bytes_per_token(self) -> int:

@@ -109,7 +109,7 @@ class GroupSpec:
     layers: List[int] = field(default_factory=list)  # cache-layer ids in this group
 
 
-@dataclass
+@dataclass(eq=False)
 class RequestPages:
     """What one live request holds: a slot, its length, one block table per group."""
 
@@ -118,6 +118,7 @@ class RequestPages:
     length: int = 0  # tokens whose keys and values are in the cache
     tables: List[List[int]] = field(default_factory=list)  # per group; NO_PAGE where given back
     closed: bool = False
+    version: int = 0  # bumped whenever a table changes (lets callers keep array copies of the tables)
 
     def pages_held(self, group: int) -> List[int]:
         return [page for page in self.tables[group] if page != NO_PAGE]
@@ -171,9 +172,11 @@ class PageTables:
         if not all(n <= pool.free_pages for n, pool in zip(need, self.pools)):
             return False
         for table, n, pool in zip(request.tables, need, self.pools):
-            pages = pool.allocate(n)
-            assert pages is not None
-            table.extend(pages)
+            if n:
+                pages = pool.allocate(n)
+                assert pages is not None
+                table.extend(pages)
+                request.version += 1
         return True
 
     def commit(self, request: RequestPages, new_tokens: int) -> None:
@@ -201,6 +204,7 @@ class PageTables:
                 pool.release(stale)
                 for p in range(dead):
                     table[p] = NO_PAGE
+                request.version += 1
 
     def close(self, request: RequestPages) -> None:
         """Gives back everything the request holds (pages of every group, the slot)."""
@@ -209,6 +213,7 @@ class PageTables:
         for group_index, pool in enumerate(self.pools):
             pool.release(request.pages_held(group_index))
             request.tables[group_index] = []
+        request.version += 1
         self.slots.release(request.slot)
         request.closed = True
         del self.live[request.request_id]

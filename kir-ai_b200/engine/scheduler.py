@@ -35,7 +35,7 @@ class AdmissionError(ValueError):
     """A request that this engine can never run (too long for the model or the cache)."""
 
 
-@dataclass
+@dataclass(eq=False)  # requests are compared by identity, never by their (long) token lists
 class Request:
     request_id: object
     prompt: List[int]
@@ -159,7 +159,7 @@ class Scheduler:
 
         # (1) decoding requests, oldest first; evict the youngest others when a page is missing
         for request in list(self.running):
-            if request not in self.running or request.pending != 1 or budget < 1:
+            if request.state != RUNNING or request.pending != 1 or budget < 1:
                 continue
             while not self.cache.reserve(request.pages, 1):
                 victims = [r for r in reversed(self.running) if r is not request and id(r) not in taken]
