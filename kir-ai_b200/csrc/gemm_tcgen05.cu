@@ -300,6 +300,208 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
 }
 
+// ---------------------------------------------------------------- many tokens: persistent kernel
+// One CTA per SM walks tiles t = blockIdx.x, + gridDim.x, ... (token tile fastest, so CTAs that
+// run side by side share a weight tile in L2).  Tensor memory holds two accumulators of BN
+// columns: while the epilogue warps read one back, convert and store it, the MMA thread already
+// fills the other with the next tile, and the TMA warp runs ahead across tile borders.
+template <int BN, typename OutT, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
+                               OutT* __restrict__ C, int M, int N, int K, long ldc, int* __restrict__ error_flag) {
+    using Smem = GemmSmem<BN>;
+    constexpr int STAGES = Smem::stages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + STAGES * Smem::stage_bytes);
+    uint64_t* full_bar = bars;                    // [STAGES] TMA -> MMA
+    uint64_t* empty_bar = bars + STAGES;          // [STAGES] MMA -> TMA
+    uint64_t* acc_full = bars + 2 * STAGES;       // [2] MMA -> epilogue
+    uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2] epilogue -> MMA
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (M + GEMM_BM - 1) / GEMM_BM, n_tiles = (N + BN - 1) / BN;
+    const int total_tiles = m_tiles * n_tiles;
+    const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+    pdl_launch_dependents();
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_descriptor(&map_x);
+        tma_prefetch_descriptor(&map_y);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_addr(&full_bar[s]), 1);
+            mbar_init(smem_addr(&empty_bar[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_addr(&acc_full[b]), 1);
+            mbar_init(smem_addr(&acc_empty[b]), 4);  // one arrival per epilogue warp
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_addr(tmem_slot), 2 * tmem_columns<BN>());
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            // k-blocks are numbered over all of this CTA's tiles; block `it` goes to stage it % STAGES
+            const int my_tiles = (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+            const long total_it = (long)my_tiles * num_kb;
+            auto issue = [&](long it, bool weights, bool activations) {
+                const int t = (int)blockIdx.x + (int)(it / num_kb) * (int)gridDim.x;
+                const int k = (int)(it % num_kb) * GEMM_BK;
+                const int s = (int)(it % STAGES);
+                const uint32_t full = smem_addr(&full_bar[s]);
+                const uint32_t dst = smem_addr(smem + s * Smem::stage_bytes);
+                if (weights) {
+                    mbar_expect_tx(full, Smem::stage_bytes);
+                    tma_load_2d(dst + Smem::x_bytes, &map_y, full, k, (t / m_tiles) * BN);
+                }
+                if (activations) tma_load_2d(dst, &map_x, full, k, (t % m_tiles) * GEMM_BM);
+            };
+            // The weights do not depend on the kernel before this one: the first ring of weight tiles is
+            // fetched at once, and only the activation tiles wait for that kernel to finish.
+            const long head = total_it < STAGES ? total_it : STAGES;
+            for (long it = 0; it < head; ++it) issue(it, true, false);
+            pdl_wait();
+            for (long it = 0; it < head; ++it) issue(it, false, true);
+            for (long it = head; it < total_it; ++it) {
+                if (!mbar_wait(smem_addr(&empty_bar[it % STAGES]), (uint32_t)(it / STAGES - 1) & 1u)) { ok = false; break; }
+                issue(it, true, true);
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            constexpr uint32_t idesc = instr_desc_bf16(GEMM_BM, BN);
+            int it = 0, local = 0;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+                const int buf = local & 1;
+                // the epilogue must have drained this accumulator (two tiles ago)
+                if (local >= 2 && !mbar_wait(smem_addr(&acc_empty[buf]), (uint32_t)((local >> 1) - 1) & 1u)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * tmem_columns<BN>());
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(smem_addr(&full_bar[s]), (uint32_t)(it / STAGES) & 1u)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t x_addr = smem_addr(smem + s * Smem::stage_bytes);
+                    const uint64_t desc_x = smem_desc_k_major_sw128(x_addr);
+                    const uint64_t desc_y = smem_desc_k_major_sw128(x_addr + Smem::x_bytes);
+#pragma unroll
+                    for (int k = 0; k < GEMM_BK / 16; ++k)
+                        mma_bf16_ss(tmem_acc, desc_x + (uint64_t)(2 * k), desc_y + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    mma_commit(smem_addr(&empty_bar[s]));
+                }
+                if (!ok) break;
+                mma_commit(smem_addr(&acc_full[buf]));
+            }
+        }
+    } else {
+        const int lane_group = warp & 3;
+        const int tile_row = lane_group * 32 + lane;
+        pdl_wait();  // the output buffer may still be read by the kernel before this one
+        int local = 0;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const int x0 = (t % m_tiles) * GEMM_BM, y0 = (t / m_tiles) * BN;
+            if (!mbar_wait(smem_addr(&acc_full[buf]), (uint32_t)(local >> 1) & 1u)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * tmem_columns<BN>()) + ((uint32_t)(lane_group * 32) << 16);
+            const int x_row = x0 + tile_row;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (y0 + c0 >= N) break;  // uniform across the warp
+                uint32_t r[16];
+                tmem_load_32x16(tmem_acc + (uint32_t)c0, r);
+                tmem_load_wait();
+                if (x_row >= M) continue;
+                float v[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+                if (EPI == 1) {
+                    // columns y0 + c0 .. + 15 are 8 gate rows then their 8 up rows: 8 outputs at (y0 + c0) / 2
+                    OutT* dst = C + (size_t)x_row * ldc + ((y0 + c0) >> 1);
+                    if (y0 + c0 + 16 <= N && sizeof(OutT) == 2 && (((uintptr_t)dst & 15) == 0)) {
+                        uint32_t packed[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            __nv_bfloat162 pair = __floats2bfloat162_rn(silu_mul(v[2 * j], v[2 * j + 8]), silu_mul(v[2 * j + 1], v[2 * j + 9]));
+                            packed[j] = *reinterpret_cast<uint32_t*>(&pair);
+                        }
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (y0 + c0 + j + 8 < N) dst[j] = from_f32<OutT>(silu_mul(v[j], v[j + 8]));
+                    }
+                } else {
+                    OutT* dst = C + (size_t)x_row * ldc + y0 + c0;
+                    const bool full = (y0 + c0 + 16 <= N) && (((uintptr_t)dst & 15) == 0);
+                    if (full && sizeof(OutT) == 2) {
+                        uint32_t packed[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            __nv_bfloat162 pair = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                            packed[j] = *reinterpret_cast<uint32_t*>(&pair);
+                        }
+                        uint4* out = reinterpret_cast<uint4*>(dst);
+                        out[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        out[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    } else if (full && sizeof(OutT) == 4) {
+                        float4* out = reinterpret_cast<float4*>(dst);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) out[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (y0 + c0 + j < N) dst[j] = from_f32<OutT>(v[j]);
+                    }
+                }
+            }
+            // this warp has read its lanes of the accumulator: hand it back to the MMA thread
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_addr(&acc_empty[buf]));
+        }
+    }
+    if (!ok) atomicExch(error_flag, 4);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 2 * tmem_columns<BN>());
+    }
+}
+
+template <int BN, typename OutT, int EPI>
+static int launch_persistent(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc,
+                             int* error_flag, cudaStream_t stream) {
+    using Smem = GemmSmem<BN>;
+    CUtensorMap map_a, map_w;
+    if (!tmap::bf16_2d_sw128(&map_a, A, M, K, lda, GEMM_BM, GEMM_BK)) return KIRAI_ERR_BAD_ALIGN;
+    if (!tmap::bf16_2d_sw128(&map_w, W, N, K, K, BN, GEMM_BK)) return KIRAI_ERR_BAD_ALIGN;
+    const long tiles = (long)((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0) sm_count = 148;
+    }
+    const unsigned grid = (unsigned)(tiles < sm_count ? tiles : sm_count);
+    auto kernel = gemm_tcgen05_persistent_kernel<BN, OutT, EPI>;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total(1));
+    if (err != cudaSuccess) return (int)err;
+    return launch_pdl(kernel, dim3(grid), dim3(GEMM_THREADS), (size_t)Smem::total(1), stream, 1u, map_a, map_w, (OutT*)C, M,
+                      N, K, ldc, error_flag);
+}
+
 template <int BN, bool SWAP, typename OutT, int EPI>
 static int launch_config(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc, int splits,
                          int* error_flag, cudaStream_t stream) {
@@ -352,9 +554,9 @@ static int gemm_dispatch(const void* A, const void* W, void* C, int M, int N, in
     if (M <= 16) KIRAI_GEMM_CASE(16, true);
     if (M <= 32) KIRAI_GEMM_CASE(32, true);
     if (M <= 64) KIRAI_GEMM_CASE(64, true);
-    if (N <= 128) KIRAI_GEMM_CASE(128, false);
-    KIRAI_GEMM_CASE(256, false);
 #undef KIRAI_GEMM_CASE
+    if (N <= 128) return launch_persistent<128, OutT, EPI>(A, W, C, M, N, K, lda, ldc, error_flag, stream);
+    return launch_persistent<256, OutT, EPI>(A, W, C, M, N, K, lda, ldc, error_flag, stream);
 }
 
 // Split count that the entry points pick for splits <= 0.

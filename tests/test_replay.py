@@ -146,3 +146,17 @@ def test_first_tokens_and_long_decoding(tiny, dtype, tmp_path):
         got = replay.step([("long", [token], [0])])
         check(dtype, got, reference, [i], f"decode at {i}")
     assert replay.close() == 0
+
+
+def test_tolerance_would_show_a_window_off_by_one(tiny):
+    """The bound used above must be able to show a fault at the window's edge: the plain logits with a
+    window one key shorter or longer differ from the true ones by many times the bfloat16 bound."""
+    if "sliding_window" not in tiny["raw"]:
+        pytest.skip("configuration without a window")
+    config, weights = plain.read_model_folder(tiny["folder"])
+    tokens = tiny["sequences"]["a"]
+    true = tiny["reference"]["a"]
+    for wrong in (config["sliding_window"] - 1, config["sliding_window"] + 1):
+        other = plain.forward_logits({**config, "sliding_window": wrong}, weights, tokens).numpy()
+        start = config["sliding_window"] + 2  # positions where the window has begun to cut
+        assert float(np.abs(other[start:] - true[start:]).max()) > 5 * tolerance("bfloat16", true)
