@@ -68,7 +68,11 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t address, float value) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(address), "f"(value) : "memory");
 }
 
-__device__ __forceinline__ float silu_mul(float gate, float up) { return gate / (1.0f + expf(-gate)) * up; }
+// silu(gate) * up with the fast exponential and reciprocal (relative error about 2^-21, far below
+// the bf16 rounding of the result); the epilogue runs beside the next tile's MMAs and must be short.
+__device__ __forceinline__ float silu_mul(float gate, float up) {
+    return gate * up * __frcp_rn(1.0f + __expf(-gate));
+}
 
 // SWAP false: X = A (rows m), Y = W (rows n), C[m, n].  SWAP true: X = W, Y = A.
 // Split-K: the CTAs of a cluster (1, 1, splits) cover one tile; each stores its 32-bit partial
