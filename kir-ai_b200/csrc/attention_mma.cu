@@ -384,18 +384,124 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16*
     }
 }
 
-// ------------------------------------------------------------------ decode kernel
-#define DC_WARPS 4
-#define DC_STAGES 3
-// keys per warp tile: 32, or 16 for the widest heads so that the warps' rings fit shared memory
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
+// The decode kernel's state when the keys, not the (few) query heads, fill the 16 rows of the
+// MMA: scores are S^T[key, head] = K Q^T and the output is O^T[dim, head] = V^T P^T, with the
+// heads (at most 8) as the 8 columns.  A thread holds heads 2t and 2t + 1 (t = lane % 4).
 template <int D>
-struct DecodeTile { static constexpr int BN = D > 128 ? 16 : 32; };
+struct HeadState {
+    float m[2], l[2];
+    float o[D / 16][4];  // m-tile i: (dim 16 i + g, heads 2t, 2t+1), (dim 16 i + g + 8, heads 2t, 2t+1)
+    __device__ __forceinline__ void init() {
+        m[0] = m[1] = -INFINITY;
+        l[0] = l[1] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    }
+};
+
+// Folds BN keys (first key j0) into the state; every head sees key j when lo <= j <= hi.
+// q_b[kk] are the B-operand fragments of Q^T for dims 16 kk .. 16 kk + 15.
+template <int D, int BN>
+__device__ __forceinline__ void warp_attend_heads(HeadState<D>& st, const uint32_t (*q_b)[2], uint32_t k_smem,
+                                                  uint32_t v_smem, int j0, int lo, int hi, float scale_log2, int lane) {
+    constexpr int MT = BN / 16;
+    float s[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        s[mt][0] = s[mt][1] = s[mt][2] = s[mt][3] = 0.0f;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            uint32_t a[4];
+            ldmatrix_x4(k_smem + tile_offset<BN>(mt * 16 + (lane & 15), kk * 2 + (lane >> 4)), a[0], a[1], a[2], a[3]);
+            mma_bf16_16816(s[mt], a, q_b[kk][0], q_b[kk][1]);
+        }
+    }
+    // mask by key position (rows g and g + 8 of each m-tile), running maximum per head
+    const int g = lane >> 2;
+    const bool interior = j0 >= lo && j0 + BN - 1 <= hi;
+    float m_new[2] = {st.m[0], st.m[1]};
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int j = j0 + mt * 16 + g + (e >> 1) * 8;
+            const bool visible = interior || (j >= lo && j <= hi);
+            s[mt][e] = visible ? s[mt][e] * scale_log2 : -INFINITY;
+            m_new[e & 1] = fmaxf(m_new[e & 1], s[mt][e]);
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 4));
+        m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 8));
+        m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 16));
+    }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        m_use[h] = m_new[h] == -INFINITY ? 0.0f : m_new[h];
+        corr[h] = exp2f(st.m[h] - m_use[h]);
+        st.m[h] = m_new[h];
+    }
+    uint32_t p_b[MT][2];  // P^T as B-operand fragments, one k16 step per m-tile of keys
+    float sum[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        const float p0 = exp2f(s[mt][0] - m_use[0]), p1 = exp2f(s[mt][1] - m_use[1]);
+        const float p2 = exp2f(s[mt][2] - m_use[0]), p3 = exp2f(s[mt][3] - m_use[1]);
+        sum[0] += p0 + p2;
+        sum[1] += p1 + p3;
+        // (key g, heads 2t, 2t+1) -> (keys 2t, 2t+1, head g): the transposed 8 x 8 block is the B fragment
+        p_b[mt][0] = movmatrix_trans(pack_bf16(p0, p1));
+        p_b[mt][1] = movmatrix_trans(pack_bf16(p2, p3));
+    }
+    st.l[0] = st.l[0] * corr[0] + sum[0];
+    st.l[1] = st.l[1] * corr[1] + sum[1];
+    // the running maximum settles after a few tiles: skip the rescaling when nothing changed
+    if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i) {
+            st.o[i][0] *= corr[0];
+            st.o[i][1] *= corr[1];
+            st.o[i][2] *= corr[0];
+            st.o[i][3] *= corr[1];
+        }
+    }
+    // O^T += V^T P^T: A = V^T (dims x keys) through transposed 8 x 8 loads of the [key][dim] tile
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i) {
+            uint32_t a[4];
+            const int row = mt * 16 + (lane & 7) + ((lane >> 4) << 3);
+            const int chunk = 2 * i + ((lane >> 3) & 1);
+            ldmatrix_x4_trans(v_smem + tile_offset<BN>(row, chunk), a[0], a[1], a[2], a[3]);
+            mma_bf16_16816(st.o[i], a, p_b[mt][0], p_b[mt][1]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ decode kernel
+#define DC_STAGES 3
+// Four warps; keys per warp tile: 32, or 16 for the widest heads so that the warps' rings fit shared memory.
+template <int D>
+struct DecodeTile {
+    static constexpr int BN = D > 128 ? 16 : 32;
+    static constexpr int WARPS = 4;
+};
 
 // Shared memory of the decode kernel: the query tile, per warp a ring of DC_STAGES (K tile, V tile)
 // filled by TMA, one mbarrier per ring slot; after the key loop the ring is reused to merge the warps.
 template <int D>
 struct DecodeSmem {
     static constexpr int BN = DecodeTile<D>::BN;
+    static constexpr int DC_WARPS = DecodeTile<D>::WARPS;
     static constexpr int q_bytes = 16 * D * 2;
     static constexpr int tile_bytes = BN * D * 2;
     static constexpr int ring_bytes = DC_WARPS * DC_STAGES * 2 * tile_bytes;
@@ -407,8 +513,10 @@ struct DecodeSmem {
 // partial: [requests, q_heads, splits, head_dim + 2] floats: unnormalised output, then max (log2 domain), then sum.
 // kv_map: the cache layer as a 2-D bf16 matrix [num_pages * 2 * kv_heads * page_size, head_dim], boxes of
 // [box_rows, 64] with the 128-byte swizzle; box_rows = min(page_size, BN) and divides BN.
-template <int D>
-__global__ void __launch_bounds__(DC_WARPS * 32)
+// HEADS: the group has at most 8 heads and they are the MMA's columns (keys fill its rows);
+// otherwise the group's (at most 16) heads are the rows, as in the prompt kernel.
+template <int D, bool HEADS>
+__global__ void __launch_bounds__(DecodeTile<D>::WARPS * 32)
 attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ q, bf16* __restrict__ out,
                         float* __restrict__ partial, const int* __restrict__ block_table,
                         const int* __restrict__ context_len, int q_heads, int kv_heads, int head_dim, long q_row_stride,
@@ -418,6 +526,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
     pdl_wait();
     using Smem = DecodeSmem<D>;
     constexpr int BN = Smem::BN;
+    constexpr int DC_WARPS = Smem::DC_WARPS;
     constexpr int PANELS = D / 64;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -466,6 +575,57 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
                                  table_width, num_pages, kv_heads, kv_head, page_size, box_rows, lane);
     };
 
+    // this warp's tiles: t_begin + warp, + DC_WARPS, ...; the ring runs DC_STAGES - 1 tiles ahead
+    const int my_first = t_begin + warp;
+    const int my_count = my_first < t_end ? (t_end - my_first + DC_WARPS - 1) / DC_WARPS : 0;
+    constexpr int MS = D + 2;
+    if (HEADS) {
+        // B-operand fragments of Q^T: (dims 16 kk + 2t, + 1 and + 8; head g), read once
+        uint32_t q_b[D / 16][2];
+        {
+            const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                q_b[kk][0] = *reinterpret_cast<const uint32_t*>(smem + tile_offset<16>(g, 2 * kk) + 4 * t);
+                q_b[kk][1] = *reinterpret_cast<const uint32_t*>(smem + tile_offset<16>(g, 2 * kk + 1) + 4 * t);
+            }
+        }
+        HeadState<D> st;
+        st.init();
+        for (int k = 0; k < DC_STAGES - 1 && k < my_count; ++k) issue(my_first + k * DC_WARPS, k);
+        for (int k = 0; k < my_count; ++k) {
+            const int ahead = k + DC_STAGES - 1;
+            if (ahead < my_count) issue(my_first + ahead * DC_WARPS, ahead % DC_STAGES);
+            const int slot = k % DC_STAGES;
+            if (!sm100::mbar_wait(sm100::smem_addr(&bars[slot]), (uint32_t)(k / DC_STAGES) & 1u)) {
+                ok = false;
+                break;
+            }
+            const uint32_t k_s = ring + slot * 2 * Smem::tile_bytes;
+            warp_attend_heads<D, BN>(st, q_b, k_s, k_s + Smem::tile_bytes, (my_first + k * DC_WARPS) * BN, key_lo, pos, scale_log2, lane);
+            __syncwarp();
+        }
+        if (!ok && lane == 0) atomicExch(error_flag, 4);
+        __syncthreads();  // every warp is done with its ring: it becomes the merge buffer
+        const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float l = st.l[h];
+            l += __shfl_xor_sync(0xffffffffu, l, 4);
+            l += __shfl_xor_sync(0xffffffffu, l, 8);
+            l += __shfl_xor_sync(0xffffffffu, l, 16);
+            float* dst = merge + ((size_t)warp * 16 + (2 * t + h)) * MS;
+#pragma unroll
+            for (int i = 0; i < D / 16; ++i) {
+                dst[16 * i + g] = st.o[i][h];
+                dst[16 * i + g + 8] = st.o[i][2 + h];
+            }
+            if (g == 0) {
+                dst[D] = st.m[h];
+                dst[D + 1] = l;
+            }
+        }
+    } else {
     int lo[2], hi[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -483,9 +643,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
     }
     WarpState<D> st;
     st.init();
-    // this warp's tiles: t_begin + warp, + DC_WARPS, ...; the ring runs DC_STAGES - 1 tiles ahead
-    const int my_first = t_begin + warp;
-    const int my_count = my_first < t_end ? (t_end - my_first + DC_WARPS - 1) / DC_WARPS : 0;
     for (int k = 0; k < DC_STAGES - 1 && k < my_count; ++k) issue(my_first + k * DC_WARPS, k);
     for (int k = 0; k < my_count; ++k) {
         const int ahead = k + DC_STAGES - 1;
@@ -502,7 +659,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
     }
     if (!ok && lane == 0) atomicExch(error_flag, 4);
     __syncthreads();  // every warp is done with its ring: it becomes the merge buffer
-    constexpr int MS = D + 2;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         float l = st.l[r];
@@ -520,6 +676,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
             dst[D] = st.m[r];
             dst[D + 1] = l;
         }
+    }
     }
     __syncthreads();
     for (int id = tid; id < group * head_dim; id += DC_WARPS * 32) {
@@ -602,11 +759,11 @@ int decode_launch(const void* q, const void* cache, void* out, float* partial, c
     CUtensorMap kv_map;
     const uint64_t rows = (uint64_t)num_pages * 2 * kv_heads * page_size;
     if (!tmap::bf16_2d_sw128(&kv_map, cache, rows, head_dim, head_dim, box_rows, 64)) return KIRAI_ERR_BAD_ALIGN;
-    auto kernel = attention_decode_kernel<D>;
+    auto kernel = (q_heads / kv_heads <= 8) ? attention_decode_kernel<D, true> : attention_decode_kernel<D, false>;
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total);
     if (err != cudaSuccess) return (int)err;
     dim3 grid(num_splits, kv_heads, requests);
-    int status = launch_pdl(kernel, grid, dim3(DC_WARPS * 32), (size_t)Smem::total, stream, 1u, kv_map, (const bf16*)q,
+    int status = launch_pdl(kernel, grid, dim3(Smem::DC_WARPS * 32), (size_t)Smem::total, stream, 1u, kv_map, (const bf16*)q,
                             (bf16*)out, partial, block_table, context_len, q_heads, kv_heads, head_dim, q_row_stride,
                             page_size, box_rows, table_width, num_pages, window, scale * 1.4426950408889634f,
                             num_splits, error_flag);

@@ -266,16 +266,16 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.T
     return out
 
 
-def decode_splits(requests: int, kv_heads: int, max_context_len: int, tile: int = 32) -> int:
-    """How many CTAs share one (request, kv head) in the decode kernel.  A CTA's four warps take
-    key tiles in turn, so a CTA with n tiles runs ceil(n / 4) rounds plus a fixed cost (set-up,
+def decode_splits(requests: int, kv_heads: int, max_context_len: int, tile: int = 32, warps: int = 4) -> int:
+    """How many CTAs share one (request, kv head) in the decode kernel.  A CTA's warps take
+    key tiles in turn, so a CTA with n tiles runs ceil(n / warps) rounds plus a fixed cost (set-up,
     merge); CTAs run in waves of 148.  The split count with the fewest estimated rounds wins."""
     pairs = max(1, requests * kv_heads)
     tiles = max(1, -(-max_context_len // tile))
     best, best_cost = 1, None
     for splits in range(1, min(64, tiles) + 1):
         waves = -(-pairs * splits // 148)
-        rounds = -(-(-(-tiles // splits)) // 4) + 3
+        rounds = -(-(-(-tiles // splits)) // warps) + 3
         cost = waves * rounds + (1 if splits > 1 else 0)
         if best_cost is None or cost < best_cost:
             best, best_cost = splits, cost
