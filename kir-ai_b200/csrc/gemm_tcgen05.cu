@@ -539,7 +539,10 @@ static int choose_splits(int M, int N, int K) {
     const int x_tiles = (N + GEMM_BM - 1) / GEMM_BM;
     const int max_splits = 4;
     const int k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
-    int splits = (120 + x_tiles - 1) / x_tiles;  // about one CTA per SM at least; two fit
+    // about one CTA per SM; with more than 32 tokens a CTA with slots for 3 or 4 partial tiles
+    // fills an SM by itself and fewer, longer CTAs measured faster
+    const int target = M <= 32 ? 144 : 112;
+    int splits = (2 * target + x_tiles) / (2 * x_tiles);  // target / x_tiles, rounded
     if (splits > max_splits) splits = max_splits;
     while (splits > 1 && k_blocks / splits < 8) --splits;
     return splits < 1 ? 1 : splits;
