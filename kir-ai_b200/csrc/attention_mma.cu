@@ -231,7 +231,7 @@ struct PrefillSmem {
     static constexpr int q_bytes = PF_ROWS * D * 2;
     static constexpr int tile_bytes = PF_BN * D * 2;
     static constexpr int ring_bytes = PF_STAGES * 2 * tile_bytes;
-    static constexpr int total = q_bytes + ring_bytes + 2 * PF_STAGES * 8;  // no slack: the base must be 1024-aligned
+    static constexpr int total = q_bytes + ring_bytes + (2 * PF_STAGES + 1) * 8;  // no slack: the base must be 1024-aligned
     static constexpr int ctas_per_sm = (2 * (total + 1024) <= 227 * 1024) ? 2 : 1;
 };
 
@@ -266,6 +266,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16*
     const uint32_t ring = q_smem + Smem::q_bytes;
     uint64_t* full_bar = (uint64_t*)(smem + Smem::q_bytes + Smem::ring_bytes);
     uint64_t* empty_bar = full_bar + PF_STAGES;
+    uint64_t* q_free = empty_bar + PF_STAGES;  // the consumers have the query tile in registers
 
     if (tid == 0) {
         sm100::tma_prefetch_descriptor(&kv_map);
@@ -273,6 +274,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16*
             sm100::mbar_init(sm100::smem_addr(&full_bar[s]), 1);
             sm100::mbar_init(sm100::smem_addr(&empty_bar[s]), PF_WARPS);
         }
+        sm100::mbar_init(sm100::smem_addr(q_free), PF_WARPS);
         sm100::mbar_fence_init();
     }
     // Q tile: row r is token (row0 + r) / group, head kv_head * group + (row0 + r) % group
@@ -301,8 +303,20 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16*
     bool ok = true;
 
     if (warp == PF_WARPS) {
-        // producer: keeps the ring full
+        // producer: keeps the ring full.  Once the consumers hold the query tile in registers its
+        // shared memory is free, and the pages of this CTA's keys are copied there: a lookup in global
+        // memory for every tile would put its latency in front of every TMA issue.
         const int* table = block_table + (long)req * table_width;
+        if (D <= 128) {
+            int* table_s = reinterpret_cast<int*>(smem);
+            const int first_page = (first_tile * PF_BN) / page_size;
+            const int last_page = min(table_width - 1, pos_last / page_size);
+            if (last_page - first_page < Smem::q_bytes / 4 && sm100::mbar_wait(sm100::smem_addr(q_free), 0)) {
+                for (int i = first_page + lane; i <= last_page; i += 32) table_s[i - first_page] = table[i];
+                table = table_s - first_page;
+                __syncwarp();
+            }
+        }
         for (int it = 0; it < num_tiles; ++it) {
             const int slot = it % PF_STAGES;
             if (it >= PF_STAGES && !sm100::mbar_wait(sm100::smem_addr(&empty_bar[slot]), (uint32_t)(it / PF_STAGES - 1) & 1u)) {
@@ -339,6 +353,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16*
         for (int kk = 0; kk < D / 16; ++kk)
             ldmatrix_x4(q_smem + tile_offset<PF_ROWS>(warp * 16 + (lane & 15), kk * 2 + (lane >> 4)), q_regs[kk][0],
                         q_regs[kk][1], q_regs[kk][2], q_regs[kk][3]);
+        __syncwarp();
+        if (lane == 0) sm100::mbar_arrive(sm100::smem_addr(q_free));
     }
     WarpState<D> st;
     st.init();
@@ -507,7 +523,8 @@ struct DecodeSmem {
     static constexpr int ring_bytes = DC_WARPS * DC_STAGES * 2 * tile_bytes;
     static constexpr int merge_bytes = DC_WARPS * 16 * (D + 2) * 4;
     static constexpr int body = q_bytes + (ring_bytes > merge_bytes ? ring_bytes : merge_bytes);
-    static constexpr int total = body + DC_WARPS * DC_STAGES * 8 + 1024;  // barriers, and slack to align to 1024
+    static constexpr int table_entries = 1024;  // block-table entries kept in shared memory (longer ranges read global memory)
+    static constexpr int total = body + DC_WARPS * DC_STAGES * 8 + table_entries * 4 + 1024;  // + barriers, + slack to align to 1024
 };
 
 // partial: [requests, q_heads, splits, head_dim + 2] floats: unnormalised output, then max (log2 domain), then sum.
@@ -566,7 +583,19 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
     }
     __syncthreads();
 
+    // The pages of this CTA's keys: copied to shared memory once, because a lookup in global memory
+    // for every tile would put its latency in front of every TMA issue.
     const int* table = block_table + (long)req * table_width;
+    {
+        int* table_s = reinterpret_cast<int*>(smem + Smem::body + DC_WARPS * DC_STAGES * 8);
+        const int first_page = (t_begin * BN) / page_size;
+        const int last_page = min(table_width - 1, (min(t_end, last_tile + 1) * BN - 1) / page_size);
+        if (last_page - first_page < Smem::table_entries) {
+            for (int i = first_page + tid; i <= last_page; i += DC_WARPS * 32) table_s[i - first_page] = table[i];
+            table = table_s - first_page;
+            __syncthreads();
+        }
+    }
     bool ok = true;
     // Fills ring slot `slot` with key tile `t`.
     auto issue = [&](int t, int slot) {
