@@ -28,6 +28,7 @@ SOURCES = [
     "sampling.cu",
     "gemm_tcgen05.cu",
     "attention_mma.cu",
+    "attention_tcgen05.cu",
 ]
 HEADERS = ["common.cuh", "sm100.cuh", "tensor_map.cuh", "no_alloc.h"]
 

@@ -249,19 +249,31 @@ def paged_attention_plain(q: torch.Tensor, cache: torch.Tensor, block_table: tor
     return out
 
 
+def attention_prefill_takes_tcgen05(q_heads: int, kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """Whether the tcgen05 prompt-attention kernel takes this shape: head size up to 128, a group size
+    that divides its 128 query rows, pages of a power-of-two size."""
+    group = q_heads // kv_heads
+    return head_dim <= 128 and head_dim % 8 == 0 and 128 % group == 0 and page_size & (page_size - 1) == 0
+
+
 def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, query_start: torch.Tensor,
-                      context_len: torch.Tensor, max_query_len: int, window: Optional[int], scale: float) -> torch.Tensor:
-    """bf16 tensor-core attention for runs of new tokens (prompt portions, or any mix): q [T, nq, d]."""
+                      context_len: torch.Tensor, max_query_len: int, window: Optional[int], scale: float,
+                      tcgen05: Optional[bool] = None) -> torch.Tensor:
+    """bf16 tensor-core attention for runs of new tokens (prompt portions, or any mix): q [T, nq, d].
+    ``tcgen05`` picks the kernel (None: the tcgen05 kernel where it takes the shape, else the
+    warp-level ``mma.sync`` kernel)."""
     _need_cuda(q, cache, block_table, query_start, context_len)
     num_pages, kv_heads, page_size, head_dim = _cache_dims(cache)
     rows, q_heads, qd, q_stride = _head_view(q)
     assert qd == head_dim and q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
     requests = context_len.numel()
     assert query_start.numel() == requests + 1 and query_start.dtype == torch.int32 and context_len.dtype == torch.int32
+    if tcgen05 is None:
+        tcgen05 = attention_prefill_takes_tcgen05(q_heads, kv_heads, head_dim, page_size)
     out = torch.empty((rows, q_heads * head_dim), dtype=q.dtype, device=q.device)
-    _call("kirai_attention_prefill_bf16", _ptr(q), _ptr(cache), _ptr(out), _ptr(block_table), _ptr(query_start),
-          _ptr(context_len), _i(requests), _i(max_query_len), _i(q_heads), _i(kv_heads), _i(head_dim), _l(q_stride),
-          _i(page_size), _i(block_table.shape[1]), _i(num_pages), _i(window or 0), _f(scale),
+    _call("kirai_attention_prefill_tc_bf16" if tcgen05 else "kirai_attention_prefill_bf16", _ptr(q), _ptr(cache), _ptr(out),
+          _ptr(block_table), _ptr(query_start), _ptr(context_len), _i(requests), _i(max_query_len), _i(q_heads), _i(kv_heads),
+          _i(head_dim), _l(q_stride), _i(page_size), _i(block_table.shape[1]), _i(num_pages), _i(window or 0), _f(scale),
           _ptr(error_flag(q.device)), _stream())
     return out
 

@@ -321,16 +321,19 @@ def test_tensor_core_attention_against_plain(ops, q_heads, kv_heads, head_dim, p
     req = torch.tensor([i for i, s in enumerate(spans) for _ in range(s[2])], dtype=torch.int32, device=DEV)
     pos = torch.tensor([p for s in spans for p in range(s[1], s[1] + s[2])], dtype=torch.int32, device=DEV)
     # only the keys up to each request's context length count: later rows are in the pages but masked
-    fast = ops.attention_prefill(q, cache, table, query_start, context_len, max(s[2] for s in spans), window, scale)
     plain = ops.paged_attention_plain(q, cache, table, req, pos, window, scale)
-    ops.check_device_errors(torch.device(DEV))
-    row = 0
-    for r, first, count in spans:
-        expected = attention_reference(q[row : row + count].cpu(), keys[r], values[r], list(range(first, first + count)), window, scale)
-        got = fast[row : row + count].float().cpu().unflatten(1, (q_heads, head_dim))
-        assert float((got - expected).abs().max()) <= 2.5e-2, (r, first, count)
-        row += count
-    assert float((fast.float() - plain.float()).abs().max()) <= 2.5e-2
+    kernels = [False] + ([True] if ops.attention_prefill_takes_tcgen05(q_heads, kv_heads, head_dim, page_size) else [])
+    for use_tcgen05 in kernels:  # the warp-level mma.sync kernel, and the tcgen05 kernel where it takes the shape
+        fast = ops.attention_prefill(q, cache, table, query_start, context_len, max(s[2] for s in spans), window, scale,
+                                     tcgen05=use_tcgen05)
+        ops.check_device_errors(torch.device(DEV))
+        row = 0
+        for r, first, count in spans:
+            expected = attention_reference(q[row : row + count].cpu(), keys[r], values[r], list(range(first, first + count)), window, scale)
+            got = fast[row : row + count].float().cpu().unflatten(1, (q_heads, head_dim))
+            assert float((got - expected).abs().max()) <= 2.5e-2, (use_tcgen05, r, first, count)
+            row += count
+        assert float((fast.float() - plain.float()).abs().max()) <= 2.5e-2
     # decode: one token per request at the end of each context, with 1, 2 and 5 splits
     if q_heads // kv_heads <= 16:
         ends = [n - 1 for n in lengths]
