@@ -14,8 +14,10 @@
 // The running maximum is lazy: the output accumulator is rescaled only when a row's maximum has
 // grown by more than 2^8 since the scale in use, which is exact (the final division uses the same
 // scale) and spares most read-modify-write passes over the accumulator.
-// Warp roles: warp 0 feeds a ring of two (K tile, V tile) slots by TMA straight from the pages,
-// one thread of warp 1 issues the MMAs, warps 2-5 are the softmax rows.  Every barrier wait is
+// Warp roles: warp 0 fetches K tiles and V tiles by TMA straight from the pages, one thread of
+// warp 1 issues the MMAs, warps 2-5 are the softmax rows.  A CTA works through its tiles in
+// sequence (P lies over S in tensor memory) and is small enough for two CTAs per SM, which
+// overlap each other: while one's rows exponentiate, the other's products run.  Every barrier wait is
 // bounded.  Same visibility rule as the other attention kernels: row at position pos sees keys
 // lo <= j <= pos.  head_dim: a multiple of 8 up to 128; the group size must divide 128.
 #include "sm100.cuh"
@@ -27,15 +29,16 @@ namespace {
 
 #define TA_ROWS 128
 #define TA_BN 128
-#define TA_STAGES 2
+#define TA_STAGES 1   // slots of the K ring, and of the V ring: two CTAs share an SM and overlap each other
 #define TA_THREADS 192
+#define TA_TMEM_COLS 256  // S (and, over its first half, P) in columns 0..127, O in columns 128..255
 
 template <int D>
 struct TcAttnSmem {
     static constexpr int panels = D / 64;
     static constexpr int q_bytes = TA_ROWS * D * 2;
     static constexpr int tile_bytes = TA_BN * D * 2;
-    static constexpr int ring_bytes = TA_STAGES * 2 * tile_bytes;
+    static constexpr int ring_bytes = TA_STAGES * 2 * tile_bytes;  // K ring, then V ring
     static constexpr int barrier_bytes = 128;
     static constexpr int table_entries = 1024;
     static constexpr int total = q_bytes + ring_bytes + barrier_bytes + table_entries * 4 + 1024;
@@ -82,14 +85,27 @@ __device__ __forceinline__ void tmem_store_32x32(uint32_t taddr, const uint32_t 
           "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+__device__ __forceinline__ void tmem_store_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
 __device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
 template <int D>
-__global__ void __launch_bounds__(TA_THREADS, 1)
+__global__ void __launch_bounds__(TA_THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ q, bf16* __restrict__ out,
                             const int* __restrict__ block_table, const int* __restrict__ query_start,
                             const int* __restrict__ context_len, int q_heads, int kv_heads, int head_dim,
@@ -116,9 +132,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
     const uint32_t q_smem = smem_addr(smem);
     const uint32_t ring = q_smem + Smem::q_bytes;
     uint64_t* bars = (uint64_t*)(smem + Smem::q_bytes + Smem::ring_bytes);
-    uint64_t* kv_full = bars;                       // [TA_STAGES]
-    uint64_t* kv_empty = bars + TA_STAGES;          // [TA_STAGES]
-    uint64_t* s_ready = bars + 2 * TA_STAGES;       // S of this tile is in tensor memory
+    uint64_t* k_full = bars;                        // [TA_STAGES] TMA -> MMA
+    uint64_t* k_empty = bars + TA_STAGES;           // [TA_STAGES] first product done with the K tile
+    uint64_t* v_full = bars + 2 * TA_STAGES;        // [TA_STAGES]
+    uint64_t* v_empty = bars + 3 * TA_STAGES;       // [TA_STAGES] second product done with the V tile
+    uint64_t* s_ready = bars + 4 * TA_STAGES;       // S of a tile is in tensor memory (and every earlier product is done)
     uint64_t* p_ready = s_ready + 1;                // P of this tile is in tensor memory (4 warps arrive)
     uint64_t* o_ready = s_ready + 2;                // the second product of this tile is done
     uint32_t* tmem_slot = (uint32_t*)(s_ready + 3);
@@ -134,8 +152,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
     if (tid == 0) {
         tma_prefetch_descriptor(&kv_map);
         for (int s = 0; s < TA_STAGES; ++s) {
-            mbar_init(smem_addr(&kv_full[s]), 1);
-            mbar_init(smem_addr(&kv_empty[s]), 1);
+            mbar_init(smem_addr(&k_full[s]), 1);
+            mbar_init(smem_addr(&k_empty[s]), 1);
+            mbar_init(smem_addr(&v_full[s]), 1);
+            mbar_init(smem_addr(&v_empty[s]), 1);
         }
         mbar_init(smem_addr(s_ready), 1);
         mbar_init(smem_addr(p_ready), 4);
@@ -143,7 +163,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
         mbar_fence_init();
     }
     if (warp == 1) {
-        tmem_alloc(smem_addr(tmem_slot), 512);
+        tmem_alloc(smem_addr(tmem_slot), TA_TMEM_COLS);
         tmem_relinquish();
     }
     // Q tile: row r is token (row0 + r) / group, head kv_head * group + (row0 + r) % group
@@ -172,7 +192,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_p = tmem_base + 128, tmem_o = tmem_base + 256;
+    const uint32_t tmem_s = tmem_base, tmem_p = tmem_base /* over S */, tmem_o = tmem_base + 128;
     bool ok = true;
 
     if (warp == 0) {
@@ -185,12 +205,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
         }
         const int boxes = TA_BN / box_rows;
         const uint32_t box_bytes = (uint32_t)box_rows * 128u * PANELS;
-        for (int it = 0; it < num_tiles; ++it) {
-            const int slot = it % TA_STAGES;
-            if (it >= TA_STAGES && !mbar_wait(smem_addr(&kv_empty[slot]), (uint32_t)(it / TA_STAGES - 1) & 1u)) { ok = false; break; }
-            const uint32_t bar = smem_addr(&kv_full[slot]);
-            const uint32_t k_dst = ring + slot * 2 * Smem::tile_bytes, v_dst = k_dst + Smem::tile_bytes;
-            const int t = first_tile + it;
+        // fills one slot of the K ring (which == 0) or of the V ring (which == 1) with key tile t
+        auto fill = [&](int t, int which, uint32_t bar, uint32_t dst) {
             int count = 0;
             for (int b = lane; b < boxes; b += 32) {
                 const int j = t * TA_BN + b * box_rows;
@@ -200,8 +216,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
             }
             count = __reduce_add_sync(0xffffffffu, count);
             if (count < boxes) {
-                // boxes without a page hold masked keys only, but their value rows must be finite, and so must
-                // their key rows here: S is read back as a whole and a NaN would survive the mask's select
+                // boxes without a page hold masked keys only; their rows are cleared all the same, because a
+                // value row is multiplied by its zero weight and must be finite
                 for (int b = 0; b < boxes; ++b) {
                     const int j = t * TA_BN + b * box_rows;
                     const int logical = j / page_size;
@@ -209,17 +225,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
                     if (page >= 0 && page < num_pages) continue;
                     for (int h = 0; h < PANELS; ++h) {
                         const uint32_t off = (uint32_t)(h * (TA_BN * 128) + b * box_rows * 128);
-                        for (int i = lane; i < box_rows * 8; i += 32) {
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(k_dst + off + i * 16), "r"(0u) : "memory");
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v_dst + off + i * 16), "r"(0u) : "memory");
-                        }
+                        for (int i = lane; i < box_rows * 8; i += 32)
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst + off + i * 16), "r"(0u) : "memory");
                     }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
             }
             if (lane == 0) {
-                if (count) mbar_expect_tx(bar, 2u * box_bytes * (uint32_t)count);
+                if (count) mbar_expect_tx(bar, box_bytes * (uint32_t)count);
                 else mbar_arrive(bar);
             }
             __syncwarp();
@@ -228,17 +242,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
                 const int logical = j / page_size;
                 const int page = (j <= pos_last && logical < table_width) ? table[logical] : -1;
                 if (page >= 0 && page < num_pages) {
-                    const int row_k = ((page * 2) * kv_heads + kv_head) * page_size + (j % page_size);
-                    const int row_v = row_k + kv_heads * page_size;
+                    const int row = ((page * 2 + which) * kv_heads + kv_head) * page_size + (j % page_size);
 #pragma unroll
-                    for (int h = 0; h < PANELS; ++h) {
-                        const uint32_t off = (uint32_t)(h * (TA_BN * 128) + b * box_rows * 128);
-                        tma_load_2d(k_dst + off, &kv_map, bar, h * 64, row_k);
-                        tma_load_2d(v_dst + off, &kv_map, bar, h * 64, row_v);
-                    }
+                    for (int h = 0; h < PANELS; ++h)
+                        tma_load_2d(dst + (uint32_t)(h * (TA_BN * 128) + b * box_rows * 128), &kv_map, bar, h * 64, row);
                 }
             }
             __syncwarp();
+        };
+        for (int it = 0; it < num_tiles && ok; ++it) {
+            const int slot = it % TA_STAGES;
+            const uint32_t parity = (uint32_t)(it / TA_STAGES - 1) & 1u;
+            if (it >= TA_STAGES && !mbar_wait(smem_addr(&k_empty[slot]), parity)) { ok = false; break; }
+            fill(first_tile + it, 0, smem_addr(&k_full[slot]), ring + slot * Smem::tile_bytes);
+            if (it >= TA_STAGES && !mbar_wait(smem_addr(&v_empty[slot]), parity)) { ok = false; break; }
+            fill(first_tile + it, 1, smem_addr(&v_full[slot]), ring + (TA_STAGES + slot) * Smem::tile_bytes);
         }
     } else if (warp == 1) {
         if (elect_one()) {
@@ -246,9 +264,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
             constexpr uint32_t idesc_pv = instr_desc_bf16_b_mn(TA_ROWS, D);     // O[128 x D], B = V as it lies (MN-major)
             for (int it = 0; it < num_tiles; ++it) {
                 const int slot = it % TA_STAGES;
-                if (!mbar_wait(smem_addr(&kv_full[slot]), (uint32_t)(it / TA_STAGES) & 1u)) { ok = false; break; }
+                const uint32_t parity = (uint32_t)(it / TA_STAGES) & 1u;
+                if (!mbar_wait_hot(smem_addr(&k_full[slot]), parity)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t k_addr = ring + slot * 2 * Smem::tile_bytes, v_addr = k_addr + Smem::tile_bytes;
+                const uint32_t k_addr = ring + slot * Smem::tile_bytes;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     // 16 dims further: 32 bytes inside the swizzle atom, or the next 64-column panel
@@ -257,16 +276,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
                     mma_bf16_ss(tmem_s, smem_desc_k_major_sw128(q_smem + off_q), smem_desc_k_major_sw128(k_addr + off_k), idesc_qk,
                                 kk > 0 ? 1u : 0u);
                 }
+                mma_commit(smem_addr(&k_empty[slot]));
                 mma_commit(smem_addr(s_ready));
-                if (!mbar_wait(smem_addr(p_ready), (uint32_t)it & 1u)) { ok = false; break; }
+                if (!mbar_wait_hot(smem_addr(&v_full[slot]), parity)) { ok = false; break; }
+                if (!mbar_wait_hot(smem_addr(p_ready), (uint32_t)it & 1u)) { ok = false; break; }
                 tc_fence_after();
+                const uint32_t v_addr = ring + (TA_STAGES + slot) * Smem::tile_bytes;
 #pragma unroll
                 for (int kk = 0; kk < TA_BN / 16; ++kk) {
                     // 16 keys further: 8 columns of packed bf16 pairs in tensor memory, two 8-row groups of the V tile
                     mma_bf16_ts(tmem_o, tmem_p + (uint32_t)(kk * 8), smem_desc_mn_major_sw128(v_addr + (uint32_t)(kk * 2048), TA_BN * 128),
                                 idesc_pv, (it > 0 || kk > 0) ? 1u : 0u);
                 }
-                mma_commit(smem_addr(&kv_empty[slot]));
+                mma_commit(smem_addr(&v_empty[slot]));
                 mma_commit(smem_addr(o_ready));
             }
         }
@@ -283,31 +305,40 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
         float l = 0.0f;
         for (int it = 0; it < num_tiles; ++it) {
             const int j0 = (first_tile + it) * TA_BN;
-            if (!mbar_wait(smem_addr(s_ready), (uint32_t)it & 1u)) { ok = false; break; }
+            // S of this tile is complete; since the MMAs run in issue order, so is the second product of
+            // the tile before: O may be rescaled and P (which lies over S) written without another wait
+            if (!mbar_wait_hot(smem_addr(s_ready), (uint32_t)it & 1u)) { ok = false; break; }
             tc_fence_after();
-            uint32_t s[4][32];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_load_32x32(tmem_s + lane_bits + (uint32_t)(c * 32), s[c]);
-            tmem_load_wait();
-            float m_tile = -INFINITY;
-#pragma unroll
+            // a tile whose keys every row of this warp sees needs no mask
+            const bool interior = __all_sync(0xffffffffu, j0 >= lo && j0 + TA_BN - 1 <= pos);
+            // pass 1: the row's maximum (four running maxima, so that the chain of dependent compares is short)
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 1
             for (int c = 0; c < 4; ++c) {
+                uint32_t s[32];
+                tmem_load_32x32(tmem_s + lane_bits + (uint32_t)(c * 32), s);
+                tmem_load_wait();
+                if (interior) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int j = j0 + c * 32 + i;
-                    const float v = (j >= lo && j <= pos) ? __uint_as_float(s[c][i]) * scale_log2 : -INFINITY;
-                    s[c][i] = __float_as_uint(v);
-                    m_tile = fmaxf(m_tile, v);
+                    for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(s[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int j = j0 + c * 32 + i;
+                        mx[i & 3] = fmaxf(mx[i & 3], (j >= lo && j <= pos) ? __uint_as_float(s[i]) : -INFINITY);
+                    }
                 }
             }
-            // the second product of the tile before must be done before P is overwritten or O rescaled
-            if (it > 0 && !mbar_wait(smem_addr(o_ready), (uint32_t)(it - 1) & 1u)) { ok = false; break; }
-            tc_fence_after();
+            const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;  // the scale is positive
             const float m_new = fmaxf(m_used, m_tile);
             const bool grow = m_new > m_used + 8.0f || (m_used == -INFINITY && m_new != -INFINITY);
+            const float factor = grow ? exp2f(m_used - m_new) : 1.0f;  // exp2(-inf) = 0 for a row that saw nothing yet
+            if (grow) {
+                l *= factor;
+                m_used = m_new;
+            }
             if (__any_sync(0xffffffffu, grow && it > 0)) {
                 // rescale this warp's rows of the accumulator (rows that do not need it multiply by 1)
-                const float factor = grow ? exp2f(m_used - m_new) : 1.0f;  // exp2(-inf) = 0 for a row that saw nothing yet
 #pragma unroll 1
                 for (int c = 0; c < D / 32; ++c) {
                     uint32_t o[32];
@@ -317,33 +348,40 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
                     for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
                     tmem_store_32x32(tmem_o + lane_bits + (uint32_t)(c * 32), o);
                 }
-                tmem_store_wait();
-            }
-            if (grow) {
-                l *= exp2f(m_used - m_new);
-                m_used = m_new;
             }
             const float m_sub = m_used == -INFINITY ? 0.0f : m_used;
-            float sum = 0.0f;
+            // pass 2: the weights, 32 keys at a time; their 16 columns of bf16 pairs go over S columns that
+            // this row has already read
+            float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t s[32];
+                tmem_load_32x32(tmem_s + lane_bits + (uint32_t)(c * 32), s);
+                tmem_load_wait();
+                uint32_t p[16];
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t p[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float a = exp2f(__uint_as_float(s[2 * c + (i >> 4)][(2 * i) & 31]) - m_sub);
-                    const float b = exp2f(__uint_as_float(s[2 * c + (i >> 4)][((2 * i) & 31) + 1]) - m_sub);
-                    sum += a + b;
+                for (int i = 0; i < 16; ++i) {
+                    float a = __uint_as_float(s[2 * i]), b = __uint_as_float(s[2 * i + 1]);
+                    if (!interior) {
+                        const int j = j0 + c * 32 + 2 * i;
+                        a = (j >= lo && j <= pos) ? a : -INFINITY;
+                        b = (j + 1 >= lo && j + 1 <= pos) ? b : -INFINITY;
+                    }
+                    // exp2(s * scale - m): one fused multiply-add and one ex2.approx per key (-inf gives 0)
+                    a = ex2_approx(fmaf(a, scale_log2, -m_sub));
+                    b = ex2_approx(fmaf(b, scale_log2, -m_sub));
+                    sum[i & 3] += a + b;
                     p[i] = pack2(a, b);
                 }
-                tmem_store_32x32(tmem_p + lane_bits + (uint32_t)(c * 32), p);
+                tmem_store_32x16(tmem_p + lane_bits + (uint32_t)(c * 16), p);
             }
-            l += sum;
+            l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
             tmem_store_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_addr(p_ready));
         }
-        if (ok) ok = mbar_wait(smem_addr(o_ready), (uint32_t)(num_tiles - 1) & 1u);
+        if (ok) ok = mbar_wait_hot(smem_addr(o_ready), (uint32_t)(num_tiles - 1) & 1u);
         tc_fence_after();
         if (ok) {
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
@@ -379,7 +417,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 512);
+        tmem_dealloc(tmem_base, TA_TMEM_COLS);
     }
 }
 

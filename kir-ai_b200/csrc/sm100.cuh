@@ -53,6 +53,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     return false;
 }
 
+// The same for waits on the critical path of a pipeline (between an MMA and the warps that consume
+// its result): polls without sleeping for a long while, so that the wake-up adds no latency.
+__device__ __forceinline__ bool mbar_wait_hot(uint32_t bar, uint32_t parity) {
+    for (uint32_t spin = 0; spin < KIRAI_WAIT_LIMIT; ++spin) {
+        if (mbar_test(bar, parity)) return true;
+        if (spin > (1u << 16)) __nanosleep(64);
+    }
+    return false;
+}
+
 // ----------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
