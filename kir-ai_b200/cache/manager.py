@@ -18,6 +18,7 @@ import numpy as np
 import torch
 
 from ..parts.base import KVCacheNeed, StateNeed
+from .native_pages import NativePageTables
 from .pages import NO_PAGE, CacheError, GroupSpec, PageTables, RequestPages
 
 
@@ -44,7 +45,7 @@ def _round_up(value: int, multiple: int) -> int:
 
 class CacheManager:
     def __init__(self, needs: Sequence[object], *, page_size: int, num_slots: int, dtype: torch.dtype = torch.float32,
-                 device=None, num_pages: Optional[int] = None, max_tokens: Optional[int] = None):
+                 device=None, num_pages: Optional[int] = None, max_tokens: Optional[int] = None, native: bool = True):
         """``needs``: one KVCacheNeed or StateNeed per cache layer.  The pool of every
         group gets ``num_pages`` pages, or enough for ``max_tokens`` tokens."""
         if num_pages is None:
@@ -70,7 +71,9 @@ class CacheManager:
             else:
                 raise CacheError(f"cache layer {layer}: unknown need {need!r}")
         self.groups = groups
-        self.tables = PageTables(groups, page_size, [num_pages] * len(groups) if groups else [], num_slots)
+        # the bookkeeping runs in native code; ``native=False`` takes the Python model of the same rules
+        tables_class = NativePageTables if native else PageTables
+        self.tables = tables_class(groups, page_size, [num_pages] * len(groups) if groups else [], num_slots)
         self.kv: List[Optional[torch.Tensor]] = []
         self.state: Dict[int, Optional[torch.Tensor]] = {}
         for group in groups:
@@ -122,13 +125,9 @@ class CacheManager:
 
     def block_table_array(self, requests: Sequence[RequestPages], group: int, min_width: int = 1) -> np.ndarray:
         """int32 [len(requests), width] of page ids, NO_PAGE where a request holds none."""
-        rows = []
-        for request in requests:
-            cached = getattr(request, "_table_arrays", None)
-            if cached is None or cached[0] != request.version:
-                cached = (request.version, [np.asarray(t, dtype=np.int32) for t in request.tables])
-                request._table_arrays = cached
-            rows.append(cached[1][group])
+        if isinstance(self.tables, NativePageTables):
+            return self.tables.fill_tables(requests, group, min_width)
+        rows = [np.asarray(r.tables[group], dtype=np.int32) for r in requests]
         width = max(min_width, max((r.size for r in rows), default=0))
         array = np.full((len(requests), width), NO_PAGE, dtype=np.int32)
         for index, row in enumerate(rows):

@@ -154,5 +154,47 @@ def build(force: bool = False, verbose_ptxas: bool = False) -> str:
     return library
 
 
+HOST_SOURCES = ["page_tables.cpp"]
+HOST_LIBRARY_NAME = "libkirai_host.so"
+
+
+def build_host(force: bool = False) -> str:
+    """Builds the host-only C++ runtime pieces (no CUDA needed) and returns the library's path."""
+    out_dir = _build_dir()
+    library = os.path.join(out_dir, HOST_LIBRARY_NAME)
+    stamp = os.path.join(out_dir, "host.stamp")
+    digest = hashlib.sha256()
+    for name in HOST_SOURCES:
+        with open(os.path.join(HERE, name), "rb") as handle:
+            digest.update(handle.read())
+    wanted = digest.hexdigest()[:16]
+    if not force and os.path.exists(library) and os.path.exists(stamp):
+        with open(stamp) as handle:
+            if handle.read().strip() == wanted:
+                return library
+    import fcntl
+
+    with open(os.path.join(out_dir, "host.lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and os.path.exists(library) and os.path.exists(stamp):
+            with open(stamp) as handle:
+                if handle.read().strip() == wanted:
+                    return library
+        compiler = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
+        if compiler is None:
+            raise BuildError("no C++ compiler found (g++ or c++) for the host runtime")
+        temporary = library + f".tmp{os.getpid()}"
+        command = [compiler, "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
+                   *[os.path.join(HERE, name) for name in HOST_SOURCES], "-o", temporary]
+        result = subprocess.run(command, capture_output=True, text=True)
+        if result.returncode != 0:
+            raise BuildError(f"building {HOST_LIBRARY_NAME} failed:\n{result.stdout}\n{result.stderr}")
+        os.replace(temporary, library)
+        with open(stamp, "w") as handle:
+            handle.write(wanted)
+    return library
+
+
 if __name__ == "__main__":
+    print(build_host(force="--force" in sys.argv))
     print(build(force="--force" in sys.argv, verbose_ptxas="--ptxas" in sys.argv))

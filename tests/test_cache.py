@@ -130,3 +130,64 @@ def test_random_orders_keep_every_page_accounted(seed, page_size, num_pages, win
         cache.close(request)
     assert cache.free_pages() == [num_pages] * len(cache.groups)
     assert cache.tables.slots.free_slots == 3
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.integers(0, 2**32 - 1), st.sampled_from([1, 4, 16]), st.integers(4, 40), st.sampled_from([None, 3, 20]))
+def test_native_tables_follow_the_python_model(seed, page_size, num_pages, window):
+    """The native page tables and the Python model, driven by the same random requests, hold the same
+    pages in the same places at every step."""
+    rng = random.Random(seed)
+    needs = [KVCacheNeed(1, 8, None), KVCacheNeed(1, 8, window)] if window else [KVCacheNeed(1, 8, None)]
+    native = CacheManager(needs, page_size=page_size, num_pages=num_pages, num_slots=3, device=None, native=True)
+    model = CacheManager(needs, page_size=page_size, num_pages=num_pages, num_slots=3, device=None, native=False)
+    assert type(native.tables).__name__ == "NativePageTables" and type(model.tables).__name__ == "PageTables"
+    live, counter = {}, 0
+    for _ in range(150):
+        action = rng.random()
+        if action < 0.25:
+            a, b = native.open(counter), model.open(counter)
+            assert (a is None) == (b is None)
+            if a is not None:
+                assert a.slot == b.slot
+                live[counter] = (a, b)
+            counter += 1
+        elif action < 0.85 and live:
+            a, b = live[rng.choice(list(live))]
+            count = rng.choice([1, 1, 2, 5, 17])
+            assert native.tables.pages_needed(a, count) == model.tables.pages_needed(b, count)
+            assert native.can_reserve(a, count) == model.can_reserve(b, count)
+            took_a, took_b = native.reserve(a, count), model.reserve(b, count)
+            assert took_a == took_b
+            if took_a:
+                native.commit(a, count)
+                model.commit(b, count)
+        elif live:
+            key = rng.choice(list(live))
+            a, b = live.pop(key)
+            native.close(a)
+            model.close(b)
+        for a, b in live.values():
+            assert a.length == b.length and a.tables == b.tables
+        for group in range(len(needs)):
+            requests = list(live.values())
+            if requests:
+                assert (native.block_table_array([a for a, _ in requests], group) ==
+                        model.block_table_array([b for _, b in requests], group)).all()
+        assert native.free_pages() == model.free_pages()
+        native.tables.check_consistency()
+        model.tables.check_consistency()
+    assert native.stats() == model.stats()
+
+
+def test_native_tables_refuse_misuse():
+    cache = manager()
+    request = cache.open("x")
+    cache.reserve(request, 5)
+    with pytest.raises(CacheError):
+        cache.commit(request, 9)
+    cache.close(request)
+    for call in (lambda: cache.reserve(request, 1), lambda: cache.commit(request, 1), lambda: cache.close(request)):
+        with pytest.raises(CacheError):
+            call()
+    assert request.closed and request.tables == [[], []]
