@@ -389,3 +389,29 @@ def test_linear_swiglu_epilogue(ops, m, inter, k, splits):
     assert float((out.float() - expected).abs().max()) <= 1e-2 * float(expected.abs().max())
     separate = ops.swiglu(ops.linear_tcgen05(x, torch.cat([gate, up])))  # rounds gate and up to bf16 in between
     assert float((out.float() - separate.float()).abs().max()) <= 2e-2 * float(expected.abs().max())
+
+
+def test_attention_with_block_tables_longer_than_the_shared_copy(ops):
+    """Contexts whose block tables exceed what the kernels keep in shared memory (1,024 entries) read
+    the table from global memory instead; a key near the start and one near the end must both be found."""
+    dtype, q_heads, kv_heads, head_dim, page_size = torch.bfloat16, 4, 1, 64, 4
+    length = 4 * 1100 + 3  # 1,101 pages
+    cache, table, keys, values = paged_setup(dtype, [length], kv_heads, head_dim, page_size, seed=11)
+    direction = torch.randn(head_dim, generator=torch.Generator().manual_seed(2))
+    direction = direction / direction.norm()
+    for marked in (5, length - 9):
+        keys[0][marked] = (direction * 40.0).to(dtype)
+    ops.kv_write(keys[0].to(DEV).contiguous(), values[0].to(DEV).contiguous(), cache, table,
+                 torch.zeros(length, dtype=torch.int32, device=DEV), torch.arange(length, dtype=torch.int32, device=DEV))
+    expected = 0.5 * (values[0][5, 0].float() + values[0][length - 9, 0].float())  # two equal scores dominate
+    q = (direction * 40.0).to(dtype).repeat(1, q_heads, 1).to(DEV)
+    ctx = torch.tensor([length], dtype=torch.int32, device=DEV)
+    scale = head_dim ** -0.5
+    for splits in (1, 3):
+        out = ops.attention_decode(q, cache, table, ctx, None, scale, splits).float().cpu().unflatten(1, (q_heads, head_dim))
+        assert float((out[0, 0] - expected).abs().max()) <= 3e-2, splits
+    qs = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    for use_tcgen05 in (False, True):
+        out = ops.attention_prefill(q, cache, table, qs, ctx, 1, None, scale, tcgen05=use_tcgen05).float().cpu().unflatten(1, (q_heads, head_dim))
+        assert float((out[0, 0] - expected).abs().max()) <= 3e-2, use_tcgen05
+    ops.check_device_errors(torch.device(DEV))
