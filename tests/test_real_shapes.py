@@ -9,15 +9,20 @@ import plain_qwen3 as plain
 
 pytestmark = pytest.mark.gpu
 
-CONFIG = dict(
-    architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=4096, intermediate_size=12288,
-    num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128, vocab_size=1000,
-    max_position_embeddings=4096, rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False,
-)
+BASE = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, head_dim=128, vocab_size=1000,
+            max_position_embeddings=4096, rms_norm_eps=1e-6, rope_theta=1000000.0)
+CONFIGS = {
+    # hidden, heads and intermediate of the 8-billion-parameter shape (untied), of the 4-billion one (tied; query
+    # width 4096 over a hidden size of 2560) and of the 32-billion one (64 query heads in groups of 8)
+    "8b": dict(BASE, hidden_size=4096, intermediate_size=12288, num_attention_heads=32, num_key_value_heads=8, tie_word_embeddings=False),
+    "4b": dict(BASE, hidden_size=2560, intermediate_size=9728, num_attention_heads=32, num_key_value_heads=8, tie_word_embeddings=True),
+    "32b": dict(BASE, hidden_size=5120, intermediate_size=25600, num_attention_heads=64, num_key_value_heads=8, tie_word_embeddings=False),
+}
 
 
-@pytest.fixture(scope="module")
-def model(tmp_path_factory):
+@pytest.fixture(scope="module", params=["8b", "4b", "32b"])
+def model(request, tmp_path_factory):
+    CONFIG = CONFIGS[request.param]
     import kirai_b200  # noqa: F401
     from kirai_b200.registry import config_from_dict
     from kirai_b200.weights import write_random_model
