@@ -100,6 +100,52 @@ def model_numbers(cfg, layers):
     )
 
 
+def generate_workload(which: str) -> int:
+    """The serving-style workloads of the larger configurations, end to end through Engine.generate."""
+    import torch
+
+    import kirai_b200  # noqa: F401
+    from kirai_b200 import Engine, SamplingParams
+    from kirai_b200.registry import config_from_dict
+
+    base = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", head_dim=128, vocab_size=151936,
+                max_position_embeddings=40960, rms_norm_eps=1e-6, rope_theta=1000000.0)
+    if which == "serving-4b":
+        raw = dict(base, num_hidden_layers=36, hidden_size=2560, intermediate_size=9728, num_attention_heads=32,
+                   num_key_value_heads=8, tie_word_embeddings=True)
+        generator = torch.Generator().manual_seed(3)
+        lengths = torch.randint(128, 4097, (64,), generator=generator).tolist()
+        new_tokens, temperature = 256, 0.0
+        engine = Engine(config=config_from_dict(raw), random_weights_seed=3, dtype="bfloat16", page_size=16, max_new_tokens=256,
+                        max_prefill_tokens=1024, prefill_chunk=512, max_concurrent_requests=64, max_cache_tokens=64 * 4400)
+    else:
+        raw = dict(base, num_hidden_layers=64, hidden_size=5120, intermediate_size=25600, num_attention_heads=64,
+                   num_key_value_heads=8, tie_word_embeddings=False)
+        generator = torch.Generator().manual_seed(4)
+        lengths = [8064] * 16
+        new_tokens, temperature = 128, 1.0
+        engine = Engine(config=config_from_dict(raw), random_weights_seed=4, dtype="bfloat16", page_size=16, max_new_tokens=128,
+                        max_prefill_tokens=2048, max_concurrent_requests=16, max_cache_tokens=16 * 8256)
+    prompts = [torch.randint(0, raw["vocab_size"], (n,), generator=generator).tolist() for n in lengths]
+    params = SamplingParams(temperature=temperature, seed=7, max_new_tokens=new_tokens, ignore_eos=True)
+    torch.cuda.synchronize()
+    started = time.perf_counter()
+    outputs = engine.generate(prompts, params)
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - started
+    generated = sum(len(o.token_ids) for o in outputs)
+    stats = engine.stats()
+    print(json.dumps({
+        "metric": f"generated tokens/s, {which} workload through Engine.generate", "value": generated / seconds,
+        "unit": "tokens/s", "n_gpus": 1, "seconds": seconds, "requests": len(prompts), "prompt_tokens": sum(lengths),
+        "generated_tokens": generated, "all_tokens_per_s": (sum(lengths) + generated) / seconds, "dtype": "bf16",
+        "data": "synthetic: uniform-random token ids, random weights", "steps": stats["steps"],
+        "graph_steps": stats["graph_steps"], "preemptions": stats["scheduler"]["preemptions"],
+        "config": {"model": which, "layers": raw["num_hidden_layers"], "hidden": raw["hidden_size"], "page_size": 16},
+    }))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -111,6 +157,11 @@ def main() -> int:
     parser.add_argument("--prefill-tokens", type=int, default=2048)
     parser.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
     parser.add_argument("--points", default="1,64", help="other decode batches to measure (comma separated, '' for none)")
+    parser.add_argument("--workload", default="decode", choices=["decode", "serving-4b", "batch-32b"],
+                        help="decode: the contract's measurement (default).  serving-4b: 64 requests with prompts of "
+                             "128..4096 tokens, 512-token prefill portions mixed with decode, 256 new tokens each, greedy, "
+                             "Qwen3-4B shape.  batch-32b: 16 requests of 8,064 prompt tokens, 128 new tokens at temperature 1, "
+                             "Qwen3-32B shape.  Both run through Engine.generate and print their own one line.")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -122,6 +173,8 @@ def main() -> int:
         return 2
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
+    if args.workload != "decode":
+        return generate_workload(args.workload)
 
     import torch
 
