@@ -508,8 +508,8 @@ __device__ __forceinline__ void warp_attend_heads(HeadState<D>& st, const uint32
 // Four warps; keys per warp tile: 32, or 16 for the widest heads so that the warps' rings fit shared memory.
 template <int D>
 struct DecodeTile {
-    static constexpr int BN = D > 128 ? 16 : 32;
-    static constexpr int WARPS = 4;
+    static constexpr int BN = 16;
+    static constexpr int WARPS = D > 128 ? 4 : 8;
 };
 
 // Shared memory of the decode kernel: the query tile, per warp a ring of DC_STAGES (K tile, V tile)

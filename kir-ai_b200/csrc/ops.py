@@ -278,7 +278,7 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.T
     return out
 
 
-def decode_splits(requests: int, kv_heads: int, max_context_len: int, tile: int = 32, warps: int = 4) -> int:
+def decode_splits(requests: int, kv_heads: int, max_context_len: int, tile: int = 16, warps: int = 8) -> int:
     """How many CTAs share one (request, kv head) in the decode kernel.  A CTA's warps take
     key tiles in turn, so a CTA with n tiles runs ceil(n / warps) rounds plus a fixed cost (set-up,
     merge); CTAs run in waves of 148.  The split count with the fewest estimated rounds wins."""
