@@ -45,7 +45,7 @@ struct GemmSmem {
     static constexpr int max_splits = BN <= 64 ? 4 : 1;  // up to 128 KB of slots beside the 96 KB ring
     static constexpr int slot_bytes = BN * GEMM_BM * 4;  // one 32-bit partial tile
     static constexpr int stages = streaming ? 4 : (200 * 1024 / stage_bytes);
-    static constexpr int barrier_bytes = 256;
+    static constexpr int barrier_bytes = 2048;  // barriers [0, 128), row scales [128, 384), partial sums of squares [512, 1536)
     static constexpr int ctas_per_sm = streaming ? 2 : 1;
     static constexpr int total(int splits) {  // + slack to align the base to 1024 bytes
         return stages * stage_bytes + barrier_bytes + (splits > 1 ? splits * slot_bytes : 0) + 1024;
@@ -54,6 +54,53 @@ struct GemmSmem {
 
 template <int BN>
 __host__ __device__ constexpr int tmem_columns() { return BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256)); }
+
+// What the epilogue does beyond storing the product.
+//  * row_sumsq != nullptr: the rows of A were left unscaled by an RMSNorm whose sums of squares came in parts,
+//    row_sumsq[part][M]; output row m is multiplied by 1 / sqrt(sum_p row_sumsq[p][m] / row_count + row_eps)
+//    (0 when that variance is 0), which is what the product of the normed rows would have been.
+//  * EPI 2 (residual and next norm): residual[m][n] += product; C[m][n] = bf16(residual * norm_weight[n]) is the
+//    unscaled input of the next product, and sumsq_out[tile][m] receives this tile's share of sum_n residual^2.
+struct Epilogue {
+    const float* row_sumsq;
+    int row_parts;
+    float row_count, row_eps;
+    float* residual;
+    const float* norm_weight;
+    float* sumsq_out;
+};
+
+__device__ __forceinline__ float row_scale_of(const Epilogue& ep, int m, int M) {
+    float total = 0.0f;
+    for (int p = 0; p < ep.row_parts; ++p) total += ep.row_sumsq[(size_t)p * M + m];
+    const float variance = total / ep.row_count + ep.row_eps;
+    return variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
+}
+// The stream's values of column n for tokens y0 + c0 .. + 15 (0 where the tile hangs over), loads only.
+// Sixteen of a row's values in the stream, when the chunk lies inside the matrix and on 16-byte boundaries
+// (of the stream and of the norm's weights alike); otherwise the epilogue reads them one by one.
+struct ResidualChunk {
+    float4 r[4];
+    bool vector;
+};
+__device__ __forceinline__ void load_residual_chunk(const Epilogue& ep, int row, int col, int M, int N, ResidualChunk& chunk) {
+    chunk.vector = false;
+    if (row >= M || col + 16 > N) return;
+    const float* res = ep.residual + (size_t)row * N + col;
+    if ((((uintptr_t)res | (uintptr_t)(ep.norm_weight + col)) & 15) != 0) return;
+    chunk.vector = true;
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) chunk.r[q4] = reinterpret_cast<const float4*>(res)[q4];
+}
+template <int BN>
+__device__ __forceinline__ void load_residual_column(const Epilogue& ep, int n, int y0, int c0, int M, int N, float* res) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int y = y0 + c0 + j;
+        res[j] = (n < N && y < M) ? ep.residual[(size_t)y * N + n] : 0.0f;
+    }
+}
+__device__ __forceinline__ void named_barrier_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -84,12 +131,14 @@ template <int BN, bool SWAP, typename OutT, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, GemmSmem<BN>::ctas_per_sm)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                     OutT* __restrict__ C, int M, int N, int K, long ldc, int k_blocks_per_split, int splits,
-                    int* __restrict__ error_flag) {
+                    Epilogue ep, int* __restrict__ error_flag) {
     using Smem = GemmSmem<BN>;
     constexpr int STAGES = Smem::stages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + STAGES * Smem::stage_bytes);
+    float* scale_s = reinterpret_cast<float*>(smem + STAGES * Smem::stage_bytes + 128);   // [BN] row scales of this tile's tokens
+    float* sumsq_s = reinterpret_cast<float*>(smem + STAGES * Smem::stage_bytes + 512);   // [4 warps][BN]
     float* slots = reinterpret_cast<float*>(smem + STAGES * Smem::stage_bytes + Smem::barrier_bytes);  // [splits][BN][128], used in the first CTA
     uint64_t* full_bar = bars;                 // [STAGES] TMA -> MMA
     uint64_t* empty_bar = bars + STAGES;       // [STAGES] MMA -> TMA
@@ -124,6 +173,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    float res[16];  // EPI 2: the stream's values under this thread's 16 outputs
+    float norm_w = 0.0f;
     bool ok = true;
     const int lane_group = warp & 3;           // epilogue warps: tensor-memory lanes 32 (warp % 4) ..
     const int tile_row = lane_group * 32 + lane;
@@ -185,6 +236,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         }
     } else {
         pdl_wait();  // the output buffer may still be read by the kernel before this one
+        // what the epilogue reads from global memory is fetched while the products run
+        if (rank == 0 && SWAP) {
+            if (ep.row_sumsq) {
+                // the scales of this tile's tokens, computed once by the first BN threads
+                if (tile_row < BN) scale_s[tile_row] = (y0 + tile_row < M) ? row_scale_of(ep, y0 + tile_row, M) : 0.0f;
+                named_barrier_128();
+            }
+            if (EPI == 2) {
+                load_residual_column<BN>(ep, x0 + tile_row, y0, 0, M, N, res);
+                norm_w = x0 + tile_row < N ? ep.norm_weight[x0 + tile_row] : 0.0f;
+            }
+        }
         if (num_kb > 0) ok = mbar_wait(smem_addr(done_bar), 0);
         tc_fence_after();
         if (splits > 1) {
@@ -212,9 +275,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         const int x_row = x0 + tile_row;  // row of X that this thread holds
         const int x_rows = SWAP ? N : M;
         const int y_rows = SWAP ? M : N;
+        const float my_scale = (!SWAP && ep.row_sumsq && x_row < M) ? row_scale_of(ep, x_row, M) : 1.0f;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
             if (y0 + c0 >= y_rows) break;  // uniform across the warp
+            if (EPI == 2 && SWAP && c0 > 0) load_residual_column<BN>(ep, x_row, y0, c0, M, N, res);
             float v[16];
             if (splits > 1) {
 #pragma unroll
@@ -235,6 +300,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 }
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+            }
+            if (ep.row_sumsq) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] *= SWAP ? scale_s[c0 + j] : my_scale;
+            }
+            if (EPI == 2 && SWAP) {
+                // this lane holds output column x_row of tokens y0 + c0 .. + 15
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int y = y0 + c0 + j;
+                    float sq = 0.0f;
+                    if (x_row < x_rows && y < y_rows) {
+                        const float r = res[j] + v[j];
+                        ep.residual[(size_t)y * N + x_row] = r;
+                        C[(size_t)y * ldc + x_row] = from_f32<OutT>(r * norm_w);
+                        sq = r * r;
+                    }
+                    sq = warp_sum(sq);
+                    if (lane == 0) sumsq_s[lane_group * BN + c0 + j] = sq;
+                }
+                continue;
             }
             if (EPI == 1 && SWAP) {
                 // this lane holds weight row x_row: rows 16k..16k+7 are gate rows, 16k+8..16k+15 their up rows
@@ -294,6 +380,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 }
             }
         }
+        if (EPI == 2 && SWAP) {
+            // this tile's share of each token's sum of squares: the four warps' parts, added in order
+            named_barrier_128();
+            if (tile_row < BN && y0 + tile_row < M)
+                ep.sumsq_out[(size_t)blockIdx.x * M + y0 + tile_row] =
+                    (sumsq_s[tile_row] + sumsq_s[BN + tile_row]) + (sumsq_s[2 * BN + tile_row] + sumsq_s[3 * BN + tile_row]);
+        }
     }
     if (!ok) atomicExch(error_flag, 4);
     tc_fence_before();
@@ -312,7 +405,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 template <int BN, typename OutT, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
-                               OutT* __restrict__ C, int M, int N, int K, long ldc, int* __restrict__ error_flag) {
+                               OutT* __restrict__ C, int M, int N, int K, long ldc, Epilogue ep,
+                               int* __restrict__ error_flag) {
     using Smem = GemmSmem<BN>;
     constexpr int STAGES = Smem::stages;
     extern __shared__ uint8_t smem_raw[];
@@ -415,21 +509,70 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
             const int buf = local & 1;
             const int x0 = (t % m_tiles) * GEMM_BM, y0 = (t / m_tiles) * BN;
+            const int x_row = x0 + tile_row;
+            // EPI 2: the stream's values are fetched two chunks of 16 columns ahead of their use, the first two
+            // before this tile's products are done
+            ResidualChunk cur, next, after;
+            if (EPI == 2) {
+                load_residual_chunk(ep, x_row, y0, M, N, cur);
+                load_residual_chunk(ep, x_row, y0 + 16, M, N, next);
+            }
             if (!mbar_wait(smem_addr(&acc_full[buf]), (uint32_t)(local >> 1) & 1u)) { ok = false; break; }
             tc_fence_after();
             const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * tmem_columns<BN>()) + ((uint32_t)(lane_group * 32) << 16);
-            const int x_row = x0 + tile_row;
+            const float my_scale = (ep.row_sumsq && x_row < M) ? row_scale_of(ep, x_row, M) : 1.0f;
+            float row_sq = 0.0f;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 if (y0 + c0 >= N) break;  // uniform across the warp
+                float4 w4[4];
+                if (EPI == 2) {
+                    if (c0 > 0) { cur = next; next = after; }
+                    load_residual_chunk(ep, x_row, c0 + 32 < BN ? y0 + c0 + 32 : N, M, N, after);
+                    if (cur.vector) {
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) w4[q4] = reinterpret_cast<const float4*>(ep.norm_weight + y0 + c0)[q4];
+                    }
+                }
+                const bool vector = EPI == 2 && cur.vector;
                 uint32_t r[16];
                 tmem_load_32x16(tmem_acc + (uint32_t)c0, r);
                 tmem_load_wait();
                 if (x_row >= M) continue;
                 float v[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
-                if (EPI == 1) {
+                for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]) * my_scale;
+                if (EPI == 2) {
+                    float* res = ep.residual + (size_t)x_row * N + y0 + c0;
+                    OutT* dst = C + (size_t)x_row * ldc + y0 + c0;
+                    if (vector && sizeof(OutT) == 2 && (((uintptr_t)dst & 15) == 0)) {
+                        uint32_t packed[8];
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            float4 sum = cur.r[q4];
+                            const float4 w = w4[q4];
+                            sum.x += v[4 * q4]; sum.y += v[4 * q4 + 1]; sum.z += v[4 * q4 + 2]; sum.w += v[4 * q4 + 3];
+                            reinterpret_cast<float4*>(res)[q4] = sum;
+                            row_sq += (sum.x * sum.x + sum.y * sum.y) + (sum.z * sum.z + sum.w * sum.w);
+                            __nv_bfloat162 lo = __floats2bfloat162_rn(sum.x * w.x, sum.y * w.y), hi = __floats2bfloat162_rn(sum.z * w.z, sum.w * w.w);
+                            packed[2 * q4] = *reinterpret_cast<uint32_t*>(&lo);
+                            packed[2 * q4 + 1] = *reinterpret_cast<uint32_t*>(&hi);
+                        }
+                        uint4* out = reinterpret_cast<uint4*>(dst);
+                        out[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        out[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if (y0 + c0 + j < N) {
+                                const float sum = res[j] + v[j];
+                                res[j] = sum;
+                                row_sq += sum * sum;
+                                dst[j] = from_f32<OutT>(sum * ep.norm_weight[y0 + c0 + j]);
+                            }
+                        }
+                    }
+                } else if (EPI == 1) {
                     // columns y0 + c0 .. + 15 are 8 gate rows then their 8 up rows: 8 outputs at (y0 + c0) / 2
                     OutT* dst = C + (size_t)x_row * ldc + ((y0 + c0) >> 1);
                     if (y0 + c0 + 16 <= N && sizeof(OutT) == 2 && (((uintptr_t)dst & 15) == 0)) {
@@ -469,6 +612,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
                     }
                 }
             }
+            if (EPI == 2 && x_row < M) ep.sumsq_out[(size_t)(t / m_tiles) * M + x_row] = row_sq;  // this column tile's share
             // this warp has read its lanes of the accumulator: hand it back to the MMA thread
             tc_fence_before();
             __syncwarp();
@@ -486,7 +630,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
 
 template <int BN, typename OutT, int EPI>
 static int launch_persistent(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc,
-                             int* error_flag, cudaStream_t stream) {
+                             const Epilogue& ep, int* error_flag, cudaStream_t stream) {
     using Smem = GemmSmem<BN>;
     CUtensorMap map_a, map_w;
     if (!tmap::bf16_2d_sw128(&map_a, A, M, K, lda, GEMM_BM, GEMM_BK)) return KIRAI_ERR_BAD_ALIGN;
@@ -503,12 +647,12 @@ static int launch_persistent(const void* A, const void* W, void* C, int M, int N
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total(1));
     if (err != cudaSuccess) return (int)err;
     return launch_pdl(kernel, dim3(grid), dim3(GEMM_THREADS), (size_t)Smem::total(1), stream, 1u, map_a, map_w, (OutT*)C, M,
-                      N, K, ldc, error_flag);
+                      N, K, ldc, ep, error_flag);
 }
 
 template <int BN, bool SWAP, typename OutT, int EPI>
 static int launch_config(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc, int splits,
-                         int* error_flag, cudaStream_t stream) {
+                         const Epilogue& ep, int* error_flag, cudaStream_t stream) {
     using Smem = GemmSmem<BN>;
     CUtensorMap map_a, map_w;
     const void* x_ptr = SWAP ? W : A;
@@ -529,7 +673,7 @@ static int launch_config(const void* A, const void* W, void* C, int M, int N, in
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total(Smem::max_splits));
     if (err != cudaSuccess) return (int)err;
     return launch_pdl(kernel, grid, dim3(GEMM_THREADS), (size_t)Smem::total(splits), stream, (unsigned)splits, map_a, map_w,
-                      (OutT*)C, M, N, K, ldc, per_split, splits, error_flag);
+                      (OutT*)C, M, N, K, ldc, per_split, splits, ep, error_flag);
 }
 
 // Split count for the swapped (few tokens) case, which is bound by the weight
@@ -550,20 +694,25 @@ static int choose_splits(int M, int N, int K) {
 
 template <typename OutT, int EPI>
 static int gemm_dispatch(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc, int splits,
-                         int* error_flag, cudaStream_t stream) {
+                         const Epilogue& ep, int* error_flag, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) return KIRAI_ERR_BAD_SIZE;
     if (K % 8 != 0 || lda % 8 != 0) return KIRAI_ERR_BAD_ALIGN;  // TMA needs 16-byte row strides
     if (EPI == 1 && N % 16 != 0) return KIRAI_ERR_BAD_SIZE;      // whole groups of 8 gate + 8 up rows
     if (splits <= 0) splits = M <= 64 ? choose_splits(M, N, K) : 1;
 #define KIRAI_GEMM_CASE(BN, SWAP) \
-    return launch_config<BN, SWAP, OutT, EPI>(A, W, C, M, N, K, lda, ldc, splits, error_flag, stream)
+    return launch_config<BN, SWAP, OutT, EPI>(A, W, C, M, N, K, lda, ldc, splits, ep, error_flag, stream)
     if (M <= 16) KIRAI_GEMM_CASE(16, true);
     if (M <= 32) KIRAI_GEMM_CASE(32, true);
     if (M <= 64) KIRAI_GEMM_CASE(64, true);
 #undef KIRAI_GEMM_CASE
-    if (N <= 128) return launch_persistent<128, OutT, EPI>(A, W, C, M, N, K, lda, ldc, error_flag, stream);
-    return launch_persistent<256, OutT, EPI>(A, W, C, M, N, K, lda, ldc, error_flag, stream);
+    if (N <= 128) return launch_persistent<128, OutT, EPI>(A, W, C, M, N, K, lda, ldc, ep, error_flag, stream);
+    return launch_persistent<256, OutT, EPI>(A, W, C, M, N, K, lda, ldc, ep, error_flag, stream);
+}
+
+static Epilogue plain_epilogue() { return Epilogue{nullptr, 0, 1.0f, 0.0f, nullptr, nullptr, nullptr}; }
+static Epilogue scaled_epilogue(const float* row_sumsq, int row_parts, float row_count, float row_eps) {
+    return Epilogue{row_sumsq, row_sumsq ? row_parts : 0, row_count, row_eps, nullptr, nullptr, nullptr};
 }
 
 // Split count that the entry points pick for splits <= 0.
@@ -572,14 +721,43 @@ KIRAI_EXPORT int kirai_gemm_bf16_auto_splits(int M, int N, int K) { return M <= 
 // C[M, N] = A[M, K] W[N, K]^T.  splits <= 0 picks the split-K count itself (at most 4).
 KIRAI_EXPORT int kirai_gemm_bf16(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc,
                                  int splits, int* error_flag, cudaStream_t stream) {
-    return gemm_dispatch<bf16, 0>(A, W, C, M, N, K, lda, ldc, splits, error_flag, stream);
+    return gemm_dispatch<bf16, 0>(A, W, C, M, N, K, lda, ldc, splits, plain_epilogue(), error_flag, stream);
 }
 KIRAI_EXPORT int kirai_gemm_bf16_out_f32(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc,
                                          int splits, int* error_flag, cudaStream_t stream) {
-    return gemm_dispatch<float, 0>(A, W, C, M, N, K, lda, ldc, splits, error_flag, stream);
+    return gemm_dispatch<float, 0>(A, W, C, M, N, K, lda, ldc, splits, plain_epilogue(), error_flag, stream);
 }
 // C[M, N / 2] = silu(gate) * up, where W's N rows come in groups of 8 gate rows followed by their 8 up rows.
 KIRAI_EXPORT int kirai_gemm_bf16_swiglu(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc,
                                         int splits, int* error_flag, cudaStream_t stream) {
-    return gemm_dispatch<bf16, 1>(A, W, C, M, N, K, lda, ldc, splits, error_flag, stream);
+    return gemm_dispatch<bf16, 1>(A, W, C, M, N, K, lda, ldc, splits, plain_epilogue(), error_flag, stream);
+}
+
+// The same products for rows of A that an RMSNorm left unscaled: row m of the result is multiplied by
+// 1 / sqrt(sum_p row_sumsq[p][m] / row_count + row_eps).  out_f32 and swiglu choose the form of C as above.
+KIRAI_EXPORT int kirai_gemm_bf16_row_scaled(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc,
+                                            int splits, int out_f32, int swiglu, const float* row_sumsq, int row_parts,
+                                            float row_count, float row_eps, int* error_flag, cudaStream_t stream) {
+    if (!row_sumsq || row_parts <= 0 || (out_f32 && swiglu)) return KIRAI_ERR_BAD_SIZE;
+    const Epilogue ep = scaled_epilogue(row_sumsq, row_parts, row_count, row_eps);
+    if (swiglu) return gemm_dispatch<bf16, 1>(A, W, C, M, N, K, lda, ldc, splits, ep, error_flag, stream);
+    if (out_f32) return gemm_dispatch<float, 0>(A, W, C, M, N, K, lda, ldc, splits, ep, error_flag, stream);
+    return gemm_dispatch<bf16, 0>(A, W, C, M, N, K, lda, ldc, splits, ep, error_flag, stream);
+}
+
+// How many parts kirai_gemm_bf16_residual_norm writes into sumsq_out for a product of this shape.
+KIRAI_EXPORT int kirai_gemm_bf16_residual_parts(int M, int N) {
+    if (M <= 64) return (N + GEMM_BM - 1) / GEMM_BM;
+    return N <= 128 ? 1 : (N + 255) / 256;
+}
+
+// residual[M, N] (32-bit) += A W^T; next[M, N] = bf16(residual * norm_weight[n]), the unscaled input of the next
+// product; sumsq_out[parts][M] = each column tile's share of sum_n residual^2, which the next product turns into
+// the norm's scale through kirai_gemm_bf16_row_scaled.
+KIRAI_EXPORT int kirai_gemm_bf16_residual_norm(const void* A, const void* W, void* next, int M, int N, int K, long lda,
+                                               int splits, float* residual, const float* norm_weight, float* sumsq_out,
+                                               int* error_flag, cudaStream_t stream) {
+    if (!residual || !norm_weight || !sumsq_out) return KIRAI_ERR_BAD_SIZE;
+    const Epilogue ep{nullptr, 0, 1.0f, 0.0f, residual, norm_weight, sumsq_out};
+    return gemm_dispatch<bf16, 2>(A, W, next, M, N, K, lda, (long)N, splits, ep, error_flag, stream);
 }

@@ -349,13 +349,15 @@ def linear_plain(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torc
 
 
 def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-                   splits: int = 0, swiglu: bool = False) -> torch.Tensor:
+                   splits: int = 0, swiglu: bool = False, row_scale: Optional[tuple] = None) -> torch.Tensor:
     """bf16 ``x`` [M, K] times ``weight`` [N, K] transposed on the tcgen05 tensor cores (32-bit accumulation).
 
     K and the row stride of ``x`` must be multiples of 8 (TMA reads rows in 16-byte units).
-    ``splits`` > 1 cuts K between the CTAs of a cluster (0: chosen from the shape, at most 8).
+    ``splits`` > 1 cuts K between the CTAs of a cluster (0: chosen from the shape, at most 4).
     With ``swiglu`` the rows of ``weight`` are 8 gate rows, their 8 up rows, 8 gate rows, ... and
     the result is silu(gate) * up, [M, N / 2].
+    ``row_scale`` = (sumsq [P, M] float32, count, eps) multiplies row m of the product by
+    1 / sqrt(sum_p sumsq[p, m] / count + eps): ``x`` then holds rows that an RMSNorm left unscaled.
     """
     _need_cuda(x, weight)
     assert x.dim() == 2 and x.stride(1) == 1 and weight.dim() == 2 and weight.is_contiguous()
@@ -364,13 +366,41 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[to
     m, k, n = x.shape[0], x.shape[1], weight.shape[0]
     if swiglu:
         assert out_dtype == torch.bfloat16 and n % 16 == 0
-        name, width = "kirai_gemm_bf16_swiglu", n // 2
-    else:
-        name, width = ("kirai_gemm_bf16" if out_dtype == torch.bfloat16 else "kirai_gemm_bf16_out_f32"), n
+    width = n // 2 if swiglu else n
     out = torch.empty((m, width), dtype=out_dtype, device=x.device)
+    if row_scale is not None:
+        sumsq, count, eps = row_scale
+        assert sumsq.dtype == torch.float32 and sumsq.dim() == 2 and sumsq.shape[1] == m and sumsq.is_contiguous()
+        _call("kirai_gemm_bf16_row_scaled", _ptr(x), _ptr(weight), _ptr(out), _i(m), _i(n), _i(k), _l(x.stride(0)),
+              _l(width), _i(splits), _i(out_dtype == torch.float32), _i(swiglu), _ptr(sumsq), _i(sumsq.shape[0]),
+              _f(float(count)), _f(float(eps)), _ptr(error_flag(x.device)), _stream())
+        return out
+    if swiglu:
+        name = "kirai_gemm_bf16_swiglu"
+    else:
+        name = "kirai_gemm_bf16" if out_dtype == torch.bfloat16 else "kirai_gemm_bf16_out_f32"
     _call(name, _ptr(x), _ptr(weight), _ptr(out), _i(m), _i(n), _i(k), _l(x.stride(0)), _l(width), _i(splits),
           _ptr(error_flag(x.device)), _stream())
     return out
+
+
+def linear_residual_norm(x: torch.Tensor, weight: torch.Tensor, resid: torch.Tensor, norm_weight: torch.Tensor,
+                         splits: int = 0) -> tuple:
+    """``resid`` [M, N] (float32, in place) += ``x`` [M, K] times ``weight`` [N, K] transposed, on the tensor cores;
+    returns (bf16(resid * norm_weight) [M, N], sumsq [P, M]): the rows of the next RMSNorm without their
+    1 / rms factor, and the parts of each row's sum of squares, which ``linear_tcgen05(row_scale=...)`` applies."""
+    _need_cuda(x, weight, resid, norm_weight)
+    assert x.dim() == 2 and x.stride(1) == 1 and weight.dim() == 2 and weight.is_contiguous()
+    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[1] == weight.shape[1]
+    m, k, n = x.shape[0], x.shape[1], weight.shape[0]
+    assert resid.dtype == torch.float32 and resid.shape == (m, n) and resid.is_contiguous()
+    assert norm_weight.dtype == torch.float32 and norm_weight.shape == (n,) and norm_weight.is_contiguous()
+    parts = int(library().kirai_gemm_bf16_residual_parts(_i(m), _i(n)))
+    rows = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    sumsq = torch.empty((parts, m), dtype=torch.float32, device=x.device)
+    _call("kirai_gemm_bf16_residual_norm", _ptr(x), _ptr(weight), _ptr(rows), _i(m), _i(n), _i(k), _l(x.stride(0)),
+          _i(splits), _ptr(resid), _ptr(norm_weight), _ptr(sumsq), _ptr(error_flag(x.device)), _stream())
+    return rows, sumsq
 
 
 def tcgen05_takes(x: torch.Tensor) -> bool:

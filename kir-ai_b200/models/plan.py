@@ -103,9 +103,11 @@ class DecoderModel:
         """The residual stream [T, H] (32-bit) and the last block's not-yet-added output."""
         resid = self.plan.embedding.forward(batch.token_ids)
         delta = None
-        for call in self.plan.order:
+        order = self.plan.order
+        for i, call in enumerate(order):
             view = cache.layer_view(call.cache) if call.cache is not None else None
-            resid, delta = self.plan.blocks[call.block].forward(resid, delta, batch, view, call.write)
+            following = self.plan.blocks[order[i + 1].block] if i + 1 < len(order) else None
+            resid, delta = self.plan.blocks[call.block].forward(resid, delta, batch, view, call.write, following)
         return resid, delta
 
     def logits(self, resid: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:

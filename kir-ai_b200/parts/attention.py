@@ -74,7 +74,20 @@ class GQAttention(Mixer):
         if self.position is not None:
             self.position.load(weights, rt)
 
-    def forward(self, x: torch.Tensor, batch, cache, write_cache: bool = True) -> torch.Tensor:
+    def takes_unscaled(self, rows: int) -> bool:
+        return self.qkv.fuses_norms(rows)
+
+    def fuses_into_norm(self, rows: int) -> bool:
+        return self.out.fuses_norms(rows)
+
+    def forward(self, x, batch, cache, write_cache: bool = True) -> torch.Tensor:
+        return self.out.forward(self._mix(x, batch, cache, write_cache))
+
+    def forward_into_norm(self, x, batch, cache, write_cache, resid, spec):
+        return self.out.forward_into_norm(self._mix(x, batch, cache, write_cache), resid, spec)
+
+    def _mix(self, x, batch, cache, write_cache: bool) -> torch.Tensor:
+        """Everything before the output projection: [T, q_heads * head_dim]."""
         ops = self.rt.ops
         nq, d = self.q_heads, self.head_dim
         nkv = 0 if self.reads_only else self.kv_heads  # kv heads that this layer projects
@@ -98,5 +111,4 @@ class GQAttention(Mixer):
             self.position.apply(q, k, batch.positions)
             if write_cache:
                 ops.kv_write(k, v, cache.kv, table, batch.request_of_token, batch.positions)
-        mixed = ops.paged_attention(q, cache.kv, table, batch, self.window, self.scale)
-        return self.out.forward(mixed)
+        return ops.paged_attention(q, cache.kv, table, batch, self.window, self.scale)

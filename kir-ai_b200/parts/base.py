@@ -50,6 +50,30 @@ class StateNeed:
     dtype: torch.dtype = torch.float32
 
 
+@dataclass(frozen=True)
+class FusedNormSpec:
+    """What a product needs to take over a norm: y = x / sqrt(mean(x^2) + eps) * weight over ``width`` columns."""
+
+    weight: torch.Tensor  # [width], float32
+    eps: float
+    width: int
+
+
+@dataclass
+class UnscaledNorm:
+    """Normed rows without their 1 / rms factor: ``rows`` = stream * weight in the runtime dtype, and the parts
+    ``sumsq`` [P, T] (float32) of each row's sum of squares.  The product that reads the rows multiplies its result
+    by 1 / sqrt(sum_p sumsq[p] / width + eps), which commutes with the product."""
+
+    rows: torch.Tensor
+    sumsq: torch.Tensor
+    width: int
+    eps: float
+
+    def row_scale(self):
+        return (self.sumsq, self.width, self.eps)
+
+
 class Runtime:
     """Where and in which precision a model runs: the device, the dtype of
     weights and activations (``torch.float32`` for the true 32-bit path,
@@ -91,6 +115,11 @@ class Norm(Part):
     def add_forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
         raise NotImplementedError
 
+    def fused_spec(self) -> Optional[FusedNormSpec]:
+        """Optional: what the product before this norm needs to take it over (see ``Block``); None keeps
+        the norm a kernel of its own."""
+        return None
+
 
 class PositionEncoding(Part):
     """Puts positions into queries and keys.  ``apply`` rewrites ``q`` [T, nq, d]
@@ -110,6 +139,12 @@ class Mixer(Part):
     (kirai_b200.cache.manager.KVLayerView or StateLayerView); when
     ``write_cache`` is false it reads a cache that another layer filled in this
     step and must not write it.
+
+    Optional, for a block that fuses norms into products: ``takes_unscaled(rows)`` true means that for a
+    batch of ``rows`` tokens ``forward`` accepts an ``UnscaledNorm`` in place of ``x``;
+    ``fuses_into_norm(rows)`` true means the mixer has
+    ``forward_into_norm(x, batch, cache, write_cache, resid, spec)``, which adds its output into the
+    32-bit stream ``resid`` in place and returns the ``UnscaledNorm`` of the sum under ``spec``.
     """
 
     def cache_need(self):
@@ -118,9 +153,24 @@ class Mixer(Part):
     def forward(self, x: torch.Tensor, batch, cache, write_cache: bool = True) -> torch.Tensor:
         raise NotImplementedError
 
+    def takes_unscaled(self, rows: int) -> bool:
+        return False
+
+    def fuses_into_norm(self, rows: int) -> bool:
+        return False
+
 
 class FeedForward(Part):
-    """Token-wise transformation: ``forward(x, batch)`` maps [T, H] to [T, H]."""
+    """Token-wise transformation: ``forward(x, batch)`` maps [T, H] to [T, H].
+
+    Optional, as for a mixer: ``takes_unscaled(rows)`` and ``fuses_into_norm(rows)`` with
+    ``forward_into_norm(x, batch, resid, spec)``."""
 
     def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
         raise NotImplementedError
+
+    def takes_unscaled(self, rows: int) -> bool:
+        return False
+
+    def fuses_into_norm(self, rows: int) -> bool:
+        return False

@@ -6,11 +6,12 @@ dense model uses the plain weight, crates/llm-backend/src/core/qwen/ops/norm.rs:
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional
 
 import torch
 
-from .base import Norm, Runtime, WeightSpec
+from .base import FusedNormSpec, Norm, Runtime, WeightSpec
 
 
 class RMSNorm(Norm):
@@ -32,6 +33,13 @@ class RMSNorm(Norm):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.rt.ops.add_rmsnorm(x, None, self.weight, self.eps, self.rt.dtype)
+
+    def fused_spec(self) -> Optional[FusedNormSpec]:
+        # the tensor-core products read and write rows in 16-byte units; KIRAI_FUSE_NORMS=0 keeps every norm a
+        # kernel of its own (for comparing the two paths)
+        if self.rt.dtype != torch.bfloat16 or self.width % 8 or os.environ.get("KIRAI_FUSE_NORMS", "1") == "0":
+            return None
+        return FusedNormSpec(self.weight, self.eps, self.width)
 
     def add_forward_rows(self, resid: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
         """The norm of ``resid[rows] + delta[rows]`` only; the stream is left untouched."""

@@ -9,7 +9,7 @@ from typing import Dict, Optional
 
 import torch
 
-from .base import FeedForward, Runtime, WeightSpec
+from .base import FeedForward, Runtime, UnscaledNorm, WeightSpec
 from .linear import Linear
 
 
@@ -38,11 +38,25 @@ class SwiGLU(FeedForward):
         else:
             self.gate_up.load(weights, rt)
 
-    def forward(self, x: torch.Tensor, batch=None) -> torch.Tensor:
+    def takes_unscaled(self, rows: int) -> bool:
+        return self.fused_weight is not None and self.down.fuses_norms(rows)
+
+    def fuses_into_norm(self, rows: int) -> bool:
+        return self.fused_weight is not None and self.down.fuses_norms(rows)
+
+    def forward(self, x, batch=None) -> torch.Tensor:
+        return self.down.forward(self._activation(x))
+
+    def forward_into_norm(self, x, batch, resid, spec):
+        return self.down.forward_into_norm(self._activation(x), resid, spec)
+
+    def _activation(self, x) -> torch.Tensor:
+        """silu(gate x) * (up x): [T, I]."""
         ops = self.rt.ops
+        if isinstance(x, UnscaledNorm):
+            return ops.linear_tcgen05(x.rows, self.fused_weight, swiglu=True, row_scale=x.row_scale())
         if self.fused_weight is not None and ops.tcgen05_takes(x):
-            return self.down.forward(ops.linear_tcgen05(x, self.fused_weight, swiglu=True))
+            return ops.linear_tcgen05(x, self.fused_weight, swiglu=True)
         if self.fused_weight is not None:
             raise ValueError("SwiGLU input is not laid out for the tensor-core kernel (rows must be 16-byte aligned)")
-        gate_up = self.gate_up.forward(x)
-        return self.down.forward(ops.swiglu(gate_up))
+        return ops.swiglu(self.gate_up.forward(x))

@@ -391,6 +391,59 @@ def test_linear_swiglu_epilogue(ops, m, inter, k, splits):
     assert float((out.float() - separate.float()).abs().max()) <= 2e-2 * float(expected.abs().max())
 
 
+@pytest.mark.parametrize("m,n,k,splits", [(1, 128, 64, 0), (5, 200, 136, 0), (16, 1000, 512, 3), (40, 520, 1032, 4),
+                                          (64, 1536, 264, 0), (65, 264, 192, 0), (300, 1000, 520, 0), (1024, 768, 256, 0)])
+def test_linear_residual_norm_epilogue_and_row_scaled_products(ops, m, n, k, splits):
+    """The product whose epilogue adds into the 32-bit stream and leaves the next norm's rows without their
+    1 / rms factor, and the products that apply that factor to their result, against the formulas."""
+    eps = 1e-5
+    x, w = rand(m, k, dtype=torch.bfloat16, scale=0.5), rand(n, k, dtype=torch.bfloat16, scale=0.1, seed=3)
+    before = rand(m, n, scale=2.0, seed=5)
+    norm_weight = (1.0 + 0.3 * rand(n, seed=6)).contiguous()
+    resid = before.clone()
+    rows, sumsq = ops.linear_residual_norm(x, w, resid, norm_weight, splits)
+    ops.check_device_errors(torch.device(DEV))
+    stream = before.double() + x.double() @ w.double().T
+    assert float((resid.double() - stream).abs().max()) <= 1e-5 * float(stream.abs().max())
+    unscaled = stream * norm_weight.double()
+    assert float((rows.double() - unscaled).abs().max()) <= 5e-3 * float(unscaled.abs().max())
+    assert sumsq.shape[1] == m
+    total = (stream ** 2).sum(1)
+    assert float(((sumsq.double().sum(0) - total) / total).abs().max()) <= 1e-5
+    # the products that follow: plain (both output types) and with the SwiGLU epilogue
+    normed = unscaled * torch.rsqrt((stream ** 2).mean(1, keepdim=True) + eps)
+    width = 272
+    w2 = rand(width, n, dtype=torch.bfloat16, scale=0.1, seed=7)
+    expected = (normed @ w2.double().T).float()
+    bound = 1e-2 * float(expected.abs().max())
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = ops.linear_tcgen05(rows, w2, out_dtype, row_scale=(sumsq, n, eps))
+        assert out.dtype == out_dtype and float((out.float() - expected).abs().max()) <= bound
+    gate, up = w2[: width // 2].contiguous(), w2[width // 2:].contiguous()
+    g, u = expected[:, : width // 2], expected[:, width // 2:]
+    expected_act = g / (1.0 + torch.exp(-g)) * u
+    act = ops.linear_tcgen05(rows, ops.interleave_gate_up(gate, up), swiglu=True, row_scale=(sumsq, n, eps))
+    assert float((act.float() - expected_act).abs().max()) <= 1e-2 * float(expected_act.abs().max())
+    # and against the separate kernels of the same path: add + norm, then the product
+    separate_stream = before.clone()
+    delta = ops.linear_tcgen05(x, w)
+    separate = ops.linear_tcgen05(ops.add_rmsnorm(separate_stream, delta, norm_weight, eps, torch.bfloat16), w2, torch.float32)
+    ops.check_device_errors(torch.device(DEV))
+    assert float((separate - expected).abs().max()) <= 2 * bound
+
+
+def test_row_scaled_product_of_a_zero_row_is_zero(ops):
+    """A row whose variance plus eps is 0 gets the scale 0, as the norm kernel gives it, not a NaN."""
+    m, n, k = 3, 64, 32
+    x, w = torch.zeros(m, k, dtype=torch.bfloat16, device=DEV), rand(n, k, dtype=torch.bfloat16)
+    resid = torch.zeros(m, n, device=DEV)
+    resid[1] = 1.0
+    rows, sumsq = ops.linear_residual_norm(x, w, resid, torch.ones(n, device=DEV))
+    out = ops.linear_tcgen05(rows, rand(16, n, dtype=torch.bfloat16, seed=2), torch.float32, row_scale=(sumsq, n, 0.0))
+    assert torch.isfinite(out).all() and float(out[0].abs().max()) == 0.0 and float(out[2].abs().max()) == 0.0
+    assert float(out[1].abs().max()) > 0.0
+
+
 def test_attention_with_block_tables_longer_than_the_shared_copy(ops):
     """Contexts whose block tables exceed what the kernels keep in shared memory (1,024 entries) read
     the table from global memory instead; a key near the start and one near the end must both be found."""

@@ -141,3 +141,52 @@ def test_block_arrangements(dtype, arrangement):
     resid, delta = block.forward(h.to(DEV), None, batch, session.cache.layer_view(0), True)
     got = resid.cpu() + delta.float().cpu()
     assert float((got - expected).abs().max()) <= tolerance(dtype, expected)
+
+
+def test_blocks_fold_norms_into_products_for_small_batches(monkeypatch):
+    """In bfloat16 a small batch runs its second norm, and the first norm of the block that follows, inside the
+    products around them; the result is that of the separate kernels, with three launches fewer for two blocks,
+    and a batch above the limit takes the separate kernels."""
+    from kirai_b200.csrc import ops
+    from kirai_b200.parts import Block, GQAttention, RMSNorm, RotaryEmbedding, SwiGLU
+    from kirai_b200.parts.base import UnscaledNorm
+    from kirai_b200.parts.linear import Linear
+
+    hidden, dtype = 48, torch.bfloat16
+    cfg = dict(num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-6, rope_theta=1e4)
+
+    def make(layer):
+        prefix = f"model.layers.{layer}."
+        return Block(RMSNorm(prefix + "input_layernorm.weight", hidden, 1e-6),
+                     GQAttention(prefix + "self_attn.", hidden, 4, 2, 16, RotaryEmbedding(16, 1e4), qk_norm_eps=1e-6),
+                     RMSNorm(prefix + "post_attention_layernorm.weight", hidden, 1e-6), SwiGLU(prefix + "mlp.", hidden, 72))
+
+    blocks = [make(0), make(1)]
+    weights = {}
+    for layer, block in enumerate(blocks):
+        weights.update(load_part(block, dtype, seed=layer))
+
+    def run(rows):
+        session = Session([b.mixer.cache_need() for b in blocks], dtype, num_pages=32)
+        h = rand(rows, hidden, seed=3)
+        batch = session.batch([("r", rows)])
+        before = ops.launch_count
+        resid, left = blocks[0].forward(h.to(DEV), None, batch, session.cache.layer_view(0), True, blocks[1])
+        middle = left
+        resid, left = blocks[1].forward(resid, left, batch, session.cache.layer_view(1), True, None)
+        ops.check_device_errors(torch.device(DEV))
+        expected = plain.decoder_layer(plain.decoder_layer(h, weights, 0, cfg, list(range(rows)), None), weights, 1, cfg,
+                                       list(range(rows)), None)
+        return resid.cpu() + left.float().cpu(), expected, middle, ops.launch_count - before
+
+    fused, expected, middle, fused_launches = run(13)
+    assert isinstance(middle, UnscaledNorm)
+    assert float((fused - expected).abs().max()) <= tolerance(dtype, expected)
+    monkeypatch.setenv("KIRAI_FUSE_NORMS", "0")
+    separate, _, middle, separate_launches = run(13)
+    assert isinstance(middle, torch.Tensor) and separate_launches == fused_launches + 3
+    assert float((fused - separate).abs().max()) <= tolerance(dtype, expected)
+    monkeypatch.delenv("KIRAI_FUSE_NORMS")
+    large, expected, middle, _ = run(Linear.FUSED_NORM_MAX_ROWS + 1)
+    assert isinstance(middle, torch.Tensor)
+    assert float((large - expected).abs().max()) <= tolerance(dtype, expected)
