@@ -41,6 +41,38 @@ KIRAI_EXPORT int kirai_embedding_bf16(const void* table, const int* ids, float* 
     return embedding_launch<bf16>(table, ids, out, tokens, hidden, vocab, error_flag, stream);
 }
 
+// The same gather from a bf16 table kept in the tensor-core product's box layout (boxes of 128 rows x 64
+// columns under the 128-byte swizzle, box (row tile, k block) at row_tile * k_blocks + k_block): the 16-byte
+// chunk c of row r of a box lies at byte r * 128 + (c ^ (r % 8)) * 16.
+__global__ void embedding_tiled_kernel(const uint4* __restrict__ boxes, const int* __restrict__ ids, float* __restrict__ out,
+                                       int hidden, int vocab, int* __restrict__ error_flag) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int token = blockIdx.x;
+    const int id = ids[token];
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) atomicExch(error_flag, 1);
+        return;
+    }
+    const int k_blocks = (hidden + 63) / 64, r = id % 128;
+    const uint4* tile = boxes + (size_t)(id / 128) * k_blocks * 1024;  // 1,024 chunks of 16 bytes per box
+    float* dst = out + (size_t)token * hidden;
+    for (int chunk = threadIdx.x; chunk * 8 < hidden; chunk += blockDim.x) {
+        const uint4 raw = tile[(size_t)(chunk / 8) * 1024 + r * 8 + ((chunk % 8) ^ (r % 8))];
+        const bf16* values = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (chunk * 8 + j < hidden) dst[chunk * 8 + j] = to_f32<bf16>(values[j]);
+    }
+}
+
+KIRAI_EXPORT int kirai_embedding_tiled_bf16(const void* boxes, const int* ids, float* out, int tokens, int hidden, int vocab,
+                                            int* error_flag, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    return launch_pdl(embedding_tiled_kernel, dim3(tokens), dim3(256), 0, stream, 1u, (const uint4*)boxes, ids, out, hidden,
+                      vocab, error_flag);
+}
+
 // ------------------------------------------------------- residual add + RMSNorm
 // resid (32-bit, in place) += delta; out = resid * 1/sqrt(mean(resid^2) + eps) * weight.
 // With row_index != nullptr, output row r reads residual row row_index[r] and

@@ -23,6 +23,11 @@
 // for that kernel only before it reads A or writes C.  W must therefore not be
 // written by the kernel that directly precedes a product in the same stream
 // (weights are constants of a loaded model).
+//
+// W comes either row-major [N, K], read through a tiled tensor map, or "tiled": cut at load time into boxes of
+// 128 rows x 64 columns, each stored as the 16 KB image that the 128-byte swizzle leaves in shared memory, box
+// (row tile, k block) at index row_tile * ceil(K / 64) + k_block, zero-padded at the edges.  A tiled box is one
+// contiguous bulk copy; streaming whole boxes reads HBM about a sixth faster than gathering 128 rows of 128 bytes.
 #include "sm100.cuh"
 #include "tensor_map.cuh"
 
@@ -31,6 +36,7 @@ using namespace sm100;
 #define GEMM_BM 128
 #define GEMM_BK 64
 #define GEMM_THREADS 192
+#define GEMM_BOX_BYTES (GEMM_BM * GEMM_BK * 2)  // one box of tiled weights
 
 // Shared memory of one CTA: the ring of stages, the barriers, then (only with split-K) one slot
 // per CTA of the cluster for the partial tiles.  The swapped, weight-streaming case (BN <= 64)
@@ -130,8 +136,8 @@ __device__ __forceinline__ float silu_mul(float gate, float up) {
 template <int BN, bool SWAP, typename OutT, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, GemmSmem<BN>::ctas_per_sm)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
-                    OutT* __restrict__ C, int M, int N, int K, long ldc, int k_blocks_per_split, int splits,
-                    Epilogue ep, int* __restrict__ error_flag) {
+                    const uint8_t* __restrict__ w_tiled, OutT* __restrict__ C, int M, int N, int K, long ldc,
+                    int k_blocks_per_split, int splits, Epilogue ep, int* __restrict__ error_flag) {
     using Smem = GemmSmem<BN>;
     constexpr int STAGES = Smem::stages;
     extern __shared__ uint8_t smem_raw[];
@@ -184,13 +190,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             // The weights do not depend on the kernel before this one: with SWAP the X operand (weights)
             // of the first ring of stages is fetched at once, and only the activations wait for it.
             const int x_first = SWAP ? 0 : 1, y_first = SWAP ? 1 : 0;  // which operand is the weights
+            // tiled weights (SWAP only): this tile's boxes lie one after the other
+            const uint8_t* boxes = w_tiled ? w_tiled + ((size_t)blockIdx.x * total_k_blocks + kb_begin) * GEMM_BOX_BYTES : nullptr;
+            auto load_x = [&](uint32_t dst, uint32_t full, int i) {
+                if (SWAP && boxes) bulk_load_1d(dst, boxes + (size_t)i * GEMM_BOX_BYTES, GEMM_BOX_BYTES, full);
+                else tma_load_2d(dst, &map_x, full, (kb_begin + i) * GEMM_BK, x0);
+            };
             const int head = num_kb < STAGES ? num_kb : STAGES;
             for (int i = 0; i < head; ++i) {
                 const uint32_t full = smem_addr(&full_bar[i]);
                 mbar_expect_tx(full, Smem::stage_bytes);
                 const uint32_t dst = smem_addr(smem + i * Smem::stage_bytes);
                 const int k = (kb_begin + i) * GEMM_BK;
-                if (x_first == 0) tma_load_2d(dst, &map_x, full, k, x0);
+                if (x_first == 0) load_x(dst, full, i);
                 if (y_first == 0) tma_load_2d(dst + Smem::x_bytes, &map_y, full, k, y0);
             }
             pdl_wait();  // what the kernel before wrote (the activations) is complete and visible
@@ -198,7 +210,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 const uint32_t full = smem_addr(&full_bar[i]);
                 const uint32_t dst = smem_addr(smem + i * Smem::stage_bytes);
                 const int k = (kb_begin + i) * GEMM_BK;
-                if (x_first == 1) tma_load_2d(dst, &map_x, full, k, x0);
+                if (x_first == 1) load_x(dst, full, i);
                 if (y_first == 1) tma_load_2d(dst + Smem::x_bytes, &map_y, full, k, y0);
             }
             for (int i = head; i < num_kb; ++i) {
@@ -209,7 +221,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 mbar_expect_tx(full, Smem::stage_bytes);
                 const uint32_t dst = smem_addr(smem + s * Smem::stage_bytes);
                 const int k = (kb_begin + i) * GEMM_BK;
-                tma_load_2d(dst, &map_x, full, k, x0);
+                load_x(dst, full, i);
                 tma_load_2d(dst + Smem::x_bytes, &map_y, full, k, y0);
             }
         }
@@ -405,8 +417,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 template <int BN, typename OutT, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
-                               OutT* __restrict__ C, int M, int N, int K, long ldc, Epilogue ep,
-                               int* __restrict__ error_flag) {
+                               const uint8_t* __restrict__ w_tiled, OutT* __restrict__ C, int M, int N, int K, long ldc,
+                               Epilogue ep, int* __restrict__ error_flag) {
     using Smem = GemmSmem<BN>;
     constexpr int STAGES = Smem::stages;
     extern __shared__ uint8_t smem_raw[];
@@ -449,30 +461,50 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
 
     if (warp == 0) {
         if (elect_one()) {
-            // k-blocks are numbered over all of this CTA's tiles; block `it` goes to stage it % STAGES
-            const int my_tiles = (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-            const long total_it = (long)my_tiles * num_kb;
-            auto issue = [&](long it, bool weights, bool activations) {
-                const int t = (int)blockIdx.x + (int)(it / num_kb) * (int)gridDim.x;
-                const int k = (int)(it % num_kb) * GEMM_BK;
-                const int s = (int)(it % STAGES);
-                const uint32_t full = smem_addr(&full_bar[s]);
-                const uint32_t dst = smem_addr(smem + s * Smem::stage_bytes);
-                if (weights) {
+            // Walks this CTA's (tile, k-block) sequence and the ring of stages with counters only: this thread's
+            // issue rate bounds the kernel, and a division per k-block showed in the product's time.
+            struct Cursor {
+                int t, kb, stage, m_tile, n_tile;
+                uint32_t round;  // how often the ring has wrapped
+            };
+            auto place = [&](Cursor& c) { c.m_tile = c.t % m_tiles, c.n_tile = c.t / m_tiles; };
+            auto advance = [&](Cursor& c) {
+                if (++c.kb == num_kb) { c.kb = 0, c.t += (int)gridDim.x; place(c); }
+                if (++c.stage == STAGES) { c.stage = 0, ++c.round; }
+            };
+            const int row_tiles = (N + GEMM_BM - 1) / GEMM_BM;
+            auto issue = [&](const Cursor& c, bool weights, bool activations) {
+                const uint32_t full = smem_addr(&full_bar[c.stage]);
+                const uint32_t dst = smem_addr(smem + c.stage * Smem::stage_bytes);
+                if (weights && w_tiled) {
+                    // BN / 128 boxes of 128 weight rows, stacked as the MMA reads them; a box past the last row
+                    // tile is left out (its columns of the accumulator are never stored)
+                    const int first = c.n_tile * (BN / GEMM_BM);
+                    const int boxes = min(BN / GEMM_BM, row_tiles - first);
+                    mbar_expect_tx(full, Smem::x_bytes + boxes * GEMM_BOX_BYTES);
+                    const uint8_t* src = w_tiled + ((size_t)first * num_kb + c.kb) * GEMM_BOX_BYTES;
+                    for (int b = 0; b < boxes; ++b)
+                        bulk_load_1d(dst + Smem::x_bytes + b * GEMM_BOX_BYTES, src + (size_t)b * num_kb * GEMM_BOX_BYTES,
+                                     GEMM_BOX_BYTES, full);
+                } else if (weights) {
                     mbar_expect_tx(full, Smem::stage_bytes);
-                    tma_load_2d(dst + Smem::x_bytes, &map_y, full, k, (t / m_tiles) * BN);
+                    tma_load_2d(dst + Smem::x_bytes, &map_y, full, c.kb * GEMM_BK, c.n_tile * BN);
                 }
-                if (activations) tma_load_2d(dst, &map_x, full, k, (t % m_tiles) * GEMM_BM);
+                if (activations) tma_load_2d(dst, &map_x, full, c.kb * GEMM_BK, c.m_tile * GEMM_BM);
             };
             // The weights do not depend on the kernel before this one: the first ring of weight tiles is
             // fetched at once, and only the activation tiles wait for that kernel to finish.
-            const long head = total_it < STAGES ? total_it : STAGES;
-            for (long it = 0; it < head; ++it) issue(it, true, false);
+            Cursor ahead{(int)blockIdx.x, 0, 0, 0, 0, 0u};
+            place(ahead);
+            Cursor behind = ahead;
+            int head = 0;
+            for (; head < STAGES && ahead.t < total_tiles; ++head) { issue(ahead, true, false); advance(ahead); }
             pdl_wait();
-            for (long it = 0; it < head; ++it) issue(it, false, true);
-            for (long it = head; it < total_it; ++it) {
-                if (!mbar_wait(smem_addr(&empty_bar[it % STAGES]), (uint32_t)(it / STAGES - 1) & 1u)) { ok = false; break; }
-                issue(it, true, true);
+            for (int i = 0; i < head; ++i) { issue(behind, false, true); advance(behind); }
+            while (ahead.t < total_tiles) {
+                if (!mbar_wait(smem_addr(&empty_bar[ahead.stage]), (ahead.round - 1u) & 1u)) { ok = false; break; }
+                issue(ahead, true, true);
+                advance(ahead);
             }
         }
     } else if (warp == 1) {
@@ -508,7 +540,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
         int local = 0;
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
             const int buf = local & 1;
-            const int x0 = (t % m_tiles) * GEMM_BM, y0 = (t / m_tiles) * BN;
+            const int n_tile = t / m_tiles;
+            const int x0 = (t % m_tiles) * GEMM_BM, y0 = n_tile * BN;
             const int x_row = x0 + tile_row;
             // EPI 2: the stream's values are fetched two chunks of 16 columns ahead of their use, the first two
             // before this tile's products are done
@@ -612,7 +645,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
                     }
                 }
             }
-            if (EPI == 2 && x_row < M) ep.sumsq_out[(size_t)(t / m_tiles) * M + x_row] = row_sq;  // this column tile's share
+            if (EPI == 2 && x_row < M) ep.sumsq_out[(size_t)n_tile * M + x_row] = row_sq;  // this column tile's share
             // this warp has read its lanes of the accumulator: hand it back to the MMA thread
             tc_fence_before();
             __syncwarp();
@@ -629,12 +662,14 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
 }
 
 template <int BN, typename OutT, int EPI>
-static int launch_persistent(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc,
+static int launch_persistent(const void* A, const void* W, bool tiled, void* C, int M, int N, int K, long lda, long ldc,
                              const Epilogue& ep, int* error_flag, cudaStream_t stream) {
     using Smem = GemmSmem<BN>;
     CUtensorMap map_a, map_w;
     if (!tmap::bf16_2d_sw128(&map_a, A, M, K, lda, GEMM_BM, GEMM_BK)) return KIRAI_ERR_BAD_ALIGN;
-    if (!tmap::bf16_2d_sw128(&map_w, W, N, K, K, BN, GEMM_BK)) return KIRAI_ERR_BAD_ALIGN;
+    if (tiled) map_w = map_a;  // not read: the boxes are fetched by address
+    else if (!tmap::bf16_2d_sw128(&map_w, W, N, K, K, BN, GEMM_BK)) return KIRAI_ERR_BAD_ALIGN;
+    if (tiled && ((uintptr_t)W & 15)) return KIRAI_ERR_BAD_ALIGN;
     const long tiles = (long)((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
     static int sm_count = 0;
     if (sm_count == 0) {
@@ -646,21 +681,23 @@ static int launch_persistent(const void* A, const void* W, void* C, int M, int N
     auto kernel = gemm_tcgen05_persistent_kernel<BN, OutT, EPI>;
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total(1));
     if (err != cudaSuccess) return (int)err;
-    return launch_pdl(kernel, dim3(grid), dim3(GEMM_THREADS), (size_t)Smem::total(1), stream, 1u, map_a, map_w, (OutT*)C, M,
-                      N, K, ldc, ep, error_flag);
+    return launch_pdl(kernel, dim3(grid), dim3(GEMM_THREADS), (size_t)Smem::total(1), stream, 1u, map_a, map_w,
+                      tiled ? (const uint8_t*)W : (const uint8_t*)nullptr, (OutT*)C, M, N, K, ldc, ep, error_flag);
 }
 
 template <int BN, bool SWAP, typename OutT, int EPI>
-static int launch_config(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc, int splits,
-                         const Epilogue& ep, int* error_flag, cudaStream_t stream) {
+static int launch_config(const void* A, const void* W, bool tiled, void* C, int M, int N, int K, long lda, long ldc,
+                         int splits, const Epilogue& ep, int* error_flag, cudaStream_t stream) {
     using Smem = GemmSmem<BN>;
-    CUtensorMap map_a, map_w;
+    CUtensorMap map_x, map_y;
     const void* x_ptr = SWAP ? W : A;
     const void* y_ptr = SWAP ? A : W;
     const uint64_t x_rows = SWAP ? N : M, y_rows = SWAP ? M : N;
     const uint64_t x_stride = SWAP ? K : lda, y_stride = SWAP ? lda : K;
-    if (!tmap::bf16_2d_sw128(&map_a, x_ptr, x_rows, K, x_stride, GEMM_BM, GEMM_BK)) return KIRAI_ERR_BAD_ALIGN;
-    if (!tmap::bf16_2d_sw128(&map_w, y_ptr, y_rows, K, y_stride, BN, GEMM_BK)) return KIRAI_ERR_BAD_ALIGN;
+    if (tiled && (!SWAP || ((uintptr_t)W & 15))) return KIRAI_ERR_BAD_ALIGN;
+    if (!tmap::bf16_2d_sw128(&map_y, y_ptr, y_rows, K, y_stride, BN, GEMM_BK)) return KIRAI_ERR_BAD_ALIGN;
+    if (tiled) map_x = map_y;  // not read: the boxes are fetched by address
+    else if (!tmap::bf16_2d_sw128(&map_x, x_ptr, x_rows, K, x_stride, GEMM_BM, GEMM_BK)) return KIRAI_ERR_BAD_ALIGN;
     const int total_k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
     if (splits < 1) splits = 1;
     if (splits > Smem::max_splits) splits = Smem::max_splits;  // slots in the first CTA's shared memory
@@ -672,8 +709,9 @@ static int launch_config(const void* A, const void* W, void* C, int M, int N, in
     auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT, EPI>;
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total(Smem::max_splits));
     if (err != cudaSuccess) return (int)err;
-    return launch_pdl(kernel, grid, dim3(GEMM_THREADS), (size_t)Smem::total(splits), stream, (unsigned)splits, map_a, map_w,
-                      (OutT*)C, M, N, K, ldc, per_split, splits, ep, error_flag);
+    return launch_pdl(kernel, grid, dim3(GEMM_THREADS), (size_t)Smem::total(splits), stream, (unsigned)splits, map_x, map_y,
+                      tiled ? (const uint8_t*)W : (const uint8_t*)nullptr, (OutT*)C, M, N, K, ldc, per_split, splits, ep,
+                      error_flag);
 }
 
 // Split count for the swapped (few tokens) case, which is bound by the weight
@@ -693,71 +731,59 @@ static int choose_splits(int M, int N, int K) {
 }
 
 template <typename OutT, int EPI>
-static int gemm_dispatch(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc, int splits,
-                         const Epilogue& ep, int* error_flag, cudaStream_t stream) {
+static int gemm_dispatch(const void* A, const void* W, bool tiled, void* C, int M, int N, int K, long lda, long ldc,
+                         int splits, const Epilogue& ep, int* error_flag, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) return KIRAI_ERR_BAD_SIZE;
     if (K % 8 != 0 || lda % 8 != 0) return KIRAI_ERR_BAD_ALIGN;  // TMA needs 16-byte row strides
     if (EPI == 1 && N % 16 != 0) return KIRAI_ERR_BAD_SIZE;      // whole groups of 8 gate + 8 up rows
     if (splits <= 0) splits = M <= 64 ? choose_splits(M, N, K) : 1;
 #define KIRAI_GEMM_CASE(BN, SWAP) \
-    return launch_config<BN, SWAP, OutT, EPI>(A, W, C, M, N, K, lda, ldc, splits, ep, error_flag, stream)
+    return launch_config<BN, SWAP, OutT, EPI>(A, W, tiled, C, M, N, K, lda, ldc, splits, ep, error_flag, stream)
     if (M <= 16) KIRAI_GEMM_CASE(16, true);
     if (M <= 32) KIRAI_GEMM_CASE(32, true);
     if (M <= 64) KIRAI_GEMM_CASE(64, true);
 #undef KIRAI_GEMM_CASE
-    if (N <= 128) return launch_persistent<128, OutT, EPI>(A, W, C, M, N, K, lda, ldc, ep, error_flag, stream);
-    return launch_persistent<256, OutT, EPI>(A, W, C, M, N, K, lda, ldc, ep, error_flag, stream);
-}
-
-static Epilogue plain_epilogue() { return Epilogue{nullptr, 0, 1.0f, 0.0f, nullptr, nullptr, nullptr}; }
-static Epilogue scaled_epilogue(const float* row_sumsq, int row_parts, float row_count, float row_eps) {
-    return Epilogue{row_sumsq, row_sumsq ? row_parts : 0, row_count, row_eps, nullptr, nullptr, nullptr};
+    if (N <= 128) return launch_persistent<128, OutT, EPI>(A, W, tiled, C, M, N, K, lda, ldc, ep, error_flag, stream);
+    return launch_persistent<256, OutT, EPI>(A, W, tiled, C, M, N, K, lda, ldc, ep, error_flag, stream);
 }
 
 // Split count that the entry points pick for splits <= 0.
 KIRAI_EXPORT int kirai_gemm_bf16_auto_splits(int M, int N, int K) { return M <= 64 ? choose_splits(M, N, K) : 1; }
 
-// C[M, N] = A[M, K] W[N, K]^T.  splits <= 0 picks the split-K count itself (at most 4).
-KIRAI_EXPORT int kirai_gemm_bf16(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc,
-                                 int splits, int* error_flag, cudaStream_t stream) {
-    return gemm_dispatch<bf16, 0>(A, W, C, M, N, K, lda, ldc, splits, plain_epilogue(), error_flag, stream);
-}
-KIRAI_EXPORT int kirai_gemm_bf16_out_f32(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc,
-                                         int splits, int* error_flag, cudaStream_t stream) {
-    return gemm_dispatch<float, 0>(A, W, C, M, N, K, lda, ldc, splits, plain_epilogue(), error_flag, stream);
-}
-// C[M, N / 2] = silu(gate) * up, where W's N rows come in groups of 8 gate rows followed by their 8 up rows.
-KIRAI_EXPORT int kirai_gemm_bf16_swiglu(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc,
-                                        int splits, int* error_flag, cudaStream_t stream) {
-    return gemm_dispatch<bf16, 1>(A, W, C, M, N, K, lda, ldc, splits, plain_epilogue(), error_flag, stream);
-}
-
-// The same products for rows of A that an RMSNorm left unscaled: row m of the result is multiplied by
-// 1 / sqrt(sum_p row_sumsq[p][m] / row_count + row_eps).  out_f32 and swiglu choose the form of C as above.
-KIRAI_EXPORT int kirai_gemm_bf16_row_scaled(const void* A, const void* W, void* C, int M, int N, int K, long lda, long ldc,
-                                            int splits, int out_f32, int swiglu, const float* row_sumsq, int row_parts,
-                                            float row_count, float row_eps, int* error_flag, cudaStream_t stream) {
-    if (!row_sumsq || row_parts <= 0 || (out_f32 && swiglu)) return KIRAI_ERR_BAD_SIZE;
-    const Epilogue ep = scaled_epilogue(row_sumsq, row_parts, row_count, row_eps);
-    if (swiglu) return gemm_dispatch<bf16, 1>(A, W, C, M, N, K, lda, ldc, splits, ep, error_flag, stream);
-    if (out_f32) return gemm_dispatch<float, 0>(A, W, C, M, N, K, lda, ldc, splits, ep, error_flag, stream);
-    return gemm_dispatch<bf16, 0>(A, W, C, M, N, K, lda, ldc, splits, ep, error_flag, stream);
-}
-
-// How many parts kirai_gemm_bf16_residual_norm writes into sumsq_out for a product of this shape.
+// How many parts the residual-and-norm form writes into sumsq_out for a product of this shape.
 KIRAI_EXPORT int kirai_gemm_bf16_residual_parts(int M, int N) {
     if (M <= 64) return (N + GEMM_BM - 1) / GEMM_BM;
     return N <= 128 ? 1 : (N + 255) / 256;
 }
 
-// residual[M, N] (32-bit) += A W^T; next[M, N] = bf16(residual * norm_weight[n]), the unscaled input of the next
-// product; sumsq_out[parts][M] = each column tile's share of sum_n residual^2, which the next product turns into
-// the norm's scale through kirai_gemm_bf16_row_scaled.
-KIRAI_EXPORT int kirai_gemm_bf16_residual_norm(const void* A, const void* W, void* next, int M, int N, int K, long lda,
-                                               int splits, float* residual, const float* norm_weight, float* sumsq_out,
-                                               int* error_flag, cudaStream_t stream) {
-    if (!residual || !norm_weight || !sumsq_out) return KIRAI_ERR_BAD_SIZE;
-    const Epilogue ep{nullptr, 0, 1.0f, 0.0f, residual, norm_weight, sumsq_out};
-    return gemm_dispatch<bf16, 2>(A, W, next, M, N, K, lda, (long)N, splits, ep, error_flag, stream);
+// Bytes of the tiled form of a [N, K] weight matrix.
+KIRAI_EXPORT long kirai_gemm_bf16_tiled_bytes(int N, int K) {
+    return (long)((N + GEMM_BM - 1) / GEMM_BM) * ((K + GEMM_BK - 1) / GEMM_BK) * GEMM_BOX_BYTES;
+}
+
+// The one entry point of the tensor-core product, A[M, K] (row stride lda) times W[N, K] transposed.
+//   tiled:  W is in the tiled form described at the top of this file, else row-major.
+//   form 0: C[M, N] bf16.  1: C[M, N] float.  2: C[M, N / 2] = silu(gate) * up, W's rows in groups of 8 gate rows
+//           followed by their 8 up rows.  3: residual[M, N] (float, in place) += product, C[M, N] =
+//           bf16(residual * norm_weight[n]) and sumsq_out[parts][M] = each column tile's share of sum_n residual^2.
+//   row_sumsq (forms 0-2, may be null): the rows of A were left unscaled by an RMSNorm; row m of the product is
+//           multiplied by 1 / sqrt(sum_p row_sumsq[p][m] / row_count + row_eps).
+//   splits <= 0 picks the split-K count itself (at most 4).
+KIRAI_EXPORT int kirai_gemm_bf16_general(const void* A, const void* W, int tiled, void* C, int M, int N, int K, long lda,
+                                         long ldc, int splits, int form, const float* row_sumsq, int row_parts,
+                                         float row_count, float row_eps, float* residual, const float* norm_weight,
+                                         float* sumsq_out, int* error_flag, cudaStream_t stream) {
+    Epilogue ep{row_sumsq, row_sumsq ? row_parts : 0, row_count, row_eps, nullptr, nullptr, nullptr};
+    if (row_sumsq && row_parts <= 0) return KIRAI_ERR_BAD_SIZE;
+    switch (form) {
+        case 0: return gemm_dispatch<bf16, 0>(A, W, tiled != 0, C, M, N, K, lda, ldc, splits, ep, error_flag, stream);
+        case 1: return gemm_dispatch<float, 0>(A, W, tiled != 0, C, M, N, K, lda, ldc, splits, ep, error_flag, stream);
+        case 2: return gemm_dispatch<bf16, 1>(A, W, tiled != 0, C, M, N, K, lda, ldc, splits, ep, error_flag, stream);
+        case 3:
+            if (!residual || !norm_weight || !sumsq_out || row_sumsq) return KIRAI_ERR_BAD_SIZE;
+            ep.residual = residual, ep.norm_weight = norm_weight, ep.sumsq_out = sumsq_out;
+            return gemm_dispatch<bf16, 2>(A, W, tiled != 0, C, M, N, K, lda, (long)N, splits, ep, error_flag, stream);
+    }
+    return KIRAI_ERR_BAD_SIZE;
 }

@@ -114,13 +114,20 @@ def check_device_errors(device: torch.device) -> None:
 
 
 # ------------------------------------------------------------------- embedding
-def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Rows ``ids`` of ``table`` [V, H] widened to the 32-bit residual stream [T, H]."""
-    _need_cuda(table, ids)
-    assert table.dim() == 2 and table.is_contiguous() and ids.dtype == torch.int32 and ids.is_contiguous()
+def embedding(table, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rows ``ids`` of ``table`` [V, H] (a tensor, or a ``TiledWeight`` shared with the output head) widened to
+    the 32-bit residual stream [T, H]."""
+    assert ids.dtype == torch.int32 and ids.is_contiguous()
     tokens, hidden = ids.numel(), table.shape[1]
     if out is None:
         out = torch.empty((tokens, hidden), dtype=torch.float32, device=table.device)
+    if isinstance(table, TiledWeight):
+        _need_cuda(table.boxes, ids)
+        _call("kirai_embedding_tiled_bf16", _ptr(table.boxes), _ptr(ids), _ptr(out), _i(tokens), _i(hidden),
+              _i(table.shape[0]), _ptr(error_flag(table.device)), _stream())
+        return out
+    _need_cuda(table, ids)
+    assert table.dim() == 2 and table.is_contiguous()
     _call(f"kirai_embedding_{_suffix(table.dtype)}", _ptr(table), _ptr(ids), _ptr(out), _i(tokens), _i(hidden),
           _i(table.shape[0]), _ptr(error_flag(table.device)), _stream())
     return out
@@ -348,58 +355,116 @@ def linear_plain(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torc
     return out
 
 
-def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+class TiledWeight:
+    """A bf16 weight matrix [N, K] in the layout that the tensor-core product streams fastest: boxes of 128 rows
+    x 64 columns, each stored as the 16 KB image that the 128-byte swizzle leaves in shared memory (the 16-byte
+    chunk c of row r at chunk c ^ (r % 8)), box (row tile, k block) at index row_tile * ceil(K / 64) + k_block,
+    zero-padded at the edges.  One box is one contiguous bulk copy."""
+
+    def __init__(self, boxes: torch.Tensor, rows: int, cols: int):
+        self.boxes, self.rows, self.cols = boxes, rows, cols
+
+    @property
+    def shape(self):
+        return (self.rows, self.cols)
+
+    @property
+    def device(self):
+        return self.boxes.device
+
+    def row_major(self) -> torch.Tensor:
+        """The matrix back in rows (for tests and for kernels that do not read boxes)."""
+        row_tiles, k_blocks = self.boxes.shape[:2]
+        chunks = self.boxes.view(row_tiles, k_blocks, 128, 8, 8)
+        plain = chunks[:, :, torch.arange(128, device=self.device)[:, None], _swizzle_index(self.device), :]
+        plain = plain.reshape(row_tiles, k_blocks, 128, 64).permute(0, 2, 1, 3).reshape(row_tiles * 128, k_blocks * 64)
+        return plain[: self.rows, : self.cols].contiguous()
+
+
+def _swizzle_index(device) -> torch.Tensor:
+    """[128, 8]: where chunk c of row r lies under the 128-byte swizzle (an involution)."""
+    rows = torch.arange(128, device=device)[:, None]
+    return torch.arange(8, device=device)[None, :] ^ (rows % 8)
+
+
+def tile_weight(weight: torch.Tensor) -> TiledWeight:
+    """Re-packs a bf16 matrix [N, K] on the device into the tiled layout (done once, at load)."""
+    _need_cuda(weight)
+    assert weight.dim() == 2 and weight.dtype == torch.bfloat16
+    n, k = weight.shape
+    row_tiles, k_blocks = (n + 127) // 128, (k + 63) // 64
+    if row_tiles * 128 != n or k_blocks * 64 != k:
+        padded = torch.zeros((row_tiles * 128, k_blocks * 64), dtype=weight.dtype, device=weight.device)
+        padded[:n, :k] = weight
+    else:
+        padded = weight
+    boxes = padded.view(row_tiles, 128, k_blocks, 8, 8).permute(0, 2, 1, 3, 4)  # [row tile, k block, row, chunk, 8]
+    boxes = boxes[:, :, torch.arange(128, device=weight.device)[:, None], _swizzle_index(weight.device), :]
+    boxes = boxes.reshape(row_tiles, k_blocks, 128 * 64).contiguous()
+    tiled_bytes = library().kirai_gemm_bf16_tiled_bytes
+    tiled_bytes.restype = ctypes.c_long
+    assert boxes.numel() * 2 == int(tiled_bytes(_i(n), _i(k)))
+    return TiledWeight(boxes, n, k)
+
+
+def _gemm(x, weight, out, n: int, k: int, width: int, splits: int, form: int, row_scale, resid, norm_weight, sumsq_out):
+    tiled = isinstance(weight, TiledWeight)
+    if row_scale is not None:
+        sumsq, count, eps = row_scale
+        assert sumsq.dtype == torch.float32 and sumsq.dim() == 2 and sumsq.shape[1] == x.shape[0] and sumsq.is_contiguous()
+        scale_args = (_ptr(sumsq), _i(sumsq.shape[0]), _f(float(count)), _f(float(eps)))
+    else:
+        scale_args = (_ptr(None), _i(0), _f(1.0), _f(0.0))
+    _call("kirai_gemm_bf16_general", _ptr(x), _ptr(weight.boxes if tiled else weight), _i(tiled), _ptr(out), _i(x.shape[0]),
+          _i(n), _i(k), _l(x.stride(0)), _l(width), _i(splits), _i(form), *scale_args,
+          _ptr(resid), _ptr(norm_weight), _ptr(sumsq_out), _ptr(error_flag(x.device)), _stream())
+
+
+def _check_product(x, weight) -> tuple:
+    if isinstance(weight, TiledWeight):
+        _need_cuda(x, weight.boxes)
+    else:
+        _need_cuda(x, weight)
+        assert weight.dim() == 2 and weight.is_contiguous() and weight.dtype == torch.bfloat16
+    assert x.dim() == 2 and x.stride(1) == 1 and x.dtype == torch.bfloat16 and x.shape[1] == weight.shape[1]
+    return x.shape[0], x.shape[1], weight.shape[0]
+
+
+def linear_tcgen05(x: torch.Tensor, weight, out_dtype: Optional[torch.dtype] = None,
                    splits: int = 0, swiglu: bool = False, row_scale: Optional[tuple] = None) -> torch.Tensor:
     """bf16 ``x`` [M, K] times ``weight`` [N, K] transposed on the tcgen05 tensor cores (32-bit accumulation).
 
-    K and the row stride of ``x`` must be multiples of 8 (TMA reads rows in 16-byte units).
-    ``splits`` > 1 cuts K between the CTAs of a cluster (0: chosen from the shape, at most 4).
-    With ``swiglu`` the rows of ``weight`` are 8 gate rows, their 8 up rows, 8 gate rows, ... and
-    the result is silu(gate) * up, [M, N / 2].
-    ``row_scale`` = (sumsq [P, M] float32, count, eps) multiplies row m of the product by
-    1 / sqrt(sum_p sumsq[p, m] / count + eps): ``x`` then holds rows that an RMSNorm left unscaled.
+    ``weight`` is a row-major tensor or a ``TiledWeight``.  K and the row stride of ``x`` must be multiples of 8
+    (TMA reads rows in 16-byte units).  ``splits`` > 1 cuts K between the CTAs of a cluster (0: chosen from the
+    shape, at most 4).  With ``swiglu`` the rows of ``weight`` are 8 gate rows, their 8 up rows, 8 gate rows, ...
+    and the result is silu(gate) * up, [M, N / 2].  ``row_scale`` = (sumsq [P, M] float32, count, eps) multiplies
+    row m of the product by 1 / sqrt(sum_p sumsq[p, m] / count + eps): ``x`` then holds rows that an RMSNorm left
+    unscaled.
     """
-    _need_cuda(x, weight)
-    assert x.dim() == 2 and x.stride(1) == 1 and weight.dim() == 2 and weight.is_contiguous()
-    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[1] == weight.shape[1]
+    m, k, n = _check_product(x, weight)
     out_dtype = out_dtype or torch.bfloat16
-    m, k, n = x.shape[0], x.shape[1], weight.shape[0]
     if swiglu:
         assert out_dtype == torch.bfloat16 and n % 16 == 0
     width = n // 2 if swiglu else n
     out = torch.empty((m, width), dtype=out_dtype, device=x.device)
-    if row_scale is not None:
-        sumsq, count, eps = row_scale
-        assert sumsq.dtype == torch.float32 and sumsq.dim() == 2 and sumsq.shape[1] == m and sumsq.is_contiguous()
-        _call("kirai_gemm_bf16_row_scaled", _ptr(x), _ptr(weight), _ptr(out), _i(m), _i(n), _i(k), _l(x.stride(0)),
-              _l(width), _i(splits), _i(out_dtype == torch.float32), _i(swiglu), _ptr(sumsq), _i(sumsq.shape[0]),
-              _f(float(count)), _f(float(eps)), _ptr(error_flag(x.device)), _stream())
-        return out
-    if swiglu:
-        name = "kirai_gemm_bf16_swiglu"
-    else:
-        name = "kirai_gemm_bf16" if out_dtype == torch.bfloat16 else "kirai_gemm_bf16_out_f32"
-    _call(name, _ptr(x), _ptr(weight), _ptr(out), _i(m), _i(n), _i(k), _l(x.stride(0)), _l(width), _i(splits),
-          _ptr(error_flag(x.device)), _stream())
+    form = 2 if swiglu else (0 if out_dtype == torch.bfloat16 else 1)
+    _gemm(x, weight, out, n, k, width, splits, form, row_scale, None, None, None)
     return out
 
 
-def linear_residual_norm(x: torch.Tensor, weight: torch.Tensor, resid: torch.Tensor, norm_weight: torch.Tensor,
+def linear_residual_norm(x: torch.Tensor, weight, resid: torch.Tensor, norm_weight: torch.Tensor,
                          splits: int = 0) -> tuple:
     """``resid`` [M, N] (float32, in place) += ``x`` [M, K] times ``weight`` [N, K] transposed, on the tensor cores;
     returns (bf16(resid * norm_weight) [M, N], sumsq [P, M]): the rows of the next RMSNorm without their
     1 / rms factor, and the parts of each row's sum of squares, which ``linear_tcgen05(row_scale=...)`` applies."""
-    _need_cuda(x, weight, resid, norm_weight)
-    assert x.dim() == 2 and x.stride(1) == 1 and weight.dim() == 2 and weight.is_contiguous()
-    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[1] == weight.shape[1]
-    m, k, n = x.shape[0], x.shape[1], weight.shape[0]
+    m, k, n = _check_product(x, weight)
+    _need_cuda(resid, norm_weight)
     assert resid.dtype == torch.float32 and resid.shape == (m, n) and resid.is_contiguous()
     assert norm_weight.dtype == torch.float32 and norm_weight.shape == (n,) and norm_weight.is_contiguous()
     parts = int(library().kirai_gemm_bf16_residual_parts(_i(m), _i(n)))
     rows = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
     sumsq = torch.empty((parts, m), dtype=torch.float32, device=x.device)
-    _call("kirai_gemm_bf16_residual_norm", _ptr(x), _ptr(weight), _ptr(rows), _i(m), _i(n), _i(k), _l(x.stride(0)),
-          _i(splits), _ptr(resid), _ptr(norm_weight), _ptr(sumsq), _ptr(error_flag(x.device)), _stream())
+    _gemm(x, weight, rows, n, k, n, splits, 3, None, resid, norm_weight, sumsq)
     return rows, sumsq
 
 
@@ -420,6 +485,8 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """The linear layer of the product path: 32-bit FMAs for float32; for bfloat16 the tcgen05
     kernel, or the CUDA-core kernel when K is not a multiple of 8 (TMA cannot read such rows)."""
+    if isinstance(weight, TiledWeight):
+        return linear_tcgen05(x if tcgen05_takes(x) else x.contiguous(), weight, out_dtype)
     if tcgen05_takes(x):
         return linear_tcgen05(x, weight, out_dtype)
     return linear_plain(x, weight, out_dtype)

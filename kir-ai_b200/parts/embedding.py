@@ -14,6 +14,17 @@ import torch
 from .base import Part, Runtime, WeightSpec
 
 
+def _table(weights, rt: Runtime, name: str, hidden_size: int):
+    """The table [V, H] on the device, one copy per stored tensor: in the tensor-core product's box layout
+    where that kernel takes it (bfloat16, H a multiple of 8; the embedding gathers rows from the boxes), else
+    row-major."""
+    if rt.dtype == torch.bfloat16 and hidden_size % 8 == 0:
+        def make():
+            return rt.ops.tile_weight(weights.stored(name).to(device=rt.device, dtype=rt.dtype))
+        return weights.shared((name, "boxes"), make)
+    return weights.on_device(name, rt.dtype)
+
+
 class Embedding(Part):
     def __init__(self, weight_name: str, vocab_size: int, hidden_size: int):
         self.weight_name, self.vocab_size, self.hidden_size = weight_name, vocab_size, hidden_size
@@ -24,7 +35,7 @@ class Embedding(Part):
 
     def load(self, weights, rt: Runtime) -> None:
         self.rt = rt
-        self.table = weights.on_device(self.weight_name, rt.dtype)
+        self.table = _table(weights, rt, self.weight_name, self.hidden_size)
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         """The 32-bit residual stream [T, H] that the blocks add into."""
@@ -43,7 +54,7 @@ class OutputHead(Part):
 
     def load(self, weights, rt: Runtime) -> None:
         self.rt = rt
-        self.weight = weights.on_device(self.weight_name, rt.dtype)
+        self.weight = _table(weights, rt, self.weight_name, self.hidden_size)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.rt.ops.linear(x, self.weight, torch.float32)

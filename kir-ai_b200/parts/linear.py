@@ -27,11 +27,10 @@ class Linear(Part):
 
     def load(self, weights, rt: Runtime) -> None:
         self.rt = rt
-        if len(self.sources) == 1:
-            self.weight = weights.on_device(self.sources[0][0], rt.dtype)
-        else:
-            parts = [weights.stored(name).to(device=rt.device, dtype=rt.dtype) for name, _ in self.sources]
-            self.weight = torch.cat(parts, dim=0).contiguous()
+        parts = [weights.stored(name).to(device=rt.device, dtype=rt.dtype) for name, _ in self.sources]
+        stacked = parts[0].contiguous() if len(parts) == 1 else torch.cat(parts, dim=0)
+        # the tensor-core product streams weights fastest from its own box layout (``ops.TiledWeight``)
+        self.weight = rt.ops.tile_weight(stacked) if self.on_tensor_cores() else stacked
 
     def forward(self, x, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         if isinstance(x, UnscaledNorm):

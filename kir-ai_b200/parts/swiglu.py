@@ -34,7 +34,7 @@ class SwiGLU(FeedForward):
             (gate_name, _), (up_name, _) = self.gate_up.sources
             gate = weights.stored(gate_name).to(device=rt.device, dtype=rt.dtype)
             up = weights.stored(up_name).to(device=rt.device, dtype=rt.dtype)
-            self.fused_weight = rt.ops.interleave_gate_up(gate, up)
+            self.fused_weight = rt.ops.tile_weight(rt.ops.interleave_gate_up(gate, up))
         else:
             self.gate_up.load(weights, rt)
 

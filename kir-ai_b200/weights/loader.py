@@ -71,6 +71,13 @@ class WeightSource:
             self._device_copies[key] = stored.to(device=self.device, dtype=dtype).contiguous()
         return self._device_copies[key]
 
+    def shared(self, key: tuple, make):
+        """What ``make()`` returns, made once per ``key`` and handed to every caller: parts that read the same
+        stored tensor in the same derived form (a tied table in a kernel's own layout) hold one copy."""
+        if key not in self._device_copies:
+            self._device_copies[key] = make()
+        return self._device_copies[key]
+
     def forget(self) -> None:
         """Drops the bookkeeping (not the tensors that parts hold)."""
         self._device_copies.clear()

@@ -31,7 +31,7 @@ def rand(*shape, dtype=torch.float32, scale=1.0, seed=0):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("vocab,hidden", [(1000, 72), (257, 200)])
+@pytest.mark.parametrize("vocab,hidden", [(1000, 72), (257, 200), (130, 4104)])
 def test_embedding(ops, dtype, vocab, hidden):
     table = rand(vocab, hidden, dtype=dtype)
     ids = torch.tensor([0, vocab - 1, 5, 5, 17], dtype=torch.int32, device=DEV)
@@ -40,6 +40,12 @@ def test_embedding(ops, dtype, vocab, hidden):
     ops.embedding(table, torch.tensor([vocab], dtype=torch.int32, device=DEV))
     with pytest.raises(ops.KernelError):
         ops.check_device_errors(torch.device(DEV))
+    if dtype == torch.bfloat16:  # the gather from the tensor-core product's box layout
+        boxes = ops.tile_weight(table)
+        assert torch.equal(ops.embedding(boxes, ids), out)
+        ops.embedding(boxes, torch.tensor([-1], dtype=torch.int32, device=DEV))
+        with pytest.raises(ops.KernelError):
+            ops.check_device_errors(torch.device(DEV))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -136,6 +142,14 @@ def test_linear_tcgen05_against_plain(ops, m, n, k, out_dtype):
     wide[:, :k] = x
     strided = ops.linear_tcgen05(wide[:, :k], w, out_dtype)
     assert torch.equal(strided, out)
+    # the same weights cut into boxes at load: the same products in the same order, bit for bit
+    tiled = ops.tile_weight(w)
+    assert tiled.shape == (n, k) and torch.equal(tiled.row_major(), w)
+    assert torch.equal(ops.linear_tcgen05(x, tiled, out_dtype), out)
+    if m <= 64:
+        assert torch.equal(ops.linear_tcgen05(x, tiled, out_dtype, splits=3), split)
+    assert torch.equal(ops.linear(wide[:, :k], tiled, out_dtype), out)
+    ops.check_device_errors(torch.device(DEV))
 
 
 def test_linear_refuses_rows_that_tma_cannot_read(ops):
@@ -389,6 +403,8 @@ def test_linear_swiglu_epilogue(ops, m, inter, k, splits):
     assert float((out.float() - expected).abs().max()) <= 1e-2 * float(expected.abs().max())
     separate = ops.swiglu(ops.linear_tcgen05(x, torch.cat([gate, up])))  # rounds gate and up to bf16 in between
     assert float((out.float() - separate.float()).abs().max()) <= 2e-2 * float(expected.abs().max())
+    assert torch.equal(ops.linear_tcgen05(x, ops.tile_weight(weight), splits=splits, swiglu=True), out)
+    ops.check_device_errors(torch.device(DEV))
 
 
 @pytest.mark.parametrize("m,n,k,splits", [(1, 128, 64, 0), (5, 200, 136, 0), (16, 1000, 512, 3), (40, 520, 1032, 4),
@@ -410,6 +426,9 @@ def test_linear_residual_norm_epilogue_and_row_scaled_products(ops, m, n, k, spl
     assert sumsq.shape[1] == m
     total = (stream ** 2).sum(1)
     assert float(((sumsq.double().sum(0) - total) / total).abs().max()) <= 1e-5
+    again = before.clone()
+    rows_tiled, sumsq_tiled = ops.linear_residual_norm(x, ops.tile_weight(w), again, norm_weight, splits)
+    assert torch.equal(rows_tiled, rows) and torch.equal(sumsq_tiled, sumsq) and torch.equal(again, resid)
     # the products that follow: plain (both output types) and with the SwiGLU epilogue
     normed = unscaled * torch.rsqrt((stream ** 2).mean(1, keepdim=True) + eps)
     width = 272
