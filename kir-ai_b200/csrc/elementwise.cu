@@ -471,6 +471,151 @@ qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_we
     }
 }
 
+// The same work for head sizes that are multiples of 4, which is every size in steps of 16: each lane holds
+// adjacent pairs (2i, 2i + 1) of both halves, so that loads and stores are 4 bytes wide in bf16 (8 in float), and a
+// warp has the loads of four heads in flight before it computes the first.  Many tokens make this kernel a
+// pure stream over q, k, v and the cache rows; with 2-byte accesses and one head at a time it ran at a quarter
+// of the memory rate.
+template <typename T> struct Pair;
+template <> struct Pair<float> {
+    using type = float2;
+    static __device__ __forceinline__ float2 widen(float2 v) { return v; }
+    static __device__ __forceinline__ float2 narrow(float a, float b) { return make_float2(a, b); }
+};
+template <> struct Pair<bf16> {
+    using type = __nv_bfloat162;
+    static __device__ __forceinline__ float2 widen(__nv_bfloat162 v) { return __bfloat1622float2(v); }
+    static __device__ __forceinline__ __nv_bfloat162 narrow(float a, float b) { return __floats2bfloat162_rn(a, b); }
+};
+#define FUSED_UNROLL 4
+
+// SLOTS: pairs per lane and half, 1 for head sizes up to 128, 2 up to 256, 4 up to 512 (the loops are unrolled over it).
+template <typename T, int SLOTS>
+__global__ void __launch_bounds__(FUSED_WARPS * 32)
+qk_norm_rope_kv_write_vec_kernel(T* __restrict__ qkv, const float* __restrict__ q_weight,
+                                 const float* __restrict__ k_weight, const float* __restrict__ inv_freq,
+                                 T* __restrict__ cache, const int* __restrict__ block_table,
+                                 const int* __restrict__ request_of_token, const int* __restrict__ positions, int rows,
+                                 int q_heads, int kv_heads, int head_dim, float eps, int page_size, int table_width,
+                                 int num_pages, int write_cache, int* __restrict__ error_flag) {
+    using P = typename Pair<T>::type;
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float cos_s[32 * FUSED_MAX_PAIRS], sin_s[32 * FUSED_MAX_PAIRS];
+    const int heads_total = q_heads + 2 * kv_heads;
+    const int row = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int pos = positions[row];
+    const int half_dim = head_dim >> 1, half_pairs = head_dim >> 2;  // pairs of adjacent values in one half
+    if (inv_freq) {
+        for (int i = threadIdx.x; i < half_dim; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sin_s[i], &cos_s[i]);
+        __syncthreads();
+    }
+    int page = -1;
+    if (write_cache) {
+        const int logical = pos / page_size;
+        page = logical < table_width ? block_table[(long)request_of_token[row] * table_width + logical] : -1;
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicExch(error_flag, 2);
+            page = -1;
+        }
+    }
+    const int slot_in_page = pos % page_size;
+    const int stride = gridDim.y * FUSED_WARPS;  // warps that share this token's heads
+    for (int base = blockIdx.y * FUSED_WARPS + warp; base < heads_total; base += stride * FUSED_UNROLL) {
+        P lo[FUSED_UNROLL][SLOTS], hi[FUSED_UNROLL][SLOTS];
+#pragma unroll
+        for (int u = 0; u < FUSED_UNROLL; ++u) {
+            const int head = base + u * stride;
+            if (head >= heads_total) break;
+            const P* x = reinterpret_cast<const P*>(qkv + (size_t)row * heads_total * head_dim + (size_t)head * head_dim);
+#pragma unroll
+            for (int j = 0; j < SLOTS; ++j) {
+                const int i = lane + 32 * j;
+                if (i < half_pairs) {
+                    lo[u][j] = x[i];
+                    hi[u][j] = x[i + half_pairs];
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < FUSED_UNROLL; ++u) {
+            const int head = base + u * stride;
+            if (head >= heads_total) break;
+            P* x = reinterpret_cast<P*>(qkv + (size_t)row * heads_total * head_dim + (size_t)head * head_dim);
+            const bool is_q = head < q_heads;
+            const bool is_k = !is_q && head < q_heads + kv_heads;
+            const int kv_head = is_q ? 0 : (is_k ? head - q_heads : head - q_heads - kv_heads);
+            P* dst = nullptr;
+            if (!is_q && write_cache) {
+                if (page < 0) continue;
+                dst = reinterpret_cast<P*>(cache + kv_row_offset(page, is_k ? 0 : 1, kv_head, slot_in_page, kv_heads, page_size, head_dim));
+            }
+            if (!is_q && !is_k) {  // value head: plain copy
+                if (dst) {
+#pragma unroll
+                    for (int j = 0; j < SLOTS; ++j) {
+                        const int i = lane + 32 * j;
+                        if (i < half_pairs) {
+                            dst[i] = lo[u][j];
+                            dst[i + half_pairs] = hi[u][j];
+                        }
+                    }
+                }
+                continue;
+            }
+            float2 a[SLOTS], b[SLOTS];
+            float acc = 0.0f;
+#pragma unroll
+            for (int j = 0; j < SLOTS; ++j) {
+                a[j] = b[j] = make_float2(0.0f, 0.0f);
+                if (lane + 32 * j < half_pairs) {
+                    a[j] = Pair<T>::widen(lo[u][j]);
+                    b[j] = Pair<T>::widen(hi[u][j]);
+                    acc = fmaf(a[j].x, a[j].x, acc);
+                    acc = fmaf(b[j].x, b[j].x, acc);
+                    acc = fmaf(a[j].y, a[j].y, acc);
+                    acc = fmaf(b[j].y, b[j].y, acc);
+                }
+            }
+            const float* weight = is_q ? q_weight : k_weight;
+            float scale = 1.0f;
+            if (weight) {
+                acc = warp_sum(acc);
+                const float variance = acc / (float)head_dim + eps;
+                scale = variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
+            }
+#pragma unroll
+            for (int j = 0; j < SLOTS; ++j) {
+                const int i = lane + 32 * j;
+                if (i < half_pairs) {
+                    float2 va = a[j], vb = b[j];
+                    if (weight) {
+                        const float2 wa = *reinterpret_cast<const float2*>(weight + 2 * i);
+                        const float2 wb = *reinterpret_cast<const float2*>(weight + 2 * i + half_dim);
+                        va.x = va.x * scale * wa.x, va.y = va.y * scale * wa.y;
+                        vb.x = vb.x * scale * wb.x, vb.y = vb.y * scale * wb.y;
+                    }
+                    if (inv_freq) {  // the rotation pairs value e of the first half with e + head_dim / 2
+                        const float c0 = cos_s[2 * i], s0 = sin_s[2 * i], c1 = cos_s[2 * i + 1], s1 = sin_s[2 * i + 1];
+                        const float ax = va.x * c0 - vb.x * s0, bx = vb.x * c0 + va.x * s0;
+                        const float ay = va.y * c1 - vb.y * s1, by = vb.y * c1 + va.y * s1;
+                        va = make_float2(ax, ay);
+                        vb = make_float2(bx, by);
+                    }
+                    const P pa = Pair<T>::narrow(va.x, va.y), pb = Pair<T>::narrow(vb.x, vb.y);
+                    x[i] = pa;
+                    x[i + half_pairs] = pb;
+                    if (dst) {
+                        dst[i] = pa;
+                        dst[i + half_pairs] = pb;
+                    }
+                }
+            }
+        }
+    }
+}
+
 template <typename T>
 static int qk_norm_rope_kv_write_launch(void* qkv, const float* q_weight, const float* k_weight, const float* inv_freq,
                                         void* cache, const int* block_table, const int* request_of_token,
@@ -483,6 +628,16 @@ static int qk_norm_rope_kv_write_launch(void* qkv, const float* q_weight, const 
     if (rows > 65535 * 1024) return KIRAI_ERR_BAD_SIZE;
     const int heads_total = q_heads + 2 * kv_heads;
     const int head_blocks = rows >= 1024 ? 1 : (heads_total + FUSED_WARPS - 1) / FUSED_WARPS;
+    const bool pairs_aligned = head_dim % 4 == 0 && ((uintptr_t)qkv & 7) == 0 && ((uintptr_t)cache & 7) == 0 &&
+                               ((uintptr_t)q_weight & 7) == 0 && ((uintptr_t)k_weight & 7) == 0;
+#define KIRAI_FUSED_VEC(SLOTS)                                                                                          \
+    return launch_pdl(qk_norm_rope_kv_write_vec_kernel<T, SLOTS>, dim3(rows, head_blocks), dim3(FUSED_WARPS * 32), 0, stream, \
+                      1u, (T*)qkv, q_weight, k_weight, inv_freq, (T*)cache, block_table, request_of_token, positions, rows, \
+                      q_heads, kv_heads, head_dim, eps, page_size, table_width, num_pages, write_cache, error_flag)
+    if (pairs_aligned && head_dim <= 128) KIRAI_FUSED_VEC(1);
+    if (pairs_aligned && head_dim <= 256) KIRAI_FUSED_VEC(2);
+    if (pairs_aligned) KIRAI_FUSED_VEC(4);
+#undef KIRAI_FUSED_VEC
     return launch_pdl(qk_norm_rope_kv_write_kernel<T>, dim3(rows, head_blocks), dim3(FUSED_WARPS * 32), 0, stream, 1u, (T*)qkv, q_weight,
                       k_weight, inv_freq, (T*)cache, block_table, request_of_token, positions, rows, q_heads, kv_heads,
                       head_dim, rotary_dim, eps, page_size, table_width, num_pages, write_cache, error_flag);
