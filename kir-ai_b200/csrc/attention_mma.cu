@@ -540,7 +540,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
                         int page_size, int box_rows, int table_width, int num_pages, int window, float scale_log2,
                         int num_splits, int* __restrict__ error_flag) {
     pdl_launch_dependents();
-    pdl_wait();
     using Smem = DecodeSmem<D>;
     constexpr int BN = Smem::BN;
     constexpr int DC_WARPS = Smem::DC_WARPS;
@@ -569,18 +568,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
         for (int s = 0; s < DC_STAGES; ++s) sm100::mbar_init(sm100::smem_addr(&bars[s]), 1);
         sm100::mbar_fence_init();
     }
-    // the query rows (the group's heads), zero beyond the group and beyond head_dim
-    {
-        constexpr int CH = D / 8;
-        const int chunks_used = head_dim / 8;
-        for (int id = tid; id < 16 * CH; id += DC_WARPS * 32) {
-            const int r = id / CH, chunk = id % CH;
-            uint4 value = make_uint4(0u, 0u, 0u, 0u);
-            if (r < group && chunk < chunks_used)
-                value = *reinterpret_cast<const uint4*>(q + (size_t)req * q_row_stride + (size_t)(kv_head * group + r) * head_dim + chunk * 8);
-            *reinterpret_cast<uint4*>(smem + tile_offset<16>(r, chunk)) = value;
-        }
-    }
     __syncthreads();
 
     // The pages of this CTA's keys: copied to shared memory once, because a lookup in global memory
@@ -607,6 +594,31 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
     // this warp's tiles: t_begin + warp, + DC_WARPS, ...; the ring runs DC_STAGES - 1 tiles ahead
     const int my_first = t_begin + warp;
     const int my_count = my_first < t_end ? (t_end - my_first + DC_WARPS - 1) / DC_WARPS : 0;
+    // Everything up to here read only what is constant during a step (context lengths, block tables).  Keys and
+    // values of earlier steps are constant too: the first tiles of the ring are fetched before the kernel before
+    // this one has finished, all but the request's last tile, which holds the token that this step appends.
+    uint32_t early = 0u;
+    for (int k = 0; k < DC_STAGES - 1 && k < my_count; ++k) {
+        if (my_first + k * DC_WARPS < last_tile) {
+            issue(my_first + k * DC_WARPS, k);
+            early |= 1u << k;
+        }
+    }
+    pdl_wait();  // the queries, and the new token's key and value, are complete and visible
+    // the query rows (the group's heads), zero beyond the group and beyond head_dim
+    {
+        constexpr int CH = D / 8;
+        const int chunks_used = head_dim / 8;
+        for (int id = tid; id < 16 * CH; id += DC_WARPS * 32) {
+            const int r = id / CH, chunk = id % CH;
+            uint4 value = make_uint4(0u, 0u, 0u, 0u);
+            if (r < group && chunk < chunks_used)
+                value = *reinterpret_cast<const uint4*>(q + (size_t)req * q_row_stride + (size_t)(kv_head * group + r) * head_dim + chunk * 8);
+            *reinterpret_cast<uint4*>(smem + tile_offset<16>(r, chunk)) = value;
+        }
+    }
+    __syncthreads();
+
     constexpr int MS = D + 2;
     if (HEADS) {
         // B-operand fragments of Q^T: (dims 16 kk + 2t, + 1 and + 8; head g), read once
@@ -621,7 +633,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
         }
         HeadState<D> st;
         st.init();
-        for (int k = 0; k < DC_STAGES - 1 && k < my_count; ++k) issue(my_first + k * DC_WARPS, k);
+        for (int k = 0; k < DC_STAGES - 1 && k < my_count; ++k)
+            if (!((early >> k) & 1u)) issue(my_first + k * DC_WARPS, k);
         for (int k = 0; k < my_count; ++k) {
             const int ahead = k + DC_STAGES - 1;
             if (ahead < my_count) issue(my_first + ahead * DC_WARPS, ahead % DC_STAGES);
@@ -672,7 +685,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
     }
     WarpState<D> st;
     st.init();
-    for (int k = 0; k < DC_STAGES - 1 && k < my_count; ++k) issue(my_first + k * DC_WARPS, k);
+    for (int k = 0; k < DC_STAGES - 1 && k < my_count; ++k)
+            if (!((early >> k) & 1u)) issue(my_first + k * DC_WARPS, k);
     for (int k = 0; k < my_count; ++k) {
         const int ahead = k + DC_STAGES - 1;
         if (ahead < my_count) issue(my_first + ahead * DC_WARPS, ahead % DC_STAGES);

@@ -388,7 +388,8 @@ qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_we
                                              int head_dim, int rotary_dim, float eps, int page_size, int table_width,
                                              int num_pages, int write_cache, int* __restrict__ error_flag) {
     pdl_launch_dependents();
-    pdl_wait();
+    // positions, the request of each token and the block tables are constant during a step: the angles and the
+    // page are worked out before the kernel before this one (the q, k, v product) has finished
     __shared__ float cos_s[32 * FUSED_MAX_PAIRS], sin_s[32 * FUSED_MAX_PAIRS];
     const int heads_total = q_heads + 2 * kv_heads;
     const int row = blockIdx.x;
@@ -408,6 +409,7 @@ qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_we
             page = -1;
         }
     }
+    pdl_wait();
     // with few tokens the heads are spread over gridDim.y blocks, so that enough blocks run at once
     for (int head = blockIdx.y * FUSED_WARPS + warp; head < heads_total; head += gridDim.y * FUSED_WARPS) {
         T* x = qkv + (size_t)row * heads_total * head_dim + (size_t)head * head_dim;
@@ -500,7 +502,8 @@ qk_norm_rope_kv_write_vec_kernel(T* __restrict__ qkv, const float* __restrict__ 
                                  int num_pages, int write_cache, int* __restrict__ error_flag) {
     using P = typename Pair<T>::type;
     pdl_launch_dependents();
-    pdl_wait();
+    // positions, the request of each token and the block tables are constant during a step: the angles and the
+    // page are worked out before the kernel before this one (the q, k, v product) has finished
     __shared__ float cos_s[32 * FUSED_MAX_PAIRS], sin_s[32 * FUSED_MAX_PAIRS];
     const int heads_total = q_heads + 2 * kv_heads;
     const int row = blockIdx.x;
@@ -520,6 +523,7 @@ qk_norm_rope_kv_write_vec_kernel(T* __restrict__ qkv, const float* __restrict__ 
             page = -1;
         }
     }
+    pdl_wait();
     const int slot_in_page = pos % page_size;
     const int stride = gridDim.y * FUSED_WARPS;  // warps that share this token's heads
     for (int base = blockIdx.y * FUSED_WARPS + warp; base < heads_total; base += stride * FUSED_UNROLL) {
