@@ -524,55 +524,49 @@ struct DecodeSmem {
     static constexpr int merge_bytes = DC_WARPS * 16 * (D + 2) * 4;
     static constexpr int body = q_bytes + (ring_bytes > merge_bytes ? ring_bytes : merge_bytes);
     static constexpr int table_entries = 1024;  // block-table entries kept in shared memory (longer ranges read global memory)
-    static constexpr int total = body + DC_WARPS * DC_STAGES * 8 + table_entries * 4 + 1024;  // + barriers, + slack to align to 1024
+    static constexpr int prefix_entries = 1025;  // balanced kernel: where each request's tiles start (up to 1,024 requests)
+    static constexpr int total = body + DC_WARPS * DC_STAGES * 8 + table_entries * 4 + prefix_entries * 4 + 1024;  // + barriers, + slack to align to 1024
 };
 
-// partial: [requests, q_heads, splits, head_dim + 2] floats: unnormalised output, then max (log2 domain), then sum.
-// kv_map: the cache layer as a 2-D bf16 matrix [num_pages * 2 * kv_heads * page_size, head_dim], boxes of
-// [box_rows, 64] with the 128-byte swizzle; box_rows = min(page_size, BN) and divides BN.
-// HEADS: the group has at most 8 heads and they are the MMA's columns (keys fill its rows);
-// otherwise the group's (at most 16) heads are the rows, as in the prompt kernel.
+// What a decode CTA needs to attend one range of key tiles of one (request, kv head).
+struct DecodeArgs {
+    const bf16* q;
+    const int* block_table;
+    int q_heads, kv_heads, head_dim;
+    long q_row_stride;
+    int page_size, box_rows, table_width, num_pages, window;
+    float scale_log2;
+    int* error_flag;
+};
+
+// The CTA's warps attend key tiles [t_begin, t_end) of (req, kv_head) for the query at position pos (the keys from
+// key_lo on; last_tile holds pos) and merge their states.  The result for the group's heads goes, unnormalised with
+// its maximum and sum, to dst_partial (row g at dst_partial + g * partial_stride: head_dim values, max, sum), or, if
+// dst_partial is null, normalised to `out`.  k_base: how many tiles this warp has put through its ring before (the
+// barriers' phases go on from there); the number for the next call is returned.  With `first` the call is the
+// CTA's first work: the tiles that earlier steps filled are requested before griddepcontrol.wait, the rest after.
 template <int D, bool HEADS>
-__global__ void __launch_bounds__(DecodeTile<D>::WARPS * 32)
-attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ q, bf16* __restrict__ out,
-                        float* __restrict__ partial, const int* __restrict__ block_table,
-                        const int* __restrict__ context_len, int q_heads, int kv_heads, int head_dim, long q_row_stride,
-                        int page_size, int box_rows, int table_width, int num_pages, int window, float scale_log2,
-                        int num_splits, int* __restrict__ error_flag) {
-    pdl_launch_dependents();
+__device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, const DecodeArgs& args, uint8_t* smem, int req,
+                                                   int kv_head, int pos, int key_lo, int last_tile, int t_begin, int t_end,
+                                                   int k_base, bool first, bf16* __restrict__ out,
+                                                   float* __restrict__ dst_partial, long partial_stride) {
     using Smem = DecodeSmem<D>;
     constexpr int BN = Smem::BN;
     constexpr int DC_WARPS = Smem::DC_WARPS;
     constexpr int PANELS = D / 64;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    const int split = blockIdx.x, kv_head = blockIdx.y, req = blockIdx.z;
+    const int q_heads = args.q_heads, kv_heads = args.kv_heads, head_dim = args.head_dim;
+    const int page_size = args.page_size, table_width = args.table_width;
+    const float scale_log2 = args.scale_log2;
     const int group = q_heads / kv_heads;  // <= 16 rows
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int ctx = context_len[req];
-    const int pos = ctx - 1;
-    const int key_lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int first_tile = key_lo / BN, last_tile = pos / BN;
-    const int tiles = last_tile - first_tile + 1;
-    const int per_split = (tiles + num_splits - 1) / num_splits;
-    const int t_begin = first_tile + split * per_split;
-    const int t_end = min(last_tile + 1, t_begin + per_split);
-
     const uint32_t q_smem = sm100::smem_addr(smem);
     const uint32_t ring = q_smem + Smem::q_bytes + warp * DC_STAGES * 2 * Smem::tile_bytes;
     uint64_t* bars = (uint64_t*)(smem + Smem::body) + warp * DC_STAGES;
     float* merge = reinterpret_cast<float*>(smem + Smem::q_bytes);  // [warps][16][D + 2], over the ring
 
-    if (tid == 0) sm100::tma_prefetch_descriptor(&kv_map);
-    if (lane == 0) {
-        for (int s = 0; s < DC_STAGES; ++s) sm100::mbar_init(sm100::smem_addr(&bars[s]), 1);
-        sm100::mbar_fence_init();
-    }
-    __syncthreads();
-
-    // The pages of this CTA's keys: copied to shared memory once, because a lookup in global memory
+    // The pages of this range's keys: copied to shared memory once, because a lookup in global memory
     // for every tile would put its latency in front of every TMA issue.
-    const int* table = block_table + (long)req * table_width;
+    const int* table = args.block_table + (long)req * table_width;
     {
         int* table_s = reinterpret_cast<int*>(smem + Smem::body + DC_WARPS * DC_STAGES * 8);
         const int first_page = (t_begin * BN) / page_size;
@@ -588,7 +582,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
     auto issue = [&](int t, int slot) {
         const uint32_t k_dst = ring + slot * 2 * Smem::tile_bytes;
         fill_kv_slot<BN, PANELS>(&kv_map, sm100::smem_addr(&bars[slot]), k_dst, k_dst + Smem::tile_bytes, t, pos, table,
-                                 table_width, num_pages, kv_heads, kv_head, page_size, box_rows, lane);
+                                 table_width, args.num_pages, kv_heads, kv_head, page_size, args.box_rows, lane);
     };
 
     // this warp's tiles: t_begin + warp, + DC_WARPS, ...; the ring runs DC_STAGES - 1 tiles ahead
@@ -598,13 +592,15 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
     // values of earlier steps are constant too: the first tiles of the ring are fetched before the kernel before
     // this one has finished, all but the request's last tile, which holds the token that this step appends.
     uint32_t early = 0u;
-    for (int k = 0; k < DC_STAGES - 1 && k < my_count; ++k) {
-        if (my_first + k * DC_WARPS < last_tile) {
-            issue(my_first + k * DC_WARPS, k);
-            early |= 1u << k;
+    if (first) {
+        for (int k = 0; k < DC_STAGES - 1 && k < my_count; ++k) {
+            if (my_first + k * DC_WARPS < last_tile) {
+                issue(my_first + k * DC_WARPS, (k_base + k) % DC_STAGES);
+                early |= 1u << k;
+            }
         }
+        pdl_wait();  // the queries, and the new token's key and value, are complete and visible
     }
-    pdl_wait();  // the queries, and the new token's key and value, are complete and visible
     // the query rows (the group's heads), zero beyond the group and beyond head_dim
     {
         constexpr int CH = D / 8;
@@ -613,7 +609,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
             const int r = id / CH, chunk = id % CH;
             uint4 value = make_uint4(0u, 0u, 0u, 0u);
             if (r < group && chunk < chunks_used)
-                value = *reinterpret_cast<const uint4*>(q + (size_t)req * q_row_stride + (size_t)(kv_head * group + r) * head_dim + chunk * 8);
+                value = *reinterpret_cast<const uint4*>(args.q + (size_t)req * args.q_row_stride + (size_t)(kv_head * group + r) * head_dim + chunk * 8);
             *reinterpret_cast<uint4*>(smem + tile_offset<16>(r, chunk)) = value;
         }
     }
@@ -634,12 +630,12 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
         HeadState<D> st;
         st.init();
         for (int k = 0; k < DC_STAGES - 1 && k < my_count; ++k)
-            if (!((early >> k) & 1u)) issue(my_first + k * DC_WARPS, k);
+            if (!((early >> k) & 1u)) issue(my_first + k * DC_WARPS, (k_base + k) % DC_STAGES);
         for (int k = 0; k < my_count; ++k) {
             const int ahead = k + DC_STAGES - 1;
-            if (ahead < my_count) issue(my_first + ahead * DC_WARPS, ahead % DC_STAGES);
-            const int slot = k % DC_STAGES;
-            if (!sm100::mbar_wait(sm100::smem_addr(&bars[slot]), (uint32_t)(k / DC_STAGES) & 1u)) {
+            if (ahead < my_count) issue(my_first + ahead * DC_WARPS, (k_base + ahead) % DC_STAGES);
+            const int slot = (k_base + k) % DC_STAGES;
+            if (!sm100::mbar_wait(sm100::smem_addr(&bars[slot]), (uint32_t)((k_base + k) / DC_STAGES) & 1u)) {
                 ok = false;
                 break;
             }
@@ -647,7 +643,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
             warp_attend_heads<D, BN>(st, q_b, k_s, k_s + Smem::tile_bytes, (my_first + k * DC_WARPS) * BN, key_lo, pos, scale_log2, lane);
             __syncwarp();
         }
-        if (!ok && lane == 0) atomicExch(error_flag, 4);
+        if (!ok && lane == 0) atomicExch(args.error_flag, 4);
         __syncthreads();  // every warp is done with its ring: it becomes the merge buffer
         const int g = lane >> 2, t = lane & 3;
 #pragma unroll
@@ -686,12 +682,12 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
     WarpState<D> st;
     st.init();
     for (int k = 0; k < DC_STAGES - 1 && k < my_count; ++k)
-            if (!((early >> k) & 1u)) issue(my_first + k * DC_WARPS, k);
+            if (!((early >> k) & 1u)) issue(my_first + k * DC_WARPS, (k_base + k) % DC_STAGES);
     for (int k = 0; k < my_count; ++k) {
         const int ahead = k + DC_STAGES - 1;
-        if (ahead < my_count) issue(my_first + ahead * DC_WARPS, ahead % DC_STAGES);
-        const int slot = k % DC_STAGES;
-        if (!sm100::mbar_wait(sm100::smem_addr(&bars[slot]), (uint32_t)(k / DC_STAGES) & 1u)) {
+        if (ahead < my_count) issue(my_first + ahead * DC_WARPS, (k_base + ahead) % DC_STAGES);
+        const int slot = (k_base + k) % DC_STAGES;
+        if (!sm100::mbar_wait(sm100::smem_addr(&bars[slot]), (uint32_t)((k_base + k) / DC_STAGES) & 1u)) {
             ok = false;
             break;
         }
@@ -700,7 +696,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
                                           scale_log2, lane);
         __syncwarp();
     }
-    if (!ok && lane == 0) atomicExch(error_flag, 4);
+    if (!ok && lane == 0) atomicExch(args.error_flag, 4);
     __syncthreads();  // every warp is done with its ring: it becomes the merge buffer
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -735,17 +731,205 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* 
             acc += src[col] * weight;
             l_all += src[D + 1] * weight;
         }
-        const int head = kv_head * group + row;
-        if (num_splits == 1) {
-            out[((size_t)req * q_heads + head) * head_dim + col] = from_f32<bf16>(l_all > 0.0f ? acc / l_all : 0.0f);
+        if (dst_partial == nullptr) {
+            out[((size_t)req * q_heads + kv_head * group + row) * head_dim + col] = from_f32<bf16>(l_all > 0.0f ? acc / l_all : 0.0f);
         } else {
-            float* dst = partial + (((size_t)req * q_heads + head) * num_splits + split) * (head_dim + 2);
+            float* dst = dst_partial + (size_t)row * partial_stride;
             dst[col] = acc;
             if (col == 0) {
                 dst[head_dim] = m_all;
                 dst[head_dim + 1] = l_all;
             }
         }
+    }
+    return k_base + my_count;
+}
+
+// One barrier per ring slot and warp; called by every thread before the first range.
+template <int D>
+__device__ __forceinline__ void decode_init_barriers(uint8_t* smem) {
+    using Smem = DecodeSmem<D>;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint64_t* bars = (uint64_t*)(smem + Smem::body) + warp * DC_STAGES;
+    if (lane == 0) {
+        for (int s = 0; s < DC_STAGES; ++s) sm100::mbar_init(sm100::smem_addr(&bars[s]), 1);
+        sm100::mbar_fence_init();
+    }
+    __syncthreads();
+}
+
+// partial: [requests, q_heads, splits, head_dim + 2] floats: unnormalised output, then max (log2 domain), then sum.
+// kv_map: the cache layer as a 2-D bf16 matrix [num_pages * 2 * kv_heads * page_size, head_dim], boxes of
+// [box_rows, 64] with the 128-byte swizzle; box_rows = min(page_size, BN) and divides BN.
+// HEADS: the group has at most 8 heads and they are the MMA's columns (keys fill its rows);
+// otherwise the group's (at most 16) heads are the rows, as in the prompt kernel.
+// Grid (splits, kv_heads, requests): every request's keys are cut into the same number of ranges.
+template <int D, bool HEADS>
+__global__ void __launch_bounds__(DecodeTile<D>::WARPS * 32)
+attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs args, bf16* __restrict__ out,
+                        float* __restrict__ partial, const int* __restrict__ context_len, int num_splits) {
+    pdl_launch_dependents();
+    constexpr int BN = DecodeSmem<D>::BN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int split = blockIdx.x, kv_head = blockIdx.y, req = blockIdx.z;
+    const int group = args.q_heads / args.kv_heads;
+    const int pos = context_len[req] - 1;
+    const int key_lo = args.window > 0 ? max(0, pos - args.window + 1) : 0;
+    const int first_tile = key_lo / BN, last_tile = pos / BN;
+    const int tiles = last_tile - first_tile + 1;
+    const int per_split = (tiles + num_splits - 1) / num_splits;
+    const int t_begin = first_tile + split * per_split;
+    const int t_end = min(last_tile + 1, t_begin + per_split);
+    if (threadIdx.x == 0) sm100::tma_prefetch_descriptor(&kv_map);
+    decode_init_barriers<D>(smem);
+    float* dst_partial = num_splits == 1 ? nullptr
+        : partial + (((size_t)req * args.q_heads + kv_head * group) * num_splits + split) * (args.head_dim + 2);
+    decode_attend_range<D, HEADS>(kv_map, args, smem, req, kv_head, pos, key_lo, last_tile, t_begin, t_end, 0, true, out,
+                                  dst_partial, (long)num_splits * (args.head_dim + 2));
+}
+
+// How the balanced kernel and its merge cut the work: the key tiles of all (request, kv head) pairs form one
+// sequence (requests in order, a request's kv heads one after the other), cut into equal ranges, one per CTA.
+#define DECODE_MAX_REQUESTS 1024
+
+// prefix[r] = tiles of one kv head of the requests before r, prefix[requests] = of all; computed by the whole block
+// (every thread loads its requests' lengths at once; a serial walk would pay a memory round trip per request).
+__device__ __forceinline__ void decode_tile_prefix(const int* __restrict__ context_len, int requests, int window,
+                                                   int tile_keys, int* prefix) {
+    for (int r = threadIdx.x; r < requests; r += blockDim.x) {
+        const int pos = context_len[r] - 1;
+        int tiles = 0;
+        if (pos >= 0) {
+            const int key_lo = window > 0 ? max(0, pos - window + 1) : 0;
+            tiles = pos / tile_keys - key_lo / tile_keys + 1;
+        }
+        prefix[r + 1] = tiles;
+    }
+    if (threadIdx.x == 0) prefix[0] = 0;
+    __syncthreads();
+    if (threadIdx.x < 32) {  // one warp scans: 32 requests per round
+        int carry = 0;
+        for (int base = 0; base < requests; base += 32) {
+            const int r = base + (int)threadIdx.x;
+            int value = r < requests ? prefix[r + 1] : 0;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int other = __shfl_up_sync(0xffffffffu, value, d);
+                if ((int)threadIdx.x >= d) value += other;
+            }
+            if (r < requests) prefix[r + 1] = carry + value;
+            carry += __shfl_sync(0xffffffffu, value, 31);
+        }
+    }
+    __syncthreads();
+}
+
+// Grid (ctas): CTA c attends tiles [c * per_cta, (c + 1) * per_cta) of the sequence above, one pair after the
+// other.  A pair that lies inside one CTA's range is finished there; a pair cut by a range border leaves a partial
+// result in slot 0 (the piece starts where the CTA's range starts) or 1 of its CTA,
+// partial[cta][slot][group row][head_dim + 2], which attention_merge_balanced_kernel adds up.  Whatever the batch
+// and the context lengths are, every CTA reads the same number of keys.
+template <int D, bool HEADS>
+__global__ void __launch_bounds__(DecodeTile<D>::WARPS * 32)
+attention_decode_balanced_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs args, bf16* __restrict__ out,
+                                 float* __restrict__ partial, const int* __restrict__ context_len, int requests) {
+    pdl_launch_dependents();
+    using Smem = DecodeSmem<D>;
+    constexpr int BN = Smem::BN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    int* prefix = reinterpret_cast<int*>(smem + Smem::body + Smem::DC_WARPS * DC_STAGES * 8 + Smem::table_entries * 4);
+    const int kv_heads = args.kv_heads, window = args.window;
+    if (threadIdx.x == 0) sm100::tma_prefetch_descriptor(&kv_map);
+    decode_tile_prefix(context_len, requests, window, BN, prefix);
+    const long total = (long)kv_heads * prefix[requests];
+    const long per_cta = (total + gridDim.x - 1) / gridDim.x;
+    const long begin = (long)blockIdx.x * per_cta, end = min(total, begin + per_cta);
+    decode_init_barriers<D>(smem);
+    bool first = true;
+    int k_base = 0;
+    // the first request with tiles in this CTA's range: the last r with kv_heads * prefix[r] <= begin
+    int req = 0;
+    {
+        int lo = 0, hi = requests;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if ((long)kv_heads * prefix[mid] <= begin) lo = mid; else hi = mid - 1;
+        }
+        req = lo;
+    }
+    for (; req < requests && begin < end; ++req) {
+        const long pair_begin = (long)kv_heads * prefix[req];
+        if (pair_begin >= end) break;
+        const int tiles = prefix[req + 1] - prefix[req];
+        if (tiles == 0) continue;
+        const int pos = context_len[req] - 1;
+        const int key_lo = window > 0 ? max(0, pos - window + 1) : 0;
+        const int first_tile = key_lo / BN, last_tile = pos / BN;
+        const int head_first = begin > pair_begin ? (int)((begin - pair_begin) / tiles) : 0;
+        for (int kv_head = head_first; kv_head < kv_heads; ++kv_head) {
+            const long start = pair_begin + (long)kv_head * tiles;
+            if (start >= end) break;
+            const long from = max(start, begin), to = min(start + tiles, end);
+            const bool whole = from == start && to == start + tiles;
+            float* dst_partial = whole ? nullptr
+                : partial + ((size_t)blockIdx.x * 2 + (from == begin ? 0 : 1)) * 16 * (args.head_dim + 2);
+            if (!first) __syncthreads();  // the merge buffer of the range before lies over the ring
+            k_base = decode_attend_range<D, HEADS>(kv_map, args, smem, req, kv_head, pos, key_lo, last_tile,
+                                                   first_tile + (int)(from - start), first_tile + (int)(to - start),
+                                                   k_base, first, out, dst_partial, (long)(args.head_dim + 2));
+            first = false;
+        }
+    }
+    if (first) pdl_wait();  // a CTA without work still orders itself after the kernel before it
+}
+
+// One block per (request, query head): adds up the pieces of a pair that more than one CTA of the balanced kernel
+// attended, in CTA order; a pair finished inside one CTA is left as that CTA wrote it.
+__global__ void __launch_bounds__(128)
+attention_merge_balanced_kernel(const float* __restrict__ partial, bf16* __restrict__ out,
+                                const int* __restrict__ context_len, int requests, int q_heads, int kv_heads,
+                                int head_dim, int window, int tile_keys, int ctas) {
+    pdl_launch_dependents();
+    __shared__ int prefix[DECODE_MAX_REQUESTS + 1];
+    __shared__ float warp_max[4];
+    const int req = blockIdx.x / q_heads, head = blockIdx.x % q_heads;
+    const int group = q_heads / kv_heads, kv_head = head / group, row = head % group;
+    decode_tile_prefix(context_len, requests, window, tile_keys, prefix);
+    const int my_tiles = prefix[req + 1] - prefix[req];
+    const long total = (long)kv_heads * prefix[requests];
+    const long start = (long)kv_heads * prefix[req] + (long)kv_head * my_tiles;
+    pdl_wait();
+    bf16* dst = out + ((size_t)req * q_heads + head) * head_dim;
+    if (my_tiles == 0) {
+        for (int col = threadIdx.x; col < head_dim; col += blockDim.x) dst[col] = from_f32<bf16>(0.0f);
+        return;
+    }
+    const long per_cta = (total + ctas - 1) / ctas;
+    const int c_first = (int)(start / per_cta), c_last = (int)((start + my_tiles - 1) / per_cta);
+    if (c_first == c_last) return;  // finished by its CTA
+    const int stride = head_dim + 2;
+    // piece of CTA c: slot 0 unless the pair starts inside that CTA's range (only c_first can)
+    const int first_slot = start == (long)c_first * per_cta ? 0 : 1;
+    auto piece = [&](int c) { return partial + (((size_t)c * 2 + (c == c_first ? first_slot : 0)) * 16 + row) * stride; };
+    float m_all = -INFINITY;
+    for (int c = c_first + (int)threadIdx.x; c <= c_last; c += blockDim.x) m_all = fmaxf(m_all, piece(c)[head_dim]);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, d));
+    if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m_all;
+    __syncthreads();
+    m_all = fmaxf(fmaxf(warp_max[0], warp_max[1]), fmaxf(warp_max[2], warp_max[3]));
+    for (int col = threadIdx.x; col < head_dim; col += blockDim.x) {
+        float acc = 0.0f, l_all = 0.0f;
+#pragma unroll 4
+        for (int c = c_first; c <= c_last; ++c) {
+            const float* src = piece(c);
+            const float weight = src[head_dim] == -INFINITY ? 0.0f : exp2f(src[head_dim] - m_all);
+            acc += src[col] * weight;
+            l_all += src[head_dim + 1] * weight;
+        }
+        dst[col] = from_f32<bf16>(l_all > 0.0f ? acc / l_all : 0.0f);
     }
 }
 
@@ -805,14 +989,38 @@ int decode_launch(const void* q, const void* cache, void* out, float* partial, c
     auto kernel = (q_heads / kv_heads <= 8) ? attention_decode_kernel<D, true> : attention_decode_kernel<D, false>;
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total);
     if (err != cudaSuccess) return (int)err;
+    const DecodeArgs args{(const bf16*)q, block_table, q_heads, kv_heads, head_dim, q_row_stride, page_size, box_rows,
+                          table_width, num_pages, window, scale * 1.4426950408889634f, error_flag};
     dim3 grid(num_splits, kv_heads, requests);
-    int status = launch_pdl(kernel, grid, dim3(Smem::DC_WARPS * 32), (size_t)Smem::total, stream, 1u, kv_map, (const bf16*)q,
-                            (bf16*)out, partial, block_table, context_len, q_heads, kv_heads, head_dim, q_row_stride,
-                            page_size, box_rows, table_width, num_pages, window, scale * 1.4426950408889634f,
-                            num_splits, error_flag);
+    int status = launch_pdl(kernel, grid, dim3(Smem::DC_WARPS * 32), (size_t)Smem::total, stream, 1u, kv_map, args,
+                            (bf16*)out, partial, context_len, num_splits);
     if (status || num_splits == 1) return status;
     return launch_pdl(attention_merge_splits_kernel, dim3(requests * q_heads), dim3(128), 0, stream, 1u,
                       (const float*)partial, (bf16*)out, head_dim, num_splits);
+}
+
+template <int D>
+int decode_balanced_launch(const void* q, const void* cache, void* out, float* partial, const int* block_table,
+                           const int* context_len, int requests, int q_heads, int kv_heads, int head_dim,
+                           long q_row_stride, int page_size, int table_width, int num_pages, int window, float scale,
+                           int ctas, int* error_flag, cudaStream_t stream) {
+    using Smem = DecodeSmem<D>;
+    const int box_rows = page_size < Smem::BN ? page_size : Smem::BN;
+    if (Smem::BN % box_rows != 0 || page_size % box_rows != 0) return KIRAI_ERR_UNSUPPORTED;  // page sizes: powers of two
+    CUtensorMap kv_map;
+    const uint64_t rows = (uint64_t)num_pages * 2 * kv_heads * page_size;
+    if (!tmap::bf16_2d_sw128(&kv_map, cache, rows, head_dim, head_dim, box_rows, 64)) return KIRAI_ERR_BAD_ALIGN;
+    auto kernel = (q_heads / kv_heads <= 8) ? attention_decode_balanced_kernel<D, true> : attention_decode_balanced_kernel<D, false>;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total);
+    if (err != cudaSuccess) return (int)err;
+    const DecodeArgs args{(const bf16*)q, block_table, q_heads, kv_heads, head_dim, q_row_stride, page_size, box_rows,
+                          table_width, num_pages, window, scale * 1.4426950408889634f, error_flag};
+    int status = launch_pdl(kernel, dim3(ctas), dim3(Smem::DC_WARPS * 32), (size_t)Smem::total, stream, 1u, kv_map, args,
+                            (bf16*)out, partial, context_len, requests);
+    if (status) return status;
+    return launch_pdl(attention_merge_balanced_kernel, dim3(requests * q_heads), dim3(128), 0, stream, 1u,
+                      (const float*)partial, (bf16*)out, context_len, requests, q_heads, kv_heads, head_dim, window,
+                      (int)Smem::BN, ctas);
 }
 
 int check_common(int q_heads, int kv_heads, int head_dim, long q_row_stride, const void* q) {
@@ -868,6 +1076,29 @@ KIRAI_EXPORT int kirai_attention_decode_bf16(const void* q, const void* cache, v
     if (head_dim <= 128) KIRAI_DC(128);
     KIRAI_DC(256);
 #undef KIRAI_DC
+}
+
+// The same with the work cut evenly: `ctas` CTAs (one per SM is the intent) each attend the same number of key
+// tiles, whatever the batch size and the context lengths are.  partial holds ctas * 2 * 16 * (head_dim + 2) floats.
+KIRAI_EXPORT int kirai_attention_decode_balanced_bf16(const void* q, const void* cache, void* out, float* partial,
+                                                      const int* block_table, const int* context_len, int requests,
+                                                      int q_heads, int kv_heads, int head_dim, long q_row_stride,
+                                                      int page_size, int table_width, int num_pages, int window,
+                                                      float scale, int ctas, int* error_flag, cudaStream_t stream) {
+    if (requests <= 0) return 0;
+    int bad = check_common(q_heads, kv_heads, head_dim, q_row_stride, q);
+    if (bad) return bad;
+    if (q_heads / kv_heads > 16) return KIRAI_ERR_UNSUPPORTED;  // the group's heads are the rows of one m16 tile
+    if (ctas < 1 || ctas > 65535 || !partial) return KIRAI_ERR_BAD_SIZE;
+    if (requests > DECODE_MAX_REQUESTS) return KIRAI_ERR_UNSUPPORTED;  // the tile prefix lives in shared memory
+#define KIRAI_DCB(D) \
+    return decode_balanced_launch<D>(q, cache, out, partial, block_table, context_len, requests, q_heads, kv_heads, \
+                                     head_dim, q_row_stride, page_size, table_width, num_pages, window, scale, ctas, \
+                                     error_flag, stream)
+    if (head_dim <= 64) KIRAI_DCB(64);
+    if (head_dim <= 128) KIRAI_DCB(128);
+    KIRAI_DCB(256);
+#undef KIRAI_DCB
 }
 
 // ----------------------------------------------------- decode without allocation

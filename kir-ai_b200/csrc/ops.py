@@ -12,6 +12,7 @@ flag that ``check_device_errors`` reads.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -301,6 +302,30 @@ def decode_splits(requests: int, kv_heads: int, max_context_len: int, tile: int 
     return best
 
 
+def decode_plan(context_lens, kv_heads: int, window: Optional[int] = None, tile: int = 16, warps: int = 8,
+                sms: int = 148) -> tuple:
+    """Which decode attention kernel a batch should take: (balanced, splits).
+
+    The split kernel gives every request the same number of CTAs, so its time is that of the longest request and
+    comes in waves of ``sms`` CTAs; the balanced kernel cuts all key tiles into ``sms`` equal ranges, which costs
+    it a second start inside most CTAs and a longer merge.  Costs are in rounds of one key tile per warp (about
+    1.35 us on the 8B layer sizes); the fixed parts were fitted to measurements of both kernels at batches of 1 to
+    64.  Balanced is chosen only when it is expected to be clearly faster: contexts of unequal length, or a batch
+    whose CTAs fill the last wave badly."""
+    lens = [min(int(n), window) if window else int(n) for n in context_lens]
+    if not lens:
+        return False, 1
+    longest = max(1, max(lens))
+    splits = decode_splits(len(lens), kv_heads, longest, tile, warps)
+    tiles = [max(1, -(-n // tile)) for n in lens]
+    waves = -(-len(lens) * kv_heads * splits // sms)
+    rounds_split = -(-(-(-max(tiles) // splits)) // warps)
+    cost_split = waves * (rounds_split + 2.5) + (2.5 if splits > 1 else 0.0)
+    rounds_balanced = -(-(-(-kv_heads * sum(tiles) // sms)) // warps)
+    cost_balanced = rounds_balanced + 9.5
+    return cost_balanced < 0.92 * cost_split, splits
+
+
 def attention_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, context_len: torch.Tensor,
                      window: Optional[int], scale: float, num_splits: int = 1) -> torch.Tensor:
     """bf16 tensor-core attention for a batch in which every request brings one token: q [R, nq, d]."""
@@ -320,6 +345,35 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Te
     return out
 
 
+_sm_counts = {}
+
+
+def sm_count(device: torch.device) -> int:
+    key = torch.device(device)
+    if key not in _sm_counts:
+        _sm_counts[key] = torch.cuda.get_device_properties(key).multi_processor_count
+    return _sm_counts[key]
+
+
+def attention_decode_balanced(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, context_len: torch.Tensor,
+                              window: Optional[int], scale: float, ctas: Optional[int] = None) -> torch.Tensor:
+    """The decode attention with the key tiles of all (request, kv head) pairs cut into ``ctas`` equal ranges
+    (default: one per SM), so that every CTA reads the same number of keys whatever the batch looks like."""
+    _need_cuda(q, cache, block_table, context_len)
+    num_pages, kv_heads, page_size, head_dim = _cache_dims(cache)
+    rows, q_heads, qd, q_stride = _head_view(q)
+    assert qd == head_dim and q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
+    assert context_len.numel() == rows and context_len.dtype == torch.int32
+    ctas = ctas or sm_count(q.device)
+    out = torch.empty((rows, q_heads * head_dim), dtype=q.dtype, device=q.device)
+    partial = torch.empty((ctas, 2, 16, head_dim + 2), dtype=torch.float32, device=q.device)
+    _call("kirai_attention_decode_balanced_bf16", _ptr(q), _ptr(cache), _ptr(out), _ptr(partial), _ptr(block_table),
+          _ptr(context_len), _i(rows), _i(q_heads), _i(kv_heads), _i(head_dim), _l(q_stride), _i(page_size),
+          _i(block_table.shape[1]), _i(num_pages), _i(window or 0), _f(scale), _i(ctas),
+          _ptr(error_flag(q.device)), _stream())
+    return out
+
+
 def paged_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, batch, window: Optional[int],
                     scale: float) -> torch.Tensor:
     """Attention of the product path over the paged cache for the tokens of ``batch``
@@ -332,6 +386,17 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
     if not fast:
         return paged_attention_plain(q, cache, block_table, batch.request_of_token, batch.positions, window, scale)
     if batch.decode_only and q_heads // kv_heads <= 16:
+        # the batch may say which kernel (a captured step does: its lengths change between replays); otherwise
+        # the host's copy of the lengths decides; KIRAI_DECODE_BALANCED=0 or 1 overrides both
+        balanced = getattr(batch, "decode_balanced", None)
+        if balanced is None and len(batch.query_lens) == batch.num_requests:
+            lens = [start + count for start, count in zip(batch.start_positions, batch.query_lens)]
+            balanced, _ = decode_plan(lens, kv_heads, window, sms=sm_count(q.device))
+        forced = os.environ.get("KIRAI_DECODE_BALANCED")
+        if forced in ("0", "1"):
+            balanced = forced == "1"
+        if balanced and batch.num_requests <= 1024:
+            return attention_decode_balanced(q, cache, block_table, batch.context_len, window, scale)
         splits = decode_splits(batch.num_requests, kv_heads, min(batch.max_context_len, window or batch.max_context_len))
         return attention_decode(q, cache, block_table, batch.context_len, window, scale, splits)
     return attention_prefill(q, cache, block_table, batch.query_start, batch.context_len, batch.max_query_len, window, scale)

@@ -45,6 +45,8 @@ class StepBatch:
     max_query_len: int = 0
     max_context_len: int = 0
     num_want: int = 0
+    # which decode attention kernel a step of single tokens takes (None: decided from the lengths above)
+    decode_balanced: Optional[bool] = None
 
     @property
     def decode_only(self) -> bool:

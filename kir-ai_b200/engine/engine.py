@@ -127,7 +127,7 @@ class Engine:
         pages = [r.pages for r in requests]
         tables = [cache.block_table_array(pages, g) for g in range(len(cache.groups))]
         width = max([1] + [t.shape[1] for t in tables])
-        graph, fresh = self.graphs.get(len(requests), width)
+        graph, fresh = self.graphs.get(len(requests), width, [p.length + 1 for p in pages])
         graph.load_inputs(
             [r.token_at(item.first) for r, item in zip(requests, scheduled)], [p.length for p in pages],
             [p.slot for p in pages], tables, [r.params.temperature for r in requests],

@@ -20,7 +20,7 @@ from .batch import StepBatch
 
 
 class DecodeGraph:
-    def __init__(self, runner, num_requests: int, table_width: int):
+    def __init__(self, runner, num_requests: int, table_width: int, balanced_attention: bool = False):
         self.runner = runner
         self.num_requests = B = num_requests
         self.table_width = table_width
@@ -51,6 +51,7 @@ class DecodeGraph:
             request_of_token=self.fixed[:B], query_start=self.fixed, context_len=self.context_len, slots=self.slots,
             block_tables=self.tables, want_rows=self.fixed[:B], query_lens=[1] * B, start_positions=[0] * B,
             slot_ids=[0] * B, max_query_len=1, max_context_len=table_width * runner.cache.page_size, num_want=B,
+            decode_balanced=balanced_attention,
         )
         self.tokens_out: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
@@ -116,11 +117,22 @@ class DecodeGraph:
 
 
 class DecodeGraphs:
-    """The captured decode steps of a runner, by (requests, table width bucket)."""
+    """The captured decode steps of a runner, by (requests, table width bucket, decode attention kernel)."""
 
     def __init__(self, runner):
         self.runner = runner
-        self.graphs: Dict[Tuple[int, int], DecodeGraph] = {}
+        self.graphs: Dict[Tuple[int, int, bool], DecodeGraph] = {}
+
+    def _balanced(self, context_lens: Sequence[int]) -> bool:
+        """The cheaper decode attention kernel by the model in ops.decode_plan, over the layers' cache needs
+        (all of a model's attention layers take the same kernel in one captured step: the widest need decides)."""
+        ops = self.runner.rt.ops
+        groups = list(self.runner.cache.groups)
+        if not groups:
+            return False
+        need = max(groups, key=lambda g: g.window or (1 << 60))
+        balanced, _ = ops.decode_plan(context_lens, need.kv_heads, need.window, sms=ops.sm_count(self.runner.rt.device))
+        return balanced
 
     @staticmethod
     def width_bucket(width: int) -> int:
@@ -129,12 +141,17 @@ class DecodeGraphs:
             bucket *= 2
         return bucket
 
-    def get(self, num_requests: int, table_width: int) -> Tuple[DecodeGraph, bool]:
-        """The graph for this shape and whether it still has to be captured."""
-        key = (num_requests, self.width_bucket(table_width))
+    def get(self, num_requests: int, table_width: int, context_lens: Optional[Sequence[int]] = None
+            ) -> Tuple[DecodeGraph, bool]:
+        """The graph for this shape and whether it still has to be captured.  ``context_lens`` (the requests'
+        lengths after this step) choose between the two decode attention kernels; each has its own capture."""
+        balanced = False
+        if context_lens is not None:
+            balanced = self._balanced(context_lens)
+        key = (num_requests, self.width_bucket(table_width), balanced)
         graph = self.graphs.get(key)
         if graph is None:
-            graph = DecodeGraph(self.runner, key[0], key[1])
+            graph = DecodeGraph(self.runner, key[0], key[1], balanced)
             self.graphs[key] = graph
             return graph, True
         return graph, False

@@ -359,6 +359,14 @@ def test_tensor_core_attention_against_plain(ops, q_heads, kv_heads, head_dim, p
             for r, end in enumerate(ends):
                 expected = attention_reference(qd[r : r + 1].cpu(), keys[r], values[r], [end], window, scale)
                 assert float((got[r : r + 1] - expected).abs().max()) <= 2.5e-2, (r, splits)
+        # the same with the keys of all (request, kv head) pairs cut into equal ranges: one CTA that walks through
+        # every pair, a few CTAs whose borders cut pairs in two or more pieces, more CTAs than there are tiles
+        for ctas in (1, 3, 7, 148, 1000):
+            got = ops.attention_decode_balanced(qd, cache, table, ctx, window, scale, ctas).float().cpu().unflatten(1, (q_heads, head_dim))
+            ops.check_device_errors(torch.device(DEV))
+            for r, end in enumerate(ends):
+                expected = attention_reference(qd[r : r + 1].cpu(), keys[r], values[r], [end], window, scale)
+                assert float((got[r : r + 1] - expected).abs().max()) <= 2.5e-2, (r, ctas)
 
 
 def test_tensor_core_attention_finds_a_far_key(ops):
@@ -378,6 +386,10 @@ def test_tensor_core_attention_finds_a_far_key(ops):
         out = ops.attention_decode(q, cache, table, ctx, None, head_dim ** -0.5, splits).float().cpu().unflatten(1, (q_heads, head_dim))
         for head in range(q_heads):
             assert float((out[0, head] - values[0][far, head // 4].float()).abs().max()) <= 2e-2
+    for ctas in (2, 5, 148):
+        out = ops.attention_decode_balanced(q, cache, table, ctx, None, head_dim ** -0.5, ctas).float().cpu().unflatten(1, (q_heads, head_dim))
+        for head in range(q_heads):
+            assert float((out[0, head] - values[0][far, head // 4].float()).abs().max()) <= 2e-2, ctas
     qs = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
     out = ops.attention_prefill(q, cache, table, qs, ctx, 1, None, head_dim ** -0.5).float().cpu().unflatten(1, (q_heads, head_dim))
     assert float((out[0, 0] - values[0][far, 0].float()).abs().max()) <= 2e-2
@@ -482,6 +494,9 @@ def test_attention_with_block_tables_longer_than_the_shared_copy(ops):
     for splits in (1, 3):
         out = ops.attention_decode(q, cache, table, ctx, None, scale, splits).float().cpu().unflatten(1, (q_heads, head_dim))
         assert float((out[0, 0] - expected).abs().max()) <= 3e-2, splits
+    for ctas in (1, 2):  # ranges of more than 1,024 pages
+        out = ops.attention_decode_balanced(q, cache, table, ctx, None, scale, ctas).float().cpu().unflatten(1, (q_heads, head_dim))
+        assert float((out[0, 0] - expected).abs().max()) <= 3e-2, ctas
     qs = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
     for use_tcgen05 in (False, True):
         out = ops.attention_prefill(q, cache, table, qs, ctx, 1, None, scale, tcgen05=use_tcgen05).float().cpu().unflatten(1, (q_heads, head_dim))

@@ -65,6 +65,25 @@ def test_last_32_one_by_one(tiny, dtype, tmp_path):
     assert replay.close() == 0
 
 
+@pytest.mark.parametrize("forced", ["0", "1"])
+def test_decoding_with_either_attention_kernel(tiny, forced, tmp_path, monkeypatch):
+    """The decode step picks between two attention kernels by the batch's lengths (equal splits per request, or all
+    keys cut into equal ranges); each is forced here, for three requests of unequal length decoding side by side."""
+    monkeypatch.setenv("KIRAI_DECODE_BALANCED", forced)
+    replay = Replay(tiny["folder"], "bfloat16", str(tmp_path / "out"), max_tokens=256, page_size=tiny["page"])
+    rids = ("a", "c", "d")
+    heads = {"a": 43, "c": 21, "d": 2}
+    for rid in rids:
+        got = replay.step([(rid, tiny["sequences"][rid][: heads[rid]], [heads[rid] - 1])])
+        check("bfloat16", got, tiny["reference"][rid], [heads[rid] - 1], f"{rid} prompt")
+    for k in range(7):
+        live = [rid for rid in rids if heads[rid] + k < len(tiny["sequences"][rid])]
+        got = replay.step([(rid, [tiny["sequences"][rid][heads[rid] + k]], [0]) for rid in live])
+        for row, rid in enumerate(live):
+            check("bfloat16", got[row : row + 1], tiny["reference"][rid], [heads[rid] + k], f"{rid} decode {k} (balanced={forced})")
+    assert replay.close() == 0
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_portions_of_changing_size(tiny, dtype, tmp_path):
     replay = Replay(tiny["folder"], dtype, str(tmp_path / "out"), max_tokens=128, page_size=tiny["page"])

@@ -145,3 +145,18 @@ def test_sampling_params_ranges():
         with pytest.raises(ValueError):
             SamplingParams(**bad)
     assert SamplingParams(temperature=0.0).greedy and SamplingParams().top_p == 1.0 and SamplingParams().temperature == 1.0
+
+
+def test_decode_plan_prefers_the_balanced_kernel_only_for_uneven_or_badly_filled_batches():
+    """The host-side choice between the two decode attention kernels (no GPU needed: it is arithmetic)."""
+    import kirai_b200  # noqa: F401
+    from kirai_b200.csrc.ops import decode_plan
+
+    assert decode_plan([4096], 8)[0] is False                      # one request: the split kernel has the lower fixed cost
+    assert decode_plan([4096] * 8, 8)[0] is False                  # equal lengths that fill one wave
+    uneven = [1024, 7168, 2048, 6000, 3000, 5000, 4000, 1500]
+    assert decode_plan(uneven, 8)[0] is True                       # the longest request would set the split kernel's time
+    assert decode_plan([n for n in uneven], 8, window=512)[0] is False  # a window makes them equal again
+    balanced, splits = decode_plan([100_000] + [500] * 15, 8)
+    assert balanced is True and splits >= 1
+    assert decode_plan([], 8) == (False, 1)
