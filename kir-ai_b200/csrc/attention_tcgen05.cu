@@ -14,11 +14,11 @@
 // The running maximum is lazy: the output accumulator is rescaled only when a row's maximum has
 // grown by more than 2^8 since the scale in use, which is exact (the final division uses the same
 // scale) and spares most read-modify-write passes over the accumulator.
-// Warp roles: warp 0 fetches K tiles and V tiles by TMA straight from the pages, one thread of
-// warp 1 issues the MMAs, warps 2-5 are the softmax rows.  A CTA works through its tiles in
-// sequence (P lies over S in tensor memory) and is small enough for two CTAs per SM, which
-// overlap each other: while one's rows exponentiate, the other's products run.  Every barrier wait is
-// bounded.  Same visibility rule as the other attention kernels: row at position pos sees keys
+// Warp roles: warp 0 fetches K tiles and V tiles by TMA straight from the pages (two slots each), one
+// thread of warp 1 issues the MMAs, warps 2-5 are the softmax rows.  S has two buffers in tensor memory
+// (P lies over the buffer its S came from): the first product of tile t + 1 is issued before the second
+// product of tile t, so it runs while the rows of tile t exponentiate.  A CTA is small enough for two per
+// SM, which fill each other's gaps.  Every barrier wait is bounded.  Same visibility rule as the other attention kernels: row at position pos sees keys
 // lo <= j <= pos.  head_dim: a multiple of 8 up to 128; the group size must divide 128.
 #include "sm100.cuh"
 #include "tensor_map.cuh"
@@ -28,10 +28,10 @@ using namespace sm100;
 namespace {
 
 #define TA_ROWS 128
-#define TA_BN 128
-#define TA_STAGES 1   // slots of the K ring, and of the V ring: two CTAs share an SM and overlap each other
+#define TA_BN 64
+#define TA_STAGES 2   // slots of the K ring, and of the V ring
 #define TA_THREADS 192
-#define TA_TMEM_COLS 256  // S (and, over its first half, P) in columns 0..127, O in columns 128..255
+#define TA_TMEM_COLS 256  // S buffers (and, over each one's first half, its P) in columns 0..63 and 64..127, O in 128..255
 
 template <int D>
 struct TcAttnSmem {
@@ -39,7 +39,8 @@ struct TcAttnSmem {
     static constexpr int q_bytes = TA_ROWS * D * 2;
     static constexpr int tile_bytes = TA_BN * D * 2;
     static constexpr int ring_bytes = TA_STAGES * 2 * tile_bytes;  // K ring, then V ring
-    static constexpr int barrier_bytes = 128;
+    static constexpr int barrier_bytes = 256;
+    static_assert((4 * TA_STAGES + 5) * 8 + 4 <= barrier_bytes, "the barriers and the tensor-memory slot must fit their region");
     static constexpr int table_entries = 1024;
     static constexpr int total = q_bytes + ring_bytes + barrier_bytes + table_entries * 4 + 1024;
 };
@@ -136,10 +137,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
     uint64_t* k_empty = bars + TA_STAGES;           // [TA_STAGES] first product done with the K tile
     uint64_t* v_full = bars + 2 * TA_STAGES;        // [TA_STAGES]
     uint64_t* v_empty = bars + 3 * TA_STAGES;       // [TA_STAGES] second product done with the V tile
-    uint64_t* s_ready = bars + 4 * TA_STAGES;       // S of a tile is in tensor memory (and every earlier product is done)
-    uint64_t* p_ready = s_ready + 1;                // P of this tile is in tensor memory (4 warps arrive)
-    uint64_t* o_ready = s_ready + 2;                // the second product of this tile is done
-    uint32_t* tmem_slot = (uint32_t*)(s_ready + 3);
+    uint64_t* s_ready = bars + 4 * TA_STAGES;       // [2] S of a tile is in its buffer (and every product issued before is done)
+    uint64_t* p_ready = s_ready + 2;                // [2] P of a tile is in tensor memory (4 warps arrive)
+    uint64_t* o_ready = s_ready + 4;                // the second product of a tile is done
+    uint32_t* tmem_slot = (uint32_t*)(s_ready + 5);
     int* table_s = reinterpret_cast<int*>(smem + Smem::q_bytes + Smem::ring_bytes + Smem::barrier_bytes);
 
     const int last_row = min(rows_total, row0 + TA_ROWS) - 1;
@@ -157,8 +158,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
             mbar_init(smem_addr(&v_full[s]), 1);
             mbar_init(smem_addr(&v_empty[s]), 1);
         }
-        mbar_init(smem_addr(s_ready), 1);
-        mbar_init(smem_addr(p_ready), 4);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_addr(&s_ready[b]), 1);
+            mbar_init(smem_addr(&p_ready[b]), 4);
+        }
         mbar_init(smem_addr(o_ready), 1);
         mbar_fence_init();
     }
@@ -192,7 +195,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_p = tmem_base /* over S */, tmem_o = tmem_base + 128;
+    const uint32_t tmem_s = tmem_base /* + 64 for odd tiles; P over the first 32 columns */, tmem_o = tmem_base + 128;
     bool ok = true;
 
     if (warp == 0) {
@@ -205,83 +208,125 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
         }
         const int boxes = TA_BN / box_rows;
         const uint32_t box_bytes = (uint32_t)box_rows * 128u * PANELS;
-        // fills one slot of the K ring (which == 0) or of the V ring (which == 1) with key tile t
-        auto fill = [&](int t, int which, uint32_t bar, uint32_t dst) {
-            int count = 0;
-            for (int b = lane; b < boxes; b += 32) {
-                const int j = t * TA_BN + b * box_rows;
-                const int logical = j / page_size;
-                const int page = (j <= pos_last && logical < table_width) ? table[logical] : -1;
-                count += (page >= 0 && page < num_pages);
+        // This warp's pace bounds the kernel (two fills per tile), so a tile's pages are looked up once, for its
+        // keys and its values alike, and sizes that are powers of two are shifted, not divided.
+        const int page_shift = __ffs(page_size) - 1, box_shift = __ffs(box_rows) - 1;
+        constexpr int PER_LANE = (TA_BN + 31) / 32;  // boxes per lane when a box is one row
+        struct TilePlan {
+            int row[PER_LANE];  // first cache row (of K; V lies kv_heads * page_size further) of this lane's boxes, or -1
+            int count;          // boxes with a page, over the warp
+        };
+        auto plan_tile = [&](int t) {
+            TilePlan plan;
+            unsigned present = 0;
+#pragma unroll
+            for (int k = 0; k < PER_LANE; ++k) {
+                const int b = lane + 32 * k;
+                plan.row[k] = -1;
+                if (b < boxes) {
+                    const int j = t * TA_BN + (b << box_shift);
+                    const int logical = j >> page_shift;
+                    const int page = (j <= pos_last && logical < table_width) ? table[logical] : -1;
+                    if (page >= 0 && page < num_pages)
+                        plan.row[k] = ((page * 2) * kv_heads + kv_head) * page_size + (j & (page_size - 1));
+                }
+                present += __popc(__ballot_sync(0xffffffffu, plan.row[k] >= 0));
             }
-            count = __reduce_add_sync(0xffffffffu, count);
-            if (count < boxes) {
+            plan.count = (int)present;
+            return plan;
+        };
+        // fills one slot of the K ring (which == 0) or of the V ring (which == 1) with the planned tile
+        auto fill = [&](const TilePlan& plan, int which, uint32_t bar, uint32_t dst) {
+            if (plan.count < boxes) {
                 // boxes without a page hold masked keys only; their rows are cleared all the same, because a
                 // value row is multiplied by its zero weight and must be finite
-                for (int b = 0; b < boxes; ++b) {
-                    const int j = t * TA_BN + b * box_rows;
-                    const int logical = j / page_size;
-                    const int page = (j <= pos_last && logical < table_width) ? table[logical] : -1;
-                    if (page >= 0 && page < num_pages) continue;
-                    for (int h = 0; h < PANELS; ++h) {
-                        const uint32_t off = (uint32_t)(h * (TA_BN * 128) + b * box_rows * 128);
-                        for (int i = lane; i < box_rows * 8; i += 32)
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst + off + i * 16), "r"(0u) : "memory");
+#pragma unroll
+                for (int k = 0; k < PER_LANE; ++k) {
+                    for (int owner = 0; owner < 32 && 32 * k + owner < boxes; ++owner) {
+                        if (__shfl_sync(0xffffffffu, plan.row[k], owner) >= 0) continue;
+                        const int b = 32 * k + owner;
+                        for (int h = 0; h < PANELS; ++h) {
+                            const uint32_t off = (uint32_t)(h * (TA_BN * 128) + (b << box_shift) * 128);
+                            for (int i = lane; i < box_rows * 8; i += 32)
+                                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst + off + i * 16), "r"(0u) : "memory");
+                        }
                     }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
             }
             if (lane == 0) {
-                if (count) mbar_expect_tx(bar, box_bytes * (uint32_t)count);
+                if (plan.count) mbar_expect_tx(bar, box_bytes * (uint32_t)plan.count);
                 else mbar_arrive(bar);
             }
             __syncwarp();
-            for (int b = lane; b < boxes; b += 32) {
-                const int j = t * TA_BN + b * box_rows;
-                const int logical = j / page_size;
-                const int page = (j <= pos_last && logical < table_width) ? table[logical] : -1;
-                if (page >= 0 && page < num_pages) {
-                    const int row = ((page * 2 + which) * kv_heads + kv_head) * page_size + (j % page_size);
+            const int value_rows = which * kv_heads * page_size;
+#pragma unroll
+            for (int k = 0; k < PER_LANE; ++k) {
+                if (plan.row[k] >= 0) {
+                    const int b = lane + 32 * k;
 #pragma unroll
                     for (int h = 0; h < PANELS; ++h)
-                        tma_load_2d(dst + (uint32_t)(h * (TA_BN * 128) + b * box_rows * 128), &kv_map, bar, h * 64, row);
+                        tma_load_2d(dst + (uint32_t)(h * (TA_BN * 128) + (b << box_shift) * 128), &kv_map, bar, h * 64,
+                                    plan.row[k] + value_rows);
                 }
             }
             __syncwarp();
         };
-        for (int it = 0; it < num_tiles && ok; ++it) {
+        // K runs one tile ahead of V: the first product of tile t + 1 is issued before the second of tile t
+        auto fill_k = [&](int it, const TilePlan& plan) {
             const int slot = it % TA_STAGES;
-            const uint32_t parity = (uint32_t)(it / TA_STAGES - 1) & 1u;
-            if (it >= TA_STAGES && !mbar_wait(smem_addr(&k_empty[slot]), parity)) { ok = false; break; }
-            fill(first_tile + it, 0, smem_addr(&k_full[slot]), ring + slot * Smem::tile_bytes);
-            if (it >= TA_STAGES && !mbar_wait(smem_addr(&v_empty[slot]), parity)) { ok = false; break; }
-            fill(first_tile + it, 1, smem_addr(&v_full[slot]), ring + (TA_STAGES + slot) * Smem::tile_bytes);
+            if (it >= TA_STAGES && !mbar_wait_hot(smem_addr(&k_empty[slot]), (uint32_t)(it / TA_STAGES - 1) & 1u)) { ok = false; return; }
+            fill(plan, 0, smem_addr(&k_full[slot]), ring + slot * Smem::tile_bytes);
+        };
+        TilePlan current = plan_tile(first_tile);
+        fill_k(0, current);
+        for (int it = 0; it < num_tiles && ok; ++it) {
+            TilePlan next = current;
+            if (it + 1 < num_tiles) {
+                next = plan_tile(first_tile + it + 1);
+                fill_k(it + 1, next);
+            }
+            if (!ok) break;
+            const int slot = it % TA_STAGES;
+            if (it >= TA_STAGES && !mbar_wait_hot(smem_addr(&v_empty[slot]), (uint32_t)(it / TA_STAGES - 1) & 1u)) { ok = false; break; }
+            fill(current, 1, smem_addr(&v_full[slot]), ring + (TA_STAGES + slot) * Smem::tile_bytes);
+            current = next;
         }
     } else if (warp == 1) {
         if (elect_one()) {
             constexpr uint32_t idesc_qk = instr_desc_bf16(TA_ROWS, TA_BN);      // S[128 x 128 keys]
             constexpr uint32_t idesc_pv = instr_desc_bf16_b_mn(TA_ROWS, D);     // O[128 x D], B = V as it lies (MN-major)
-            for (int it = 0; it < num_tiles; ++it) {
+            // S(it) = Q K(it)^T into buffer it & 1
+            auto first_product = [&](int it) {
                 const int slot = it % TA_STAGES;
-                const uint32_t parity = (uint32_t)(it / TA_STAGES) & 1u;
-                if (!mbar_wait_hot(smem_addr(&k_full[slot]), parity)) { ok = false; break; }
+                if (!mbar_wait_hot(smem_addr(&k_full[slot]), (uint32_t)(it / TA_STAGES) & 1u)) { ok = false; return; }
                 tc_fence_after();
                 const uint32_t k_addr = ring + slot * Smem::tile_bytes;
+                const uint32_t s_acc = tmem_s + (uint32_t)((it & 1) * TA_BN);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     // 16 dims further: 32 bytes inside the swizzle atom, or the next 64-column panel
                     const uint32_t off_q = (uint32_t)((kk >> 2) * (TA_ROWS * 128) + (kk & 3) * 32);
                     const uint32_t off_k = (uint32_t)((kk >> 2) * (TA_BN * 128) + (kk & 3) * 32);
-                    mma_bf16_ss(tmem_s, smem_desc_k_major_sw128(q_smem + off_q), smem_desc_k_major_sw128(k_addr + off_k), idesc_qk,
+                    mma_bf16_ss(s_acc, smem_desc_k_major_sw128(q_smem + off_q), smem_desc_k_major_sw128(k_addr + off_k), idesc_qk,
                                 kk > 0 ? 1u : 0u);
                 }
                 mma_commit(smem_addr(&k_empty[slot]));
-                mma_commit(smem_addr(s_ready));
-                if (!mbar_wait_hot(smem_addr(&v_full[slot]), parity)) { ok = false; break; }
-                if (!mbar_wait_hot(smem_addr(p_ready), (uint32_t)it & 1u)) { ok = false; break; }
+                mma_commit(smem_addr(&s_ready[it & 1]));
+            };
+            first_product(0);
+            for (int it = 0; it < num_tiles && ok; ++it) {
+                // the next tile's scores are computed while this tile's rows exponentiate; the products run in
+                // issue order, so this one finds its buffer free (the second product of tile it - 1 read it)
+                if (it + 1 < num_tiles) first_product(it + 1);
+                if (!ok) break;
+                const int slot = it % TA_STAGES;
+                if (!mbar_wait_hot(smem_addr(&v_full[slot]), (uint32_t)(it / TA_STAGES) & 1u)) { ok = false; break; }
+                if (!mbar_wait_hot(smem_addr(&p_ready[it & 1]), (uint32_t)(it >> 1) & 1u)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t v_addr = ring + (TA_STAGES + slot) * Smem::tile_bytes;
+                const uint32_t tmem_p = tmem_s + (uint32_t)((it & 1) * TA_BN);
 #pragma unroll
                 for (int kk = 0; kk < TA_BN / 16; ++kk) {
                     // 16 keys further: 8 columns of packed bf16 pairs in tensor memory, two 8-row groups of the V tile
@@ -305,30 +350,36 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
         float l = 0.0f;
         for (int it = 0; it < num_tiles; ++it) {
             const int j0 = (first_tile + it) * TA_BN;
-            // S of this tile is complete; since the MMAs run in issue order, so is the second product of
-            // the tile before: O may be rescaled and P (which lies over S) written without another wait
-            if (!mbar_wait_hot(smem_addr(s_ready), (uint32_t)it & 1u)) { ok = false; break; }
+            // S of this tile is complete in buffer it & 1
+            if (!mbar_wait_hot(smem_addr(&s_ready[it & 1]), (uint32_t)(it >> 1) & 1u)) { ok = false; break; }
             tc_fence_after();
-            // a tile whose keys every row of this warp sees needs no mask
-            const bool interior = __all_sync(0xffffffffu, j0 >= lo && j0 + TA_BN - 1 <= pos);
-            // pass 1: the row's maximum (four running maxima, so that the chain of dependent compares is short)
-            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t s[32];
-                tmem_load_32x32(tmem_s + lane_bits + (uint32_t)(c * 32), s);
+            const uint32_t s_buf = tmem_s + lane_bits + (uint32_t)((it & 1) * TA_BN);
+            // the row's 64 scores, read once
+            uint32_t s[TA_BN];
+            {
+                uint32_t half0[32], half1[32];
+                tmem_load_32x32(s_buf, half0);
+                tmem_load_32x32(s_buf + 32u, half1);
                 tmem_load_wait();
-                if (interior) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(s[i]));
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int j = j0 + c * 32 + i;
-                        mx[i & 3] = fmaxf(mx[i & 3], (j >= lo && j <= pos) ? __uint_as_float(s[i]) : -INFINITY);
-                    }
+                for (int i = 0; i < 32; ++i) {
+                    s[i] = half0[i];
+                    s[32 + i] = half1[i];
                 }
             }
+            // a tile whose keys every row of this warp sees needs no mask
+            const bool interior = __all_sync(0xffffffffu, j0 >= lo && j0 + TA_BN - 1 <= pos);
+            if (!interior) {
+#pragma unroll
+                for (int i = 0; i < TA_BN; ++i) {
+                    const int j = j0 + i;
+                    if (!(j >= lo && j <= pos)) s[i] = __float_as_uint(-INFINITY);
+                }
+            }
+            // the row's maximum (four running maxima, so that the chain of dependent compares is short)
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < TA_BN; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(s[i]));
             const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;  // the scale is positive
             const float m_new = fmaxf(m_used, m_tile);
             const bool grow = m_new > m_used + 8.0f || (m_used == -INFINITY && m_new != -INFINITY);
@@ -338,7 +389,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
                 m_used = m_new;
             }
             if (__any_sync(0xffffffffu, grow && it > 0)) {
-                // rescale this warp's rows of the accumulator (rows that do not need it multiply by 1)
+                // rescale this warp's rows of the accumulator (rows that do not need it multiply by 1), once the
+                // second product of the tile before has added into it; that product is not behind this tile's
+                // scores in issue order, so it is waited for
+                if (!mbar_wait_hot(smem_addr(o_ready), (uint32_t)(it - 1) & 1u)) { ok = false; break; }
+                tc_fence_after();
 #pragma unroll 1
                 for (int c = 0; c < D / 32; ++c) {
                     uint32_t o[32];
@@ -350,37 +405,31 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
                 }
             }
             const float m_sub = m_used == -INFINITY ? 0.0f : m_used;
-            // pass 2: the weights, 32 keys at a time; their 16 columns of bf16 pairs go over S columns that
-            // this row has already read
+            // the weights: exp2(s * scale - m), one fused multiply-add and one ex2.approx per key (-inf gives 0);
+            // their 32 columns of bf16 pairs go over the first half of this tile's S buffer
             float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t s[32];
-                tmem_load_32x32(tmem_s + lane_bits + (uint32_t)(c * 32), s);
-                tmem_load_wait();
+#pragma unroll
+            for (int c = 0; c < TA_BN / 32; ++c) {
                 uint32_t p[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    float a = __uint_as_float(s[2 * i]), b = __uint_as_float(s[2 * i + 1]);
-                    if (!interior) {
-                        const int j = j0 + c * 32 + 2 * i;
-                        a = (j >= lo && j <= pos) ? a : -INFINITY;
-                        b = (j + 1 >= lo && j + 1 <= pos) ? b : -INFINITY;
-                    }
-                    // exp2(s * scale - m): one fused multiply-add and one ex2.approx per key (-inf gives 0)
-                    a = ex2_approx(fmaf(a, scale_log2, -m_sub));
-                    b = ex2_approx(fmaf(b, scale_log2, -m_sub));
+                    const float a = ex2_approx(fmaf(__uint_as_float(s[c * 32 + 2 * i]), scale_log2, -m_sub));
+                    const float b = ex2_approx(fmaf(__uint_as_float(s[c * 32 + 2 * i + 1]), scale_log2, -m_sub));
                     sum[i & 3] += a + b;
                     p[i] = pack2(a, b);
                 }
-                tmem_store_32x16(tmem_p + lane_bits + (uint32_t)(c * 16), p);
+                tmem_store_32x16(s_buf + (uint32_t)(c * 16), p);
             }
             l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
             tmem_store_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_addr(p_ready));
+            if (lane == 0) mbar_arrive(smem_addr(&p_ready[it & 1]));
         }
+        // The last tile's scores were issued before the second product of the tile before it, so passing their
+        // barrier says nothing about that product: the barrier's phases are waited for one after the other (a
+        // parity wait cannot tell a phase from the one two before it).
+        if (ok && num_tiles >= 2) ok = mbar_wait_hot(smem_addr(o_ready), (uint32_t)(num_tiles - 2) & 1u);
         if (ok) ok = mbar_wait_hot(smem_addr(o_ready), (uint32_t)(num_tiles - 1) & 1u);
         tc_fence_after();
         if (ok) {
