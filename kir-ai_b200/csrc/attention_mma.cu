@@ -167,31 +167,42 @@ template <int BN, int PANELS>
 __device__ __forceinline__ void fill_kv_slot(const CUtensorMap* kv_map, uint32_t bar, uint32_t k_dst, uint32_t v_dst, int t,
                                              int last_key, const int* table, int table_width, int num_pages,
                                              int kv_heads, int kv_head, int page_size, int box_rows, int lane) {
+    // The warp that calls this sets the pace of the kernel it feeds (once per tile), so the pages are looked up
+    // in one pass, a lane per box, and a page size that is a power of two is shifted by, not divided by.
+    constexpr int PER_LANE = (BN + 31) / 32;  // boxes per lane when a box is one row
     const int boxes = BN / box_rows;
     const uint32_t box_bytes = (uint32_t)box_rows * 128u * PANELS;  // of K, and as much of V
-    // first pass: how many boxes have a page (the barrier must know the byte count before any copy lands)
+    const bool shift = (page_size & (page_size - 1)) == 0;
+    const int page_shift = __ffs(page_size) - 1;
+    int row_k[PER_LANE];  // first cache row of this lane's boxes (K; V lies kv_heads * page_size further), or -1
     int count = 0;
-    for (int b = lane; b < boxes; b += 32) {
-        const int j = t * BN + b * box_rows;
-        const int logical = j / page_size;
-        const int page = (j <= last_key && logical < table_width) ? table[logical] : -1;
-        count += (page >= 0 && page < num_pages);
+#pragma unroll
+    for (int k = 0; k < PER_LANE; ++k) {
+        const int b = lane + 32 * k;
+        row_k[k] = -1;
+        if (b < boxes) {
+            const int j = t * BN + b * box_rows;
+            const int logical = shift ? j >> page_shift : j / page_size;
+            const int page = (j <= last_key && logical < table_width) ? table[logical] : -1;
+            if (page >= 0 && page < num_pages) row_k[k] = ((page * 2) * kv_heads + kv_head) * page_size + (j - logical * page_size);
+        }
+        count += __popc(__ballot_sync(0xffffffffu, row_k[k] >= 0));
     }
-    count = __reduce_add_sync(0xffffffffu, count);
-    // Boxes without a page: the warp clears their value rows together (their keys are masked by
-    // position whatever they hold, but a value row is multiplied by its zero weight and must be
-    // finite).  This happens before the barrier is armed, so that whoever passes the barrier
+    // Boxes without a page (past the last key, or given back by the window): the warp clears their value rows
+    // together (their keys are masked by position whatever they hold, but a value row is multiplied by its zero
+    // weight and must be finite).  This happens before the barrier is armed, so that whoever passes the barrier
     // (another warp, in the prompt kernel) sees the cleared rows.
     if (count < boxes) {
-        for (int b = 0; b < boxes; ++b) {
-            const int j = t * BN + b * box_rows;
-            const int logical = j / page_size;
-            const int page = (j <= last_key && logical < table_width) ? table[logical] : -1;
-            if (page >= 0 && page < num_pages) continue;
-            for (int h = 0; h < PANELS; ++h) {
-                const uint32_t off = (uint32_t)(h * (BN * 128) + b * box_rows * 128);
-                for (int i = lane; i < box_rows * 8; i += 32)
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v_dst + off + i * 16), "r"(0u) : "memory");
+#pragma unroll
+        for (int k = 0; k < PER_LANE; ++k) {
+            for (int owner = 0; owner < 32 && 32 * k + owner < boxes; ++owner) {
+                if (__shfl_sync(0xffffffffu, row_k[k], owner) >= 0) continue;
+                const int b = 32 * k + owner;
+                for (int h = 0; h < PANELS; ++h) {
+                    const uint32_t off = (uint32_t)(h * (BN * 128) + b * box_rows * 128);
+                    for (int i = lane; i < box_rows * 8; i += 32)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v_dst + off + i * 16), "r"(0u) : "memory");
+                }
             }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -202,18 +213,16 @@ __device__ __forceinline__ void fill_kv_slot(const CUtensorMap* kv_map, uint32_t
         else sm100::mbar_arrive(bar);
     }
     __syncwarp();
-    for (int b = lane; b < boxes; b += 32) {
-        const int j = t * BN + b * box_rows;
-        const int logical = j / page_size;
-        const int page = (j <= last_key && logical < table_width) ? table[logical] : -1;
-        if (page >= 0 && page < num_pages) {
-            const int row_k = ((page * 2) * kv_heads + kv_head) * page_size + (j % page_size);
-            const int row_v = row_k + kv_heads * page_size;
+    const int value_rows = kv_heads * page_size;
+#pragma unroll
+    for (int k = 0; k < PER_LANE; ++k) {
+        if (row_k[k] >= 0) {
+            const int b = lane + 32 * k;
 #pragma unroll
             for (int h = 0; h < PANELS; ++h) {
                 const uint32_t off = (uint32_t)(h * (BN * 128) + b * box_rows * 128);
-                sm100::tma_load_2d(k_dst + off, kv_map, bar, h * 64, row_k);
-                sm100::tma_load_2d(v_dst + off, kv_map, bar, h * 64, row_v);
+                sm100::tma_load_2d(k_dst + off, kv_map, bar, h * 64, row_k[k]);
+                sm100::tma_load_2d(v_dst + off, kv_map, bar, h * 64, row_k[k] + value_rows);
             }
         }
     }

@@ -388,11 +388,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
                 l *= factor;
                 m_used = m_new;
             }
+            // The second product of the tile before is not behind this tile's scores in issue order.  Its barrier is
+            // waited for in every tile, here if the accumulator must be rescaled and at the end of the tile
+            // otherwise (by then it has long completed): a parity wait cannot tell a phase from the one two before
+            // or after it, so no phase may be skipped.
+            bool seen_before = it == 0;
             if (__any_sync(0xffffffffu, grow && it > 0)) {
                 // rescale this warp's rows of the accumulator (rows that do not need it multiply by 1), once the
-                // second product of the tile before has added into it; that product is not behind this tile's
-                // scores in issue order, so it is waited for
+                // second product of the tile before has added into it
                 if (!mbar_wait_hot(smem_addr(o_ready), (uint32_t)(it - 1) & 1u)) { ok = false; break; }
+                seen_before = true;
                 tc_fence_after();
 #pragma unroll 1
                 for (int c = 0; c < D / 32; ++c) {
@@ -422,14 +427,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
             }
             l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
             tmem_store_wait();
+            if (!seen_before && !mbar_wait_hot(smem_addr(o_ready), (uint32_t)(it - 1) & 1u)) { ok = false; break; }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_addr(&p_ready[it & 1]));
         }
-        // The last tile's scores were issued before the second product of the tile before it, so passing their
-        // barrier says nothing about that product: the barrier's phases are waited for one after the other (a
-        // parity wait cannot tell a phase from the one two before it).
-        if (ok && num_tiles >= 2) ok = mbar_wait_hot(smem_addr(o_ready), (uint32_t)(num_tiles - 2) & 1u);
         if (ok) ok = mbar_wait_hot(smem_addr(o_ready), (uint32_t)(num_tiles - 1) & 1u);
         tc_fence_after();
         if (ok) {

@@ -369,6 +369,33 @@ def test_tensor_core_attention_against_plain(ops, q_heads, kv_heads, head_dim, p
                 assert float((got[r : r + 1] - expected).abs().max()) <= 2.5e-2, (r, ctas)
 
 
+def test_prompt_attention_of_thousands_of_tokens_with_both_kernels(ops):
+    """A prompt long enough that hundreds of CTAs each walk dozens of key tiles: the pipelines' barriers go through
+    many phases (a wait that skipped a phase once stalled only at this size), and the two kernels must agree."""
+    dtype, q_heads, kv_heads, head_dim, page_size, tokens = torch.bfloat16, 8, 2, 128, 16, 4096
+    pages = tokens // page_size + 1
+    generator = torch.Generator().manual_seed(9)
+    cache = (torch.randn(pages, 2, kv_heads, page_size, head_dim, generator=generator) * 0.5).to(dtype).to(DEV)
+    table = torch.arange(pages, dtype=torch.int32, device=DEV)[None, :].contiguous()
+    q = (torch.randn(tokens, q_heads, head_dim, generator=generator)).to(dtype).to(DEV)
+    qs = torch.tensor([0, tokens], dtype=torch.int32, device=DEV)
+    ctx = torch.tensor([tokens], dtype=torch.int32, device=DEV)
+    scale = head_dim ** -0.5
+    for _ in range(3):  # the stall was a matter of timing: several launches
+        fast = ops.attention_prefill(q, cache, table, qs, ctx, tokens, None, scale, tcgen05=True)
+        ops.check_device_errors(torch.device(DEV))
+    slow = ops.attention_prefill(q, cache, table, qs, ctx, tokens, None, scale, tcgen05=False)
+    ops.check_device_errors(torch.device(DEV))
+    assert float((fast.float() - slow.float()).abs().max()) <= 2.5e-2
+    # a few rows against 32-bit arithmetic
+    keys = cache[:, 0].permute(0, 2, 1, 3).reshape(-1, kv_heads, head_dim)[:tokens].float().cpu()
+    values = cache[:, 1].permute(0, 2, 1, 3).reshape(-1, kv_heads, head_dim)[:tokens].float().cpu()
+    for row in (0, 63, 64, 2047, 4095):
+        expected = attention_reference(q[row : row + 1].cpu(), keys.to(dtype), values.to(dtype), [row], None, scale)
+        got = fast[row : row + 1].float().cpu().unflatten(1, (q_heads, head_dim))
+        assert float((got - expected).abs().max()) <= 2.5e-2, row
+
+
 def test_tensor_core_attention_finds_a_far_key(ops):
     """One key among hundreds, far back and on a page edge, is made to dominate: the output must be its value."""
     dtype, q_heads, kv_heads, head_dim, page_size = torch.bfloat16, 8, 2, 128, 16
