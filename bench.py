@@ -250,6 +250,7 @@ def main() -> int:
         torch.cuda.synchronize()
         e2e_seconds = time.perf_counter() - t0
         assert engine.counters["graph_steps"] - launches_before == steps
+        engine.drain()  # the engine queues decode steps one ahead
         # (b) on the device: the captured step feeds itself; pages for the steps ahead are reserved first
         ahead = warmup + steps
         for r in requests:
@@ -278,7 +279,7 @@ def main() -> int:
         result = dict(batch=batch, device_ms=device_ms, tokens_per_s=batch / (device_ms / 1e3),
                       e2e_tokens_per_s=batch * steps / e2e_seconds, e2e_ms=e2e_seconds / steps * 1e3,
                       bytes=step_bytes, gbs=step_bytes / (device_ms / 1e3) / 1e9, context=mean_context,
-                      kernels=graph.kernels_per_replay, h2d=graph.input_bytes, d2h=4 * batch)
+                      kernels=graph.kernels_per_replay, h2d=graph.ahead_input_bytes, d2h=4 * batch + 4)
         for r in requests:
             engine.scheduler.abort(r)
         return result

@@ -20,7 +20,7 @@ from ..sampling.sampler import sample
 from .batch import StepEntry
 from .graphs import DecodeGraphs
 from .runner import ModelRunner
-from .scheduler import Request, Scheduler
+from .scheduler import RUNNING, Request, Scheduled, Scheduler
 
 MAX_NEW_TOKENS_CAP = 65_536       # crates/llm-engine/src/main.rs:25-29
 MAX_PREFILL_TOKENS_CAP = 262_144
@@ -41,7 +41,7 @@ class Engine:
                  dtype: str = "bfloat16", device: str = "cuda:0", max_new_tokens: int = 256,
                  max_prefill_tokens: int = 2048, max_concurrent_requests: int = 4, page_size: int = 16,
                  max_cache_tokens: Optional[int] = None, prefill_chunk: Optional[int] = None,
-                 runner: Optional[ModelRunner] = None, cuda_graphs: bool = True):
+                 runner: Optional[ModelRunner] = None, cuda_graphs: bool = True, overlap_steps: bool = True):
         if not 1 <= max_new_tokens <= MAX_NEW_TOKENS_CAP:
             raise ValueError(f"--max-new-tokens must be within 1..{MAX_NEW_TOKENS_CAP}")
         if not 1 <= max_prefill_tokens <= MAX_PREFILL_TOKENS_CAP:
@@ -77,6 +77,8 @@ class Engine:
         self._next_id = 0
         self.counters = {"steps": 0, "graph_steps": 0, "prompt_tokens": 0, "generated_tokens": 0}
         self.graphs = DecodeGraphs(runner) if cuda_graphs else None
+        self.overlap_steps = overlap_steps
+        self._in_flight = None  # (scheduled, LaunchedStep) of a decode step that is queued or running
 
     # ------------------------------------------------------------------ generate
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> Request:
@@ -90,15 +92,83 @@ class Engine:
         return request
 
     def step(self) -> List[Request]:
-        """One scheduler step; returns the requests that finished in it."""
-        scheduled = self.scheduler.schedule()
-        if self.graphs is not None and scheduled and all(item.count == 1 for item in scheduled):
-            sampled = self._decode_step_with_graph(scheduled)
-        else:
-            sampled = self._general_step(scheduled)
-        self.runner.rt.ops.check_device_errors(self.runner.rt.device)
+        """One scheduler step; returns the requests that finished in it.
+
+        Decode steps that replay a captured graph are queued one ahead: while the device runs a step, the host
+        prepares and queues the next one for the same requests (its input tokens are the ones the running step
+        samples, already on the device), and only then waits for the running step's tokens.  A request that turns
+        out to have finished (end-of-sequence token) has its token of the step queued ahead dropped."""
+        if self._in_flight is None:
+            scheduled = self.scheduler.schedule()
+            if not (self.graphs is not None and scheduled and all(item.count == 1 for item in scheduled)):
+                sampled = self._general_step(scheduled)
+                self.runner.rt.ops.check_device_errors(self.runner.rt.device)
+                self.counters["steps"] += 1
+                return self.scheduler.update(scheduled, sampled)
+            self._in_flight = self._launch_decode(scheduled, ahead=False)
+        current = self._in_flight
+        self._in_flight = self._launch_ahead(current) if self.overlap_steps else None
+        return self._retire(current)
+
+    def drain(self) -> List[Request]:
+        """Waits for a step that is still queued or running and records it; returns the requests it finished."""
+        if self._in_flight is None:
+            return []
+        current, self._in_flight = self._in_flight, None
+        return self._retire(current)
+
+    def _retire(self, flight) -> List[Request]:
+        scheduled, launched = flight
+        tokens = launched.wait()
+        # a request that finished while this step was queued behind its last one: the token is dropped
+        live = [(item, token) for item, token in zip(scheduled, tokens) if item.request.state == RUNNING]
         self.counters["steps"] += 1
-        return self.scheduler.update(scheduled, sampled)
+        return self.scheduler.update([item for item, _ in live], [token for _, token in live])
+
+    def _launch_ahead(self, flight):
+        """Queues the decode step after ``flight`` for the same requests, if nothing about the batch can change:
+        nobody waits for admission, nobody reaches its token limit in ``flight``, every request gets its page
+        without an eviction, and the step replays the same captured graph.  Otherwise None."""
+        scheduled, launched = flight
+        scheduler = self.scheduler
+        if scheduler.waiting or len(scheduled) != len(scheduler.running):
+            return None
+        for item in scheduled:
+            request = item.request
+            if request.state != RUNNING or len(request.output) + 2 > request.max_new_tokens:
+                return None
+        pages = [item.request.pages for item in scheduled]
+        cache = self.runner.cache
+        if not all(cache.reserve(p, 1) for p in pages):
+            return None  # what was reserved stays with its request and is used by its next step
+        ahead = [Scheduled(item.request, item.first + 1, 1, True) for item in scheduled]
+        return self._launch_decode(ahead, ahead=True, same_graph=launched.graph)
+
+    def _launch_decode(self, scheduled, ahead: bool, same_graph=None):
+        """Every request brings one token: queues the captured step for this many requests (the scheduler, or
+        ``_launch_ahead``, has reserved the pages) and returns (scheduled, launched step), or None if ``ahead``
+        and the step would need another graph."""
+        cache = self.runner.cache
+        requests = [item.request for item in scheduled]
+        pages = [r.pages for r in requests]
+        tables = [cache.block_table_array(pages, g) for g in range(len(cache.groups))]
+        width = max([1] + [t.shape[1] for t in tables])
+        graph, fresh = self.graphs.get(len(requests), width, [p.length + 1 for p in pages])
+        if ahead and (fresh or graph is not same_graph):
+            return None  # a capture, or another graph's buffers: that step is queued after this one is known
+        extra = 1 if ahead else 0  # draws that the step in flight will have used
+        graph.load_inputs(
+            None if ahead else [r.token_at(item.first) for r, item in zip(requests, scheduled)],
+            [p.length for p in pages], [p.slot for p in pages], tables, [r.params.temperature for r in requests],
+            [r.params.top_p for r in requests], [rng.draw(r.seed, r.draws_used + extra) for r in requests],
+        )
+        if fresh:
+            graph.capture()
+        launched = graph.launch()
+        for p in pages:
+            cache.commit(p, 1)  # bookkeeping only: the step's cache writes are queued in stream order
+        self.counters["graph_steps"] += 1
+        return scheduled, launched
 
     def _general_step(self, scheduled) -> List[Optional[int]]:
         entries = []
@@ -119,28 +189,6 @@ class Engine:
                 sampled[i] = token
         return sampled
 
-    def _decode_step_with_graph(self, scheduled) -> List[Optional[int]]:
-        """Every request brings one token: replay the captured step for this many requests.
-        The scheduler has reserved the pages; the inputs go to the graph's fixed buffers."""
-        cache = self.runner.cache
-        requests = [item.request for item in scheduled]
-        pages = [r.pages for r in requests]
-        tables = [cache.block_table_array(pages, g) for g in range(len(cache.groups))]
-        width = max([1] + [t.shape[1] for t in tables])
-        graph, fresh = self.graphs.get(len(requests), width, [p.length + 1 for p in pages])
-        graph.load_inputs(
-            [r.token_at(item.first) for r, item in zip(requests, scheduled)], [p.length for p in pages],
-            [p.slot for p in pages], tables, [r.params.temperature for r in requests],
-            [r.params.top_p for r in requests], [rng.draw(r.seed, r.draws_used) for r in requests],
-        )
-        if fresh:
-            graph.capture()
-        tokens = graph.replay().cpu().tolist()
-        for p in pages:
-            cache.commit(p, 1)
-        self.counters["graph_steps"] += 1
-        return list(tokens)
-
     def generate(self, prompts: Sequence[Sequence[int]],
                  params: Union[None, SamplingParams, Sequence[SamplingParams]] = None) -> List[GenerationOutput]:
         """Generates a continuation for every prompt (lists of token ids); results in the prompts' order."""
@@ -151,6 +199,7 @@ class Engine:
         requests = [self.add_request(prompt, p) for prompt, p in zip(prompts, params)]
         while self.scheduler.has_work():
             self.step()
+        self.drain()
         outputs = []
         for request in requests:
             self.counters["prompt_tokens"] += len(request.prompt)

@@ -56,6 +56,11 @@ class DecodeGraph:
         self.tokens_out: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.kernels_per_replay = 0
+        # results of launched steps come back through pinned buffers, two of them in turn: a step's result is
+        # read by the host while the step after it is already queued
+        self.host_tokens = [torch.zeros(B, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.host_flag = [torch.zeros(1, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.launches = 0
 
     def _body(self) -> None:
         ops = self.runner.rt.ops
@@ -67,12 +72,14 @@ class DecodeGraph:
         self.tokens_out = ops.sample_rows(logits, floats[:B], floats[B : 2 * B], floats[2 * B :])
         ops.decode_advance(self.token_ids, self.tokens_out, self.positions, self.context_len)
 
-    def load_inputs(self, token_ids: Sequence[int], positions: Sequence[int], slots: Sequence[int],
+    def load_inputs(self, token_ids: Optional[Sequence[int]], positions: Sequence[int], slots: Sequence[int],
                     tables: Sequence[np.ndarray], temperatures: Sequence[float], top_ps: Sequence[float],
                     draws: Sequence[float]) -> None:
-        """Copies a step's inputs from pinned host memory to the fixed device buffers (two copies)."""
+        """Copies a step's inputs from pinned host memory to the fixed device buffers (two copies).
+        ``token_ids`` None leaves the token buffer as the step before left it: the tokens it sampled."""
         B = self.num_requests
-        self._host[0].copy_(torch.as_tensor(token_ids, dtype=torch.int32))
+        if token_ids is not None:
+            self._host[0].copy_(torch.as_tensor(token_ids, dtype=torch.int32))
         position_tensor = torch.as_tensor(positions, dtype=torch.int32)
         self._host[1].copy_(position_tensor)
         self._host[2].copy_(position_tensor + 1)
@@ -84,12 +91,18 @@ class DecodeGraph:
         self.host_floats[:B] = torch.as_tensor(temperatures, dtype=torch.float32)
         self.host_floats[B : 2 * B] = torch.as_tensor(top_ps, dtype=torch.float32)
         self.host_floats[2 * B :] = torch.as_tensor(draws, dtype=torch.float32)
-        self.dev_ints.copy_(self.host_ints, non_blocking=True)
+        first = 0 if token_ids is not None else self.offsets[1]
+        self.dev_ints[first:].copy_(self.host_ints[first:], non_blocking=True)
         self.dev_floats.copy_(self.host_floats, non_blocking=True)
 
     @property
     def input_bytes(self) -> int:
         return self.host_ints.numel() * 4 + self.host_floats.numel() * 4
+
+    @property
+    def ahead_input_bytes(self) -> int:
+        """What a step copies that takes its tokens from the step before it on the device."""
+        return (self.host_ints.numel() - self.offsets[1]) * 4 + self.host_floats.numel() * 4
 
     def capture(self) -> None:
         """Runs the step once eagerly (so that everything lazy has happened), then captures it.
@@ -114,6 +127,34 @@ class DecodeGraph:
     def replay(self) -> torch.Tensor:
         self.graph.replay()
         return self.tokens_out
+
+    def launch(self) -> "LaunchedStep":
+        """Replays without waiting: the sampled tokens and the device error word are copied to pinned host
+        memory behind the step, and an event marks the copies' end."""
+        index = self.launches & 1
+        self.launches += 1
+        self.graph.replay()
+        self.host_tokens[index].copy_(self.tokens_out, non_blocking=True)
+        self.host_flag[index].copy_(self.runner.rt.ops.error_flag(self.runner.rt.device), non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return LaunchedStep(self, index, event)
+
+
+class LaunchedStep:
+    """A decode step that is queued or running on the device."""
+
+    def __init__(self, graph: DecodeGraph, index: int, event: torch.cuda.Event):
+        self.graph, self.index, self.event = graph, index, event
+
+    def wait(self) -> List[int]:
+        """Waits for the step; raises if a kernel set the device error word; returns the sampled tokens."""
+        self.event.synchronize()
+        ops = self.graph.runner.rt.ops
+        value = int(self.graph.host_flag[self.index][0])
+        if value != 0:
+            ops.check_device_errors(self.graph.runner.rt.device)  # reads, clears and raises
+        return self.graph.host_tokens[self.index].tolist()
 
 
 class DecodeGraphs:
@@ -153,5 +194,4 @@ class DecodeGraphs:
         if graph is None:
             graph = DecodeGraph(self.runner, key[0], key[1], balanced)
             self.graphs[key] = graph
-            return graph, True
-        return graph, False
+        return graph, graph.graph is None

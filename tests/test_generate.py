@@ -114,6 +114,42 @@ def test_eviction_and_recompute_give_the_same_tokens(tiny):
     assert tight.stats()["scheduler"]["preemptions"] >= 1 and sum(o.preemptions for o in outputs) >= 1
 
 
+def test_steps_queued_ahead_give_the_same_tokens_and_drop_what_follows_a_stop(tiny):
+    """Decode steps are queued one ahead of the host's knowledge of their input tokens.  With and without that, the
+    same requests (different lengths, seeded sampling, one stop token that ends a request early while its next
+    step is already queued) must produce the same tokens, and nothing stays reserved."""
+    from kirai_b200 import Engine, SamplingParams
+
+    vocab = tiny["raw"]["vocab_size"]
+    prompts = [random_tokens(n, vocab, 30 + n) for n in (7, 12, 4)]
+    base = dict(dtype="float32", page_size=tiny["page"], max_prefill_tokens=16, max_concurrent_requests=3,
+                max_new_tokens=32, max_cache_tokens=512)
+    plain_params = [SamplingParams(temperature=0.9, top_p=0.95, seed=21 + i, max_new_tokens=24, ignore_eos=True) for i in range(3)]
+    reference = Engine(tiny["folder"], overlap_steps=False, **base).generate(prompts, plain_params)
+    # a stop token for the second request: the 6th token that it generates without one
+    stop = reference[1].token_ids[5]
+    params = list(plain_params)
+    params[1] = SamplingParams(temperature=0.9, top_p=0.95, seed=22, max_new_tokens=24, eos_token_id=stop)
+    expected = Engine(tiny["folder"], overlap_steps=False, **base).generate(prompts, params)
+    assert expected[1].finish_reason == "stop" and len(expected[1].token_ids) <= 6
+    engine = Engine(tiny["folder"], overlap_steps=True, **base)
+    outputs = engine.generate(prompts, params)
+    for got, want in zip(outputs, expected):
+        assert got.token_ids == want.token_ids and got.finish_reason == want.finish_reason
+    stats = engine.stats()
+    assert stats["graph_steps"] > 0
+    assert stats["cache"]["live_requests"] == 0 and all(g["used"] == 0 for g in stats["cache"]["groups"])
+    # step by step: every call returns the requests that one step finished, and a drained engine holds nothing
+    stepping = Engine(tiny["folder"], overlap_steps=True, **base)
+    requests = [stepping.add_request(p, q) for p, q in zip(prompts, params)]
+    finished = []
+    while stepping.scheduler.has_work():
+        finished += stepping.step()
+    finished += stepping.drain()
+    assert sorted(id(r) for r in finished) == sorted(id(r) for r in requests)
+    assert [r.output for r in requests] == [o.token_ids for o in expected]
+
+
 def test_command_line(tiny):
     command = [sys.executable, os.path.join(ROOT, "bin", "kirai"), "generate", "--snapshot", tiny["folder"],
                "--prompt-ids", "5,17,3,44", "--prompt-ids", "9,8,7", "--max-tokens", "6", "--temperature", "0",
