@@ -414,6 +414,79 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 // run side by side share a weight tile in L2).  Tensor memory holds two accumulators of BN
 // columns: while the epilogue warps read one back, convert and store it, the MMA thread already
 // fills the other with the next tile, and the TMA warp runs ahead across tile borders.
+// The residual-and-norm epilogue of one 128 x BN tile for one warp (32 rows), with coalesced global accesses.  A
+// thread holds a row of the accumulator, so touching the 32-bit stream from that layout costs a cache-line
+// wavefront per row and instruction, eight times the lines' worth; measured, the epilogue then took longer than
+// the tile's products.  Here 32 columns at a time go through a per-warp staging buffer in shared memory (16-byte
+// slots, slot c of row r at c ^ (r % 8)) and come back with eight lanes per row, so that an instruction covers four
+// rows of 128 contiguous bytes.  Needs N % 4 == 0 and 16-byte aligned stream, norm weights and output.
+__device__ __forceinline__ void epilogue_residual_norm_coalesced(const Epilogue& ep, __nv_bfloat16* __restrict__ C, long ldc,
+                                                                 uint32_t tmem_acc, float4* stage, int row0, int y0,
+                                                                 int columns, int M, int N, int n_tile, int lane) {
+    const int sub_row = lane >> 3, slot = lane & 7;  // in the coalesced layout: row 4 i + sub_row, columns 4 slot .. + 3
+    float row_sq[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    // the stream's values of a chunk, in the coalesced layout; requested one chunk ahead of their use
+    auto load_chunk = [&](int c0, float4 (&res)[8]) {
+        const int gc = y0 + c0 + slot * 4;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int gr = row0 + 4 * i + sub_row;
+            res[i] = (c0 < columns && gr < M && gc + 4 <= N) ? *reinterpret_cast<const float4*>(ep.residual + (size_t)gr * N + gc)
+                                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    float4 res[8], res_next[8];
+    load_chunk(0, res);
+#pragma unroll 1
+    for (int c0 = 0; c0 < columns; c0 += 32) {
+        if (y0 + c0 >= N) break;  // uniform across the warp
+        const int gc = y0 + c0 + slot * 4;
+        const bool col_ok = gc + 4 <= N;
+        load_chunk(c0 + 32, res_next);
+        const float4 w = col_ok ? *reinterpret_cast<const float4*>(ep.norm_weight + gc) : make_float4(0.f, 0.f, 0.f, 0.f);
+        uint32_t r[32];
+        tmem_load_32x32(tmem_acc + (uint32_t)c0, r);
+        tmem_load_wait();
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            stage[lane * 8 + (q ^ (lane & 7))] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                             __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int local_row = 4 * i + sub_row;
+            const int gr = row0 + local_row;
+            const float4 acc = stage[local_row * 8 + (slot ^ (local_row & 7))];
+            float sq = 0.0f;
+            if (gr < M && col_ok) {
+                float4 sum = res[i];
+                sum.x += acc.x, sum.y += acc.y, sum.z += acc.z, sum.w += acc.w;
+                *reinterpret_cast<float4*>(ep.residual + (size_t)gr * N + gc) = sum;
+                sq = (sum.x * sum.x + sum.y * sum.y) + (sum.z * sum.z + sum.w * sum.w);
+                __nv_bfloat162 lo = __floats2bfloat162_rn(sum.x * w.x, sum.y * w.y), hi = __floats2bfloat162_rn(sum.z * w.z, sum.w * w.w);
+                uint2 packed;
+                packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(C + (size_t)gr * ldc + gc) = packed;
+            }
+            sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+            sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+            sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+            row_sq[i] += sq;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) res[i] = res_next[i];
+        __syncwarp();  // the staging buffer is rewritten by the next chunk
+    }
+    if (slot == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int gr = row0 + 4 * i + sub_row;
+            if (gr < M) ep.sumsq_out[(size_t)n_tile * M + gr] = row_sq[i];  // this column tile's share
+        }
+    }
+}
+
 template <int BN, typename OutT, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
@@ -537,6 +610,9 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
         const int lane_group = warp & 3;
         const int tile_row = lane_group * 32 + lane;
         pdl_wait();  // the output buffer may still be read by the kernel before this one
+        // whether the residual-and-norm epilogue can take its coalesced form (whole 16-byte pieces everywhere)
+        const bool coalesced = EPI == 2 && N % 4 == 0 && ldc % 4 == 0 &&
+                               (((uintptr_t)ep.residual | (uintptr_t)ep.norm_weight | (uintptr_t)C) & 15) == 0;
         int local = 0;
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
             const int buf = local & 1;
@@ -546,13 +622,32 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
             // EPI 2: the stream's values are fetched two chunks of 16 columns ahead of their use, the first two
             // before this tile's products are done
             ResidualChunk cur, next, after;
-            if (EPI == 2) {
+            if (EPI == 2 && !coalesced) {
                 load_residual_chunk(ep, x_row, y0, M, N, cur);
                 load_residual_chunk(ep, x_row, y0 + 16, M, N, next);
+            }
+            if (EPI == 2 && coalesced) {
+                // while this tile's products run: ask for its part of the stream to be brought into L2 (the weights
+                // that stream through in between push it out); a line of 128 bytes per request, a row per lane
+                const int gr = x0 + lane_group * 32 + lane;
+                if (gr < M) {
+                    const char* line = reinterpret_cast<const char*>(ep.residual + (size_t)gr * N + y0);
+                    const int bytes = min(BN, N - y0) * 4;
+                    for (int off = 0; off < bytes; off += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(line + off));
+                }
             }
             if (!mbar_wait(smem_addr(&acc_full[buf]), (uint32_t)(local >> 1) & 1u)) { ok = false; break; }
             tc_fence_after();
             const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * tmem_columns<BN>()) + ((uint32_t)(lane_group * 32) << 16);
+            if (EPI == 2 && sizeof(OutT) == 2 && coalesced) {
+                float4* stage = reinterpret_cast<float4*>(smem + STAGES * Smem::stage_bytes + Smem::barrier_bytes) + lane_group * 256;
+                epilogue_residual_norm_coalesced(ep, reinterpret_cast<__nv_bfloat16*>(C), ldc, tmem_acc, stage, x0 + lane_group * 32,
+                                                 y0, BN, M, N, n_tile, lane);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_addr(&acc_empty[buf]));
+                continue;
+            }
             const float my_scale = (ep.row_sumsq && x_row < M) ? row_scale_of(ep, x_row, M) : 1.0f;
             float row_sq = 0.0f;
 #pragma unroll 1
@@ -679,9 +774,10 @@ static int launch_persistent(const void* A, const void* W, bool tiled, void* C, 
     }
     const unsigned grid = (unsigned)(tiles < sm_count ? tiles : sm_count);
     auto kernel = gemm_tcgen05_persistent_kernel<BN, OutT, EPI>;
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total(1));
+    const int smem_bytes = Smem::total(1) + (EPI == 2 ? 4 * 32 * 32 * 4 : 0);  // + the epilogue's staging buffers
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (err != cudaSuccess) return (int)err;
-    return launch_pdl(kernel, dim3(grid), dim3(GEMM_THREADS), (size_t)Smem::total(1), stream, 1u, map_a, map_w,
+    return launch_pdl(kernel, dim3(grid), dim3(GEMM_THREADS), (size_t)smem_bytes, stream, 1u, map_a, map_w,
                       tiled ? (const uint8_t*)W : (const uint8_t*)nullptr, (OutT*)C, M, N, K, ldc, ep, error_flag);
 }
 

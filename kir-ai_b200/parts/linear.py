@@ -8,6 +8,7 @@ and reads them under their stored names
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -48,7 +49,8 @@ class Linear(Part):
 
     def fuses_norms(self, rows: int) -> bool:
         """Whether a batch of ``rows`` tokens should have the norms next to this product folded into it."""
-        return self.on_tensor_cores() and rows <= self.FUSED_NORM_MAX_ROWS
+        limit = int(os.environ.get("KIRAI_FUSED_NORM_MAX_ROWS", self.FUSED_NORM_MAX_ROWS))
+        return self.on_tensor_cores() and rows <= limit
 
     def forward_into_norm(self, x: torch.Tensor, resid: torch.Tensor, spec: FusedNormSpec) -> UnscaledNorm:
         """resid += x W^T in place; returns the sum's rows under the norm ``spec`` without their 1 / rms factor."""
