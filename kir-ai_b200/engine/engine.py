@@ -127,12 +127,14 @@ class Engine:
 
     def _launch_ahead(self, flight):
         """Queues the decode step after ``flight`` for the same requests, if nothing about the batch can change:
-        nobody waits for admission, nobody reaches its token limit in ``flight``, every request gets its page
+        nobody can be admitted (no one waits, or the running set is full), nobody reaches its token limit in ``flight``, every request gets its page
         without an eviction, and the step replays the same captured graph.  Otherwise None."""
         scheduled, launched = flight
         scheduler = self.scheduler
-        if scheduler.waiting or len(scheduled) != len(scheduler.running):
+        if len(scheduled) != len(scheduler.running):
             return None
+        if scheduler.waiting and len(scheduler.running) < scheduler.max_running:
+            return None  # a waiting request may be admitted into the next step
         for item in scheduled:
             request = item.request
             if request.state != RUNNING or len(request.output) + 2 > request.max_new_tokens:
