@@ -8,11 +8,13 @@
 //    where the query rows enumerate (token, head of the group) pairs, so that
 //    the heads of a group share each key/value tile; 4 warps own 16 rows each
 //    and a fifth keeps a ring of 3 key/value tiles full by TMA from the pages;
-//  * the decode kernel, for batches in which every request brings one token:
-//    one CTA per (request, kv head, split of the context); the group's heads
-//    are the (few) query rows, each warp walks its own key tiles through its
-//    own TMA ring, the warps' states are merged in shared memory, and with
-//    several splits a second kernel merges the splits' partial states.
+//  * the decode kernels, for batches in which every request brings one token: the group's heads are the (few)
+//    query rows, each of a CTA's warps walks its own 16-key tiles through its own three-slot TMA ring, and the
+//    warps' states are merged in shared memory.  The split kernel runs one CTA per (request, kv head, split of
+//    the context) and a second kernel merges the splits; the balanced kernel cuts the key tiles of all
+//    (request, kv head) pairs into one equal range per CTA and merges only the pairs that a range border cut.
+//    Both read what a step cannot change (block tables, lengths, keys and values of earlier steps) before they
+//    wait for the kernel before them.
 //
 // Keys are visible to a row at position pos when lo <= j <= pos, lo = max(0,
 // pos - window + 1) with a window, else 0 (same rule as the plain kernel).
@@ -514,7 +516,8 @@ __device__ __forceinline__ void warp_attend_heads(HeadState<D>& st, const uint32
 
 // ------------------------------------------------------------------ decode kernel
 #define DC_STAGES 3
-// Four warps; keys per warp tile: 32, or 16 for the widest heads so that the warps' rings fit shared memory.
+// Keys per warp tile: 16 (one page at the usual page size); eight warps, four for the widest heads so that the
+// warps' rings fit shared memory.
 template <int D>
 struct DecodeTile {
     static constexpr int BN = 16;

@@ -13,10 +13,11 @@
 // of warp 1 issues the MMAs and owns the tensor-memory allocation, warps 2-5
 // read the accumulator back (tcgen05.ld) and store the tile.  With split-K the
 // CTAs of a thread-block cluster cover ranges of K of one tile and the partial
-// tiles are added through distributed shared memory, in rank order.  An
-// epilogue variant applies SwiGLU to interleaved gate and up rows.  Every
-// barrier wait is bounded; a wait that runs out sets the device error flag and
-// the CTA winds down.
+// tiles are added through distributed shared memory, in rank order.  Epilogue
+// variants: SwiGLU over interleaved gate and up rows; the residual add with the
+// next RMSNorm's unscaled rows and sums of squares; a per-row 1/rms scale on the
+// result (see Epilogue).  Every barrier wait is bounded; a wait that runs out sets
+// the device error flag and the CTA winds down.
 //
 // The kernel is launched with programmatic stream serialization and starts
 // fetching W before the kernel before it in the stream has finished; it waits
