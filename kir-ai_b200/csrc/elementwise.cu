@@ -620,6 +620,125 @@ qk_norm_rope_kv_write_vec_kernel(T* __restrict__ qkv, const float* __restrict__ 
     }
 }
 
+// The same work for bf16 heads of 64, 128 or 256: LANES = head_dim / 16 lanes share a head, each with eight adjacent
+// values of both halves (16-byte loads and stores), so that a warp handles 32 / LANES heads at once.  With one pair
+// of values per lane and instruction the kernel above is bound by its instruction count when there are thousands of
+// tokens (16.9 M warp instructions for 2,048 tokens of 48 heads); this form needs about a sixth per value.
+template <int LANES>
+__global__ void __launch_bounds__(FUSED_WARPS * 32)
+qk_norm_rope_kv_write_wide_kernel(bf16* __restrict__ qkv, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                                  const float* __restrict__ inv_freq, bf16* __restrict__ cache,
+                                  const int* __restrict__ block_table, const int* __restrict__ request_of_token,
+                                  const int* __restrict__ positions, int rows, int q_heads, int kv_heads, float eps,
+                                  int page_size, int table_width, int num_pages, int write_cache,
+                                  int* __restrict__ error_flag) {
+    constexpr int HEAD_DIM = LANES * 16, HALF = HEAD_DIM / 2, HEADS_PER_WARP = 32 / LANES;
+    pdl_launch_dependents();
+    // positions, the request of each token and the block tables are constant during a step: the angles and the
+    // page are worked out before the kernel before this one (the q, k, v product) has finished
+    __shared__ __align__(16) float cos_s[HALF], sin_s[HALF];
+    const int heads_total = q_heads + 2 * kv_heads;
+    const int row = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int pos = positions[row];
+    if (inv_freq) {
+        for (int i = threadIdx.x; i < HALF; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sin_s[i], &cos_s[i]);
+        __syncthreads();
+    }
+    int page = -1;
+    if (write_cache) {
+        const int logical = pos / page_size;
+        page = logical < table_width ? block_table[(long)request_of_token[row] * table_width + logical] : -1;
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicExch(error_flag, 2);
+            page = -1;
+        }
+    }
+    const int slot_in_page = pos % page_size;
+    pdl_wait();
+    const int sub = lane % LANES;  // this lane's eight values of each half start at 8 * sub
+    const int stride = gridDim.y * FUSED_WARPS * HEADS_PER_WARP;  // heads that the token's warps take per round
+    const bool any_norm = q_weight != nullptr || k_weight != nullptr;
+    for (int base = (blockIdx.y * FUSED_WARPS + warp) * HEADS_PER_WARP; base < heads_total; base += stride) {
+        // whole warps stay in the loop for the shuffles; lanes past the last head carry zeros and store nothing
+        const int head = base + lane / LANES;
+        const bool live = head < heads_total;
+        const bool is_q = head < q_heads;
+        const bool is_k = !is_q && head < q_heads + kv_heads;
+        uint4* x = reinterpret_cast<uint4*>(qkv + (size_t)row * heads_total * HEAD_DIM + (size_t)(live ? head : 0) * HEAD_DIM);
+        uint4 raw_lo = make_uint4(0u, 0u, 0u, 0u), raw_hi = raw_lo;
+        if (live) {
+            raw_lo = x[sub];
+            raw_hi = x[sub + LANES];
+        }
+        uint4* dst = nullptr;
+        if (live && !is_q && write_cache && page >= 0) {
+            const int kv_head = is_k ? head - q_heads : head - q_heads - kv_heads;
+            dst = reinterpret_cast<uint4*>(cache + kv_row_offset(page, is_k ? 0 : 1, kv_head, slot_in_page, kv_heads, page_size, HEAD_DIM));
+        }
+        const bool transform = live && (is_q || is_k);
+        float lo[8], hi[8];
+        {
+            const __nv_bfloat162* pl = reinterpret_cast<const __nv_bfloat162*>(&raw_lo);
+            const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&raw_hi);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 a = __bfloat1622float2(pl[j]), b = __bfloat1622float2(ph[j]);
+                lo[2 * j] = a.x, lo[2 * j + 1] = a.y, hi[2 * j] = b.x, hi[2 * j + 1] = b.y;
+            }
+        }
+        const float* weight = is_q ? q_weight : k_weight;
+        if (any_norm) {  // the same for every lane of the warp
+            float acc = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc = fmaf(lo[j], lo[j], fmaf(hi[j], hi[j], acc));
+#pragma unroll
+            for (int d = 1; d < LANES; d <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+            if (transform && weight) {
+                const float variance = acc / (float)HEAD_DIM + eps;
+                const float scale = variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
+                const float4* wl = reinterpret_cast<const float4*>(weight + 8 * sub);
+                const float4* wh = reinterpret_cast<const float4*>(weight + HALF + 8 * sub);
+                const float4 w0 = wl[0], w1 = wl[1], w2 = wh[0], w3 = wh[1];
+                const float wlo[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                const float whi[8] = {w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) lo[j] = lo[j] * scale * wlo[j], hi[j] = hi[j] * scale * whi[j];
+            }
+        }
+        if (transform && inv_freq) {
+            const float4* cs = reinterpret_cast<const float4*>(cos_s + 8 * sub);
+            const float4* sn = reinterpret_cast<const float4*>(sin_s + 8 * sub);
+            const float4 c0 = cs[0], c1 = cs[1], s0 = sn[0], s1 = sn[1];
+            const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float a = lo[j], b = hi[j];
+                lo[j] = a * c[j] - b * sv[j];
+                hi[j] = b * c[j] + a * sv[j];
+            }
+        }
+        if (!live) continue;
+        uint4 out_lo = raw_lo, out_hi = raw_hi;
+        if (transform) {
+            __nv_bfloat162* pl = reinterpret_cast<__nv_bfloat162*>(&out_lo);
+            __nv_bfloat162* ph = reinterpret_cast<__nv_bfloat162*>(&out_hi);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                pl[j] = __floats2bfloat162_rn(lo[2 * j], lo[2 * j + 1]);
+                ph[j] = __floats2bfloat162_rn(hi[2 * j], hi[2 * j + 1]);
+            }
+            x[sub] = out_lo;
+            x[sub + LANES] = out_hi;
+        }
+        if (dst) {
+            dst[sub] = out_lo;
+            dst[sub + LANES] = out_hi;
+        }
+    }
+}
+
 template <typename T>
 static int qk_norm_rope_kv_write_launch(void* qkv, const float* q_weight, const float* k_weight, const float* inv_freq,
                                         void* cache, const int* block_table, const int* request_of_token,
@@ -634,6 +753,20 @@ static int qk_norm_rope_kv_write_launch(void* qkv, const float* q_weight, const 
     const int head_blocks = rows >= 1024 ? 1 : (heads_total + FUSED_WARPS - 1) / FUSED_WARPS;
     const bool pairs_aligned = head_dim % 4 == 0 && ((uintptr_t)qkv & 7) == 0 && ((uintptr_t)cache & 7) == 0 &&
                                ((uintptr_t)q_weight & 7) == 0 && ((uintptr_t)k_weight & 7) == 0;
+    // bf16 heads of 64, 128 or 256 on 16-byte boundaries: the wide kernel
+    if (sizeof(T) == 2 && (head_dim == 64 || head_dim == 128 || head_dim == 256) && ((uintptr_t)qkv & 15) == 0 &&
+        ((uintptr_t)cache & 15) == 0 && ((uintptr_t)q_weight & 15) == 0 && ((uintptr_t)k_weight & 15) == 0) {
+        const int per_warp = 32 / (head_dim / 16);
+        const int wide_blocks = rows >= 1024 ? 1 : (heads_total + FUSED_WARPS * per_warp - 1) / (FUSED_WARPS * per_warp);
+#define KIRAI_FUSED_WIDE(LANES)                                                                                         \
+    return launch_pdl(qk_norm_rope_kv_write_wide_kernel<LANES>, dim3(rows, wide_blocks), dim3(FUSED_WARPS * 32), 0, stream, \
+                      1u, (bf16*)qkv, q_weight, k_weight, inv_freq, (bf16*)cache, block_table, request_of_token, positions, \
+                      rows, q_heads, kv_heads, eps, page_size, table_width, num_pages, write_cache, error_flag)
+        if (head_dim == 64) KIRAI_FUSED_WIDE(4);
+        if (head_dim == 128) KIRAI_FUSED_WIDE(8);
+        KIRAI_FUSED_WIDE(16);
+#undef KIRAI_FUSED_WIDE
+    }
 #define KIRAI_FUSED_VEC(SLOTS)                                                                                          \
     return launch_pdl(qk_norm_rope_kv_write_vec_kernel<T, SLOTS>, dim3(rows, head_blocks), dim3(FUSED_WARPS * 32), 0, stream, \
                       1u, (T*)qkv, q_weight, k_weight, inv_freq, (T*)cache, block_table, request_of_token, positions, rows, \

@@ -237,7 +237,7 @@ def test_kv_write_and_paged_attention(ops, dtype, q_heads, kv_heads, head_dim, p
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("q_heads,kv_heads,head_dim", [(6, 2, 48), (4, 4, 16), (8, 2, 128), (2, 1, 512)])
+@pytest.mark.parametrize("q_heads,kv_heads,head_dim", [(6, 2, 48), (4, 4, 16), (8, 2, 128), (2, 1, 512), (3, 1, 64), (5, 2, 256), (32, 8, 128)])
 def test_fused_norm_rope_cache_write_equals_the_separate_kernels(ops, dtype, q_heads, kv_heads, head_dim):
     page_size, lengths = 8, [11, 30]
     cache_a, table, _, _ = paged_setup(dtype, lengths, kv_heads, head_dim, page_size)
