@@ -194,8 +194,10 @@ def main() -> int:
     page_size = 16
     context = args.context
     torch.cuda.set_device(0)
+    # what a request may generate while the others are still being filled, and while it is warmed up and timed twice
+    new_token_cap = max_batch * -(-context // args.prefill_tokens) + 4 * (warmup + steps) + 64
     engine = Engine(config=config, random_weights_seed=2, dtype="bfloat16", page_size=page_size,
-                    max_new_tokens=4096, max_prefill_tokens=args.prefill_tokens, max_concurrent_requests=max_batch,
+                    max_new_tokens=new_token_cap, max_prefill_tokens=args.prefill_tokens, max_concurrent_requests=max_batch,
                     max_cache_tokens=max_batch * (context + 256))
     runner = engine.runner
     generator = torch.Generator().manual_seed(1234)
@@ -235,7 +237,7 @@ def main() -> int:
         budget = args.prefill_tokens
         fill_steps = batch * -(-context // budget)
         filled = max(16, context - (2 * (warmup + steps) + 4) - fill_steps)
-        params = SamplingParams(temperature=0.0, max_new_tokens=4096, ignore_eos=True)
+        params = SamplingParams(temperature=0.0, max_new_tokens=new_token_cap, ignore_eos=True)
         requests = [engine.add_request(random_prompt(filled), params) for _ in range(batch)]
         while any(r.pending > 1 or not r.output for r in requests):
             engine.step()  # prompt portions under the token budget, then the first sampled tokens
