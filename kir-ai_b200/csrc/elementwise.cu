@@ -60,9 +60,15 @@ __global__ void embedding_tiled_kernel(const uint4* __restrict__ boxes, const in
     for (int chunk = threadIdx.x; chunk * 8 < hidden; chunk += blockDim.x) {
         const uint4 raw = tile[(size_t)(chunk / 8) * 1024 + r * 8 + ((chunk % 8) ^ (r % 8))];
         const bf16* values = reinterpret_cast<const bf16*>(&raw);
+        if (chunk * 8 + 8 <= hidden && (((uintptr_t)(dst + chunk * 8)) & 15) == 0) {
+            float4* wide = reinterpret_cast<float4*>(dst + chunk * 8);
+            wide[0] = make_float4(to_f32<bf16>(values[0]), to_f32<bf16>(values[1]), to_f32<bf16>(values[2]), to_f32<bf16>(values[3]));
+            wide[1] = make_float4(to_f32<bf16>(values[4]), to_f32<bf16>(values[5]), to_f32<bf16>(values[6]), to_f32<bf16>(values[7]));
+        } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (chunk * 8 + j < hidden) dst[chunk * 8 + j] = to_f32<bf16>(values[j]);
+            for (int j = 0; j < 8; ++j)
+                if (chunk * 8 + j < hidden) dst[chunk * 8 + j] = to_f32<bf16>(values[j]);
+        }
     }
 }
 
