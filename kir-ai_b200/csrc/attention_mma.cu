@@ -949,18 +949,36 @@ __global__ void attention_merge_splits_kernel(const float* __restrict__ partial,
                                               int num_splits) {
     pdl_launch_dependents();
     pdl_wait();
-    // one block per (request, head)
+    // one block per (request, head); the splits are read eight at a time, so that their loads are in flight together
     const size_t rh = blockIdx.x;
-    const float* base = partial + rh * num_splits * (head_dim + 2);
+    const int stride = head_dim + 2;
+    const float* base = partial + rh * num_splits * stride;
     float m_all = -INFINITY;
-    for (int s = 0; s < num_splits; ++s) m_all = fmaxf(m_all, base[(size_t)s * (head_dim + 2) + head_dim]);
+    for (int s0 = 0; s0 < num_splits; s0 += 8) {
+        float m[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) m[u] = s0 + u < num_splits ? base[(size_t)(s0 + u) * stride + head_dim] : -INFINITY;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) m_all = fmaxf(m_all, m[u]);
+    }
     for (int col = threadIdx.x; col < head_dim; col += blockDim.x) {
         float acc = 0.0f, l_all = 0.0f;
-        for (int s = 0; s < num_splits; ++s) {
-            const float* src = base + (size_t)s * (head_dim + 2);
-            const float weight = src[head_dim] == -INFINITY ? 0.0f : exp2f(src[head_dim] - m_all);
-            acc += src[col] * weight;
-            l_all += src[head_dim + 1] * weight;
+        for (int s0 = 0; s0 < num_splits; s0 += 8) {
+            float m[8], l[8], value[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const bool live = s0 + u < num_splits;
+                const float* src = base + (size_t)(live ? s0 + u : 0) * stride;
+                m[u] = live ? src[head_dim] : -INFINITY;
+                l[u] = live ? src[head_dim + 1] : 0.0f;
+                value[u] = live ? src[col] : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float weight = m[u] == -INFINITY ? 0.0f : exp2f(m[u] - m_all);
+                acc += value[u] * weight;
+                l_all += l[u] * weight;
+            }
         }
         out[rh * head_dim + col] = from_f32<bf16>(l_all > 0.0f ? acc / l_all : 0.0f);
     }
