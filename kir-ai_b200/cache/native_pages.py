@@ -157,6 +157,27 @@ class NativePageTables:
         self.live[request_id] = request
         return request
 
+    # -- for the native scheduler, which opens and closes requests itself ----------------------------
+    def new_key(self) -> int:
+        """A key that no request of these tables has had."""
+        key = self._next_key
+        self._next_key += 1
+        return key
+
+    def adopt(self, request_id, key: int, slot: int) -> NativeRequest:
+        """The handle of a request that native code has opened under ``key``."""
+        if request_id in self.live:
+            raise CacheError(f"request {request_id!r} is already live")
+        request = NativeRequest(self, request_id, key, slot)
+        self.live[request_id] = request
+        return request
+
+    def disown(self, request: NativeRequest) -> None:
+        """Marks the handle of a request that native code has closed."""
+        if not request.closed:
+            request.closed = True
+            self.live.pop(request.request_id, None)
+
     def _alive(self, request: NativeRequest) -> None:
         if request.closed:
             raise CacheError(f"request {request.request_id!r} is closed")

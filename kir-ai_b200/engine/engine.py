@@ -20,7 +20,7 @@ from ..sampling.sampler import sample
 from .batch import StepEntry
 from .graphs import DecodeGraphs
 from .runner import ModelRunner
-from .scheduler import RUNNING, Request, Scheduled, Scheduler
+from .scheduler import RUNNING, NativeScheduler, Request, Scheduled, Scheduler
 
 MAX_NEW_TOKENS_CAP = 65_536       # crates/llm-engine/src/main.rs:25-29
 MAX_PREFILL_TOKENS_CAP = 262_144
@@ -69,7 +69,12 @@ class Engine:
                 runner = ModelRunner.from_folder(snapshot, **common)
         self.runner = runner
         self.max_new_tokens = max_new_tokens
-        self.scheduler = Scheduler(
+        # the scheduler's decisions run in native code when the cache's page tables do (the default); the Python
+        # class decides the same and stays as the readable model
+        from ..cache.native_pages import NativePageTables
+
+        scheduler_class = NativeScheduler if isinstance(runner.cache.tables, NativePageTables) else Scheduler
+        self.scheduler = scheduler_class(
             runner.cache, max_batched_tokens=max_prefill_tokens, max_running=max_concurrent_requests,
             prefill_chunk=prefill_chunk, max_positions=runner.model.plan.max_positions,
             default_max_new_tokens=max_new_tokens,

@@ -49,6 +49,7 @@ class Request:
     computed: int = 0              # tokens whose keys and values are in the cache
     draws_used: int = 0            # random draws consumed so far
     preemptions: int = 0
+    key: int = 0                   # the native scheduler's name for the request
 
     @property
     def tokens(self) -> List[int]:
@@ -249,3 +250,133 @@ class Scheduler:
             self.waiting.remove(request)
         request.finish_reason = "aborted"
         self._finish(request)
+
+
+class NativeScheduler(Scheduler):
+    """The same scheduler with its decisions made in native code (csrc/scheduler.cpp) on the native page tables.
+
+    The native side knows requests by key and counts; token values, options and stop conditions stay here, and
+    the lists ``waiting`` and ``running`` and the requests' fields mirror what the native side decided.  The Python
+    class above is the readable model of the same rules; the tests run both on the same random workloads."""
+
+    def __init__(self, cache, **kwargs):
+        super().__init__(cache, **kwargs)
+        import ctypes
+
+        from ..cache.native_pages import NativePageTables, _library
+
+        if not isinstance(cache.tables, NativePageTables):
+            raise ValueError("the native scheduler works on the native page tables")
+        self._ctypes = ctypes
+        self._lib = lib = _library()
+        lib.kirai_sched_create.restype = ctypes.c_void_p
+        lib.kirai_sched_create.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_long, ctypes.c_long, ctypes.c_long]
+        lib.kirai_sched_destroy.argtypes = [ctypes.c_void_p]
+        lib.kirai_sched_add.argtypes = [ctypes.c_void_p, ctypes.c_long, ctypes.c_long]
+        lib.kirai_sched_abort.argtypes = [ctypes.c_void_p, ctypes.c_long]
+        lib.kirai_sched_forget.argtypes = [ctypes.c_void_p, ctypes.c_long]
+        lib.kirai_sched_stat.restype = ctypes.c_long
+        lib.kirai_sched_stat.argtypes = [ctypes.c_void_p, ctypes.c_int]
+        pointer = ctypes.c_void_p
+        lib.kirai_sched_schedule.argtypes = [ctypes.c_void_p, pointer, pointer, pointer, pointer, ctypes.c_int, pointer,
+                                             pointer, pointer, pointer, pointer]
+        lib.kirai_sched_update.argtypes = [ctypes.c_void_p, pointer, pointer, pointer, pointer, ctypes.c_int]
+        self._tables = cache.tables
+        self._handle = lib.kirai_sched_create(cache.tables._handle, len(cache.tables.groups), cache.page_size,
+                                              self.max_batched_tokens, self.max_running, self.prefill_chunk or -1)
+        if not self._handle:
+            raise ValueError("the native scheduler could not be created")
+        self._by_key = {}
+
+    def __del__(self):
+        handle, self._handle = getattr(self, "_handle", None), None
+        if handle:
+            self._lib.kirai_sched_destroy(handle)
+
+    def _check(self, code: int, what: str) -> int:
+        if code == -7:
+            raise RuntimeError("scheduler made no progress: no request fits the free pages")
+        if code < 0:
+            raise RuntimeError(f"native scheduler: {what} failed with code {code}")
+        return code
+
+    def add(self, request_id, prompt: Sequence[int], params: SamplingParams) -> Request:
+        request = super().add(request_id, prompt, params)
+        request.key = self._tables.new_key()
+        self._by_key[request.key] = request
+        self._check(self._lib.kirai_sched_add(self._handle, request.key, len(request.prompt)), "add")
+        return request
+
+    def schedule(self) -> List[Scheduled]:
+        ctypes = self._ctypes
+        capacity = len(self.waiting) + len(self.running) + 1
+        longs = lambda: (ctypes.c_long * capacity)()  # noqa: E731
+        ints = lambda: (ctypes.c_int * capacity)()  # noqa: E731
+        keys, first, count, sample = longs(), longs(), longs(), ints()
+        preempted, admitted, slots = longs(), longs(), ints()
+        num_preempted, num_admitted = ctypes.c_int(0), ctypes.c_int(0)
+        runs = self._check(self._lib.kirai_sched_schedule(
+            self._handle, keys, first, count, sample, capacity, preempted, ctypes.byref(num_preempted), admitted, slots,
+            ctypes.byref(num_admitted)), "schedule")
+        for i in range(num_preempted.value):  # mirror the evictions, in the order they happened
+            victim = self._by_key[preempted[i]]
+            self._tables.disown(victim.pages)
+            victim.pages = None
+            victim.computed = 0
+            victim.state = WAITING
+            victim.preemptions += 1
+            self.running.remove(victim)
+            self.waiting.appendleft(victim)
+            self.stats["preemptions"] += 1
+        for i in range(num_admitted.value):
+            request = self._by_key[admitted[i]]
+            assert self.waiting[0] is request
+            self.waiting.popleft()
+            request.pages = self._tables.adopt(request.request_id, request.key, slots[i])
+            for tensor in self.cache.state.values():  # a fresh state slot, as CacheManager.open leaves it
+                if tensor is not None:
+                    tensor[request.pages.slot].zero_()
+            request.state = RUNNING
+            self.running.append(request)
+        chosen = [Scheduled(self._by_key[keys[i]], first[i], count[i], bool(sample[i])) for i in range(runs)]
+        self.stats["steps"] += 1
+        self.stats["scheduled_tokens"] += sum(item.count for item in chosen)
+        return chosen
+
+    def update(self, scheduled: Sequence[Scheduled], sampled: Sequence[Optional[int]]) -> List[Request]:
+        finished = super().update(scheduled, sampled)  # the Python side of it; _finish below does not touch the pages
+        ctypes = self._ctypes
+        runs = len(scheduled)
+        done = {id(request) for request in finished}
+        keys = (ctypes.c_long * max(runs, 1))(*[item.request.key for item in scheduled])
+        counts = (ctypes.c_long * max(runs, 1))(*[item.count for item in scheduled])
+        sampled_flags = (ctypes.c_int * max(runs, 1))(*[1 if item.sample else 0 for item in scheduled])
+        finished_flags = (ctypes.c_int * max(runs, 1))(*[1 if id(item.request) in done else 0 for item in scheduled])
+        self._check(self._lib.kirai_sched_update(self._handle, keys, counts, sampled_flags, finished_flags, runs), "update")
+        for request in finished:
+            self._forget(request)
+        return finished
+
+    def _finish(self, request: Request) -> None:
+        # the native side closes the pages (in update or abort); here only the mirror
+        if request.pages is not None:
+            self._tables.disown(request.pages)
+            request.pages = None
+        request.state = FINISHED
+        if request in self.running:
+            self.running.remove(request)
+        self.stats["finished"] += 1
+
+    def _forget(self, request: Request) -> None:
+        self._lib.kirai_sched_forget(self._handle, request.key)
+        self._by_key.pop(request.key, None)
+
+    def abort(self, request: Request) -> None:
+        if request.state == FINISHED:
+            return
+        self._check(self._lib.kirai_sched_abort(self._handle, request.key), "abort")
+        if request in self.waiting:
+            self.waiting.remove(request)
+        request.finish_reason = "aborted"
+        self._finish(request)
+        self._forget(request)

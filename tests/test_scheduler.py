@@ -160,3 +160,62 @@ def test_decode_plan_prefers_the_balanced_kernel_only_for_uneven_or_badly_filled
     balanced, splits = decode_plan([100_000] + [500] * 15, 8)
     assert balanced is True and splits >= 1
     assert decode_plan([], 8) == (False, 1)
+
+
+def drive_random_workload(scheduler_class, seed):
+    """A random workload (arrivals over time, stop tokens, aborts, few pages and slots) through a scheduler; the
+    trace of every decision and of what was left at the end."""
+    import random
+
+    rnd = random.Random(seed)
+    page_size, num_pages, slots = rnd.choice([2, 4, 8]), rnd.randint(6, 40), rnd.randint(1, 5)
+    cache = CacheManager([KVCacheNeed(1, 8, None), KVCacheNeed(1, 8, 8)], page_size=page_size, num_pages=num_pages,
+                         num_slots=slots, device=None)
+    scheduler = scheduler_class(cache, max_batched_tokens=rnd.choice([4, 16, 33]), max_running=rnd.randint(1, 5), max_positions=512,
+                                default_max_new_tokens=64, prefill_chunk=rnd.choice([None, 3, 8]))
+    arrivals = [(rnd.randint(1, 40), rnd.randint(1, 12), rnd.randint(0, 30)) for _ in range(rnd.randint(1, 12))]
+    trace, step, added = [], 0, 0
+    while scheduler.has_work() or added < len(arrivals):
+        while added < len(arrivals) and arrivals[added][2] <= step:
+            prompt_len, new_tokens, _ = arrivals[added]
+            added += 1
+            try:
+                scheduler.add(f"r{added}", list(range(prompt_len)), SamplingParams(temperature=0.0, max_new_tokens=new_tokens, eos_token_id=5))
+            except AdmissionError:
+                trace.append(("refused", added))
+        step += 1
+        if not scheduler.has_work():
+            continue
+        try:
+            chosen = scheduler.schedule()
+        except RuntimeError:
+            trace.append(("stuck",))
+            break
+        for item in chosen:
+            assert item.first == item.request.pages.length == item.request.computed
+            cache.commit(item.request.pages, item.count)
+        sampled = [(5 if rnd.random() < 0.05 else 7) if item.sample else None for item in chosen]
+        trace.append([(item.request.request_id, item.first, item.count, item.sample) for item in chosen])
+        trace.append(("finished", sorted(r.request_id for r in scheduler.update(chosen, sampled))))
+        if rnd.random() < 0.03 and scheduler.running:
+            victim = rnd.choice(scheduler.running)
+            scheduler.abort(victim)
+            trace.append(("abort", victim.request_id))
+        cache.tables.check_consistency()
+        assert step < 5000
+    trace.append(("left", cache.free_pages(), cache.tables.slots.free_slots, dict(scheduler.stats)))
+    return trace, scheduler.stats["preemptions"]
+
+
+def test_native_scheduler_decides_as_the_python_model_does():
+    """The scheduler in native code (the one the engine uses) against the Python class, step by step, on random
+    workloads that admit, cut prompts, evict, recompute, stop, abort and refuse."""
+    from kirai_b200.engine.scheduler import NativeScheduler
+
+    evictions = 0
+    for seed in range(150):
+        expected, preempted = drive_random_workload(Scheduler, seed)
+        got, _ = drive_random_workload(NativeScheduler, seed)
+        assert got == expected, f"seed {seed}"
+        evictions += preempted
+    assert evictions > 20  # the workloads do run out of pages
