@@ -154,7 +154,7 @@ def build(force: bool = False, verbose_ptxas: bool = False) -> str:
     return library
 
 
-HOST_SOURCES = ["page_tables.cpp", "scheduler.cpp"]
+HOST_SOURCES = ["page_tables.cpp", "scheduler.cpp", "safetensors_reader.cpp"]
 HOST_LIBRARY_NAME = "libkirai_host.so"
 
 

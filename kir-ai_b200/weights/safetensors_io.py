@@ -98,11 +98,44 @@ def parse_header(blob: bytes, payload_bytes: int, where: str) -> Dict[str, Tenso
     return entries
 
 
-class SafetensorsFile:
-    """One memory-mapped safetensors file; tensors are read lazily by name."""
+_CODES = {1: "model_artifact_missing", 2: "model_integrity_failed", 3: "unsupported_capability"}
+_native_library = None
 
-    def __init__(self, path: str | os.PathLike):
+
+def _native():
+    """The host library with the native reader (csrc/safetensors_reader.cpp), its functions typed."""
+    global _native_library
+    if _native_library is None:
+        import ctypes
+
+        from ..csrc import build as _build
+
+        lib = ctypes.CDLL(_build.build_host())
+        lib.kirai_st_open.restype = ctypes.c_void_p
+        lib.kirai_st_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_int), ctypes.c_char_p, ctypes.c_int]
+        lib.kirai_st_close.argtypes = [ctypes.c_void_p]
+        lib.kirai_st_count.argtypes = [ctypes.c_void_p]
+        lib.kirai_st_entry.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_char_p, ctypes.c_int, ctypes.c_char_p, ctypes.c_int,
+                                       ctypes.POINTER(ctypes.c_long), ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_long),
+                                       ctypes.POINTER(ctypes.c_long)]
+        lib.kirai_st_payload.restype = ctypes.c_void_p
+        lib.kirai_st_payload.argtypes = [ctypes.c_void_p]
+        _native_library = lib
+    return _native_library
+
+
+class SafetensorsFile:
+    """One memory-mapped safetensors file; tensors are read lazily by name.
+
+    The file is mapped and its header parsed and checked in native code (csrc/safetensors_reader.cpp); with
+    ``native=False`` the Python reader of this module does the same (the tests hold the two against each other)."""
+
+    def __init__(self, path: str | os.PathLike, native: bool = True):
         self.path = os.fspath(path)
+        self._native_handle = None
+        if native:
+            self._open_native()
+            return
         try:
             self._handle = open(self.path, "rb")
         except FileNotFoundError:
@@ -120,6 +153,35 @@ class SafetensorsFile:
         self.entries = parse_header(blob, size - self._data_start, self.path)
         self._map = mmap.mmap(self._handle.fileno(), 0, access=mmap.ACCESS_READ)
 
+    def _open_native(self) -> None:
+        import ctypes
+
+        lib = _native()
+        code = ctypes.c_int(0)
+        message = ctypes.create_string_buffer(1024)
+        handle = lib.kirai_st_open(self.path.encode("utf-8"), ctypes.byref(code), message, len(message))
+        if not handle:
+            text = message.value.decode("utf-8", "replace")
+            raise SafetensorsError(_CODES.get(code.value, "model_integrity_failed"), text)
+        self._native_handle = handle
+        self._payload = lib.kirai_st_payload(handle)
+        self.entries = {}
+        name, dtype = ctypes.create_string_buffer(4096), ctypes.create_string_buffer(16)
+        shape, rank = (ctypes.c_long * 16)(), ctypes.c_int(0)
+        begin, end = ctypes.c_long(0), ctypes.c_long(0)
+        for index in range(lib.kirai_st_count(handle)):
+            status = lib.kirai_st_entry(handle, index, name, len(name), dtype, len(dtype), shape, ctypes.byref(rank),
+                                        ctypes.byref(begin), ctypes.byref(end))
+            if status != 0:
+                raise SafetensorsError("model_integrity_failed", f"{self.path}: a tensor name or shape is too long to read")
+            self.entries[name.value.decode("utf-8")] = TensorEntry(dtype.value.decode("ascii"), tuple(shape[: rank.value]),
+                                                                   begin.value, end.value)
+
+    def __del__(self):
+        handle, self._native_handle = getattr(self, "_native_handle", None), None
+        if handle and _native_library is not None:
+            _native_library.kirai_st_close(handle)
+
     def names(self) -> Iterable[str]:
         return self.entries.keys()
 
@@ -129,18 +191,26 @@ class SafetensorsFile:
         dtype, _ = _DTYPES[entry.dtype]
         if entry.end == entry.begin:
             return torch.empty(entry.shape, dtype=dtype)
-        view = memoryview(self._map)[self._data_start + entry.begin : self._data_start + entry.end]
         import warnings
 
+        if self._native_handle is not None:
+            import ctypes
+
+            view = (ctypes.c_ubyte * (entry.end - entry.begin)).from_address(self._payload + entry.begin)
+            view._owner = self  # the tensor keeps the view, and the view keeps the mapping, alive
+        else:
+            view = memoryview(self._map)[self._data_start + entry.begin : self._data_start + entry.end]
         with warnings.catch_warnings():
             warnings.simplefilter("ignore")  # torch warns that the buffer is not writable
             flat = torch.frombuffer(view, dtype=dtype)
         return flat.reshape(entry.shape)
 
     def close(self) -> None:
-        # Tensors handed out keep views of the map alive; only drop our own references.
-        self._map = None
-        self._handle.close()
+        # Tensors handed out keep views of the map alive; only drop our own references.  (The native mapping
+        # goes when the last tensor over it and this object are gone.)
+        if self._native_handle is None:
+            self._map = None
+            self._handle.close()
 
 
 class ModelFiles:
@@ -213,4 +283,4 @@ def write_safetensors(path: str | os.PathLike, tensors: Mapping[str, torch.Tenso
         handle.write(blob)
         for name in order:
             tensor = tensors[name].detach().cpu().contiguous()
-            handle.write(tensor.view(torch.uint8).numpy().tobytes() if tensor.numel() else b"")
+            handle.write(tensor.reshape(-1).view(torch.uint8).numpy().tobytes() if tensor.numel() else b"")

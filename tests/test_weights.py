@@ -61,8 +61,55 @@ def test_malformed_files_are_refused(tmp_path, case):
         elif case == "shape_bytes":
             entry["shape"] = [3]
         _write_raw(path, json.dumps({"a": entry}).encode(), b"\0" * 8)
-    with pytest.raises(SafetensorsError):
-        SafetensorsFile(path)
+    codes = []
+    for native in (True, False):  # the native reader and the Python one refuse the same files for the same reason
+        with pytest.raises(SafetensorsError) as err:
+            SafetensorsFile(path, native=native)
+        codes.append(err.value.code)
+    assert codes[0] == codes[1]
+
+
+def test_native_reader_and_python_reader_agree(tmp_path):
+    """Files with every dtype, empty and many-dimensional tensors, metadata, names that need escaping and padding
+    after the header: the reader in native code (the default) and the Python reader give the same entries and bytes."""
+    generator = torch.Generator().manual_seed(0)
+    tensors = {
+        "plain.weight": torch.randn(7, 5, generator=generator),
+        "half": torch.randn(3, 4, generator=generator).to(torch.bfloat16),
+        "sixteen": torch.randn(9, generator=generator).to(torch.float16),
+        "double": torch.randn(2, 2, generator=generator).to(torch.float64),
+        "ids": torch.arange(11, dtype=torch.int64),
+        "table": torch.arange(6, dtype=torch.int32).view(2, 3),
+        "small": torch.arange(5, dtype=torch.int16),
+        "bytes": torch.arange(4, dtype=torch.uint8),
+        "signed": torch.arange(-2, 2, dtype=torch.int8),
+        "flags": torch.tensor([True, False, True]),
+        "empty": torch.zeros(0, 3),
+        "scalar": torch.tensor(2.5),
+        "deep": torch.randn(2, 1, 3, 1, 2, generator=generator),
+        'quoted "name" with \\ and \u00e9 \u4e2d': torch.ones(2),
+    }
+    path = tmp_path / "all.safetensors"
+    write_safetensors(path, tensors, metadata={"format": "pt", "note": "{[\"nested\"]}"})
+    native, python = SafetensorsFile(path), SafetensorsFile(path, native=False)
+    assert native._native_handle is not None and python._native_handle is None
+    assert dict(native.entries) == dict(python.entries) and set(native.names()) == set(tensors)
+    for name, tensor in tensors.items():
+        got = native.tensor(name)
+        assert got.dtype == tensor.dtype and got.shape == tensor.shape
+        assert torch.equal(got, tensor) and torch.equal(python.tensor(name), tensor)
+    # a tensor outlives the reader object that handed it out
+    kept = native.tensor("plain.weight")
+    del native
+    assert torch.equal(kept, tensors["plain.weight"])
+    # a header written by hand: spaces, members in another order, an extra member, a repeated name
+    header = (b'  { "__metadata__" : {"a": [1, 2.5e3, null, true]} ,\n "x":{"data_offsets":[0,8],"shape":[2],"extra":{"k":[]},'
+              b'"dtype":"F32"}, "y": {"dtype":"U8","shape":[3],"data_offsets":[8,11]}, "y": {"dtype":"I8","shape":[1,3],'
+              b'"data_offsets":[8,11]} }   ')
+    _write_raw(tmp_path / "hand.safetensors", header, bytes(range(11)))
+    native, python = SafetensorsFile(tmp_path / "hand.safetensors"), SafetensorsFile(tmp_path / "hand.safetensors", native=False)
+    assert dict(native.entries) == dict(python.entries)
+    assert native.entries["y"].dtype == "I8" and torch.equal(native.tensor("y"), python.tensor("y"))
 
 
 def test_missing_folder_content_and_index(tmp_path):
