@@ -156,6 +156,7 @@ def main() -> int:
     parser.add_argument("--context", type=int, default=4096)
     parser.add_argument("--prefill-tokens", type=int, default=2048)
     parser.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
+    parser.add_argument("--page-size", type=int, default=16, help="tokens per cache page (a power of two)")
     parser.add_argument("--points", default="1,64", help="other decode batches to measure (comma separated, '' for none)")
     parser.add_argument("--workload", default="decode", choices=["decode", "serving-4b", "batch-32b"],
                         help="decode: the contract's measurement (default).  serving-4b: 64 requests with prompts of "
@@ -191,7 +192,7 @@ def main() -> int:
     peaks, peak_source = load_peaks()
     batches = [args.batch] + [int(b) for b in args.points.split(",") if b.strip()]
     max_batch = max(batches)
-    page_size = 16
+    page_size = args.page_size
     context = args.context
     torch.cuda.set_device(0)
     # what a request may generate while the others are still being filled, and while it is warmed up and timed twice

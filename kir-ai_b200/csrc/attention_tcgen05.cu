@@ -1,10 +1,10 @@
 // Prompt attention over the paged cache on the tcgen05 tensor cores.
 //
 // One CTA per (request, kv head, tile of 128 query rows); the rows enumerate (token, head of
-// the group) pairs, so the group's heads share every key/value tile.  Per tile of 128 keys:
+// the group) pairs, so the group's heads share every key/value tile.  Per tile of 64 keys:
 //
 //   S = Q K^T      tcgen05.mma, both operands from shared memory (K-major, 128-byte swizzle),
-//                  S [128 x 128] in tensor memory;
+//                  S [128 x 64] in tensor memory;
 //   softmax        128 threads, one query row each: the row comes back with tcgen05.ld, is masked
 //                  by position, exponentiated against a running maximum, and goes to tensor
 //                  memory again as bf16 (tcgen05.st) to be the A operand of the second product;
@@ -18,7 +18,12 @@
 // thread of warp 1 issues the MMAs, warps 2-5 are the softmax rows.  S has two buffers in tensor memory
 // (P lies over the buffer its S came from): the first product of tile t + 1 is issued before the second
 // product of tile t, so it runs while the rows of tile t exponentiate.  A CTA is small enough for two per
-// SM, which fill each other's gaps.  Every barrier wait is bounded.  Same visibility rule as the other attention kernels: row at position pos sees keys
+// SM, which fill each other's gaps.  Every barrier wait is bounded.
+// The load warp's requests set the pace (clock stamps: about 100 cycles each), so a page's rows come whole,
+// both 64-column panels in one request, through a 4-dimensional tensor map (columns, 8 rows, panels, groups of
+// 8 rows) that leaves a tile as [group][panel][8 rows][128 bytes]; head sizes that are no multiple of 64 and
+// pages under 8 tokens take one request per panel and at most 8 rows into the same layout.
+// Same visibility rule as the other attention kernels: row at position pos sees keys
 // lo <= j <= pos.  head_dim: a multiple of 8 up to 128; the group size must divide 128.
 #include "sm100.cuh"
 #include "tensor_map.cuh"
@@ -51,15 +56,23 @@ __device__ __forceinline__ uint32_t panel_offset(int row, int chunk) {
     return (uint32_t)((chunk >> 3) * (ROWS * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
-// K-major operand (rows of 128 bytes, 8-row groups 1024 bytes apart): see sm100::smem_desc_k_major_sw128.
+// Key and value tiles lie in shared memory as [group of 8 rows][64-column panel][8 rows][128 bytes] with the
+// 128-byte swizzle (a row's two panels in one group, so that one TMA request can bring whole rows): row `row` of
+// panel `panel` starts here.
+template <int PANELS>
+__device__ __forceinline__ uint32_t kv_row_offset(int row, int panel) {
+    return (uint32_t)((row >> 3) * (PANELS * 1024) + panel * 1024 + (row & 7) * 128);
+}
+
+// K-major operand (rows of 128 bytes, 8-row groups a given stride apart): see sm100::smem_desc_k_major_sw128_groups.
 // MN-major operand with the 128-byte swizzle: 64 contiguous MN elements per 128-byte row, one row
-// per K index, 8-row groups `1024` bytes apart (stride offset), the next 64 MN elements `panel_bytes`
+// per K index, 8-row groups `group_bytes` apart (stride offset), the next 64 MN elements `panel_bytes`
 // further (leading offset).
-__device__ __forceinline__ uint64_t smem_desc_mn_major_sw128(uint32_t addr, uint32_t panel_bytes) {
+__device__ __forceinline__ uint64_t smem_desc_mn_major_sw128(uint32_t addr, uint32_t panel_bytes, uint32_t group_bytes) {
     uint64_t desc = 0;
     desc |= (uint64_t)((addr & 0x3FFFF) >> 4);
     desc |= (uint64_t)((panel_bytes >> 4) & 0x3FFF) << 16;
-    desc |= (uint64_t)(1024 >> 4) << 32;
+    desc |= (uint64_t)((group_bytes >> 4) & 0x3FFF) << 32;
     desc |= (uint64_t)1 << 46;
     desc |= (uint64_t)2 << 61;
     return desc;
@@ -110,8 +123,8 @@ __global__ void __launch_bounds__(TA_THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ q, bf16* __restrict__ out,
                             const int* __restrict__ block_table, const int* __restrict__ query_start,
                             const int* __restrict__ context_len, int q_heads, int kv_heads, int head_dim,
-                            long q_row_stride, int page_size, int box_rows, int table_width, int num_pages, int window,
-                            float scale_log2, int* __restrict__ error_flag) {
+                            long q_row_stride, int page_size, int box_rows, int piece_rows, int table_width, int num_pages,
+                            int window, float scale_log2, int* __restrict__ error_flag) {
     pdl_launch_dependents();
     pdl_wait();
     using Smem = TcAttnSmem<D>;
@@ -246,9 +259,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
                         if (__shfl_sync(0xffffffffu, plan.row[k], owner) >= 0) continue;
                         const int b = 32 * k + owner;
                         for (int h = 0; h < PANELS; ++h) {
-                            const uint32_t off = (uint32_t)(h * (TA_BN * 128) + (b << box_shift) * 128);
                             for (int i = lane; i < box_rows * 8; i += 32)
-                                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst + off + i * 16), "r"(0u) : "memory");
+                                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst + kv_row_offset<PANELS>((b << box_shift) + (i >> 3), h) + (i & 7) * 16), "r"(0u) : "memory");
                         }
                     }
                 }
@@ -264,11 +276,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
 #pragma unroll
             for (int k = 0; k < PER_LANE; ++k) {
                 if (plan.row[k] >= 0) {
-                    const int b = lane + 32 * k;
+                    const int first = (lane + 32 * k) << box_shift;  // the box's first row in the tile
+                    if (piece_rows == 0) {
+                        // one request for the box's whole rows (a multiple of 8 of them, both panels)
+                        tma_load_4d(dst + kv_row_offset<PANELS>(first, 0), &kv_map, bar, 0, 0, 0, (plan.row[k] + value_rows) >> 3);
+                    } else {
+                        // pieces of at most 8 rows of one panel
+                        for (int sub = 0; sub < box_rows; sub += piece_rows)
 #pragma unroll
-                    for (int h = 0; h < PANELS; ++h)
-                        tma_load_2d(dst + (uint32_t)(h * (TA_BN * 128) + (b << box_shift) * 128), &kv_map, bar, h * 64,
-                                    plan.row[k] + value_rows);
+                            for (int h = 0; h < PANELS; ++h)
+                                tma_load_2d(dst + kv_row_offset<PANELS>(first + sub, h), &kv_map, bar, h * 64,
+                                            plan.row[k] + value_rows + sub);
+                    }
                 }
             }
             __syncwarp();
@@ -308,9 +327,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
                 for (int kk = 0; kk < D / 16; ++kk) {
                     // 16 dims further: 32 bytes inside the swizzle atom, or the next 64-column panel
                     const uint32_t off_q = (uint32_t)((kk >> 2) * (TA_ROWS * 128) + (kk & 3) * 32);
-                    const uint32_t off_k = (uint32_t)((kk >> 2) * (TA_BN * 128) + (kk & 3) * 32);
-                    mma_bf16_ss(s_acc, smem_desc_k_major_sw128(q_smem + off_q), smem_desc_k_major_sw128(k_addr + off_k), idesc_qk,
-                                kk > 0 ? 1u : 0u);
+                    const uint32_t off_k = (uint32_t)((kk >> 2) * 1024 + (kk & 3) * 32);
+                    mma_bf16_ss(s_acc, smem_desc_k_major_sw128(q_smem + off_q),
+                                smem_desc_k_major_sw128_groups(k_addr + off_k, PANELS * 1024), idesc_qk, kk > 0 ? 1u : 0u);
                 }
                 mma_commit(smem_addr(&k_empty[slot]));
                 mma_commit(smem_addr(&s_ready[it & 1]));
@@ -330,8 +349,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
 #pragma unroll
                 for (int kk = 0; kk < TA_BN / 16; ++kk) {
                     // 16 keys further: 8 columns of packed bf16 pairs in tensor memory, two 8-row groups of the V tile
-                    mma_bf16_ts(tmem_o, tmem_p + (uint32_t)(kk * 8), smem_desc_mn_major_sw128(v_addr + (uint32_t)(kk * 2048), TA_BN * 128),
-                                idesc_pv, (it > 0 || kk > 0) ? 1u : 0u);
+                    mma_bf16_ts(tmem_o, tmem_p + (uint32_t)(kk * 8),
+                                smem_desc_mn_major_sw128(v_addr + (uint32_t)(kk * 2 * PANELS * 1024), 1024, PANELS * 1024), idesc_pv,
+                                (it > 0 || kk > 0) ? 1u : 0u);
                 }
                 mma_commit(smem_addr(&v_empty[slot]));
                 mma_commit(smem_addr(o_ready));
@@ -483,14 +503,19 @@ int launch(const void* q, const void* cache, void* out, const int* block_table, 
     if (TA_BN % box_rows != 0 || page_size % box_rows != 0) return KIRAI_ERR_UNSUPPORTED;
     CUtensorMap kv_map;
     const uint64_t rows = (uint64_t)num_pages * 2 * kv_heads * page_size;
-    if (!tmap::bf16_2d_sw128(&kv_map, cache, rows, head_dim, head_dim, box_rows, 64)) return KIRAI_ERR_BAD_ALIGN;
+    // whole rows of a box in one request where the sizes allow it; else pieces of one panel and at most 8 rows
+    int piece_rows = 0;
+    if (head_dim % 64 != 0 || box_rows % 8 != 0 || !tmap::bf16_kv_boxes_sw128(&kv_map, cache, rows, head_dim, box_rows)) {
+        piece_rows = box_rows < 8 ? box_rows : 8;
+        if (!tmap::bf16_2d_sw128(&kv_map, cache, rows, head_dim, head_dim, piece_rows, 64)) return KIRAI_ERR_BAD_ALIGN;
+    }
     auto kernel = attention_prefill_tc_kernel<D>;
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total);
     if (err != cudaSuccess) return (int)err;
     dim3 grid((unsigned)(((long)max_query_len * group + TA_ROWS - 1) / TA_ROWS), kv_heads, requests);
     return launch_pdl(kernel, grid, dim3(TA_THREADS), (size_t)Smem::total, stream, 1u, kv_map, (const bf16*)q, (bf16*)out,
                       block_table, query_start, context_len, q_heads, kv_heads, head_dim, q_row_stride, page_size, box_rows,
-                      table_width, num_pages, window, scale * 1.4426950408889634f, error_flag);
+                      piece_rows, table_width, num_pages, window, scale * 1.4426950408889634f, error_flag);
 }
 
 }  // namespace

@@ -113,6 +113,16 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 // (64 bf16) and which TMA wrote with the 128-byte swizzle: 8-row groups are
 // 1024 bytes apart (stride byte offset), the leading offset is unused (1), the
 // descriptor version is 1 and the layout type 2 (SWIZZLE_128B).
+// The same with the 8-row groups `group_bytes` apart (tiles whose groups interleave several 64-column panels).
+__device__ __forceinline__ uint64_t smem_desc_k_major_sw128_groups(uint32_t addr, uint32_t group_bytes) {
+    uint64_t desc = 0;
+    desc |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    desc |= (uint64_t)1 << 16;
+    desc |= (uint64_t)((group_bytes >> 4) & 0x3FFF) << 32;
+    desc |= (uint64_t)1 << 46;
+    desc |= (uint64_t)2 << 61;
+    return desc;
+}
 __device__ __forceinline__ uint64_t smem_desc_k_major_sw128(uint32_t addr) {
     uint64_t desc = 0;
     desc |= (uint64_t)((addr & 0x3FFFF) >> 4);

@@ -313,7 +313,11 @@ def test_argmax_and_sampling(ops, vocab):
 
 @pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,window",
                          [(6, 2, 48, 8, None), (5, 5, 16, 4, 7), (8, 2, 128, 16, 40), (32, 8, 128, 16, None),
-                          (3, 1, 80, 1, None), (4, 2, 256, 64, 33), (16, 1, 64, 16, None)])
+                          (3, 1, 80, 1, None), (4, 2, 256, 64, 33), (16, 1, 64, 16, None),
+                          # how the tcgen05 kernel fetches a page: whole rows in one request (head sizes 64 and 128,
+                          # pages of 8 tokens and more, up to more than a tile), else panel by panel, 8 rows at most
+                          (4, 2, 96, 32, None), (8, 4, 80, 4, 9), (8, 2, 128, 64, None), (4, 1, 128, 128, 50),
+                          (2, 2, 64, 8, None), (2, 1, 192, 16, None)])
 def test_tensor_core_attention_against_plain(ops, q_heads, kv_heads, head_dim, page_size, window):
     """Prompt portions that start in the middle of a context, and single decoded tokens, through the
     tensor-core kernels and through the plain kernel, against 32-bit arithmetic."""
