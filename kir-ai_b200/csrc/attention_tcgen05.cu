@@ -113,6 +113,11 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// Two positive finite floats as a bf16 pair, rounded to nearest (ties upward) with integer instructions: the
+// conversion instruction shares the pipe of ex2, which the softmax rows keep busy.
+__device__ __forceinline__ uint32_t pack2_weights(float lo, float hi) {
+    return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -441,7 +446,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
                     const float a = ex2_approx(fmaf(__uint_as_float(s[c * 32 + 2 * i]), scale_log2, -m_sub));
                     const float b = ex2_approx(fmaf(__uint_as_float(s[c * 32 + 2 * i + 1]), scale_log2, -m_sub));
                     sum[i & 3] += a + b;
-                    p[i] = pack2(a, b);
+                    p[i] = pack2_weights(a, b);
                 }
                 tmem_store_32x16(s_buf + (uint32_t)(c * 16), p);
             }

@@ -20,7 +20,7 @@ from ..sampling.sampler import sample
 from .batch import StepEntry
 from .graphs import DecodeGraphs
 from .runner import ModelRunner
-from .scheduler import RUNNING, NativeScheduler, Request, Scheduled, Scheduler
+from .scheduler import FINISHED, RUNNING, NativeScheduler, Request, Scheduled, Scheduler
 
 MAX_NEW_TOKENS_CAP = 65_536       # crates/llm-engine/src/main.rs:25-29
 MAX_PREFILL_TOKENS_CAP = 262_144
@@ -121,6 +121,17 @@ class Engine:
             return []
         current, self._in_flight = self._in_flight, None
         return self._retire(current)
+
+    def abort(self, request: Request) -> List[Request]:
+        """Ends a request between steps (finish reason "aborted") and gives back what it holds.  A step that is still
+        queued or running is waited for first, so that no kernel in flight reads pages that are handed out again;
+        the requests which that step finished are returned.  The reference checks its cancellation tokens at the
+        same places, between prompt portions and between decode steps
+        (crates/llm-native-runtime/src/native_text/driver.rs:440-454, 801-804)."""
+        finished = self.drain()
+        if request.state != FINISHED:
+            self.scheduler.abort(request)
+        return finished
 
     def _retire(self, flight) -> List[Request]:
         scheduled, launched = flight

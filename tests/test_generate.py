@@ -150,6 +150,37 @@ def test_steps_queued_ahead_give_the_same_tokens_and_drop_what_follows_a_stop(ti
     assert [r.output for r in requests] == [o.token_ids for o in expected]
 
 
+def test_abort_between_steps_leaves_the_others_untouched(tiny):
+    """A request is ended while it decodes (a step for it may already be queued) and another while it still waits:
+    the rest generate what they generate without them, and nothing stays reserved."""
+    from kirai_b200 import Engine, SamplingParams
+
+    vocab = tiny["raw"]["vocab_size"]
+    prompts = [random_tokens(n, vocab, 50 + n) for n in (9, 5, 13, 6)]
+    base = dict(dtype="float32", page_size=tiny["page"], max_prefill_tokens=16, max_concurrent_requests=3,
+                max_new_tokens=32, max_cache_tokens=512)
+    params = [SamplingParams(temperature=0.7, top_p=0.9, seed=40 + i, max_new_tokens=20, ignore_eos=True) for i in range(4)]
+    expected = Engine(tiny["folder"], **base).generate(prompts, params)
+    engine = Engine(tiny["folder"], **base)
+    requests = [engine.add_request(p, q) for p, q in zip(prompts, params)]
+    finished = []
+    while len(requests[1].output) < 7:  # the second request is in the middle of its decoding
+        finished += engine.step()
+    finished += engine.abort(requests[1])
+    finished += engine.abort(requests[3])  # the fourth still waits for a free place among the running
+    assert requests[1].finish_reason == "aborted" and 7 <= len(requests[1].output) < 20
+    assert requests[3].finish_reason == "aborted" and requests[3].output == []
+    assert requests[1].output == expected[1].token_ids[: len(requests[1].output)]
+    while engine.scheduler.has_work():
+        finished += engine.step()
+    finished += engine.drain()
+    assert requests[0].output == expected[0].token_ids and requests[2].output == expected[2].token_ids
+    assert sorted(id(r) for r in finished) == sorted(id(requests[i]) for i in (0, 2))
+    stats = engine.stats()
+    assert stats["cache"]["live_requests"] == 0 and all(g["used"] == 0 for g in stats["cache"]["groups"])
+    assert engine.abort(requests[0]) == [] and requests[0].finish_reason == "length"  # ending a finished request changes nothing
+
+
 def test_command_line(tiny):
     command = [sys.executable, os.path.join(ROOT, "bin", "kirai"), "generate", "--snapshot", tiny["folder"],
                "--prompt-ids", "5,17,3,44", "--prompt-ids", "9,8,7", "--max-tokens", "6", "--temperature", "0",
