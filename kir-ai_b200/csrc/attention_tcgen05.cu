@@ -14,13 +14,13 @@
 // The running maximum is lazy: the output accumulator is rescaled only when a row's maximum has
 // grown by more than 2^8 since the scale in use, which is exact (the final division uses the same
 // scale) and spares most read-modify-write passes over the accumulator.
-// Warp roles: warp 0 fetches K tiles and V tiles by TMA straight from the pages (two slots each), one
+// Warp roles: warp 0 fetches K tiles and warp 6 V tiles by TMA straight from the pages (two slots each), one
 // thread of warp 1 issues the MMAs, warps 2-5 are the softmax rows.  S has two buffers in tensor memory
 // (P lies over the buffer its S came from): the first product of tile t + 1 is issued before the second
 // product of tile t, so it runs while the rows of tile t exponentiate.  A CTA is small enough for two per
 // SM, which fill each other's gaps.  Every barrier wait is bounded.
-// The load warp's requests set the pace (clock stamps: about 100 cycles each), so a page's rows come whole,
-// both 64-column panels in one request, through a 4-dimensional tensor map (columns, 8 rows, panels, groups of
+// A load warp's requests cost it about 100 cycles each (clock stamps) and one warp for both rings set the pace of
+// the kernel: hence a warp per ring, and a page's rows come whole, both 64-column panels in one request, through a 4-dimensional tensor map (columns, 8 rows, panels, groups of
 // 8 rows) that leaves a tile as [group][panel][8 rows][128 bytes]; head sizes that are no multiple of 64 and
 // pages under 8 tokens take one request per panel and at most 8 rows into the same layout.
 // Same visibility rule as the other attention kernels: row at position pos sees keys
@@ -35,7 +35,7 @@ namespace {
 #define TA_ROWS 128
 #define TA_BN 64
 #define TA_STAGES 2   // slots of the K ring, and of the V ring
-#define TA_THREADS 192
+#define TA_THREADS 224
 #define TA_TMEM_COLS 256  // S buffers (and, over each one's first half, its P) in columns 0..63 and 64..127, O in 128..255
 
 template <int D>
@@ -216,8 +216,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
     const uint32_t tmem_s = tmem_base /* + 64 for odd tiles; P over the first 32 columns */, tmem_o = tmem_base + 128;
     bool ok = true;
 
-    if (warp == 0) {
-        // producer
+    if (warp == 0 || warp == 6) {
+        // the two load warps: warp 0 feeds the K ring, warp 6 the V ring, each at its own pace (a request costs its
+        // warp about 100 cycles, and one warp for both rings set the pace of the kernel)
+        const int which = warp == 0 ? 0 : 1;
         const int* table = block_table + (long)req * table_width;
         {
             const int first_page = (first_tile * TA_BN) / page_size;
@@ -297,25 +299,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
             }
             __syncwarp();
         };
-        // K runs one tile ahead of V: the first product of tile t + 1 is issued before the second of tile t
-        auto fill_k = [&](int it, const TilePlan& plan) {
+        uint64_t* full = which == 0 ? k_full : v_full;
+        uint64_t* empty = which == 0 ? k_empty : v_empty;
+        for (int it = 0; it < num_tiles; ++it) {
+            const TilePlan plan = plan_tile(first_tile + it);
             const int slot = it % TA_STAGES;
-            if (it >= TA_STAGES && !mbar_wait_hot(smem_addr(&k_empty[slot]), (uint32_t)(it / TA_STAGES - 1) & 1u)) { ok = false; return; }
-            fill(plan, 0, smem_addr(&k_full[slot]), ring + slot * Smem::tile_bytes);
-        };
-        TilePlan current = plan_tile(first_tile);
-        fill_k(0, current);
-        for (int it = 0; it < num_tiles && ok; ++it) {
-            TilePlan next = current;
-            if (it + 1 < num_tiles) {
-                next = plan_tile(first_tile + it + 1);
-                fill_k(it + 1, next);
-            }
-            if (!ok) break;
-            const int slot = it % TA_STAGES;
-            if (it >= TA_STAGES && !mbar_wait_hot(smem_addr(&v_empty[slot]), (uint32_t)(it / TA_STAGES - 1) & 1u)) { ok = false; break; }
-            fill(current, 1, smem_addr(&v_full[slot]), ring + (TA_STAGES + slot) * Smem::tile_bytes);
-            current = next;
+            if (it >= TA_STAGES && !mbar_wait_hot(smem_addr(&empty[slot]), (uint32_t)(it / TA_STAGES - 1) & 1u)) { ok = false; break; }
+            fill(plan, which, smem_addr(&full[slot]), ring + (which * TA_STAGES + slot) * Smem::tile_bytes);
         }
     } else if (warp == 1) {
         if (elect_one()) {
@@ -363,7 +353,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
             }
         }
     } else {
-        // softmax rows: this thread owns query row r (tensor-memory lane r)
+        // softmax rows (warps 2-5): this thread owns query row r (tensor-memory lane r)
         const int lane_group = warp & 3;
         const int r = lane_group * 32 + lane;
         const uint32_t lane_bits = (uint32_t)(lane_group * 32) << 16;
