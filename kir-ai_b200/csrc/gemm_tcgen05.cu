@@ -29,6 +29,8 @@
 // 128 rows x 64 columns, each stored as the 16 KB image that the 128-byte swizzle leaves in shared memory, box
 // (row tile, k block) at index row_tile * ceil(K / 64) + k_block, zero-padded at the edges.  A tiled box is one
 // contiguous bulk copy; streaming whole boxes reads HBM about a sixth faster than gathering 128 rows of 128 bytes.
+#include <cstdlib>
+
 #include "sm100.cuh"
 #include "tensor_map.cuh"
 
@@ -42,8 +44,11 @@ using namespace sm100;
 // Shared memory of one CTA: the ring of stages, the barriers, then (only with split-K) one slot
 // per CTA of the cluster for the partial tiles.  The swapped, weight-streaming case (BN <= 64)
 // keeps the ring small enough for two CTAs per SM, so that every SM streams weights even when
-// there are fewer tiles than two waves; the many-token case takes as many stages as fit.
-template <int BN>
+// there are fewer tiles than two waves (but see DEEP below); the many-token case takes as many stages as fit.
+// DEEP (weight-streaming case, BN <= 32): a launch with no more CTAs than SMs gains nothing from a second CTA per
+// SM; its CTAs take a longer ring instead, because 4 stages of 16 KB in each of 128 CTAs are 8 MB in flight, fewer
+// than the memory system needs to run at its rate (about 1.5 us of latency x 6.4 TB/s).
+template <int BN, bool DEEP = false>
 struct GemmSmem {
     static constexpr bool streaming = BN <= 64;
     static constexpr int x_bytes = GEMM_BM * GEMM_BK * 2;
@@ -51,9 +56,11 @@ struct GemmSmem {
     static constexpr int stage_bytes = x_bytes + y_bytes;
     static constexpr int max_splits = BN <= 64 ? 4 : 1;  // up to 128 KB of slots beside the 96 KB ring
     static constexpr int slot_bytes = BN * GEMM_BM * 4;  // one 32-bit partial tile
-    static constexpr int stages = streaming ? 4 : (200 * 1024 / stage_bytes);
+    static constexpr int stages = streaming ? (DEEP ? (BN <= 16 ? 7 : 6) : 4) : (200 * 1024 / stage_bytes);
     static constexpr int barrier_bytes = 2048;  // barriers [0, 128), row scales [128, 384), partial sums of squares [512, 1536)
-    static constexpr int ctas_per_sm = streaming ? 2 : 1;
+    static_assert(!streaming || (2 * stages + 1) * 8 + 4 <= 128, "the streaming kernel's barriers must end before the row scales");
+    static_assert(!DEEP || BN <= 32, "the long ring is for the smallest tiles");
+    static constexpr int ctas_per_sm = streaming && !DEEP ? 2 : 1;
     static constexpr int total(int splits) {  // + slack to align the base to 1024 bytes
         return stages * stage_bytes + barrier_bytes + (splits > 1 ? splits * slot_bytes : 0) + 1024;
     }
@@ -134,12 +141,12 @@ __device__ __forceinline__ float silu_mul(float gate, float up) {
 // which adds the slots in rank order and stores the result: no partial sum goes to global memory.
 // EPI 0 stores C.  EPI 1 expects W's rows interleaved in eights (8 gate rows, the 8 matching up
 // rows, ...) and stores silu(gate) * up, [M, N / 2].
-template <int BN, bool SWAP, typename OutT, int EPI>
-__global__ void __launch_bounds__(GEMM_THREADS, GemmSmem<BN>::ctas_per_sm)
+template <int BN, bool SWAP, typename OutT, int EPI, bool DEEP>
+__global__ void __launch_bounds__(GEMM_THREADS, GemmSmem<BN, DEEP>::ctas_per_sm)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                     const uint8_t* __restrict__ w_tiled, OutT* __restrict__ C, int M, int N, int K, long ldc,
                     int k_blocks_per_split, int splits, Epilogue ep, int* __restrict__ error_flag) {
-    using Smem = GemmSmem<BN>;
+    using Smem = GemmSmem<BN, DEEP>;
     constexpr int STAGES = Smem::stages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -782,6 +789,23 @@ static int launch_persistent(const void* A, const void* W, bool tiled, void* C, 
                       tiled ? (const uint8_t*)W : (const uint8_t*)nullptr, (OutT*)C, M, N, K, ldc, ep, error_flag);
 }
 
+static int sm_count() {
+    static const int count = [] {
+        int device = 0, value = 0;
+        if (cudaGetDevice(&device) != cudaSuccess) return 0;
+        if (cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+        return value;
+    }();
+    return count;
+}
+static bool deep_rings() {
+    static const bool on = [] {
+        const char* text = getenv("KIRAI_GEMM_DEEP");
+        return !(text && text[0] == '0');
+    }();
+    return on;
+}
+
 template <int BN, bool SWAP, typename OutT, int EPI>
 static int launch_config(const void* A, const void* W, bool tiled, void* C, int M, int N, int K, long lda, long ldc,
                          int splits, const Epilogue& ep, int* error_flag, cudaStream_t stream) {
@@ -803,12 +827,23 @@ static int launch_config(const void* A, const void* W, bool tiled, void* C, int 
     splits = (total_k_blocks + per_split - 1) / per_split;
     dim3 grid((unsigned)((x_rows + GEMM_BM - 1) / GEMM_BM), (unsigned)((y_rows + BN - 1) / BN), (unsigned)splits);
     if (grid.y > 65535) return KIRAI_ERR_BAD_SIZE;
-    auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT, EPI>;
+    const uint8_t* boxes = tiled ? (const uint8_t*)W : (const uint8_t*)nullptr;
+    if constexpr (BN <= 32) {
+        // no more CTAs than SMs: one CTA per SM with the long ring (KIRAI_GEMM_DEEP=0 keeps the short one, to compare)
+        if ((long)grid.x * grid.y * grid.z <= sm_count() && deep_rings()) {
+            using Deep = GemmSmem<BN, true>;
+            auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT, EPI, true>;
+            cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Deep::total(Deep::max_splits));
+            if (err != cudaSuccess) return (int)err;
+            return launch_pdl(kernel, grid, dim3(GEMM_THREADS), (size_t)Deep::total(splits), stream, (unsigned)splits, map_x,
+                              map_y, boxes, (OutT*)C, M, N, K, ldc, per_split, splits, ep, error_flag);
+        }
+    }
+    auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT, EPI, false>;
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total(Smem::max_splits));
     if (err != cudaSuccess) return (int)err;
     return launch_pdl(kernel, grid, dim3(GEMM_THREADS), (size_t)Smem::total(splits), stream, (unsigned)splits, map_x, map_y,
-                      tiled ? (const uint8_t*)W : (const uint8_t*)nullptr, (OutT*)C, M, N, K, ldc, per_split, splits, ep,
-                      error_flag);
+                      boxes, (OutT*)C, M, N, K, ldc, per_split, splits, ep, error_flag);
 }
 
 // Split count for the swapped (few tokens) case, which is bound by the weight
