@@ -187,6 +187,31 @@ std::string describe(const std::vector<long>& shape) {
     return out + "]";
 }
 
+// Whether the bytes are well-formed UTF-8 (JSON text is; a header that is not could not be handed on as names).
+bool valid_utf8(const char* text, size_t length) {
+    const unsigned char* p = reinterpret_cast<const unsigned char*>(text);
+    const unsigned char* end = p + length;
+    while (p < end) {
+        const unsigned char c = *p;
+        int more;
+        unsigned minimum;
+        unsigned value;
+        if (c < 0x80) { ++p; continue; }
+        if ((c & 0xE0) == 0xC0) more = 1, minimum = 0x80, value = c & 0x1Fu;
+        else if ((c & 0xF0) == 0xE0) more = 2, minimum = 0x800, value = c & 0x0Fu;
+        else if ((c & 0xF8) == 0xF0) more = 3, minimum = 0x10000, value = c & 0x07u;
+        else return false;
+        if (end - p <= more) return false;
+        for (int i = 1; i <= more; ++i) {
+            if ((p[i] & 0xC0) != 0x80) return false;
+            value = (value << 6) | (p[i] & 0x3Fu);
+        }
+        if (value < minimum || value > 0x10FFFF || (value >= 0xD800 && value <= 0xDFFF)) return false;
+        p += more + 1;
+    }
+    return true;
+}
+
 // Parses the header into entries, checking every offset against the payload.
 bool parse_header(const char* blob, size_t length, long payload_bytes, const std::string& where, std::vector<Entry>& entries,
                   Failure& failure) {
@@ -194,6 +219,7 @@ bool parse_header(const char* blob, size_t length, long payload_bytes, const std
         failure = {2, where + ": " + what};
         return false;
     };
+    if (!valid_utf8(blob, length)) return broken("header is not valid JSON");
     Json json{blob, blob + length};
     if (!json.take('{')) return broken("header must be a JSON object");
     if (!json.take('}')) {

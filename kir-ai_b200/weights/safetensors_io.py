@@ -174,8 +174,11 @@ class SafetensorsFile:
                                         ctypes.byref(begin), ctypes.byref(end))
             if status != 0:
                 raise SafetensorsError("model_integrity_failed", f"{self.path}: a tensor name or shape is too long to read")
-            self.entries[name.value.decode("utf-8")] = TensorEntry(dtype.value.decode("ascii"), tuple(shape[: rank.value]),
-                                                                   begin.value, end.value)
+            try:
+                key = name.value.decode("utf-8")
+            except UnicodeDecodeError:
+                raise SafetensorsError("model_integrity_failed", f"{self.path}: a tensor name is not valid UTF-8") from None
+            self.entries[key] = TensorEntry(dtype.value.decode("ascii"), tuple(shape[: rank.value]), begin.value, end.value)
 
     def __del__(self):
         handle, self._native_handle = getattr(self, "_native_handle", None), None

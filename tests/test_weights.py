@@ -31,7 +31,7 @@ def _write_raw(path, header: bytes, payload: bytes = b"", length=None):
 
 
 @pytest.mark.parametrize("case", ["short", "huge_header", "past_eof", "bad_json", "not_object", "no_tensors",
-                                  "missing_dtype", "inverted", "past_payload", "bad_dtype", "shape_bytes"])
+                                  "missing_dtype", "inverted", "past_payload", "bad_dtype", "shape_bytes", "not_utf8"])
 def test_malformed_files_are_refused(tmp_path, case):
     path = tmp_path / "model.safetensors"
     good = {"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]}}
@@ -47,6 +47,8 @@ def test_malformed_files_are_refused(tmp_path, case):
         _write_raw(path, b"[1,2]")
     elif case == "no_tensors":
         _write_raw(path, json.dumps({"__metadata__": {}}).encode())
+    elif case == "not_utf8":  # a tensor name with a broken multi-byte sequence
+        _write_raw(path, json.dumps(good).encode().replace(b'"a"', b'"a\xc5\x22x"'), b"\0" * 8)
     else:
         entry = dict(good["a"])
         if case == "missing_dtype":
