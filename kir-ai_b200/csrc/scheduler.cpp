@@ -15,7 +15,7 @@
 // finished.  It works on the page tables of page_tables.cpp through their C interface.
 //
 // C interface: functions return >= 0 on success; -2 unknown request, -6 bad argument, -7 no progress possible
-// (no request fits the free pages), -8 an output array is too small.
+// (no request fits the free pages), -8 the output arrays are too small (nothing has been decided then).
 #include <algorithm>
 #include <cstdint>
 #include <deque>
@@ -133,6 +133,9 @@ KIRAI_HOST_EXPORT int kirai_sched_schedule(void* handle, long* keys, long* first
                                            long* preempted_keys, int* num_preempted, long* admitted_keys,
                                            int* admitted_slots, int* num_admitted) {
     Scheduler& s = *static_cast<Scheduler*>(handle);
+    // every request may be chosen, evicted or admitted once: arrays that could not hold them all are refused before
+    // anything is reserved or evicted
+    if (capacity < 0 || (size_t)capacity < s.running.size() + s.waiting.size()) return -8;
     long budget = s.max_batched_tokens;
     int chosen = 0;
     std::vector<long> preempted, admitted;
