@@ -3,7 +3,9 @@
 // tests): every step (1) each running request that is decoding gets its one token, evicting the most recently
 // admitted other running request when its next page is missing; (2) what is left of the token budget goes to
 // prompt portions of running requests, shrunk to the pages that are free; (3) waiting requests are admitted in
-// arrival order while a state slot is free and the running set is below its limit.  An evicted request gives its
+// arrival order while a state slot is free and the running set is below its limit (and no running request found
+// the pages short in (2)); (4) if nothing at all could run, the most recently admitted running request is evicted
+// until the oldest can go on.  An evicted request gives its
 // pages and slot back and goes to the front of the waiting queue to be recomputed.  The reference keeps its policy
 // in native code as well: the generation loop that never runs the last sampled token
 // (crates/llm-native-runtime/src/native_text/driver.rs:439-477), admission by a concurrency limit
@@ -170,17 +172,27 @@ KIRAI_HOST_EXPORT int kirai_sched_schedule(void* handle, long* keys, long* first
         }
         if (reserved && !choose(key, e.computed, 1, true)) return -8;
     }
-    // (2) prompt portions of running requests
-    for (long key : s.running) {
-        Entry& e = s.entries[key];
-        if (taken.count(key) || budget < 1 || e.pending() < 1) continue;
-        const long tokens = fit_to_pages(s, key, portion(s, e, budget));
-        if (tokens < 1) continue;
-        if (kirai_pages_reserve(s.pages, key, tokens) != 1) return -6;
-        if (!choose(key, e.computed, tokens, tokens == e.pending())) return -8;
-    }
-    // (3) admit waiting requests in order
-    while (!s.waiting.empty() && budget >= 1 && (long)s.running.size() < s.max_running) {
+    // (2) prompt portions of running requests; starved: one of them found no page for even one token
+    bool starved = false;
+    int failure = 0;
+    auto prompt_portions = [&]() {
+        starved = false;
+        for (long key : s.running) {
+            Entry& e = s.entries[key];
+            if (taken.count(key) || budget < 1 || e.pending() < 1) continue;
+            const long tokens = fit_to_pages(s, key, portion(s, e, budget));
+            if (tokens < 1) {
+                starved = true;
+                continue;
+            }
+            if (kirai_pages_reserve(s.pages, key, tokens) != 1) { failure = -6; return; }
+            if (!choose(key, e.computed, tokens, tokens == e.pending())) { failure = -8; return; }
+        }
+    };
+    prompt_portions();
+    if (failure) return failure;
+    // (3) admit waiting requests in order, unless a running request already found no page for its prompt
+    while (!starved && !s.waiting.empty() && budget >= 1 && (long)s.running.size() < s.max_running) {
         const long key = s.waiting.front();
         Entry& e = s.entries[key];
         const int slot = kirai_pages_open(s.pages, key);
@@ -197,6 +209,13 @@ KIRAI_HOST_EXPORT int kirai_sched_schedule(void* handle, long* keys, long* first
         s.running.push_back(key);
         admitted.push_back(key);
         if (!choose(key, 0, tokens, tokens == e.pending())) return -8;
+    }
+    // (4) nothing could run: every running request is in mid-prompt and the pages are all held (a decoding request
+    // would have evicted the others in (1)).  The youngest gives its pages to the others until the oldest can go on.
+    while (chosen == 0 && s.running.size() > 1) {
+        preempt(s, s.running.back(), preempted);  // not admitted in this step: an admitted request was chosen
+        prompt_portions();
+        if (failure) return failure;
     }
     if (chosen == 0 && (!s.waiting.empty() || !s.running.empty())) return -7;
     if ((int)preempted.size() > capacity || (int)admitted.size() > capacity) return -8;

@@ -9,9 +9,11 @@ request is never run through the model, as in the reference's loop
 (crates/llm-native-runtime/src/native_text/driver.rs:439-477).
 
 When pages run out: a prompt portion shrinks to the pages that are free, or
-waits; a decoding request that cannot get its next page evicts the most
-recently admitted other running request, whose pages and slot are freed and
-which goes back to the front of the waiting queue to be recomputed (its prompt
+waits (and nobody new is admitted while one waits); a decoding request that
+cannot get its next page evicts the most recently admitted other running
+request, and so does a step in which nothing at all could run (all running
+requests in mid-prompt, all pages held); the evicted request's pages and slot
+are freed and it goes back to the front of the waiting queue to be recomputed (its prompt
 and the tokens it has generated are prefilled again; its random draws continue
 where they were).  A request that could not run even alone is refused when it is
 added.  The reference sizes each request's cache up front and refuses what
@@ -174,19 +176,25 @@ class Scheduler:
                 continue
             # nothing left to evict: the request waits for pages (others that were chosen will free some)
         # (2) prompt portions of running requests
-        for request in self.running:
-            if id(request) in taken or budget < 1 or request.pending < 1:
-                continue
-            count = self._fit_to_pages(request, self._portion(request, budget))
-            if count < 1:
-                continue
-            ok = self.cache.reserve(request.pages, count)
-            assert ok
-            chosen.append(Scheduled(request, request.computed, count, count == request.pending))
-            taken.add(id(request))
-            budget -= count
-        # (3) admit waiting requests in order
-        while self.waiting and budget >= 1 and len(self.running) < self.max_running:
+        def prompt_portions(budget: int):
+            starved = False
+            for request in self.running:
+                if id(request) in taken or budget < 1 or request.pending < 1:
+                    continue
+                count = self._fit_to_pages(request, self._portion(request, budget))
+                if count < 1:
+                    starved = True
+                    continue
+                ok = self.cache.reserve(request.pages, count)
+                assert ok
+                chosen.append(Scheduled(request, request.computed, count, count == request.pending))
+                taken.add(id(request))
+                budget -= count
+            return budget, starved
+
+        budget, starved = prompt_portions(budget)
+        # (3) admit waiting requests in order, unless a running request already found no page for its prompt
+        while not starved and self.waiting and budget >= 1 and len(self.running) < self.max_running:
             request = self.waiting[0]
             pages = self.cache.open(request.request_id)
             if pages is None:
@@ -205,6 +213,12 @@ class Scheduler:
             chosen.append(Scheduled(request, 0, count, count == request.pending))
             taken.add(id(request))
             budget -= count
+        # (4) nothing could run: every running request is in mid-prompt and the pages are all held (a decoding
+        # request would have evicted the others in (1)).  The youngest gives its pages to the others until the
+        # oldest can go on; a request that is alone always fits (it was refused at admission otherwise).
+        while not chosen and len(self.running) > 1:
+            self._preempt(self.running[-1])
+            budget, starved = prompt_portions(budget)
         if not chosen and self.has_work():
             raise RuntimeError("scheduler made no progress: no request fits the free pages")
         self.stats["steps"] += 1

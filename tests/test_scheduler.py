@@ -118,6 +118,27 @@ def test_portion_shrinks_to_free_pages():
     assert [(c.request.request_id, c.count, c.sample) for c in chosen] == [("a", 14, True), ("b", 8, False)]
 
 
+@pytest.mark.parametrize("native", [False, True])
+def test_two_prompts_that_stall_each_other_in_mid_prompt(native):
+    # 100 pages of 16 tokens; two prompts of 1,280 tokens (80 pages each) cut into portions of 256: after three steps
+    # both hold pages, neither can finish its prompt and nobody decodes.  The younger one must give way.
+    from kirai_b200.engine.scheduler import NativeScheduler
+
+    cache = CacheManager([KVCacheNeed(1, 8, None)], page_size=16, num_pages=100, num_slots=4, device=None)
+    scheduler = (NativeScheduler if native else Scheduler)(
+        cache, max_batched_tokens=512, max_running=4, prefill_chunk=256, max_positions=4096, default_max_new_tokens=8)
+    a = scheduler.add("a", list(range(1280)), SamplingParams(max_new_tokens=4, seed=0))
+    b = scheduler.add("b", list(range(1280)), SamplingParams(max_new_tokens=4, seed=0))
+    trace = run(scheduler, cache)
+    assert a.preemptions == 0 and b.preemptions >= 1 and scheduler.stats["preemptions"] == b.preemptions
+    assert len(a.output) == 4 and len(b.output) == 4 and a.finish_reason == b.finish_reason == "length"
+    assert cache.free_pages() == [100]
+    # while a request waits for pages in mid-prompt nobody new is admitted: b comes back only after a has finished
+    # its prompt or freed pages, and is then recomputed from its first token
+    restarts = [entry for step in trace for entry in step if entry[0] == "b" and entry[1] == 0]
+    assert len(restarts) == 1 + b.preemptions
+
+
 def test_abort_frees_everything():
     cache, scheduler = make()
     request = scheduler.add("a", list(range(10)), SamplingParams(max_new_tokens=5, seed=0))
@@ -186,11 +207,7 @@ def drive_random_workload(scheduler_class, seed):
         step += 1
         if not scheduler.has_work():
             continue
-        try:
-            chosen = scheduler.schedule()
-        except RuntimeError:
-            trace.append(("stuck",))
-            break
+        chosen = scheduler.schedule()  # always finds something to run: it raises if it is stuck
         for item in chosen:
             assert item.first == item.request.pages.length == item.request.computed
             cache.commit(item.request.pages, item.count)
