@@ -81,7 +81,9 @@ class Engine:
         )
         self._next_id = 0
         self.counters = {"steps": 0, "graph_steps": 0, "prompt_tokens": 0, "generated_tokens": 0}
-        self.graphs = DecodeGraphs(runner) if cuda_graphs else None
+        # decode steps are replayed from CUDA graphs only when every part of the model promises that this is safe
+        # (Part.capture_safe); a model with a part that does not say so runs every step eagerly
+        self.graphs = DecodeGraphs(runner) if cuda_graphs and runner.model.plan.capture_safe() else None
         self.overlap_steps = overlap_steps
         self._in_flight = None  # (scheduled, LaunchedStep) of a decode step that is queued or running
 

@@ -19,6 +19,21 @@ import torch
 from .batch import StepBatch
 
 
+class NotOnHost:
+    """Stands where a StepBatch has a host list that a captured step cannot have (what it would say changes from
+    replay to replay).  Any use raises, so that a part that walks requests on the host is found at capture, not by
+    wrong results later."""
+
+    def __init__(self, field: str, instead: str):
+        self._message = (f"a captured decode step has no host copy of batch.{field}: read batch.{instead} on the device, "
+                         "or leave capture_safe false on the part so that its steps run eagerly")
+
+    def _refuse(self, *args, **kwargs):
+        raise RuntimeError(self._message)
+
+    __getitem__ = __iter__ = __len__ = __bool__ = __contains__ = _refuse
+
+
 class DecodeGraph:
     def __init__(self, runner, num_requests: int, table_width: int, balanced_attention: bool = False):
         self.runner = runner
@@ -33,9 +48,12 @@ class DecodeGraph:
             offsets.append(cursor)
             cursor += -(-size // 4) * 4
         self.offsets = offsets
-        self.host_ints = torch.zeros(cursor, dtype=torch.int32).pin_memory()
+        # pinned staging buffers, two of each in turn: a step queued ahead copies from one while the host fills the
+        # other for the step after it
+        self.host_ints = [torch.zeros(cursor, dtype=torch.int32).pin_memory() for _ in range(2)]
         self.dev_ints = torch.zeros(cursor, dtype=torch.int32, device=device)
-        self.host_floats = torch.zeros(3 * B, dtype=torch.float32).pin_memory()
+        self.host_floats = [torch.zeros(3 * B, dtype=torch.float32).pin_memory() for _ in range(2)]
+        self.loads = 0
         self.dev_floats = torch.zeros(3 * B, dtype=torch.float32, device=device)
         self.fixed = torch.arange(B + 1, dtype=torch.int32, device=device)
 
@@ -45,15 +63,16 @@ class DecodeGraph:
         self.token_ids, self.positions = section(0, self.dev_ints), section(1, self.dev_ints)
         self.context_len, self.slots = section(2, self.dev_ints), section(3, self.dev_ints)
         self.tables = [section(4 + g, self.dev_ints).view(B, table_width) for g in range(groups)]
-        self._host = [section(i, self.host_ints) for i in range(len(self.sections))]
+        self._host = [[section(i, ints) for i in range(len(self.sections))] for ints in self.host_ints]
         self.batch = StepBatch(
             num_tokens=B, num_requests=B, token_ids=self.token_ids, positions=self.positions,
             request_of_token=self.fixed[:B], query_start=self.fixed, context_len=self.context_len, slots=self.slots,
-            block_tables=self.tables, want_rows=self.fixed[:B], query_lens=[1] * B, start_positions=[0] * B,
-            slot_ids=[0] * B, max_query_len=1, max_context_len=table_width * runner.cache.page_size, num_want=B,
+            block_tables=self.tables, want_rows=self.fixed[:B], query_lens=[1] * B,
+            start_positions=NotOnHost("start_positions", "positions"), slot_ids=NotOnHost("slot_ids", "slots"), max_query_len=1, max_context_len=table_width * runner.cache.page_size, num_want=B,
             decode_balanced=balanced_attention,
         )
         self.tokens_out: Optional[torch.Tensor] = None
+        self.logits_out: Optional[torch.Tensor] = None  # [B, V] float32 of the last replay (for checks; nothing reads it otherwise)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.kernels_per_replay = 0
         # results of launched steps come back through pinned buffers, two of them in turn: a step's result is
@@ -66,7 +85,7 @@ class DecodeGraph:
         ops = self.runner.rt.ops
         model = self.runner.model
         resid, delta = model.forward(self.batch, self.runner.cache)
-        logits = model.logits(resid, delta, self.batch.want_rows)
+        logits = self.logits_out = model.logits(resid, delta, self.batch.want_rows)
         B = self.num_requests
         floats = self.dev_floats
         self.tokens_out = ops.sample_rows(logits, floats[:B], floats[B : 2 * B], floats[2 * B :])
@@ -78,38 +97,44 @@ class DecodeGraph:
         """Copies a step's inputs from pinned host memory to the fixed device buffers (two copies).
         ``token_ids`` None leaves the token buffer as the step before left it: the tokens it sampled."""
         B = self.num_requests
+        turn = self.loads & 1
+        self.loads += 1
+        host, host_ints, host_floats = self._host[turn], self.host_ints[turn], self.host_floats[turn]
         if token_ids is not None:
-            self._host[0].copy_(torch.as_tensor(token_ids, dtype=torch.int32))
+            host[0].copy_(torch.as_tensor(token_ids, dtype=torch.int32))
         position_tensor = torch.as_tensor(positions, dtype=torch.int32)
-        self._host[1].copy_(position_tensor)
-        self._host[2].copy_(position_tensor + 1)
-        self._host[3].copy_(torch.as_tensor(slots, dtype=torch.int32))
+        host[1].copy_(position_tensor)
+        host[2].copy_(position_tensor + 1)
+        host[3].copy_(torch.as_tensor(slots, dtype=torch.int32))
         for g, table in enumerate(tables):
             padded = np.full((B, self.table_width), -1, dtype=np.int32)
             padded[:, : table.shape[1]] = table
-            self._host[4 + g].copy_(torch.from_numpy(padded.reshape(-1)))
-        self.host_floats[:B] = torch.as_tensor(temperatures, dtype=torch.float32)
-        self.host_floats[B : 2 * B] = torch.as_tensor(top_ps, dtype=torch.float32)
-        self.host_floats[2 * B :] = torch.as_tensor(draws, dtype=torch.float32)
+            host[4 + g].copy_(torch.from_numpy(padded.reshape(-1)))
+        host_floats[:B] = torch.as_tensor(temperatures, dtype=torch.float32)
+        host_floats[B : 2 * B] = torch.as_tensor(top_ps, dtype=torch.float32)
+        host_floats[2 * B :] = torch.as_tensor(draws, dtype=torch.float32)
         first = 0 if token_ids is not None else self.offsets[1]
-        self.dev_ints[first:].copy_(self.host_ints[first:], non_blocking=True)
-        self.dev_floats.copy_(self.host_floats, non_blocking=True)
+        self.dev_ints[first:].copy_(host_ints[first:], non_blocking=True)
+        self.dev_floats.copy_(host_floats, non_blocking=True)
 
     @property
     def input_bytes(self) -> int:
-        return self.host_ints.numel() * 4 + self.host_floats.numel() * 4
+        return self.host_ints[0].numel() * 4 + self.host_floats[0].numel() * 4
 
     @property
     def ahead_input_bytes(self) -> int:
         """What a step copies that takes its tokens from the step before it on the device."""
-        return (self.host_ints.numel() - self.offsets[1]) * 4 + self.host_floats.numel() * 4
+        return (self.host_ints[0].numel() - self.offsets[1]) * 4 + self.host_floats[0].numel() * 4
 
     def capture(self) -> None:
         """Runs the step once eagerly (so that everything lazy has happened), then captures it.
-        The inputs must describe a valid step; what the eager run writes to the cache is written
-        again, identically, by the first replay."""
+        The inputs must describe a valid step; the keys and values that the eager run writes to the pages are
+        written again, identically, by the first replay, and the fixed-size state of mixers that keep one is put
+        back as it was, so that the first replay advances it once."""
         ops = self.runner.rt.ops
         saved = self.dev_ints.clone()
+        state = self.runner.cache.state
+        saved_state = {layer: tensor.clone() for layer, tensor in state.items() if tensor is not None}
         stream = torch.cuda.Stream(device=self.runner.rt.device)
         stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):
@@ -117,6 +142,8 @@ class DecodeGraph:
         torch.cuda.current_stream().wait_stream(stream)
         torch.cuda.synchronize()
         self.dev_ints.copy_(saved)  # undo the eager run's advance
+        for layer, tensor in saved_state.items():
+            state[layer].copy_(tensor)
         before = ops.launch_count
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):

@@ -53,7 +53,7 @@ class ModelRunner:
         rt.ops.library()  # builds or loads the kernels now; a missing library fails here, loudly
         plan = plan_for_config(config)
         model = DecoderModel(plan, rt)
-        source = weights_source_factory(plan.weight_specs(), device)
+        source = weights_source_factory(plan.weight_specs(), device, plan.ignorable_weights)
         model.load(source)
         source.forget()
         cache = CacheManager(plan.cache_needs, page_size=page_size, num_slots=num_slots, dtype=rt.dtype, device=device,
@@ -63,14 +63,14 @@ class ModelRunner:
     @classmethod
     def from_folder(cls, model_dir: str, **kwargs) -> "ModelRunner":
         config = load_config(model_dir)
-        return cls.build(config, lambda specs, device: weight_loader.open_checked(model_dir, specs, device), **kwargs)
+        return cls.build(config, lambda specs, device, ignorable: weight_loader.open_checked(model_dir, specs, device, ignorable), **kwargs)
 
     @classmethod
     def from_random(cls, config, seed: int, *, std: float = 0.02, norm_jitter: float = 0.0, **kwargs) -> "ModelRunner":
         """Random weights made on the device, without a model folder (for measurements at real sizes)."""
-        def factory(specs, device):
+        def factory(specs, device, ignorable):
             tensors = random_tensors(specs, seed, std=std, norm_jitter=norm_jitter, dtype=torch.bfloat16, device=device)
-            return weight_loader.from_tensors(tensors, specs, device)
+            return weight_loader.from_tensors(tensors, specs, device, ignorable)
         return cls.build(config, factory, **kwargs)
 
     def step(self, entries: Sequence[StepEntry], **kwargs):

@@ -45,6 +45,7 @@ class ModelPlan:
     vocab_size: int
     hidden_size: int
     max_positions: Optional[int] = None
+    ignorable_weights: List[str] = field(default_factory=list)  # tensors a folder may hold that no part wants
     cache_needs: List[object] = field(default_factory=list)  # filled by validate(): one need per cache layer
 
     def validate(self) -> "ModelPlan":
@@ -76,6 +77,11 @@ class ModelPlan:
 
     def parts(self):
         return [self.embedding, *self.blocks, self.final_norm, self.head]
+
+    def capture_safe(self) -> bool:
+        """Whether a step of single tokens may be recorded into a CUDA graph: every part promises it
+        (``Part.capture_safe``)."""
+        return all(bool(getattr(part, "capture_safe", False)) for part in self.parts())
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         specs: Dict[str, WeightSpec] = {}

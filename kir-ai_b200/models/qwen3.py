@@ -40,4 +40,6 @@ def build_qwen3_plan(cfg: Qwen3Config) -> ModelPlan:
         vocab_size=cfg.vocab_size,
         hidden_size=cfg.hidden_size,
         max_positions=cfg.max_position_embeddings,
+        # some tied checkpoints still ship the head; the reference asks only for the names it needs and loads them
+        ignorable_weights=["lm_head.weight"] if cfg.tie_word_embeddings else [],
     ).validate()

@@ -53,6 +53,12 @@ class GQAttention(Mixer):
     def cache_need(self):
         return KVCacheNeed(self.kv_heads, self.head_dim, self.window)
 
+    @property
+    def capture_safe(self) -> bool:
+        """The kernels read positions, lengths and block tables on the device; the position encoding is a part of
+        its own and answers for itself."""
+        return self.position is None or bool(self.position.capture_safe)
+
     def weight_specs(self) -> Dict[str, WeightSpec]:
         specs = {**self.qkv.weight_specs(), **self.out.weight_specs()}
         if self.qk_norm_eps is not None:

@@ -92,7 +92,18 @@ class Runtime:
 
 
 class Part:
-    """Base of every part: the tensors it wants, and how it takes them."""
+    """Base of every part: the tensors it wants, and how it takes them.
+
+    ``capture_safe`` true is a part's promise that, for a step in which every request brings one token, its
+    ``forward`` can be recorded once into a CUDA graph and replayed with other inputs: it launches on the current
+    stream only, never waits for the device, and takes everything that changes from step to step (tokens,
+    positions, lengths, slots, block tables) from the batch's device tensors, not from its host copies
+    (``start_positions``, ``slot_ids``; a captured step has none, and reading them raises).  A mixer with state of
+    its own must also advance that state exactly once per run of the step.  The engine replays captured decode
+    steps only for a plan all of whose parts promise this; otherwise every step runs eagerly.  The default is
+    false, so a part written without thinking of graphs is never captured."""
+
+    capture_safe = False
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         return {}

@@ -41,6 +41,10 @@ class Block(Part):
     def _parts(self):
         return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None]
 
+    @property
+    def capture_safe(self) -> bool:
+        return all(bool(getattr(part, "capture_safe", False)) for part in self._parts())
+
     def weight_specs(self) -> Dict[str, WeightSpec]:
         specs: Dict[str, WeightSpec] = {}
         for part in self._parts():

@@ -26,6 +26,8 @@ def _table(weights, rt: Runtime, name: str, hidden_size: int):
 
 
 class Embedding(Part):
+    capture_safe = True
+
     def __init__(self, weight_name: str, vocab_size: int, hidden_size: int):
         self.weight_name, self.vocab_size, self.hidden_size = weight_name, vocab_size, hidden_size
         self.table: Optional[torch.Tensor] = None
@@ -44,6 +46,8 @@ class Embedding(Part):
 
 class OutputHead(Part):
     """Logits = W x in 32-bit, W [V, H] (its own tensor, or the embedding table when tied)."""
+
+    capture_safe = True
 
     def __init__(self, weight_name: str, vocab_size: int, hidden_size: int):
         self.weight_name, self.vocab_size, self.hidden_size = weight_name, vocab_size, hidden_size

@@ -17,6 +17,8 @@ from .base import FusedNormSpec, Part, Runtime, UnscaledNorm, WeightSpec
 
 
 class Linear(Part):
+    capture_safe = True
+
     def __init__(self, sources: Sequence[Tuple[str, int]], in_features: int):
         self.sources: List[Tuple[str, int]] = list(sources)
         self.in_features = in_features

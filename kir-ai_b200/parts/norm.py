@@ -15,6 +15,8 @@ from .base import FusedNormSpec, Norm, Runtime, WeightSpec
 
 
 class RMSNorm(Norm):
+    capture_safe = True
+
     def __init__(self, weight_name: str, width: int, eps: float):
         self.weight_name = weight_name
         self.width = width

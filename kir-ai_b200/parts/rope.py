@@ -15,6 +15,8 @@ from .base import PositionEncoding, Runtime
 
 
 class RotaryEmbedding(PositionEncoding):
+    capture_safe = True
+
     def __init__(self, head_dim: int, theta: float, rotary_dim: Optional[int] = None):
         self.head_dim = head_dim
         self.rotary_dim = head_dim if rotary_dim is None else rotary_dim

@@ -83,10 +83,12 @@ class WeightSource:
         self._device_copies.clear()
 
 
-def check(specs: Mapping[str, WeightSpec], present: Mapping[str, tuple]) -> None:
-    """``present`` maps name -> (dtype name, shape).  Raises WeightError on any mismatch."""
+def check(specs: Mapping[str, WeightSpec], present: Mapping[str, tuple], ignorable=()) -> None:
+    """``present`` maps name -> (dtype name, shape).  Raises WeightError on any mismatch.  Names in ``ignorable``
+    may be present without being wanted: a tied checkpoint that still ships its output head loads in the
+    reference, which only asks for the names it needs (crates/llm-models/src/qwen.rs:215-260)."""
     missing = [name for name in specs if name not in present]
-    unexpected = [name for name in present if name not in specs]
+    unexpected = [name for name in present if name not in specs and name not in set(ignorable)]
     wrong = []
     for name, spec in specs.items():
         if name not in present:
@@ -106,16 +108,16 @@ _TORCH_NAMES = {torch.float32: "F32", torch.bfloat16: "BF16", torch.float16: "F1
                 torch.int64: "I64", torch.int32: "I32", torch.int16: "I16", torch.int8: "I8", torch.uint8: "U8"}
 
 
-def open_checked(model_dir: str, specs: Mapping[str, WeightSpec], device) -> WeightSource:
+def open_checked(model_dir: str, specs: Mapping[str, WeightSpec], device, ignorable=()) -> WeightSource:
     """Opens a model folder, checks it against ``specs`` and returns the source for ``load``."""
     files = ModelFiles(model_dir)
     present = {name: (files.entry(name).dtype, files.entry(name).shape) for name in files.names()}
-    check(specs, present)
+    check(specs, present, ignorable)
     return WeightSource(files, device)
 
 
-def from_tensors(tensors: Mapping[str, torch.Tensor], specs: Mapping[str, WeightSpec], device) -> WeightSource:
+def from_tensors(tensors: Mapping[str, torch.Tensor], specs: Mapping[str, WeightSpec], device, ignorable=()) -> WeightSource:
     """The same check for tensors already in memory (random weights made on the device)."""
     present = {name: (_TORCH_NAMES.get(t.dtype, str(t.dtype)), tuple(t.shape)) for name, t in tensors.items()}
-    check(specs, present)
+    check(specs, present, ignorable)
     return WeightSource(dict(tensors), device)

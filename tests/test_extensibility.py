@@ -50,11 +50,25 @@ def define_toys():
                     out[t] = (state * self.gain).to(x.dtype)
             return out
 
+    class DeviceRunningAverageMixer(RunningAverageMixer):
+        """The same mixer, fit for a captured decode step: when every request brings one token it reads the
+        requests' slots on the device and advances each state once, with no host loop."""
+
+        capture_safe = True
+
+        def forward(self, x, batch, cache, write_cache=True):
+            if batch.max_query_len != 1:
+                return super().forward(x, batch, cache, write_cache)
+            slots = batch.slots.long()
+            state = cache.state.index_select(0, slots) * self.decay + x.float()
+            cache.state.index_copy_(0, slots, state)
+            return (state * self.gain).to(x.dtype)
+
     class NeighbourPairRotation(PositionEncoding):
         """Rotates the pairs (2i, 2i + 1) by position * theta^(-i / (d/2)): another pairing than the half split."""
 
-        def __init__(self, head_dim, theta):
-            self.head_dim, self.theta = head_dim, theta
+        def __init__(self, head_dim, theta, capture_safe=False):
+            self.head_dim, self.theta, self.capture_safe = head_dim, theta, capture_safe  # device arithmetic only
 
         def load(self, weights, rt):
             self.rt = rt
@@ -73,9 +87,12 @@ def define_toys():
     class TopOneOfTwo(FeedForward):
         """A router picks one of two SwiGLU experts per token (router logits in 32-bit)."""
 
-        def __init__(self, prefix, hidden, inter):
+        def __init__(self, prefix, hidden, inter, on_device=False):
             self.router = Linear([(prefix + "router.weight", 2)], hidden)
             self.experts = [SwiGLU(prefix + f"experts.{e}.", hidden, inter) for e in range(2)]
+            # gathering each expert's rows needs their count on the host; the device form runs both experts on every
+            # row and keeps the chosen one, which a captured step can do
+            self.capture_safe = self.on_device = on_device
 
         def weight_specs(self):
             specs = dict(self.router.weight_specs())
@@ -91,6 +108,9 @@ def define_toys():
 
         def forward(self, x, batch=None):
             choice = self.router.forward(x, torch.float32).argmax(dim=-1)
+            if self.on_device:
+                both = [expert.forward(x) for expert in self.experts]
+                return torch.where((choice == 0)[:, None], both[0], both[1])
             out = torch.zeros_like(x)
             for e, expert in enumerate(self.experts):
                 rows = (choice == e).nonzero().flatten()
@@ -109,6 +129,7 @@ def define_toys():
         eps: float = 1e-5
         decay: float = 0.75
         theta: float = 100.0
+        device_parts: bool = False  # the variants of the toy parts that a captured decode step can hold
         architecture = "ToyHybridForCausalLM"
 
         @classmethod
@@ -120,16 +141,18 @@ def define_toys():
 
     def build_plan(cfg):
         H = cfg.hidden_size
+        average = DeviceRunningAverageMixer if cfg.device_parts else RunningAverageMixer
 
         def attention(prefix, reads_only=False):
-            return GQAttention(prefix, H, cfg.heads, cfg.kv_heads, cfg.head_dim, NeighbourPairRotation(cfg.head_dim, cfg.theta),
+            return GQAttention(prefix, H, cfg.heads, cfg.kv_heads, cfg.head_dim,
+                               NeighbourPairRotation(cfg.head_dim, cfg.theta, cfg.device_parts),
                                qk_norm_eps=cfg.eps, reads_only=reads_only)
 
         blocks = [
-            Block(RMSNorm("b0.n1", H, cfg.eps), RunningAverageMixer("b0.gain", H, cfg.decay), RMSNorm("b0.n2", H, cfg.eps),
+            Block(RMSNorm("b0.n1", H, cfg.eps), average("b0.gain", H, cfg.decay), RMSNorm("b0.n2", H, cfg.eps),
                   SwiGLU("b0.mlp.", H, cfg.inter)),
             Block(RMSNorm("b1.n1", H, cfg.eps), attention("b1.attn."), RMSNorm("b1.n2", H, cfg.eps),
-                  TopOneOfTwo("b1.moe.", H, cfg.inter)),
+                  TopOneOfTwo("b1.moe.", H, cfg.inter, cfg.device_parts)),
             Block(RMSNorm("b2.n1", H, cfg.eps), attention("b2.attn.", reads_only=True), None,
                   SwiGLU("b2.mlp.", H, cfg.inter), arrangement="parallel"),
         ]
@@ -233,6 +256,74 @@ def test_toy_architecture_is_registered_built_and_stepped(dtype, tmp_path):
     logits = runner.step([StepEntry(again, sequences["b"], range(9))]).cpu()
     if dtype == torch.float32:
         assert float((logits - expected["b"][0]).abs().max()) <= tolerance(dtype, expected["b"][0])
+
+
+def plain_toy_generate(cfg, weights, prompt, params):
+    """Token by token with the plain toy model and the plain sampler, and the engine's draws."""
+    from kirai_b200.sampling import rng
+
+    tokens, out = list(prompt), []
+    for k in range(params.max_new_tokens):
+        logits = plain_toy_logits(cfg, weights, tokens)[0][-1]
+        if params.temperature == 0.0:
+            out.append(plain.argmax_first(logits))
+        else:
+            out.append(plain.sample_top_p(logits, params.temperature, params.top_p, rng.draw(params.seed, k)))
+        tokens.append(out[-1])
+    return out
+
+
+@pytest.mark.parametrize("device_parts", [False, True])
+def test_toy_architecture_generates_through_the_engine(device_parts, tmp_path):
+    """The toy architecture through ``Engine.generate``: scheduler, prompt portions, seeded sampling, a pool so small
+    that a request which holds a state slot is evicted and recomputed, and CUDA graphs switched on.  With parts that
+    walk requests on the host the engine must run every step eagerly; with parts that promise ``capture_safe`` it
+    replays captured decode steps, and the state advances once per token either way."""
+    ToyConfig = define_toys()
+    from kirai_b200 import Engine, SamplingParams
+    from kirai_b200.weights import write_random_model
+
+    cfg = ToyConfig(device_parts=device_parts)
+    write_random_model(str(tmp_path), cfg, seed=4, std=0.08)
+    _, weights = plain.read_model_folder(str(tmp_path))
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(70 + n)).tolist() for n in (9, 14, 6)]
+    params = [SamplingParams(temperature=0.0, max_new_tokens=12),
+              SamplingParams(temperature=0.8, top_p=0.9, seed=31, max_new_tokens=12),
+              SamplingParams(temperature=1.1, top_p=1.0, seed=32, max_new_tokens=12)]
+    expected = [plain_toy_generate(cfg, weights, prompt, p) for prompt, p in zip(prompts, params)]
+    # 11 pages of 4 tokens: the three requests grow to 20, 25 and 17 tokens (5 + 7 + 5 pages), so one is evicted
+    engine = Engine(str(tmp_path), dtype="float32", page_size=4, max_prefill_tokens=8, max_concurrent_requests=3,
+                    max_new_tokens=12, max_cache_tokens=44, cuda_graphs=True)
+    assert engine.runner.model.plan.capture_safe() is device_parts
+    outputs = engine.generate(prompts, params)
+    assert [o.token_ids for o in outputs] == expected
+    stats = engine.stats()
+    assert stats["scheduler"]["preemptions"] >= 1 and sum(o.preemptions for o in outputs) >= 1
+    assert (stats["graph_steps"] > 0) is device_parts
+    assert stats["cache"]["live_requests"] == 0 and all(g["used"] == 0 for g in stats["cache"]["groups"])
+    # the same with every step eager
+    eager = Engine(str(tmp_path), dtype="float32", page_size=4, max_prefill_tokens=8, max_concurrent_requests=3,
+                   max_new_tokens=12, max_cache_tokens=44, cuda_graphs=False)
+    assert [o.token_ids for o in eager.generate(prompts, params)] == expected
+
+
+def test_a_captured_step_refuses_parts_that_read_host_lists(tmp_path):
+    """A captured step's batch has no host copy of slots and start positions; a mixer that walks them (the toy's
+    first form) must raise at capture, with a message that says what to do, never read a placeholder."""
+    ToyConfig = define_toys()
+    from kirai_b200.engine.graphs import DecodeGraph
+    from kirai_b200.engine.runner import ModelRunner
+    from kirai_b200.weights import write_random_model
+
+    write_random_model(str(tmp_path), ToyConfig(), seed=4, std=0.08)
+    runner = ModelRunner.from_folder(str(tmp_path), dtype="float32", page_size=4, max_tokens=64, num_slots=2)
+    request = runner.cache.open("a")
+    assert runner.cache.reserve(request, 1)
+    graph = DecodeGraph(runner, 1, 16)
+    graph.load_inputs([3], [0], [request.slot], [runner.cache.block_table_array([request], 0)], [0.0], [1.0], [0.5])
+    with pytest.raises(RuntimeError, match="no host copy of batch.slot_ids"):
+        graph.capture()
+    torch.cuda.synchronize()
 
 
 def test_plan_validation_refuses_bad_orders():

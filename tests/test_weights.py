@@ -150,6 +150,25 @@ def test_one_error_lists_missing_unexpected_and_wrong(tmp_path):
     assert "model.norm.weight: dtype I32" in text
 
 
+def test_tied_folder_may_still_hold_the_output_head(tmp_path):
+    """Some tied checkpoints ship lm_head.weight all the same; the reference loads them
+    (crates/llm-models/src/qwen.rs:215-260 asks only for the names it needs).  Any other extra stays an error."""
+    config = config_from_dict(CONFIG_A)  # tied
+    plan = plan_for_config(config)
+    specs = plan.weight_specs()
+    assert "lm_head.weight" not in specs and plan.ignorable_weights == ["lm_head.weight"]
+    tensors = random_tensors(specs, seed=1)
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+    write_safetensors(tmp_path / "model.safetensors", tensors)
+    source = open_checked(str(tmp_path), specs, "cpu", plan.ignorable_weights)
+    assert source.stored("model.norm.weight").shape == (64,)
+    with pytest.raises(WeightError) as err:
+        open_checked(str(tmp_path), specs, "cpu")  # nothing declared ignorable: the extra is listed
+    assert err.value.unexpected == ["lm_head.weight"]
+    untied = plan_for_config(config_from_dict(CONFIG_B))
+    assert untied.ignorable_weights == []
+
+
 def test_dtype_policy_keeps_stored_width(tmp_path):
     config = config_from_dict(CONFIG_A)
     specs = plan_for_config(config).weight_specs()
