@@ -17,6 +17,13 @@
 #define KIRAI_ERR_BAD_ALIGN (-3)
 #define KIRAI_ERR_UNSUPPORTED (-4)
 
+// Values of the device error word (set instead of faulting; read by the host after a step).
+#define KIRAI_FLAG_BAD_TOKEN 1
+#define KIRAI_FLAG_NO_PAGE_WRITE 2
+#define KIRAI_FLAG_NO_PAGE_READ 3
+#define KIRAI_FLAG_WAIT_RAN_OUT 4
+#define KIRAI_FLAG_NO_MAXIMUM 5
+
 typedef __nv_bfloat16 bf16;
 
 template <typename T>

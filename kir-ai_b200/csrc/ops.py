@@ -27,6 +27,7 @@ _ERROR_NAMES = {
     2: "a token's position has no page in its request's block table (cache write)",
     3: "a key position has no page in its request's block table (attention read)",
     4: "a bounded wait inside a kernel ran out",
+    5: "a row of logits has no maximum (every entry is NaN or -inf); token 0 was written for it",
 }
 
 _REFUSALS = {
@@ -583,7 +584,8 @@ def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
     _need_cuda(logits)
     assert logits.dim() == 2 and logits.dtype == torch.float32 and logits.is_contiguous()
     out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-    _call("kirai_argmax_rows", _ptr(logits), _ptr(out), _i(logits.shape[0]), _i(logits.shape[1]), _stream())
+    _call("kirai_argmax_rows", _ptr(logits), _ptr(out), _i(logits.shape[0]), _i(logits.shape[1]),
+          _ptr(error_flag(logits.device)), _stream())
     return out
 
 
@@ -597,5 +599,5 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Te
     scratch = torch.empty_like(logits)
     out = torch.empty(rows, dtype=torch.int32, device=logits.device)
     _call("kirai_sample_rows", _ptr(logits), _ptr(scratch), _ptr(temperature), _ptr(top_p), _ptr(draw), _ptr(out),
-          _i(rows), _i(logits.shape[1]), _stream())
+          _i(rows), _i(logits.shape[1]), _ptr(error_flag(logits.device)), _stream())
     return out

@@ -24,7 +24,8 @@ __device__ __forceinline__ void argmax_combine(float& best, int& best_index, flo
     }
 }
 
-// Block-wide argmax with the lowest index on ties; every thread gets the result.
+// Block-wide argmax with the lowest index on ties; every thread gets the result.  A row in which nothing is
+// greater than -infinity (all NaN, all -inf) has no maximum: the result is then -1, for the caller to handle.
 __device__ int block_argmax(const float* __restrict__ row, int vocab, float inv_temperature, float* out_max) {
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
@@ -68,21 +69,31 @@ __device__ int block_argmax(const float* __restrict__ row, int vocab, float inv_
         argmax_combine(best, best_index, other, other_index);
     }
     if (out_max) *out_max = best;
-    return best_index;
+    return best_index == 0x7fffffff ? -1 : best_index;
 }
 
-__global__ void __launch_bounds__(SAMPLE_THREADS) argmax_rows_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
+// A row without a maximum: token 0 is written (an index inside the vocabulary) and the device error word set.
+__device__ __forceinline__ void no_maximum(int* __restrict__ out, int r, int* __restrict__ error_flag) {
+    if (threadIdx.x == 0) {
+        out[r] = 0;
+        if (error_flag) atomicExch(error_flag, KIRAI_FLAG_NO_MAXIMUM);
+    }
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_rows_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab, int* __restrict__ error_flag) {
     pdl_launch_dependents();
     pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * vocab;
     const int best = block_argmax(row, vocab, 1.0f, nullptr);
+    if (best < 0) return no_maximum(out, blockIdx.x, error_flag);
     if (threadIdx.x == 0) out[blockIdx.x] = best;
 }
 
-KIRAI_EXPORT int kirai_argmax_rows(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
+KIRAI_EXPORT int kirai_argmax_rows(const float* logits, int* out, int rows, int vocab, int* error_flag, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return KIRAI_ERR_BAD_SIZE;
-    const int pdl_status = launch_pdl(argmax_rows_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, 1u, logits, out, vocab);
+    const int pdl_status = launch_pdl(argmax_rows_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, 1u, logits, out, vocab, error_flag);
     return pdl_status;
 }
 
@@ -155,7 +166,7 @@ __device__ int nth_equal(const float* __restrict__ probs, int vocab, float value
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const float* __restrict__ logits, float* __restrict__ probs_scratch,
                    const float* __restrict__ temperature, const float* __restrict__ top_p,
-                   const float* __restrict__ draw, int* __restrict__ out, int vocab) {
+                   const float* __restrict__ draw, int* __restrict__ out, int vocab, int* __restrict__ error_flag) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float scratch[32];
@@ -163,14 +174,14 @@ sample_rows_kernel(const float* __restrict__ logits, float* __restrict__ probs_s
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * vocab;
     const float temp = temperature[r];
+    const int best = block_argmax(row, vocab, 1.0f, nullptr);
+    if (best < 0) return no_maximum(out, r, error_flag);  // before anything is read at that index
     if (!(temp > 0.0f)) {  // greedy
-        const int best = block_argmax(row, vocab, 1.0f, nullptr);
         if (threadIdx.x == 0) out[r] = best;
         return;
     }
     float* probs = probs_scratch + (size_t)r * vocab;
     float max_scaled;
-    const int best = block_argmax(row, vocab, 1.0f, nullptr);
     max_scaled = row[best] / temp;
     float acc = 0.0f;
     for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
@@ -249,9 +260,9 @@ sample_rows_kernel(const float* __restrict__ logits, float* __restrict__ probs_s
 // probs_scratch: [rows, vocab] floats, overwritten.  temperature <= 0 means greedy for that row.
 KIRAI_EXPORT int kirai_sample_rows(const float* logits, float* probs_scratch, const float* temperature,
                                    const float* top_p, const float* draw, int* out, int rows, int vocab,
-                                   cudaStream_t stream) {
+                                   int* error_flag, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return KIRAI_ERR_BAD_SIZE;
-    const int pdl_status = launch_pdl(sample_rows_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, 1u, logits, probs_scratch, temperature, top_p, draw, out, vocab);
+    const int pdl_status = launch_pdl(sample_rows_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, 1u, logits, probs_scratch, temperature, top_p, draw, out, vocab, error_flag);
     return pdl_status;
 }

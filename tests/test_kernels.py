@@ -198,6 +198,41 @@ def attention_reference(q, k, v, positions, window, scale):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_sampler_on_the_cases_of_the_reference(ops):
+    """crates/llm-sampler/src/lib.rs:222-294 through the device sampler, all rows in one launch: greedy, the first of
+    equal maxima, a draw inside the nucleus, and ties inside the nucleus taken in index order."""
+    from test_plain_reference import REFERENCE_TOP_P_CASES
+
+    width = 4
+    rows = [([-1.0, 0.25, 3.5, 3.0], 0.0, 1.0, 0.0, 2), ([1.0, 2.0, 2.0, -1e30], 0.0, 1.0, 0.0, 1)]
+    rows += [(logits + [-1e30] * (width - len(logits)), t, p, draw, token) for logits, t, p, draw, token in REFERENCE_TOP_P_CASES]
+    logits = torch.tensor([r[0] for r in rows], device=DEV)
+    column = lambda i: torch.tensor([r[i] for r in rows], dtype=torch.float32, device=DEV)  # noqa: E731
+    got = ops.sample_rows(logits, column(1), column(2), column(3)).tolist()
+    assert got == [r[4] for r in rows]
+    assert ops.argmax_rows(logits).tolist()[:2] == [2, 1]
+    ops.check_device_errors(torch.device(DEV))
+
+
+def test_a_row_without_a_maximum_sets_the_error_word_and_stays_in_bounds(ops):
+    """All NaN or all -inf: no entry is greater than -inf.  Token 0 is written (nothing is read at a made-up index)
+    and the device error word says so; rows beside it are sampled as usual."""
+    logits = torch.randn(4, 300, device=DEV)
+    logits[1] = float("nan")
+    logits[2] = float("-inf")
+    zeros, ones = torch.zeros(4, device=DEV), torch.ones(4, device=DEV)
+    for temperature in (zeros, ones):
+        got = ops.sample_rows(logits, temperature, ones, zeros + 0.5).tolist()
+        assert got[1] == 0 and got[2] == 0 and 0 <= got[0] < 300 and 0 <= got[3] < 300
+        with pytest.raises(ops.KernelError, match="no maximum"):
+            ops.check_device_errors(torch.device(DEV))
+    assert ops.argmax_rows(logits).tolist()[1:3] == [0, 0]
+    with pytest.raises(ops.KernelError, match="no maximum"):
+        ops.check_device_errors(torch.device(DEV))
+    assert ops.argmax_rows(logits[:1]).tolist() == [int(logits[0].argmax())]
+    ops.check_device_errors(torch.device(DEV))
+
+
 @pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,window",
                          [(6, 2, 48, 8, None), (5, 5, 16, 4, 7), (8, 1, 128, 16, 40), (3, 1, 80, 1, None)])
 def test_kv_write_and_paged_attention(ops, dtype, q_heads, kv_heads, head_dim, page_size, window):
@@ -309,6 +344,41 @@ def test_argmax_and_sampling(ops, vocab):
             if vocab <= 1000:  # small enough that the sequential 32-bit walk of the plain implementation is exact too
                 expected = plain.sample_top_p(logits[row], float(temperatures[row]), float(top_ps[row]), draw)
                 assert abs(place - int(rank[expected])) <= 1, (row, draw, got[row], expected)
+
+
+def test_sampler_on_the_cases_of_the_reference(ops):
+    """crates/llm-sampler/src/lib.rs:222-294 through the device sampler, all rows in one launch: greedy, the first of
+    equal maxima, a draw inside the nucleus, and ties inside the nucleus taken in index order."""
+    from test_plain_reference import REFERENCE_TOP_P_CASES
+
+    width = 4
+    rows = [([-1.0, 0.25, 3.5, 3.0], 0.0, 1.0, 0.0, 2), ([1.0, 2.0, 2.0, -1e30], 0.0, 1.0, 0.0, 1)]
+    rows += [(logits + [-1e30] * (width - len(logits)), t, p, draw, token) for logits, t, p, draw, token in REFERENCE_TOP_P_CASES]
+    logits = torch.tensor([r[0] for r in rows], device=DEV)
+    column = lambda i: torch.tensor([r[i] for r in rows], dtype=torch.float32, device=DEV)  # noqa: E731
+    got = ops.sample_rows(logits, column(1), column(2), column(3)).tolist()
+    assert got == [r[4] for r in rows]
+    assert ops.argmax_rows(logits).tolist()[:2] == [2, 1]
+    ops.check_device_errors(torch.device(DEV))
+
+
+def test_a_row_without_a_maximum_sets_the_error_word_and_stays_in_bounds(ops):
+    """All NaN or all -inf: no entry is greater than -inf.  Token 0 is written (nothing is read at a made-up index)
+    and the device error word says so; rows beside it are sampled as usual."""
+    logits = torch.randn(4, 300, device=DEV)
+    logits[1] = float("nan")
+    logits[2] = float("-inf")
+    zeros, ones = torch.zeros(4, device=DEV), torch.ones(4, device=DEV)
+    for temperature in (zeros, ones):
+        got = ops.sample_rows(logits, temperature, ones, zeros + 0.5).tolist()
+        assert got[1] == 0 and got[2] == 0 and 0 <= got[0] < 300 and 0 <= got[3] < 300
+        with pytest.raises(ops.KernelError, match="no maximum"):
+            ops.check_device_errors(torch.device(DEV))
+    assert ops.argmax_rows(logits).tolist()[1:3] == [0, 0]
+    with pytest.raises(ops.KernelError, match="no maximum"):
+        ops.check_device_errors(torch.device(DEV))
+    assert ops.argmax_rows(logits[:1]).tolist() == [int(logits[0].argmax())]
+    ops.check_device_errors(torch.device(DEV))
 
 
 @pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,window",

@@ -116,6 +116,63 @@ def test_attention_part_in_portions(dtype, q_heads, kv_heads, head_dim, window, 
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("cut", [(2,), (1, 1)])
+def test_attention_part_on_a_case_worked_by_hand(dtype, cut):
+    """The order norm -> rotation and the mapping of query heads to kv heads, on numbers that come from no code.
+
+    Six query heads over two kv heads (groups of 3), heads of 16, two tokens, eps 0; q and k norms share a weight
+    that is 1 everywhere except 3 at component 8, the partner of component 0 under the half-split pairing (frequency
+    theta^0 = 1, so the pair turns by the position in radians).  Projected rows, the same at both tokens: every query
+    head e0; kv head 0 has k = e0, kv head 1 has k = e8; values: kv head 0 e0 then e1, kv head 1 10 e0 then 10 e1.
+    Norm first: a unit vector of 16 has mean square 1/16, scale 4: q = 4 e0, kv 0's k = 4 e0, kv 1's k = 12 e8.
+    Rotation at the second token: q1 = 4 (cos 1 e0 + sin 1 e8); kv 0: k1 = the same; kv 1: k1 = 12 (-sin 1 e0 + cos 1 e8).
+    Scores of the second token, times 16^-1/2: kv 0: 4 cos 1 and 4; kv 1: 12 sin 1 and 0.  So a head on kv 0 mixes its
+    two values with weights 0.1371944, 0.8628056 and a head on kv 1 with 0.9999588, 0.0000412 (times 10).
+    Round-robin heads (h % 2) would swap heads 1 and 4; rotation before the norm would put the weight 3 on the turned
+    component and give kv 0 the second score (16 cos^2 1 + 144 sin^2 1) / 4 = 26.66."""
+    from kirai_b200.parts import GQAttention, RotaryEmbedding
+    from kirai_b200.weights.loader import from_tensors
+    from part_helpers import runtime
+
+    d, hidden = 16, 96
+    attention = GQAttention("a.", hidden, 6, 2, d, RotaryEmbedding(d, 777.0), qk_norm_eps=0.0)
+    norm = torch.ones(d)
+    norm[8] = 3.0
+    unit = lambda index, scale=1.0: torch.nn.functional.one_hot(torch.tensor(index), hidden).float() * scale  # noqa: E731
+    both = unit(0) + unit(1)  # a row that answers 1 to either token
+    q = torch.zeros(6 * d, hidden)
+    for head in range(6):
+        q[head * d] = both
+    k = torch.zeros(2 * d, hidden)
+    k[0], k[d + 8] = both, both
+    v = torch.zeros(2 * d, hidden)
+    v[0], v[1], v[d], v[d + 1] = unit(0), unit(1), unit(0, 10.0), unit(1, 10.0)
+    tensors = {"a.q_proj.weight": q, "a.k_proj.weight": k, "a.v_proj.weight": v, "a.o_proj.weight": torch.eye(hidden),
+               "a.q_norm.weight": norm, "a.k_norm.weight": norm}
+    tensors = {name: t.to(torch.bfloat16) for name, t in tensors.items()}
+    attention.load(from_tensors(tensors, attention.weight_specs(), DEV), runtime(dtype))
+    session = Session([attention.cache_need()], dtype, page_size=4)
+    x = torch.stack([unit(0), unit(1)]).to(dtype).to(DEV)
+    outputs, start = [], 0
+    for count in cut:  # both tokens in one step, or the second as a decoded token
+        batch = session.batch([("r", count)])
+        outputs.append(attention.forward(x[start : start + count], batch, session.cache.layer_view(0), True))
+        session.commit()
+        start += count
+    got = torch.cat(outputs).float().cpu().reshape(2, 6, d)
+    on_kv0, on_kv1 = torch.zeros(d), torch.zeros(d)
+    on_kv0[0], on_kv0[1] = 0.1371944, 0.8628056
+    on_kv1[0], on_kv1[1] = 9.9995883, 0.0004117
+    bound = 2e-5 if dtype == torch.float32 else 0.02
+    for head in range(6):
+        first = torch.zeros(d)
+        first[0] = 1.0 if head < 3 else 10.0
+        assert float((got[0, head] - first).abs().max()) <= bound, head          # the first token sees itself only
+        expected = on_kv0 if head < 3 else on_kv1
+        assert float((got[1, head] - expected).abs().max()) <= bound * (1.0 if head < 3 else 10.0), (head, got[1, head, :2])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("arrangement", ["pre_norm", "parallel"])
 def test_block_arrangements(dtype, arrangement):
     from kirai_b200.parts import Block, GQAttention, RMSNorm, RotaryEmbedding, SwiGLU
