@@ -54,6 +54,14 @@ class CacheManager:
             num_pages = max(1, _round_up(max_tokens, page_size) // page_size)
         self.page_size, self.num_pages, self.num_slots = page_size, num_pages, num_slots
         self.dtype, self.device = dtype, (torch.device(device) if device is not None else None)
+        # a page size that the attention kernels of this dtype would refuse at the first step is refused here
+        from ..csrc.ops import page_size_refusal
+
+        for layer, need in enumerate(needs):
+            if isinstance(need, KVCacheNeed):
+                reason = page_size_refusal(dtype, need.head_dim, page_size)
+                if reason is not None:
+                    raise CacheError(f"cache layer {layer}: {reason}")
         groups: List[GroupSpec] = []
         self._layer_place: Dict[int, tuple] = {}  # cache layer -> ("kv", group, index in group) | ("state", key)
         for layer, need in enumerate(needs):

@@ -66,6 +66,7 @@ class _PoolView:
     free_pages = property(lambda self: self._stat(1))
     used_pages = property(lambda self: self._stat(2))
     high_water = property(lambda self: self._stat(3))
+    handed_out = property(lambda self: self._stat(4))
 
 
 class _SlotsView:
@@ -234,7 +235,8 @@ class NativePageTables:
         return {
             "page_size": self.page_size,
             "groups": [
-                {"window": g.window, "layers": len(g.layers), "pages": p.num_pages, "used": p.used_pages, "high_water": p.high_water}
+                {"window": g.window, "layers": len(g.layers), "pages": p.num_pages, "used": p.used_pages, "high_water": p.high_water,
+                 "handed_out": p.handed_out}
                 for g, p in zip(self.groups, self.pools)
             ],
             "slots_free": self.slots.free_slots,

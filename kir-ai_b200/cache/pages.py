@@ -37,6 +37,7 @@ class PagePool:
         self._free: List[int] = list(range(num_pages - 1, -1, -1))
         self._held = [False] * num_pages
         self.high_water = 0
+        self.handed_out = 0  # pages given out since creation; more than num_pages means that pages were used again
 
     @property
     def free_pages(self) -> int:
@@ -58,6 +59,7 @@ class PagePool:
                 raise CacheError(f"page {page} was on the free list while held")
             self._held[page] = True
         self.high_water = max(self.high_water, self.used_pages)
+        self.handed_out += count
         return pages
 
     def release(self, pages: List[int]) -> None:
@@ -239,7 +241,8 @@ class PageTables:
         return {
             "page_size": self.page_size,
             "groups": [
-                {"window": g.window, "layers": len(g.layers), "pages": p.num_pages, "used": p.used_pages, "high_water": p.high_water}
+                {"window": g.window, "layers": len(g.layers), "pages": p.num_pages, "used": p.used_pages, "high_water": p.high_water,
+                 "handed_out": p.handed_out}
                 for g, p in zip(self.groups, self.pools)
             ],
             "slots_free": self.slots.free_slots,

@@ -258,6 +258,29 @@ def paged_attention_plain(q: torch.Tensor, cache: torch.Tensor, block_table: tor
     return out
 
 
+def attention_takes_tensor_cores(dtype: torch.dtype, head_dim: int) -> bool:
+    """Whether attention over a cache of this dtype and head size runs on the tensor-core kernels (else the
+    CUDA-core kernel, which takes any size)."""
+    return dtype == torch.bfloat16 and head_dim % 8 == 0 and 0 < head_dim <= 256
+
+
+def page_size_refusal(dtype: torch.dtype, head_dim: int, page_size: int) -> Optional[str]:
+    """Why the attention kernels for this dtype and head size cannot read pages of ``page_size`` tokens, or None.
+    The tensor-core kernels fetch keys and values by TMA in boxes of whole page rows that tile their 16- and 64-key
+    tiles: a page must be a power of two up to 64 tokens, or a multiple of 64.  The CUDA-core kernel (32-bit, and
+    head sizes the others do not take) reads row by row and takes any page size."""
+    if page_size < 1:
+        return f"a cache page holds at least one token, got {page_size}"
+    if not attention_takes_tensor_cores(dtype, head_dim):
+        return None
+    if page_size <= 64 and page_size & (page_size - 1) == 0:
+        return None
+    if page_size % 64 == 0:
+        return None
+    return (f"pages of {page_size} tokens: the bfloat16 attention kernels (head size {head_dim}) take pages of "
+            "1, 2, 4, 8, 16, 32 or 64 tokens, or a multiple of 64")
+
+
 def attention_prefill_takes_tcgen05(q_heads: int, kv_heads: int, head_dim: int, page_size: int) -> bool:
     """Whether the tcgen05 prompt-attention kernel takes this shape: head size up to 128, a group size
     that divides its 128 query rows, pages of a power-of-two size."""
@@ -382,8 +405,7 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
     tensor-core kernels (the decode kernel when every request brings one token), or the plain
     kernel for head sizes they do not take (not a multiple of 8, or above 256)."""
     head_dim, q_heads, kv_heads = q.shape[2], q.shape[1], cache.shape[2]
-    fast = (q.dtype == torch.bfloat16 and head_dim % 8 == 0 and head_dim <= 256 and q.stride(0) % 8 == 0
-            and q.data_ptr() % 16 == 0)
+    fast = attention_takes_tensor_cores(q.dtype, head_dim) and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
     if not fast:
         return paged_attention_plain(q, cache, block_table, batch.request_of_token, batch.positions, window, scale)
     if batch.decode_only and q_heads // kv_heads <= 16:

@@ -24,6 +24,7 @@ struct Pool {
     std::vector<int> free_list;  // stack: the page freed last is given out first
     std::vector<char> held;
     int high_water = 0;
+    long handed_out = 0;  // pages given out since creation; more than num_pages means that pages were used again
     int used() const { return num_pages - (int)free_list.size(); }
 };
 
@@ -125,6 +126,7 @@ KIRAI_HOST_EXPORT int kirai_pages_reserve(void* handle, long key, long new_token
             pool.free_list.pop_back();
             if (pool.held[page]) return -4;
             pool.held[page] = 1;
+            ++pool.handed_out;
             request.tables[g].push_back(page);
             changed = true;
         }
@@ -223,7 +225,7 @@ KIRAI_HOST_EXPORT int kirai_pages_fill_tables(void* handle, const long* keys, in
     }
     return 0;
 }
-// what: 0 pages of the pool, 1 free, 2 used, 3 high water.  group < 0: slots (0 total, 1 free), live requests (2).
+// what: 0 pages of the pool, 1 free, 2 used, 3 high water, 4 pages handed out since creation (saturating).  group < 0: slots (0 total, 1 free), live requests (2).
 KIRAI_HOST_EXPORT int kirai_pages_stat(void* handle, int group, int what) {
     Tables& t = *static_cast<Tables*>(handle);
     if (group < 0) {
@@ -239,6 +241,7 @@ KIRAI_HOST_EXPORT int kirai_pages_stat(void* handle, int group, int what) {
         case 1: return (int)pool.free_list.size();
         case 2: return pool.used();
         case 3: return pool.high_water;
+        case 4: return pool.handed_out > 0x7fffffffL ? 0x7fffffff : (int)pool.handed_out;
     }
     return -6;
 }

@@ -222,3 +222,42 @@ class DecodeGraphs:
             graph = DecodeGraph(self.runner, key[0], key[1], balanced)
             self.graphs[key] = graph
         return graph, graph.graph is None
+
+
+def captured_and_eager_logits(graphs: DecodeGraphs, requests: Sequence[object], tokens: Sequence[int]) -> dict:
+    """A check of the captured decode step against the step function, on the same cache state.
+
+    ``requests`` (page handles of live requests) each bring one token of ``tokens``.  The step runs through the
+    captured graph, and the step after it is queued behind it the way the engine queues ahead: its input tokens
+    are the ones the first step sampled (greedy), taken on the device.  Then the same two steps run through
+    ``run_step``, which writes the same keys and values to the same places again and commits them.  Returns the
+    four logits tensors [B, V] and the tokens of the first step; the requests end two tokens longer.
+    """
+    from .batch import StepEntry
+    from .step import run_step
+
+    runner = graphs.runner
+    cache = runner.cache
+    B = len(requests)
+    for request in requests:
+        if not cache.reserve(request, 2):
+            raise RuntimeError("no pages left for the two steps of the check")
+    lengths = [request.length for request in requests]
+    tables = [cache.block_table_array(requests, g) for g in range(len(cache.groups))]
+    width = max([1] + [t.shape[1] for t in tables])
+    graph, fresh = graphs.get(B, width, [n + 1 for n in lengths])
+    greedy = ([0.0] * B, [1.0] * B, [0.0] * B)
+    graph.load_inputs(list(tokens), lengths, [r.slot for r in requests], tables, *greedy)
+    if fresh:
+        graph.capture()
+    first = graph.launch()
+    captured_first = graph.logits_out.clone()
+    graph.load_inputs(None, [n + 1 for n in lengths], [r.slot for r in requests], tables, *greedy)
+    second = graph.launch()
+    captured_second = graph.logits_out.clone()
+    sampled = first.wait()
+    second.wait()
+    eager_first = run_step(runner.model, cache, [StepEntry(r, [int(t)], [0]) for r, t in zip(requests, tokens)])
+    eager_second = run_step(runner.model, cache, [StepEntry(r, [int(t)], [0]) for r, t in zip(requests, sampled)])
+    return {"captured": (captured_first, captured_second), "eager": (eager_first, eager_second), "sampled": sampled,
+            "balanced": graph.batch.decode_balanced, "kernels": graph.kernels_per_replay}

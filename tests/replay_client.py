@@ -43,3 +43,8 @@ class Replay:
         code = self.process.wait(timeout=120)
         self.process.stdout.close()
         return code
+
+    def stats(self) -> dict:
+        """The cache's statistics as trace_run wrote them at exit (needs ``extra=("--stats", <out_dir>/stats.json)``)."""
+        with open(os.path.join(self.out_dir, "stats.json")) as handle:
+            return json.load(handle)

@@ -191,3 +191,25 @@ def test_native_tables_refuse_misuse():
         with pytest.raises(CacheError):
             call()
     assert request.closed and request.tables == [[], []]
+
+
+def test_page_sizes_the_kernels_would_refuse_are_refused_when_the_cache_is_made():
+    """The bfloat16 attention kernels read pages by TMA boxes that tile their key tiles; a page size they cannot
+    take is refused by the cache manager, with the reason, not by a kernel at the first step.  The 32-bit path and
+    head sizes that go to the CUDA-core kernel take any page size."""
+    import torch
+
+    from kirai_b200.csrc.ops import page_size_refusal
+
+    need = [KVCacheNeed(2, 128, None)]
+    for page_size in (1, 2, 4, 8, 16, 32, 64, 128, 192):
+        assert page_size_refusal(torch.bfloat16, 128, page_size) is None
+        CacheManager(need, page_size=page_size, num_pages=4, num_slots=1, dtype=torch.bfloat16, device=None)
+    for page_size in (3, 12, 24, 48, 96, 100):
+        assert "pages of" in page_size_refusal(torch.bfloat16, 128, page_size)
+        with pytest.raises(CacheError, match="attention kernels"):
+            CacheManager(need, page_size=page_size, num_pages=4, num_slots=1, dtype=torch.bfloat16, device=None)
+        CacheManager(need, page_size=page_size, num_pages=4, num_slots=1, dtype=torch.float32, device=None)
+        CacheManager([KVCacheNeed(2, 20, None)], page_size=page_size, num_pages=4, num_slots=1, dtype=torch.bfloat16, device=None)
+    with pytest.raises(CacheError):
+        CacheManager(need, page_size=0, num_pages=4, num_slots=1, dtype=torch.float32, device=None)

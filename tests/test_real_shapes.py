@@ -10,7 +10,7 @@ import plain_qwen3 as plain
 pytestmark = pytest.mark.gpu
 
 BASE = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, head_dim=128, vocab_size=1000,
-            max_position_embeddings=4096, rms_norm_eps=1e-6, rope_theta=1000000.0)
+            max_position_embeddings=8192, rms_norm_eps=1e-6, rope_theta=1000000.0)
 CONFIGS = {
     # hidden, heads and intermediate of the 8-billion-parameter shape (untied), of the 4-billion one (tied; query
     # width 4096 over a hidden size of 2560) and of the 32-billion one (64 query heads in groups of 8)
@@ -31,7 +31,8 @@ def model(request, tmp_path_factory):
     write_random_model(folder, config_from_dict(CONFIG), seed=2, std=0.02, norm_jitter=0.1)
     config, weights = plain.read_model_folder(folder)
     tokens = torch.randint(0, CONFIG["vocab_size"], (150,), generator=torch.Generator().manual_seed(3)).tolist()
-    return dict(folder=folder, tokens=tokens, reference=plain.forward_logits(config, weights, tokens).numpy())
+    return dict(name=request.param, folder=folder, tokens=tokens, config=config, weights=weights,
+                reference=plain.forward_logits(config, weights, tokens).numpy())
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -66,3 +67,113 @@ def test_cuts_at_real_layer_sizes(model, dtype):
     decode = runner.step([StepEntry(a, tokens[101:102], [0]), StepEntry(b, tokens[40:41], [0])]).cpu().numpy()  # decode-only batch
     assert float(np.abs(decode[0] - reference[101]).max()) <= bound
     assert float(np.abs(decode[1] - reference[40]).max()) <= bound
+
+
+LONG = 4300  # tokens of the long sequence: contexts beyond 4,096, so that a decode step cuts the keys into several splits
+
+
+@pytest.fixture(scope="module")
+def long_reference(model):
+    """One long sequence and its plain logits at the places the tests below look at.  Requests of different lengths
+    are prefixes of it: logits at a position do not depend on what follows, so one plain pass serves them all."""
+    vocab = model["config"]["vocab_size"]
+    tokens = torch.randint(0, vocab, (LONG,), generator=torch.Generator().manual_seed(11)).tolist()
+    with torch.no_grad():
+        logits = plain.forward_logits(model["config"], model["weights"], tokens).numpy()
+    return dict(tokens=tokens, logits=logits)
+
+
+# lengths of the live requests' caches before the checked step: long and equal (several splits over the context),
+# unequal (the kernel that cuts all keys into equal ranges), and more than 16 rows (norms as kernels of their own)
+BATCHES = {
+    "one": [4200],
+    "eight_equal": [4100] * 8,
+    "eight_unequal": [4200, 37, 4111, 1500, 64, 2300, 900, 4160],
+    "twenty": [4200, 37, 4111, 1500, 64, 2300, 900, 4160, 15, 16, 17, 3000, 4096, 4095, 1, 2048, 333, 4250, 129, 640],
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_captured_decode_steps_at_long_contexts(model, long_reference, dtype):
+    """What a benchmark of decode steps times, checked: the captured decode step, and the step queued behind it that
+    takes its tokens from the first on the device, against the step function on the same cache state (logits, both
+    steps) and against the plain implementation (first step), at real layer widths, contexts beyond 4,096 tokens,
+    batches of 1, 8 and 20, equal and unequal lengths."""
+    from kirai_b200.engine.batch import StepEntry
+    from kirai_b200.engine.graphs import DecodeGraphs, captured_and_eager_logits
+    from kirai_b200.engine.runner import ModelRunner
+
+    tokens, reference = long_reference["tokens"], long_reference["logits"]
+    scale = float(np.abs(reference).max())
+    bound = 1e-4 if dtype == "float32" else 0.02 * scale
+    most = max(sum(lengths) for lengths in BATCHES.values())
+    runner = ModelRunner.from_folder(model["folder"], dtype=dtype, page_size=16, max_tokens=most + 64 * 20, num_slots=20)
+    graphs = DecodeGraphs(runner)
+    kernels_seen = set()
+    for name, lengths in BATCHES.items():
+        requests = [runner.cache.open((name, i)) for i in range(len(lengths))]
+        for request, n in zip(requests, lengths):  # fill the caches: prompts in portions of at most 2,048 tokens
+            for start in range(0, n, 2048):
+                runner.step([StepEntry(request, tokens[start : min(n, start + 2048)], [])])
+        result = captured_and_eager_logits(graphs, requests, [tokens[n] for n in lengths])
+        kernels_seen.add(result["balanced"])
+        captured, eager = result["captured"], result["eager"]
+        for step in range(2):
+            difference = float((captured[step] - eager[step]).abs().max())
+            assert difference <= bound, f"{name}: captured step {step} differs from the step function by {difference}"
+        expected = reference[lengths]  # the token at position n is the last of a sequence of n + 1 tokens
+        for which, logits in (("captured", captured[0]), ("step function", eager[0])):
+            difference = float(np.abs(logits.cpu().numpy() - expected).max())
+            assert difference <= bound, f"{name}: {which} differs from the plain implementation by {difference}"
+        # the sampled tokens that the queued step took as its input are the greatest logits of the first step
+        assert result["sampled"] == captured[0].argmax(dim=-1).tolist()
+        for request, n in zip(requests, lengths):
+            assert request.length == n + 2
+            runner.cache.close(request)
+    if dtype == "bfloat16":
+        assert kernels_seen == {False, True}  # both decode attention kernels were captured and checked
+    assert all(g["used"] == 0 for g in runner.cache.stats()["groups"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_schedule_on_a_full_pool_at_real_layer_sizes(model, dtype):
+    """The mixed schedule of the replay tests (up to four live requests, portions of some beside decoded tokens of
+    others) at real layer widths, on a pool exactly as large as the most that is ever held, so that it runs full and
+    pages are used again."""
+    if model["name"] != "8b":
+        pytest.skip("once, at the widths of the 8-billion-parameter shape")
+    from test_replay import mixed_schedule, tokens_held_at_most
+
+    from kirai_b200.engine.batch import StepEntry
+    from kirai_b200.engine.runner import ModelRunner
+
+    vocab = model["config"]["vocab_size"]
+    sizes = [("a", 75), ("b", 40), ("c", 53), ("d", 9), ("e", 61), ("f", 34)]
+    sequences = {rid: torch.randint(0, vocab, (n,), generator=torch.Generator().manual_seed(200 + k)).tolist()
+                 for k, (rid, n) in enumerate(sizes)}
+    reference = {rid: plain.forward_logits(model["config"], model["weights"], toks).numpy() for rid, toks in sequences.items()}
+    steps = mixed_schedule(sequences)
+    page = 16
+    most = tokens_held_at_most(steps, page)
+    runner = ModelRunner.from_folder(model["folder"], dtype=dtype, page_size=page, max_tokens=most, num_slots=4)
+    live = {}
+    for entries, end in steps:
+        batch = []
+        for rid, first, count in entries:
+            if rid not in live:
+                live[rid] = runner.cache.open(rid)
+            batch.append(StepEntry(live[rid], sequences[rid][first : first + count], range(count)))
+        logits = runner.step(batch).cpu().numpy()
+        row = 0
+        for rid, first, count in entries:
+            expected = reference[rid][first : first + count]
+            bound = 1e-4 if dtype == "float32" else 0.02 * float(np.abs(reference[rid]).max())
+            difference = float(np.abs(logits[row : row + count] - expected).max())
+            assert difference <= bound, f"{rid} at {first}+{count}: {difference}"
+            row += count
+        for rid in end:
+            runner.cache.close(live.pop(rid))
+    group = runner.cache.stats()["groups"][0]
+    handed_out = sum(-(-n // page) for _, n in sizes)
+    assert group["pages"] == most // page == group["high_water"] and group["used"] == 0
+    assert group["handed_out"] == handed_out > group["pages"]

@@ -135,14 +135,21 @@ def mixed_schedule(sequences):
     return steps
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_mixed_requests_with_page_reuse(tiny, dtype, tmp_path):
-    # The most that live requests hold at once, each count rounded up to 64, is 320 tokens
-    # (a 128, b 64, c 64, e 64); all six requests together would need 448.  The pool's free list
-    # is a stack, so what a finished request gives back is the first thing the next one gets.
-    replay = Replay(tiny["folder"], dtype, str(tmp_path / "out"), max_tokens=320, page_size=tiny["page"])
-    sequences, reference = tiny["sequences"], tiny["reference"]
-    for entries, end in mixed_schedule(sequences):
+def tokens_held_at_most(steps, page_size):
+    """The most tokens that live requests hold at any time under a schedule, each request's count rounded up to
+    whole pages: a request holds its pages from its first step until the step that names it in ``end`` is over."""
+    held, most = {}, 0
+    for entries, end in steps:
+        for rid, first, count in entries:
+            held[rid] = -(-(first + count) // page_size) * page_size
+        most = max(most, sum(held.values()))
+        for rid in end:
+            del held[rid]
+    return most
+
+
+def run_mixed(replay, sequences, reference, dtype, steps):
+    for entries, end in steps:
         batch = [(rid, sequences[rid][first : first + count], range(count)) for rid, first, count in entries]
         got = replay.step(batch, end=end)
         row = 0
@@ -151,6 +158,33 @@ def test_mixed_requests_with_page_reuse(tiny, dtype, tmp_path):
                   f"mixed {rid} at {first}+{count}")
             row += count
     assert replay.close() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_requests_with_page_reuse(tiny, dtype, tmp_path):
+    """Six requests, at most four live, on a pool that is exactly as large as the most that live requests ever
+    hold at once (counted in whole pages), so that the pool runs full and every later request gets pages that an
+    earlier one gave back.  The cache's own statistics must say so: the high-water mark is the pool size, and more
+    pages were handed out than the pool has."""
+    sequences, reference = tiny["sequences"], tiny["reference"]
+    steps = mixed_schedule(sequences)
+    page = tiny["page"]
+    most = tokens_held_at_most(steps, page)
+    everything = sum(-(-len(tokens) // page) * page for tokens in sequences.values())
+    assert most <= 0.8 * everything  # the six requests would not fit together
+    replay = Replay(tiny["folder"], dtype, str(tmp_path / "out"), max_tokens=most, page_size=page,
+                    extra=("--stats", str(tmp_path / "out" / "stats.json")))
+    run_mixed(replay, sequences, reference, dtype, steps)
+    stats = replay.stats()
+    assert stats["live_requests"] == 0
+    full = [g for g in stats["groups"] if g["window"] is None]
+    assert full, "every tiny configuration has a layer that keeps all keys"
+    for group in full:
+        assert group["pages"] == most // page and group["high_water"] == group["pages"] and group["used"] == 0
+        assert group["handed_out"] == everything // page > group["pages"]
+    for group in stats["groups"]:
+        if group["window"] is not None:  # pages behind the window went back while their requests were still live
+            assert group["handed_out"] == everything // page and group["high_water"] < group["pages"]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
