@@ -158,6 +158,8 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
     parser.add_argument("--page-size", type=int, default=16, help="tokens per cache page (a power of two)")
     parser.add_argument("--points", default="1,64", help="other decode batches to measure (comma separated, '' for none)")
+    parser.add_argument("--no-check", action="store_true",
+                        help="skip the check of the captured decode step against the step function before each timing")
     parser.add_argument("--workload", default="decode", choices=["decode", "serving-4b", "batch-32b"],
                         help="decode: the contract's measurement (default).  serving-4b: 64 requests with prompts of "
                              "128..4096 tokens, 512-token prefill portions mixed with decode, 256 new tokens each, greedy, "
@@ -231,8 +233,38 @@ def main() -> int:
                "frac": prefill_flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), "flops": prefill_flops}
 
     # ------------------------------------------------------------------ decode
+    checks = {}
+
+    def check_decode(batch):
+        """What is timed below, checked first: on `batch` requests filled to the context length, the captured decode
+        step and the step queued behind it give the logits of the step function on the same cache state."""
+        from kirai_b200.engine.graphs import captured_and_eager_logits
+
+        cache = runner.cache
+        requests = [cache.open(("check", batch, i)) for i in range(batch)]
+        filled = context - 8
+        for request in requests:
+            prompt = random_prompt(filled)
+            for first in range(0, filled, args.prefill_tokens):
+                runner.step([StepEntry(request, prompt[first : first + args.prefill_tokens], [])], check_errors=False)
+        result = captured_and_eager_logits(engine.graphs, requests, random_prompt(batch))
+        worst, scale = 0.0, 0.0
+        for captured, eager in zip(result["captured"], result["eager"]):
+            if not bool(torch.isfinite(captured).all()) or not bool(torch.isfinite(eager).all()):
+                raise SystemExit(f"check failed at batch {batch}: logits are not finite")
+            worst = max(worst, float((captured - eager).abs().max()))
+            scale = max(scale, float(eager.abs().max()))
+        for request in requests:
+            cache.close(request)
+        ops.check_device_errors(runner.rt.device)
+        if worst > 0.02 * scale:  # the bound of the bfloat16 tests
+            raise SystemExit(f"check failed at batch {batch}: captured and eager logits differ by {worst} (largest logit {scale})")
+        checks[batch] = {"max_abs_diff": worst, "largest_logit": scale}
+
     def measure_decode(batch):
         """Fills `batch` requests' caches through the engine, then times decode steps two ways."""
+        if not args.no_check:
+            check_decode(batch)
         # Requests that finish their prompt early decode while the others are still being filled, one
         # token per fill step; start them that much lower so that all end near the context length.
         budget = args.prefill_tokens
@@ -315,6 +347,8 @@ def main() -> int:
                 "h2d_bytes_per_step": main_result["h2d"], "d2h_bytes_per_step": main_result["d2h"]},
         "gpu_launches": main_result["kernels"] * steps,
         "clocks": clock_record,
+        "checked": bool(checks) and all(b in checks for b in batches),
+        "check": {f"decode_b{b}": checks[b] for b in checks},
     }
     print(json.dumps(line))
     return 0

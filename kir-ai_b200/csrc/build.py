@@ -29,6 +29,7 @@ SOURCES = [
     "gemm_tcgen05.cu",
     "attention_mma.cu",
     "attention_tcgen05.cu",
+    "wait_selftest.cu",
 ]
 HEADERS = ["common.cuh", "sm100.cuh", "tensor_map.cuh", "no_alloc.h"]
 

@@ -115,6 +115,16 @@ def check_device_errors(device: torch.device) -> None:
         raise KernelError(f"a kernel reported: {_ERROR_NAMES.get(value, f'error {value}')}")
 
 
+def wait_selftest(device: torch.device, limit: int = 10_000, arrive: bool = False) -> int:
+    """Launches the self-test of the bounded waits: a kernel that waits, at most ``limit`` polls, for a barrier on
+    which nothing arrives (or, with ``arrive``, on which another thread does).  A wait that runs out sets the device
+    error word, which ``check_device_errors`` turns into a KernelError; the kernel returns either way.  Returns the
+    number of polls after which the wait gave up (0 if it was answered)."""
+    polls = torch.zeros(1, dtype=torch.int32, device=device)
+    _call("kirai_wait_selftest", ctypes.c_uint(limit), _i(1 if arrive else 0), _ptr(error_flag(device)), _ptr(polls), _stream())
+    return int(polls.item())
+
+
 # ------------------------------------------------------------------- embedding
 def embedding(table, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Rows ``ids`` of ``table`` [V, H] (a tensor, or a ``TiledWeight`` shared with the output head) widened to

@@ -45,13 +45,14 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 // `limit` polls it gives up and returns false, and the caller records the
 // failure and winds the kernel down instead of hanging the device.
 #define KIRAI_WAIT_LIMIT (1u << 24)
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t spin = 0; spin < KIRAI_WAIT_LIMIT; ++spin) {
+__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, uint32_t limit) {
+    for (uint32_t spin = 0; spin < limit; ++spin) {
         if (mbar_test(bar, parity)) return true;
         if (spin > 64) __nanosleep(spin > 4096 ? 256 : 32);
     }
     return false;
 }
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) { return mbar_wait_limited(bar, parity, KIRAI_WAIT_LIMIT); }
 
 // The same for waits on the critical path of a pipeline (between an MMA and the warps that consume
 // its result): polls without sleeping for a long while, so that the wake-up adds no latency.

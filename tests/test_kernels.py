@@ -198,6 +198,26 @@ def attention_reference(q, k, v, positions, window, scale):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_device_stays_usable(ops):
+    """Every barrier wait in the kernels gives up after a number of polls, sets the device error word and lets the
+    kernel return.  The self-test kernel waits for a barrier that nothing completes: the host must read "a bounded
+    wait ... ran out", and the launches after it must run as if nothing had happened."""
+    device = torch.device(DEV)
+    assert ops.wait_selftest(device, limit=10_000, arrive=True) == 0   # the control: an answered wait is no error
+    ops.check_device_errors(device)
+    assert ops.wait_selftest(device, limit=10_000) == 10_000
+    with pytest.raises(ops.KernelError, match="bounded wait inside a kernel ran out"):
+        ops.check_device_errors(device)
+    ops.check_device_errors(device)  # reading the word cleared it
+    x = rand(5, 64, dtype=torch.bfloat16)
+    w = rand(24, 64, dtype=torch.bfloat16, seed=1)
+    out = ops.linear(x, w)  # a tensor-core product with its own barrier waits, right after
+    assert float((out.float() - x.float() @ w.float().T).abs().max()) <= tol(torch.bfloat16, 8.0)
+    ops.check_device_errors(device)
+    with pytest.raises(ops.KernelError, match="refused"):
+        ops.wait_selftest(device, limit=1 << 21)
+
+
 def test_sampler_on_the_cases_of_the_reference(ops):
     """crates/llm-sampler/src/lib.rs:222-294 through the device sampler, all rows in one launch: greedy, the first of
     equal maxima, a draw inside the nucleus, and ties inside the nucleus taken in index order."""
@@ -344,6 +364,26 @@ def test_argmax_and_sampling(ops, vocab):
             if vocab <= 1000:  # small enough that the sequential 32-bit walk of the plain implementation is exact too
                 expected = plain.sample_top_p(logits[row], float(temperatures[row]), float(top_ps[row]), draw)
                 assert abs(place - int(rank[expected])) <= 1, (row, draw, got[row], expected)
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_device_stays_usable(ops):
+    """Every barrier wait in the kernels gives up after a number of polls, sets the device error word and lets the
+    kernel return.  The self-test kernel waits for a barrier that nothing completes: the host must read "a bounded
+    wait ... ran out", and the launches after it must run as if nothing had happened."""
+    device = torch.device(DEV)
+    assert ops.wait_selftest(device, limit=10_000, arrive=True) == 0   # the control: an answered wait is no error
+    ops.check_device_errors(device)
+    assert ops.wait_selftest(device, limit=10_000) == 10_000
+    with pytest.raises(ops.KernelError, match="bounded wait inside a kernel ran out"):
+        ops.check_device_errors(device)
+    ops.check_device_errors(device)  # reading the word cleared it
+    x = rand(5, 64, dtype=torch.bfloat16)
+    w = rand(24, 64, dtype=torch.bfloat16, seed=1)
+    out = ops.linear(x, w)  # a tensor-core product with its own barrier waits, right after
+    assert float((out.float() - x.float() @ w.float().T).abs().max()) <= tol(torch.bfloat16, 8.0)
+    ops.check_device_errors(device)
+    with pytest.raises(ops.KernelError, match="refused"):
+        ops.wait_selftest(device, limit=1 << 21)
 
 
 def test_sampler_on_the_cases_of_the_reference(ops):
