@@ -27,6 +27,7 @@ SOURCES = [
     "attention_plain.cu",
     "sampling.cu",
     "gemm_tcgen05.cu",
+    "gemm_chain.cu",
     "attention_mma.cu",
     "attention_tcgen05.cu",
     "wait_selftest.cu",

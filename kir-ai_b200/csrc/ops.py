@@ -84,6 +84,14 @@ launch_count = 0  # entry points called so far (each launches one to three kerne
 
 
 def _call(name: str, *args) -> None:
+    """Launches one entry point on the current stream.  Products that were held back to be launched together
+    (see ``chained_products``) go first: launches keep the order in which they were asked for."""
+    if _pending:
+        flush_products()
+    _launch(name, *args)
+
+
+def _launch(name: str, *args) -> None:
     global launch_count
     fn = getattr(library(), name)
     fn.restype = ctypes.c_int
@@ -112,6 +120,9 @@ def check_device_errors(device: torch.device) -> None:
     value = int(flag.item())
     if value != 0:
         flag.zero_()
+        if value == 4:  # a kernel gave up in mid-work: counters that it shares with its next launch start from zero again
+            for workspace in _chain_workspaces.values():
+                workspace.zero_()
         raise KernelError(f"a kernel reported: {_ERROR_NAMES.get(value, f'error {value}')}")
 
 
@@ -505,17 +516,135 @@ def tile_weight(weight: torch.Tensor) -> TiledWeight:
     return TiledWeight(boxes, n, k)
 
 
-def _gemm(x, weight, out, n: int, k: int, width: int, splits: int, form: int, row_scale, resid, norm_weight, sumsq_out):
+# ---- products held back and launched together
+# A decode step of a few tokens runs product after product, each bound by its weight stream, and every launch pays a
+# ramp of its own.  Inside ``chained_products()`` a product of at most 64 rows with tiled weights is not launched at
+# once: it is put on a list, and the list goes out as ONE persistent kernel (csrc/gemm_chain.cu, whose weight stream
+# runs on from product to product) as soon as anything else is launched or the block ends.  Results are therefore
+# not computed when ``linear_tcgen05`` returns, only when the next kernel of another kind has been asked for: code
+# inside such a block must touch activations through the functions of this module only (every one of them sends the
+# list out first), never through torch arithmetic or a copy to the host.
+chain_stamps = None     # a tensor of sms * 6 * 4 int64: the chain kernel writes its clock stamps there (measurements)
+# Off by default: on the 8B layer sizes the chain measured slower than the products launched one by one (see the
+# head of csrc/gemm_chain.cu for the figures and the reasons); True lets the model's steps use it.
+chain_products = False
+_chain_depth = 0
+_pending: list = []
+_chain_workspaces: dict = {}
+
+
+class chained_products:
+    """``with ops.chained_products(): ...`` holds products back as described above; ``enabled=False`` does nothing."""
+
+    def __init__(self, enabled: bool = True):
+        self.enabled = enabled and chain_products
+
+    def __enter__(self):
+        global _chain_depth
+        if self.enabled:
+            _chain_depth += 1
+        return self
+
+    def __exit__(self, kind, value, traceback):
+        global _chain_depth
+        if self.enabled:
+            _chain_depth -= 1
+            if _chain_depth == 0:
+                if kind is None:
+                    flush_products()
+                else:
+                    _pending.clear()  # an error on the way: nothing half-described is launched
+        return False
+
+
+def chaining() -> bool:
+    """Whether products are being held back right now."""
+    return _chain_depth > 0 and chain_products
+
+
+def _chain_workspace(device: torch.device) -> torch.Tensor:
+    """One workspace per device (partial tiles and counters, 10 MB): chains on one device run one after the other, as
+    everything of a step does; two streams that ran chains at the same time would need one each."""
+    key = torch.device(device)
+    if key.index is None:
+        key = torch.device("cuda", torch.cuda.current_device())
+    if key not in _chain_workspaces:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the workspace of chained products must exist before a stream capture begins: "
+                              "run the step once outside the capture")
+        size = library().kirai_gemm_chain_workspace_bytes
+        size.restype = ctypes.c_long
+        _chain_workspaces[key] = torch.zeros(int(size()), dtype=torch.uint8, device=device)
+    return _chain_workspaces[key]
+
+
+def _launch_product(item) -> None:
+    x, weight, out, n, k, width, splits, form, row_scale, resid, norm_weight, sumsq_out = item
     tiled = isinstance(weight, TiledWeight)
     if row_scale is not None:
         sumsq, count, eps = row_scale
-        assert sumsq.dtype == torch.float32 and sumsq.dim() == 2 and sumsq.shape[1] == x.shape[0] and sumsq.is_contiguous()
         scale_args = (_ptr(sumsq), _i(sumsq.shape[0]), _f(float(count)), _f(float(eps)))
     else:
         scale_args = (_ptr(None), _i(0), _f(1.0), _f(0.0))
-    _call("kirai_gemm_bf16_general", _ptr(x), _ptr(weight.boxes if tiled else weight), _i(tiled), _ptr(out), _i(x.shape[0]),
-          _i(n), _i(k), _l(x.stride(0)), _l(width), _i(splits), _i(form), *scale_args,
-          _ptr(resid), _ptr(norm_weight), _ptr(sumsq_out), _ptr(error_flag(x.device)), _stream())
+    _launch("kirai_gemm_bf16_general", _ptr(x), _ptr(weight.boxes if tiled else weight), _i(tiled), _ptr(out), _i(x.shape[0]),
+            _i(n), _i(k), _l(x.stride(0)), _l(width), _i(splits), _i(form), *scale_args,
+            _ptr(resid), _ptr(norm_weight), _ptr(sumsq_out), _ptr(error_flag(x.device)), _stream())
+
+
+def flush_products() -> None:
+    """Launches the products that were held back: one alone through the single-product kernel, several as one chain."""
+    global _pending
+    items, _pending = _pending, []
+    if not items:
+        return
+    if len(items) > 1:
+        count = len(items)
+        pointers, longs, ints, floats = ctypes.c_void_p * count, ctypes.c_long * count, ctypes.c_int * count, ctypes.c_float * count
+
+        def ptrs(values):
+            return pointers(*[0 if v is None else v.data_ptr() for v in values])
+
+        x0 = items[0][0]
+        workspace = _chain_workspace(x0.device)
+        scales = [item[8] for item in items]
+        fn = library().kirai_gemm_chain_bf16
+        fn.restype = ctypes.c_int
+        status = fn(
+            _i(count), _i(x0.shape[0]), ptrs([item[0] for item in items]), longs(*[item[0].stride(0) for item in items]),
+            ptrs([item[1].boxes for item in items]), ptrs([item[2] for item in items]), longs(*[item[5] for item in items]),
+            ints(*[item[3] for item in items]), ints(*[item[4] for item in items]), ints(*[item[7] for item in items]),
+            ptrs([None if sc is None else sc[0] for sc in scales]), ints(*[0 if sc is None else sc[0].shape[0] for sc in scales]),
+            floats(*[1.0 if sc is None else float(sc[1]) for sc in scales]), floats(*[0.0 if sc is None else float(sc[2]) for sc in scales]),
+            ptrs([item[9] for item in items]), ptrs([item[10] for item in items]), ptrs([item[11] for item in items]),
+            _ptr(workspace), _l(workspace.numel()), _ptr(error_flag(x0.device)), _ptr(chain_stamps), _stream())
+        if status == 0:
+            global launch_count
+            launch_count += 1
+            return
+        if status not in _REFUSALS:
+            _check(status, "kirai_gemm_chain_bf16")
+        # refused (a shape the chain does not take): one by one
+    for item in items:
+        _launch_product(item)
+
+
+def _gemm(x, weight, out, n: int, k: int, width: int, splits: int, form: int, row_scale, resid, norm_weight, sumsq_out):
+    if row_scale is not None:
+        sumsq = row_scale[0]
+        assert sumsq.dtype == torch.float32 and sumsq.dim() == 2 and sumsq.shape[1] == x.shape[0] and sumsq.is_contiguous()
+    item = (x, weight, out, n, k, width, splits, form, row_scale, resid, norm_weight, sumsq_out)
+    if chaining() and isinstance(weight, TiledWeight) and x.shape[0] <= 64 and splits == 0:
+        if _pending and _pending[0][0].shape[0] != x.shape[0]:
+            flush_products()
+        _pending.append(item)
+        limit = library().kirai_gemm_chain_max_phases
+        limit.restype = ctypes.c_int
+        if len(_pending) >= int(limit()):
+            flush_products()
+        return
+    if _pending:
+        flush_products()
+    _launch_product(item)
 
 
 def _check_product(x, weight) -> tuple:

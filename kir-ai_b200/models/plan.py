@@ -83,6 +83,11 @@ class ModelPlan:
         (``Part.capture_safe``)."""
         return all(bool(getattr(part, "capture_safe", False)) for part in self.parts())
 
+    def kernels_only(self) -> bool:
+        """Whether products may be held back and launched together: every part promises to touch activations
+        through the kernels only (``Part.kernels_only``)."""
+        return all(bool(getattr(part, "kernels_only", False)) for part in self.parts())
+
     def weight_specs(self) -> Dict[str, WeightSpec]:
         specs: Dict[str, WeightSpec] = {}
         for part in self.parts():
@@ -99,6 +104,8 @@ class DecoderModel:
     def __init__(self, plan: ModelPlan, rt: Runtime):
         self.plan = plan.validate()
         self.rt = rt
+        # with parts that touch activations through the kernels only, a step's small products are launched together
+        self._kernels_only = plan.kernels_only() and hasattr(rt.ops, "chained_products")
 
     def load(self, weights) -> "DecoderModel":
         for part in self.plan.parts():
@@ -107,16 +114,19 @@ class DecoderModel:
 
     def forward(self, batch, cache) -> tuple:
         """The residual stream [T, H] (32-bit) and the last block's not-yet-added output."""
-        resid = self.plan.embedding.forward(batch.token_ids)
-        delta = None
-        order = self.plan.order
-        for i, call in enumerate(order):
-            view = cache.layer_view(call.cache) if call.cache is not None else None
-            following = self.plan.blocks[order[i + 1].block] if i + 1 < len(order) else None
-            resid, delta = self.plan.blocks[call.block].forward(resid, delta, batch, view, call.write, following)
+        with self.rt.ops.chained_products(self._kernels_only):
+            resid = self.plan.embedding.forward(batch.token_ids)
+            delta = None
+            order = self.plan.order
+            for i, call in enumerate(order):
+                view = cache.layer_view(call.cache) if call.cache is not None else None
+                following = self.plan.blocks[order[i + 1].block] if i + 1 < len(order) else None
+                resid, delta = self.plan.blocks[call.block].forward(resid, delta, batch, view, call.write, following)
         return resid, delta
 
     def logits(self, resid: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
         """32-bit logits [len(rows), V] of the token rows ``rows`` (int32, on the device)."""
-        normed = self.plan.final_norm.add_forward_rows(resid, delta, rows)
-        return self.plan.head.forward(normed)
+        with self.rt.ops.chained_products(self._kernels_only):
+            normed = self.plan.final_norm.add_forward_rows(resid, delta, rows)
+            logits = self.plan.head.forward(normed)
+        return logits

@@ -59,6 +59,10 @@ class GQAttention(Mixer):
         its own and answers for itself."""
         return self.position is None or bool(self.position.capture_safe)
 
+    @property
+    def kernels_only(self) -> bool:
+        return self.position is None or bool(self.position.kernels_only)
+
     def weight_specs(self) -> Dict[str, WeightSpec]:
         specs = {**self.qkv.weight_specs(), **self.out.weight_specs()}
         if self.qk_norm_eps is not None:

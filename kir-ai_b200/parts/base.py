@@ -105,6 +105,13 @@ class Part:
 
     capture_safe = False
 
+    # ``kernels_only`` true is a part's promise that it reads and writes activations through the kernels of
+    # ``rt.ops`` only: no torch arithmetic on them, no copy to the host.  ``ops`` may then hold products back and
+    # launch several of them as one kernel (``ops.chained_products``): a tensor that a product returns is filled only
+    # when the next kernel of another kind is launched.  The model runs its blocks that way only when every part
+    # promises this; otherwise every product is launched when it is asked for.
+    kernels_only = False
+
     def weight_specs(self) -> Dict[str, WeightSpec]:
         return {}
 

@@ -45,6 +45,10 @@ class Block(Part):
     def capture_safe(self) -> bool:
         return all(bool(getattr(part, "capture_safe", False)) for part in self._parts())
 
+    @property
+    def kernels_only(self) -> bool:
+        return all(bool(getattr(part, "kernels_only", False)) for part in self._parts())
+
     def weight_specs(self) -> Dict[str, WeightSpec]:
         specs: Dict[str, WeightSpec] = {}
         for part in self._parts():

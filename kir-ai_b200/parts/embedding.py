@@ -27,6 +27,7 @@ def _table(weights, rt: Runtime, name: str, hidden_size: int):
 
 class Embedding(Part):
     capture_safe = True
+    kernels_only = True
 
     def __init__(self, weight_name: str, vocab_size: int, hidden_size: int):
         self.weight_name, self.vocab_size, self.hidden_size = weight_name, vocab_size, hidden_size
@@ -48,6 +49,7 @@ class OutputHead(Part):
     """Logits = W x in 32-bit, W [V, H] (its own tensor, or the embedding table when tied)."""
 
     capture_safe = True
+    kernels_only = True
 
     def __init__(self, weight_name: str, vocab_size: int, hidden_size: int):
         self.weight_name, self.vocab_size, self.hidden_size = weight_name, vocab_size, hidden_size

@@ -18,6 +18,7 @@ from .base import FusedNormSpec, Part, Runtime, UnscaledNorm, WeightSpec
 
 class Linear(Part):
     capture_safe = True
+    kernels_only = True
 
     def __init__(self, sources: Sequence[Tuple[str, int]], in_features: int):
         self.sources: List[Tuple[str, int]] = list(sources)
@@ -44,6 +45,10 @@ class Linear(Part):
     # a decode step of one request gains 4 %, batches of 8 to 32 gain nothing, and from 64 rows on the separate
     # norm kernel wins, because the product after it loads its first weight tiles while the norm runs.
     FUSED_NORM_MAX_ROWS = 16
+    # Where products are held back and run as one persistent kernel, the separate norm would cut that kernel in
+    # two, and the weight stream that a folded norm once delayed runs on regardless: every batch that the
+    # weight-streaming products take (up to 64 rows) has its norms folded in.
+    FUSED_NORM_MAX_ROWS_CHAINED = 64
 
     def on_tensor_cores(self) -> bool:
         """Whether this layer's products run on the tensor-core kernel, which alone has the fused epilogues."""
@@ -51,7 +56,8 @@ class Linear(Part):
 
     def fuses_norms(self, rows: int) -> bool:
         """Whether a batch of ``rows`` tokens should have the norms next to this product folded into it."""
-        limit = int(os.environ.get("KIRAI_FUSED_NORM_MAX_ROWS", self.FUSED_NORM_MAX_ROWS))
+        chaining = getattr(self.rt.ops, "chaining", None)
+        limit = self.FUSED_NORM_MAX_ROWS_CHAINED if chaining is not None and chaining() else self.FUSED_NORM_MAX_ROWS
         return self.on_tensor_cores() and rows <= limit
 
     def forward_into_norm(self, x: torch.Tensor, resid: torch.Tensor, spec: FusedNormSpec) -> UnscaledNorm:

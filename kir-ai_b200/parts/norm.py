@@ -16,6 +16,7 @@ from .base import FusedNormSpec, Norm, Runtime, WeightSpec
 
 class RMSNorm(Norm):
     capture_safe = True
+    kernels_only = True
 
     def __init__(self, weight_name: str, width: int, eps: float):
         self.weight_name = weight_name

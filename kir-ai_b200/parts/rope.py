@@ -16,6 +16,7 @@ from .base import PositionEncoding, Runtime
 
 class RotaryEmbedding(PositionEncoding):
     capture_safe = True
+    kernels_only = True
 
     def __init__(self, head_dim: int, theta: float, rotary_dim: Optional[int] = None):
         self.head_dim = head_dim

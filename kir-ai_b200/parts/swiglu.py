@@ -15,6 +15,7 @@ from .linear import Linear
 
 class SwiGLU(FeedForward):
     capture_safe = True
+    kernels_only = True
 
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, names: Optional[Dict[str, str]] = None):
         n = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}

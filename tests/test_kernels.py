@@ -198,6 +198,78 @@ def attention_reference(q, k, v, positions, window, scale):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows", [1, 8, 16, 23, 64])
+@pytest.mark.parametrize("hidden,q_width,inter,qkv_width", [(200, 136, 328, 264), (4096, 4096, 1536, 6144), (128, 64, 16, 96)])
+def test_products_held_back_and_launched_as_one_kernel(ops, monkeypatch, rows, hidden, q_width, inter, qkv_width):
+    """A layer's products (output projection with the residual and the next norm, gate/up with SwiGLU, down with the
+    residual and the norm, the next q/k/v) through ``chained_products`` as one persistent kernel, against the same
+    calls launched one by one and against 32-bit arithmetic; twice in a row, since the kernel leaves its counters for
+    its next launch."""
+    eps = 1e-6
+    bf = torch.bfloat16
+    monkeypatch.setattr(ops, "chain_products", True)
+    w_o, w_gate, w_up = rand(hidden, q_width, dtype=bf, scale=0.05), rand(inter, hidden, dtype=bf, scale=0.05, seed=1), rand(inter, hidden, dtype=bf, scale=0.05, seed=2)
+    w_down, w_qkv = rand(hidden, inter, dtype=bf, scale=0.05, seed=3), rand(qkv_width, hidden, dtype=bf, scale=0.05, seed=4)
+    norm1, norm2 = 1.0 + 0.1 * rand(hidden, seed=5), 1.0 + 0.1 * rand(hidden, seed=6)
+    tiled = {name: ops.tile_weight(w) for name, w in (("o", w_o), ("down", w_down), ("qkv", w_qkv))}
+    tiled["gate_up"] = ops.tile_weight(ops.interleave_gate_up(w_gate, w_up))
+    x = rand(rows, q_width, dtype=bf, seed=7)
+    stream0 = rand(rows, hidden, scale=2.0, seed=8)
+
+    def layer(stream):
+        rows1, sumsq1 = ops.linear_residual_norm(x, tiled["o"], stream, norm1)
+        act = ops.linear_tcgen05(rows1, tiled["gate_up"], swiglu=True, row_scale=(sumsq1, hidden, eps))
+        rows2, sumsq2 = ops.linear_residual_norm(act, tiled["down"], stream, norm2)
+        return ops.linear_tcgen05(rows2, tiled["qkv"], row_scale=(sumsq2, hidden, eps))
+
+    single_stream = stream0.clone()
+    single = layer(single_stream)
+    before = ops.launch_count
+    for attempt in range(2):
+        chained_stream = stream0.clone()
+        with ops.chained_products():
+            chained = layer(chained_stream)
+            assert ops.chaining()
+        ops.check_device_errors(torch.device(DEV))
+        assert not ops.chaining()
+        # 32-bit arithmetic on the same bf16 inputs, with the roundings to bf16 where the kernels round
+        r1 = stream0 + x.float() @ w_o.float().T
+        n1 = (r1 * norm1).to(bf).float() * torch.rsqrt((r1 ** 2).mean(-1, keepdim=True) + eps)
+        gate, up = n1 @ w_gate.float().T, n1 @ w_up.float().T
+        a = (gate / (1.0 + torch.exp(-gate)) * up).to(bf).float()
+        r2 = r1 + a @ w_down.float().T
+        n2 = (r2 * norm2).to(bf).float() * torch.rsqrt((r2 ** 2).mean(-1, keepdim=True) + eps)
+        expected = n2 @ w_qkv.float().T
+        scale = float(expected.abs().max())
+        assert float((chained.float() - expected).abs().max()) <= tol(bf, scale)
+        assert float((chained_stream - r2).abs().max()) <= tol(bf, float(r2.abs().max()))
+        assert float((chained.float() - single.float()).abs().max()) <= tol(bf, scale)
+        assert float((chained_stream - single_stream).abs().max()) <= tol(bf, float(r2.abs().max()))
+    assert ops.launch_count - before == 2  # four products, one launch, each time
+
+
+def test_products_held_back_go_out_before_any_other_kernel(ops, monkeypatch):
+    """Launch order is kept: a kernel of another kind, asked for while products are held back, sees their results."""
+    bf = torch.bfloat16
+    monkeypatch.setattr(ops, "chain_products", True)
+    w1, w2 = ops.tile_weight(rand(256, 128, dtype=bf, scale=0.1)), ops.tile_weight(rand(128, 256, dtype=bf, scale=0.1, seed=1))
+    x = rand(5, 128, dtype=bf, seed=2)
+    stream = torch.zeros(5, 128, device=DEV)
+    with ops.chained_products():
+        y = ops.linear_tcgen05(ops.linear_tcgen05(x, w1), w2)
+        ops.add_into_residual(stream, y)  # not a product: the two held back are launched first
+        z = ops.linear_tcgen05(y, w1)     # held back until the block ends
+    expected = (x.float() @ w1.row_major().float().T).to(bf).float() @ w2.row_major().float().T
+    assert float((stream - expected).abs().max()) <= tol(bf, float(expected.abs().max()))
+    assert float((z.float() - y.float() @ w1.row_major().float().T).abs().max()) <= tol(bf, float(z.float().abs().max()))
+    with pytest.raises(RuntimeError, match="boom"):
+        with ops.chained_products():
+            ops.linear_tcgen05(x, w1)
+            raise RuntimeError("boom")
+    assert not ops.chaining() and ops.linear_tcgen05(x, w1).shape == (5, 256)  # nothing stayed behind
+    ops.check_device_errors(torch.device(DEV))
+
+
 def test_a_bounded_wait_that_runs_out_is_reported_and_the_device_stays_usable(ops):
     """Every barrier wait in the kernels gives up after a number of polls, sets the device error word and lets the
     kernel return.  The self-test kernel waits for a barrier that nothing completes: the host must read "a bounded
@@ -364,6 +436,78 @@ def test_argmax_and_sampling(ops, vocab):
             if vocab <= 1000:  # small enough that the sequential 32-bit walk of the plain implementation is exact too
                 expected = plain.sample_top_p(logits[row], float(temperatures[row]), float(top_ps[row]), draw)
                 assert abs(place - int(rank[expected])) <= 1, (row, draw, got[row], expected)
+
+
+@pytest.mark.parametrize("rows", [1, 8, 16, 23, 64])
+@pytest.mark.parametrize("hidden,q_width,inter,qkv_width", [(200, 136, 328, 264), (4096, 4096, 1536, 6144), (128, 64, 16, 96)])
+def test_products_held_back_and_launched_as_one_kernel(ops, monkeypatch, rows, hidden, q_width, inter, qkv_width):
+    """A layer's products (output projection with the residual and the next norm, gate/up with SwiGLU, down with the
+    residual and the norm, the next q/k/v) through ``chained_products`` as one persistent kernel, against the same
+    calls launched one by one and against 32-bit arithmetic; twice in a row, since the kernel leaves its counters for
+    its next launch."""
+    eps = 1e-6
+    bf = torch.bfloat16
+    monkeypatch.setattr(ops, "chain_products", True)
+    w_o, w_gate, w_up = rand(hidden, q_width, dtype=bf, scale=0.05), rand(inter, hidden, dtype=bf, scale=0.05, seed=1), rand(inter, hidden, dtype=bf, scale=0.05, seed=2)
+    w_down, w_qkv = rand(hidden, inter, dtype=bf, scale=0.05, seed=3), rand(qkv_width, hidden, dtype=bf, scale=0.05, seed=4)
+    norm1, norm2 = 1.0 + 0.1 * rand(hidden, seed=5), 1.0 + 0.1 * rand(hidden, seed=6)
+    tiled = {name: ops.tile_weight(w) for name, w in (("o", w_o), ("down", w_down), ("qkv", w_qkv))}
+    tiled["gate_up"] = ops.tile_weight(ops.interleave_gate_up(w_gate, w_up))
+    x = rand(rows, q_width, dtype=bf, seed=7)
+    stream0 = rand(rows, hidden, scale=2.0, seed=8)
+
+    def layer(stream):
+        rows1, sumsq1 = ops.linear_residual_norm(x, tiled["o"], stream, norm1)
+        act = ops.linear_tcgen05(rows1, tiled["gate_up"], swiglu=True, row_scale=(sumsq1, hidden, eps))
+        rows2, sumsq2 = ops.linear_residual_norm(act, tiled["down"], stream, norm2)
+        return ops.linear_tcgen05(rows2, tiled["qkv"], row_scale=(sumsq2, hidden, eps))
+
+    single_stream = stream0.clone()
+    single = layer(single_stream)
+    before = ops.launch_count
+    for attempt in range(2):
+        chained_stream = stream0.clone()
+        with ops.chained_products():
+            chained = layer(chained_stream)
+            assert ops.chaining()
+        ops.check_device_errors(torch.device(DEV))
+        assert not ops.chaining()
+        # 32-bit arithmetic on the same bf16 inputs, with the roundings to bf16 where the kernels round
+        r1 = stream0 + x.float() @ w_o.float().T
+        n1 = (r1 * norm1).to(bf).float() * torch.rsqrt((r1 ** 2).mean(-1, keepdim=True) + eps)
+        gate, up = n1 @ w_gate.float().T, n1 @ w_up.float().T
+        a = (gate / (1.0 + torch.exp(-gate)) * up).to(bf).float()
+        r2 = r1 + a @ w_down.float().T
+        n2 = (r2 * norm2).to(bf).float() * torch.rsqrt((r2 ** 2).mean(-1, keepdim=True) + eps)
+        expected = n2 @ w_qkv.float().T
+        scale = float(expected.abs().max())
+        assert float((chained.float() - expected).abs().max()) <= tol(bf, scale)
+        assert float((chained_stream - r2).abs().max()) <= tol(bf, float(r2.abs().max()))
+        assert float((chained.float() - single.float()).abs().max()) <= tol(bf, scale)
+        assert float((chained_stream - single_stream).abs().max()) <= tol(bf, float(r2.abs().max()))
+    assert ops.launch_count - before == 2  # four products, one launch, each time
+
+
+def test_products_held_back_go_out_before_any_other_kernel(ops, monkeypatch):
+    """Launch order is kept: a kernel of another kind, asked for while products are held back, sees their results."""
+    bf = torch.bfloat16
+    monkeypatch.setattr(ops, "chain_products", True)
+    w1, w2 = ops.tile_weight(rand(256, 128, dtype=bf, scale=0.1)), ops.tile_weight(rand(128, 256, dtype=bf, scale=0.1, seed=1))
+    x = rand(5, 128, dtype=bf, seed=2)
+    stream = torch.zeros(5, 128, device=DEV)
+    with ops.chained_products():
+        y = ops.linear_tcgen05(ops.linear_tcgen05(x, w1), w2)
+        ops.add_into_residual(stream, y)  # not a product: the two held back are launched first
+        z = ops.linear_tcgen05(y, w1)     # held back until the block ends
+    expected = (x.float() @ w1.row_major().float().T).to(bf).float() @ w2.row_major().float().T
+    assert float((stream - expected).abs().max()) <= tol(bf, float(expected.abs().max()))
+    assert float((z.float() - y.float() @ w1.row_major().float().T).abs().max()) <= tol(bf, float(z.float().abs().max()))
+    with pytest.raises(RuntimeError, match="boom"):
+        with ops.chained_products():
+            ops.linear_tcgen05(x, w1)
+            raise RuntimeError("boom")
+    assert not ops.chaining() and ops.linear_tcgen05(x, w1).shape == (5, 256)  # nothing stayed behind
+    ops.check_device_errors(torch.device(DEV))
 
 
 def test_a_bounded_wait_that_runs_out_is_reported_and_the_device_stays_usable(ops):

@@ -177,3 +177,34 @@ def test_mixed_schedule_on_a_full_pool_at_real_layer_sizes(model, dtype):
     handed_out = sum(-(-n // page) for _, n in sizes)
     assert group["pages"] == most // page == group["high_water"] and group["used"] == 0
     assert group["handed_out"] == handed_out > group["pages"]
+
+
+def test_steps_with_products_launched_as_one_kernel(model, monkeypatch):
+    """The model's steps with ``ops.chain_products`` set (a layer's weight-streaming products as phases of one
+    persistent kernel): single decoded tokens of three requests side by side, norms folded into the products, against
+    the plain implementation."""
+    if model["name"] == "32b":
+        pytest.skip("two shapes are enough here")
+    from kirai_b200.csrc import ops
+    from kirai_b200.engine.batch import StepEntry
+    from kirai_b200.engine.runner import ModelRunner
+
+    monkeypatch.setattr(ops, "chain_products", True)
+    runner = ModelRunner.from_folder(model["folder"], dtype="bfloat16", page_size=16, max_tokens=1024, num_slots=4)
+    tokens, reference = model["tokens"], model["reference"]
+    bound = 0.02 * float(np.abs(reference).max())
+    heads = [100, 37, 64]
+    requests = [runner.cache.open(i) for i in range(3)]
+    for request, head in zip(requests, heads):
+        runner.step([StepEntry(request, tokens[:head], [])])
+    before = ops.launch_count
+    for k in range(6):
+        logits = runner.step([StepEntry(r, [tokens[h + k]], [0]) for r, h in zip(requests, heads)]).cpu().numpy()
+        for row, head in enumerate(heads):
+            assert float(np.abs(logits[row] - reference[head + k]).max()) <= bound, (k, row)
+    # per step and layer one launch for the four products instead of four (2 layers: 6 launches fewer a step)
+    chained = (ops.launch_count - before) / 6
+    monkeypatch.setattr(ops, "chain_products", False)
+    before = ops.launch_count
+    runner.step([StepEntry(r, [tokens[h + 6]], [0]) for r, h in zip(requests, heads)])
+    assert ops.launch_count - before > chained + 3
