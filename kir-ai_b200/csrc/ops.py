@@ -311,9 +311,10 @@ def attention_prefill_takes_tcgen05(q_heads: int, kv_heads: int, head_dim: int, 
 
 def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, query_start: torch.Tensor,
                       context_len: torch.Tensor, max_query_len: int, window: Optional[int], scale: float,
-                      tcgen05: Optional[bool] = None) -> torch.Tensor:
+                      tcgen05: Optional[bool] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """bf16 tensor-core attention for runs of new tokens (prompt portions, or any mix): q [T, nq, d].
-    ``tcgen05`` picks the kernel (None: the tcgen05 kernel where it takes the shape, else the
+    ``query_start`` holds rows of ``q`` and of the result, so the requests given may be a part of a larger batch
+    (``out`` is then the whole batch's result, of which only their rows are written).  ``tcgen05`` picks the kernel (None: the tcgen05 kernel where it takes the shape, else the
     warp-level ``mma.sync`` kernel)."""
     _need_cuda(q, cache, block_table, query_start, context_len)
     num_pages, kv_heads, page_size, head_dim = _cache_dims(cache)
@@ -323,7 +324,9 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.T
     assert query_start.numel() == requests + 1 and query_start.dtype == torch.int32 and context_len.dtype == torch.int32
     if tcgen05 is None:
         tcgen05 = attention_prefill_takes_tcgen05(q_heads, kv_heads, head_dim, page_size)
-    out = torch.empty((rows, q_heads * head_dim), dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty((rows, q_heads * head_dim), dtype=q.dtype, device=q.device)
+    assert out.shape == (rows, q_heads * head_dim) and out.dtype == q.dtype and out.is_contiguous()
     _call("kirai_attention_prefill_tc_bf16" if tcgen05 else "kirai_attention_prefill_bf16", _ptr(q), _ptr(cache), _ptr(out),
           _ptr(block_table), _ptr(query_start), _ptr(context_len), _i(requests), _i(max_query_len), _i(q_heads), _i(kv_heads),
           _i(head_dim), _l(q_stride), _i(page_size), _i(block_table.shape[1]), _i(num_pages), _i(window or 0), _f(scale),
@@ -372,14 +375,17 @@ def decode_plan(context_lens, kv_heads: int, window: Optional[int] = None, tile:
 
 
 def attention_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, context_len: torch.Tensor,
-                     window: Optional[int], scale: float, num_splits: int = 1) -> torch.Tensor:
-    """bf16 tensor-core attention for a batch in which every request brings one token: q [R, nq, d]."""
+                     window: Optional[int], scale: float, num_splits: int = 1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bf16 tensor-core attention for a batch in which every request brings one token: q [R, nq, d] (row r of ``q``,
+    of the tables and of the result belongs to request r; ``out`` may be the head of a larger result)."""
     _need_cuda(q, cache, block_table, context_len)
     num_pages, kv_heads, page_size, head_dim = _cache_dims(cache)
     rows, q_heads, qd, q_stride = _head_view(q)
     assert qd == head_dim and q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
     assert context_len.numel() == rows and context_len.dtype == torch.int32
-    out = torch.empty((rows, q_heads * head_dim), dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty((rows, q_heads * head_dim), dtype=q.dtype, device=q.device)
+    assert out.shape == (rows, q_heads * head_dim) and out.dtype == q.dtype and out.is_contiguous()
     partial = None
     if num_splits > 1:
         partial = torch.empty((rows, q_heads, num_splits, head_dim + 2), dtype=torch.float32, device=q.device)
@@ -401,7 +407,8 @@ def sm_count(device: torch.device) -> int:
 
 
 def attention_decode_balanced(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, context_len: torch.Tensor,
-                              window: Optional[int], scale: float, ctas: Optional[int] = None) -> torch.Tensor:
+                              window: Optional[int], scale: float, ctas: Optional[int] = None,
+                              out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The decode attention with the key tiles of all (request, kv head) pairs cut into ``ctas`` equal ranges
     (default: one per SM), so that every CTA reads the same number of keys whatever the batch looks like."""
     _need_cuda(q, cache, block_table, context_len)
@@ -410,7 +417,9 @@ def attention_decode_balanced(q: torch.Tensor, cache: torch.Tensor, block_table:
     assert qd == head_dim and q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
     assert context_len.numel() == rows and context_len.dtype == torch.int32
     ctas = ctas or sm_count(q.device)
-    out = torch.empty((rows, q_heads * head_dim), dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty((rows, q_heads * head_dim), dtype=q.dtype, device=q.device)
+    assert out.shape == (rows, q_heads * head_dim) and out.dtype == q.dtype and out.is_contiguous()
     partial = torch.empty((ctas, 2, 16, head_dim + 2), dtype=torch.float32, device=q.device)
     _call("kirai_attention_decode_balanced_bf16", _ptr(q), _ptr(cache), _ptr(out), _ptr(partial), _ptr(block_table),
           _ptr(context_len), _i(rows), _i(q_heads), _i(kv_heads), _i(head_dim), _l(q_stride), _i(page_size),
@@ -429,21 +438,40 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
     fast = attention_takes_tensor_cores(q.dtype, head_dim) and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
     if not fast:
         return paged_attention_plain(q, cache, block_table, batch.request_of_token, batch.positions, window, scale)
-    if batch.decode_only and q_heads // kv_heads <= 16:
-        # the batch may say which kernel (a captured step does: its lengths change between replays); otherwise
-        # the host's copy of the lengths decides; KIRAI_DECODE_BALANCED=0 or 1 overrides both
-        balanced = getattr(batch, "decode_balanced", None)
-        if balanced is None and len(batch.query_lens) == batch.num_requests:
-            lens = [start + count for start, count in zip(batch.start_positions, batch.query_lens)]
-            balanced, _ = decode_plan(lens, kv_heads, window, sms=sm_count(q.device))
-        forced = os.environ.get("KIRAI_DECODE_BALANCED")
-        if forced in ("0", "1"):
-            balanced = forced == "1"
-        if balanced and batch.num_requests <= 1024:
-            return attention_decode_balanced(q, cache, block_table, batch.context_len, window, scale)
-        splits = decode_splits(batch.num_requests, kv_heads, min(batch.max_context_len, window or batch.max_context_len))
-        return attention_decode(q, cache, block_table, batch.context_len, window, scale, splits)
+    decode_rows = batch.num_requests if batch.decode_only else getattr(batch, "num_decode", 0)
+    if decode_rows and q_heads // kv_heads <= 16:
+        # The requests that bring one token stand first in the batch (the batch builder puts them there) and take the
+        # decode kernels, which split a long context over many CTAs; prompt portions take the prompt kernel, and both
+        # write their rows of one result.  A prompt kernel alone would give a decoding request one CTA per kv head.
+        out = torch.empty((q.shape[0], q_heads * head_dim), dtype=q.dtype, device=q.device)
+        _decode_rows(q[:decode_rows], cache, block_table[:decode_rows], batch, decode_rows, window, scale, out[:decode_rows])
+        if decode_rows < batch.num_requests:
+            attention_prefill(q, cache, block_table[decode_rows:], batch.query_start[decode_rows:], batch.context_len[decode_rows:],
+                              batch.max_query_len, window, scale, out=out)
+        return out
     return attention_prefill(q, cache, block_table, batch.query_start, batch.context_len, batch.max_query_len, window, scale)
+
+
+def _decode_rows(q, cache, block_table, batch, rows: int, window: Optional[int], scale: float, out: torch.Tensor) -> None:
+    """The decode attention of the first ``rows`` requests of ``batch`` (one token each)."""
+    kv_heads = cache.shape[2]
+    context_len = batch.context_len[:rows]
+    # the batch may say which kernel (a captured step does: its lengths change between replays); otherwise
+    # the host's copy of the lengths decides; KIRAI_DECODE_BALANCED=0 or 1 overrides both
+    balanced = getattr(batch, "decode_balanced", None)
+    longest = batch.max_context_len
+    if balanced is None:
+        lens = [start + count for start, count in zip(batch.start_positions[:rows], batch.query_lens[:rows])]
+        balanced, _ = decode_plan(lens, kv_heads, window, sms=sm_count(q.device))
+        longest = max(lens)
+    forced = os.environ.get("KIRAI_DECODE_BALANCED")
+    if forced in ("0", "1"):
+        balanced = forced == "1"
+    if balanced and rows <= 1024:
+        attention_decode_balanced(q, cache, block_table, context_len, window, scale, out=out)
+        return
+    splits = decode_splits(rows, kv_heads, min(longest, window or longest))
+    attention_decode(q, cache, block_table, context_len, window, scale, splits, out=out)
 
 
 # ------------------------------------------------------------------------ linear

@@ -45,6 +45,9 @@ class StepBatch:
     max_query_len: int = 0
     max_context_len: int = 0
     num_want: int = 0
+    # how many requests at the head of the batch bring exactly one token: the batch builder puts them first, so
+    # that kernels made for single tokens can take rows [0, num_decode) and the others the rest
+    num_decode: int = 0
     # which decode attention kernel a step of single tokens takes (None: decided from the lengths above)
     decode_balanced: Optional[bool] = None
 
@@ -54,7 +57,15 @@ class StepBatch:
 
 
 def build_batch(entries: Sequence[StepEntry], cache, device) -> StepBatch:
-    """Packs the entries (whose pages are already reserved) into a StepBatch on ``device``."""
+    """Packs the entries (whose pages are already reserved) into a StepBatch on ``device``.
+
+    Inside the batch the requests that bring one token come first (in their order), then the others (in theirs);
+    ``want_rows`` still lists the wanted places in the order of ``entries`` and of each ``want``, so the caller's
+    logits come back in the order it gave."""
+    given = list(entries)
+    order = [i for i, e in enumerate(given) if len(e.tokens) == 1] + [i for i, e in enumerate(given) if len(e.tokens) != 1]
+    num_decode = sum(1 for e in given if len(e.tokens) == 1)
+    entries = [given[i] for i in order]
     query_lens = [len(e.tokens) for e in entries]
     starts = [e.request.length for e in entries]
     total = sum(query_lens)
@@ -63,16 +74,17 @@ def build_batch(entries: Sequence[StepEntry], cache, device) -> StepBatch:
     positions = np.empty(total, dtype=np.int32)
     request_of_token = np.empty(total, dtype=np.int32)
     query_start = np.zeros(count + 1, dtype=np.int32)
-    want_rows: List[int] = []
+    first_row = [0] * count  # by place in ``given``
     row = 0
     for index, entry in enumerate(entries):
         n = query_lens[index]
         token_ids[row : row + n] = np.asarray(entry.tokens, dtype=np.int64)
         positions[row : row + n] = np.arange(starts[index], starts[index] + n, dtype=np.int32)
         request_of_token[row : row + n] = index
-        want_rows.extend(row + w for w in entry.want)
+        first_row[order[index]] = row
         row += n
         query_start[index + 1] = row
+    want_rows: List[int] = [first_row[i] + w for i, entry in enumerate(given) for w in entry.want]
     context_len = np.asarray([s + n for s, n in zip(starts, query_lens)], dtype=np.int32)
     slots = np.asarray([e.request.slot for e in entries], dtype=np.int32)
     requests = [e.request for e in entries]
@@ -113,4 +125,5 @@ def build_batch(entries: Sequence[StepEntry], cache, device) -> StepBatch:
         max_query_len=max(query_lens) if query_lens else 0,
         max_context_len=int(context_len.max()) if count else 0,
         num_want=int(want.size),
+        num_decode=num_decode,
     )

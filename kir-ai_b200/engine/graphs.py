@@ -69,7 +69,7 @@ class DecodeGraph:
             request_of_token=self.fixed[:B], query_start=self.fixed, context_len=self.context_len, slots=self.slots,
             block_tables=self.tables, want_rows=self.fixed[:B], query_lens=[1] * B,
             start_positions=NotOnHost("start_positions", "positions"), slot_ids=NotOnHost("slot_ids", "slots"), max_query_len=1, max_context_len=table_width * runner.cache.page_size, num_want=B,
-            decode_balanced=balanced_attention,
+            num_decode=B, decode_balanced=balanced_attention,
         )
         self.tokens_out: Optional[torch.Tensor] = None
         self.logits_out: Optional[torch.Tensor] = None  # [B, V] float32 of the last replay (for checks; nothing reads it otherwise)

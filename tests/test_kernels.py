@@ -197,7 +197,6 @@ def attention_reference(q, k, v, positions, window, scale):
     return out
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rows", [1, 8, 16, 23, 64])
 @pytest.mark.parametrize("hidden,q_width,inter,qkv_width", [(200, 136, 328, 264), (4096, 4096, 1536, 6144), (128, 64, 16, 96)])
 def test_products_held_back_and_launched_as_one_kernel(ops, monkeypatch, rows, hidden, q_width, inter, qkv_width):
@@ -325,6 +324,7 @@ def test_a_row_without_a_maximum_sets_the_error_word_and_stays_in_bounds(ops):
     ops.check_device_errors(torch.device(DEV))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,window",
                          [(6, 2, 48, 8, None), (5, 5, 16, 4, 7), (8, 1, 128, 16, 40), (3, 1, 80, 1, None)])
 def test_kv_write_and_paged_attention(ops, dtype, q_heads, kv_heads, head_dim, page_size, window):

@@ -106,8 +106,8 @@ def test_captured_decode_steps_at_long_contexts(model, long_reference, dtype):
     tokens, reference = long_reference["tokens"], long_reference["logits"]
     scale = float(np.abs(reference).max())
     bound = 1e-4 if dtype == "float32" else 0.02 * scale
-    most = max(sum(lengths) for lengths in BATCHES.values())
-    runner = ModelRunner.from_folder(model["folder"], dtype=dtype, page_size=16, max_tokens=most + 64 * 20, num_slots=20)
+    most = max(sum(lengths) for lengths in BATCHES.values()) + 3400  # and the two requests of the mixed step
+    runner = ModelRunner.from_folder(model["folder"], dtype=dtype, page_size=16, max_tokens=most + 64 * 22, num_slots=22)
     graphs = DecodeGraphs(runner)
     kernels_seen = set()
     for name, lengths in BATCHES.items():
@@ -127,6 +127,23 @@ def test_captured_decode_steps_at_long_contexts(model, long_reference, dtype):
             assert difference <= bound, f"{name}: {which} differs from the plain implementation by {difference}"
         # the sampled tokens that the queued step took as its input are the greatest logits of the first step
         assert result["sampled"] == captured[0].argmax(dim=-1).tolist()
+        if name == "eight_unequal":
+            # a mixed step: the same requests decode on (their caches hold the sequence's tokens up to n, then the two
+            # sampled ones, so only what a fresh prompt gives can be compared with the plain logits) beside a prompt
+            # portion of another request, given FIRST: inside the batch the single tokens stand first and take the
+            # decode kernels, and the logits come back in the order asked for
+            fresh = runner.cache.open((name, "fresh"))
+            again = runner.cache.open((name, "again"))
+            runner.step([StepEntry(again, tokens[:3000], [])])
+            mixed = runner.step([StepEntry(fresh, tokens[:300], [299, 0]), StepEntry(again, [tokens[3000]], [0])]
+                                + [StepEntry(r, [5], []) for r in requests[:3]]).cpu().numpy()
+            assert mixed.shape[0] == 3
+            for row, place in enumerate([299, 0, 3000]):
+                difference = float(np.abs(mixed[row] - reference[place]).max())
+                assert difference <= bound, f"mixed step, place {place}: {difference}"
+            for request in (fresh, again):
+                runner.cache.close(request)
+            lengths = [n + 1 if i < 3 else n for i, n in enumerate(lengths)]
         for request, n in zip(requests, lengths):
             assert request.length == n + 2
             runner.cache.close(request)
