@@ -100,6 +100,23 @@ def model_numbers(cfg, layers):
     )
 
 
+def ideal_seconds(step_log, numbers, cfg, peaks):
+    """The least time the logged steps could take on this GPU: every step reads every weight once and the cache of
+    the requests in it (bytes / measured copy bandwidth) and multiplies its tokens through the layers and its queries
+    with their keys (flops / measured bf16 rate); a step takes the greater of the two, and the steps add up."""
+    nq, d, layers = cfg["num_attention_heads"], cfg["head_dim"], cfg["num_hidden_layers"]
+    total, byte_steps = 0.0, 0
+    for step in step_log:
+        tokens = sum(count for _, count in step)
+        step_bytes = numbers["weight_bytes"] + sum(first + count for first, count in step) * numbers["kv_bytes_per_token"]
+        pairs = sum(count * first + count * (count + 1) // 2 for first, count in step)  # (query, key) pairs
+        flops = tokens * numbers["linear_flops_per_token"] + 4 * nq * d * layers * pairs + 2 * numbers["head_elems"] * len(step)
+        by_bytes, by_flops = step_bytes / (peaks["hbm_gbs"] * 1e9), flops / (peaks["bf16_tflops"] * 1e12)
+        total += max(by_bytes, by_flops)
+        byte_steps += by_bytes >= by_flops
+    return total, byte_steps
+
+
 def generate_workload(which: str) -> int:
     """The serving-style workloads of the larger configurations, end to end through Engine.generate."""
     import torch
@@ -116,32 +133,46 @@ def generate_workload(which: str) -> int:
         generator = torch.Generator().manual_seed(3)
         lengths = torch.randint(128, 4097, (64,), generator=generator).tolist()
         new_tokens, temperature = 256, 0.0
-        engine = Engine(config=config_from_dict(raw), random_weights_seed=3, dtype="bfloat16", page_size=16, max_new_tokens=256,
-                        max_prefill_tokens=1024, prefill_chunk=512, max_concurrent_requests=64, max_cache_tokens=64 * 4400)
+        # prompts go in portions of 512 tokens, eight of them to a step beside the tokens of the requests that decode
+        options = dict(max_new_tokens=256, max_prefill_tokens=4096, prefill_chunk=512, max_concurrent_requests=64,
+                       max_cache_tokens=64 * 4400)
+        engine = Engine(config=config_from_dict(raw), random_weights_seed=3, dtype="bfloat16", page_size=16, **options)
     else:
         raw = dict(base, num_hidden_layers=64, hidden_size=5120, intermediate_size=25600, num_attention_heads=64,
                    num_key_value_heads=8, tie_word_embeddings=False)
         generator = torch.Generator().manual_seed(4)
         lengths = [8064] * 16
         new_tokens, temperature = 128, 1.0
-        engine = Engine(config=config_from_dict(raw), random_weights_seed=4, dtype="bfloat16", page_size=16, max_new_tokens=128,
-                        max_prefill_tokens=2048, max_concurrent_requests=16, max_cache_tokens=16 * 8256)
+        options = dict(max_new_tokens=128, max_prefill_tokens=2048, max_concurrent_requests=16, max_cache_tokens=16 * 8256)
+        engine = Engine(config=config_from_dict(raw), random_weights_seed=4, dtype="bfloat16", page_size=16, **options)
     prompts = [torch.randint(0, raw["vocab_size"], (n,), generator=generator).tolist() for n in lengths]
     params = SamplingParams(temperature=temperature, seed=7, max_new_tokens=new_tokens, ignore_eos=True)
+    peaks, peak_source = load_peaks()
+    engine.step_log = []
+    clocks = ClockSampler()
+    clocks.start()
     torch.cuda.synchronize()
     started = time.perf_counter()
     outputs = engine.generate(prompts, params)
     torch.cuda.synchronize()
     seconds = time.perf_counter() - started
+    clock_record = clocks.stop()
     generated = sum(len(o.token_ids) for o in outputs)
     stats = engine.stats()
+    numbers = model_numbers(raw, raw["num_hidden_layers"])
+    ideal, byte_steps = ideal_seconds(engine.step_log, numbers, raw, peaks)
     print(json.dumps({
         "metric": f"generated tokens/s, {which} workload through Engine.generate", "value": generated / seconds,
         "unit": "tokens/s", "n_gpus": 1, "seconds": seconds, "requests": len(prompts), "prompt_tokens": sum(lengths),
         "generated_tokens": generated, "all_tokens_per_s": (sum(lengths) + generated) / seconds, "dtype": "bf16",
         "data": "synthetic: uniform-random token ids, random weights", "steps": stats["steps"],
-        "graph_steps": stats["graph_steps"], "preemptions": stats["scheduler"]["preemptions"],
-        "config": {"model": which, "layers": raw["num_hidden_layers"], "hidden": raw["hidden_size"], "page_size": 16},
+        "graph_steps": stats["graph_steps"], "graphs_captured": len(engine.graphs.graphs), "preemptions": stats["scheduler"]["preemptions"],
+        "roofline": {"bound": "per step the greater of bytes / hbm and flops / bf16", "ideal_s": ideal, "measured_s": seconds,
+                     "frac": ideal / seconds, "steps_bound_by_bytes": byte_steps, "steps_logged": len(engine.step_log), "of": peak_source,
+                     "note": "the measured time holds the graph captures and the host's work between steps"},
+        "clocks": clock_record,
+        "config": {"model": which, "layers": raw["num_hidden_layers"], "hidden": raw["hidden_size"], "page_size": 16,
+                   **{k: v for k, v in options.items()}},
     }))
     return 0
 

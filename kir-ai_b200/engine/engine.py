@@ -61,8 +61,9 @@ class Engine:
                 if max_positions:
                     per_request = min(per_request, max_positions)
                 max_cache_tokens = max_concurrent_requests * per_request
-            common = dict(dtype=dtype, device=device, page_size=page_size, max_tokens=max_cache_tokens,
-                          num_slots=max_concurrent_requests)
+            # one slot and one page beyond the requests' are for the padding rows of captured decode steps
+            common = dict(dtype=dtype, device=device, page_size=page_size, max_tokens=max_cache_tokens + (page_size if cuda_graphs else 0),
+                          num_slots=max_concurrent_requests + (1 if cuda_graphs else 0))
             if random_weights_seed is not None:
                 runner = ModelRunner.from_random(config, random_weights_seed, **common)
             else:
@@ -80,12 +81,26 @@ class Engine:
             default_max_new_tokens=max_new_tokens,
         )
         self._next_id = 0
+        # None, or a list that receives one entry per step that is launched: [(tokens in the cache before, new tokens)
+        # of every request in it] (measurements compute a step's bytes and flops from it)
+        self.step_log: Optional[list] = None
         self.counters = {"steps": 0, "graph_steps": 0, "prompt_tokens": 0, "generated_tokens": 0}
         # decode steps are replayed from CUDA graphs only when every part of the model promises that this is safe
         # (Part.capture_safe); a model with a part that does not say so runs every step eagerly
         self.graphs = DecodeGraphs(runner) if cuda_graphs and runner.model.plan.capture_safe() else None
         self.overlap_steps = overlap_steps
         self._in_flight = None  # (scheduled, LaunchedStep) of a decode step that is queued or running
+        # Captured decode steps exist for a few batch sizes only (a capture costs tens of milliseconds, and a batch
+        # shrinks request by request as requests finish): a step of n requests replays the graph of the next size up,
+        # its spare rows filled with a padding request that holds one page and one slot of its own, whose one token
+        # at position 0 is computed and thrown away.  Without a spare slot every batch size gets its own graph.
+        self._padding = None
+        if self.graphs is not None:
+            padding = runner.cache.open(("padding rows of captured steps",))
+            if padding is not None and runner.cache.reserve(padding, 1):
+                self._padding = padding
+            elif padding is not None:
+                runner.cache.close(padding)
 
     # ------------------------------------------------------------------ generate
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> Request:
@@ -171,20 +186,24 @@ class Engine:
         cache = self.runner.cache
         requests = [item.request for item in scheduled]
         pages = [r.pages for r in requests]
-        tables = [cache.block_table_array(pages, g) for g in range(len(cache.groups))]
+        spare = (self.graphs.batch_bucket(len(requests)) - len(requests)) if self._padding is not None else 0
+        rows = pages + [self._padding] * spare  # spare rows: the padding request's token at position 0, again and again
+        tables = [cache.block_table_array(rows, g) for g in range(len(cache.groups))]
         width = max([1] + [t.shape[1] for t in tables])
-        graph, fresh = self.graphs.get(len(requests), width, [p.length + 1 for p in pages])
+        graph, fresh = self.graphs.get(len(rows), width, [p.length + 1 for p in rows])
         if ahead and (fresh or graph is not same_graph):
             return None  # a capture, or another graph's buffers: that step is queued after this one is known
         extra = 1 if ahead else 0  # draws that the step in flight will have used
         graph.load_inputs(
-            None if ahead else [r.token_at(item.first) for r, item in zip(requests, scheduled)],
-            [p.length for p in pages], [p.slot for p in pages], tables, [r.params.temperature for r in requests],
-            [r.params.top_p for r in requests], [rng.draw(r.seed, r.draws_used + extra) for r in requests],
+            None if ahead else [r.token_at(item.first) for r, item in zip(requests, scheduled)] + [0] * spare,
+            [p.length for p in rows], [p.slot for p in rows], tables, [r.params.temperature for r in requests] + [0.0] * spare,
+            [r.params.top_p for r in requests] + [1.0] * spare, [rng.draw(r.seed, r.draws_used + extra) for r in requests] + [0.0] * spare,
         )
         if fresh:
             graph.capture()
         launched = graph.launch()
+        if self.step_log is not None:
+            self.step_log.append([(p.length, 1) for p in pages])
         for p in pages:
             cache.commit(p, 1)  # bookkeeping only: the step's cache writes are queued in stream order
         self.counters["graph_steps"] += 1
@@ -192,6 +211,8 @@ class Engine:
 
     def _general_step(self, scheduled) -> List[Optional[int]]:
         entries = []
+        if self.step_log is not None:
+            self.step_log.append([(item.first, item.count) for item in scheduled])
         for item in scheduled:
             tokens = item.request.token_slice(item.first, item.count)
             entries.append(StepEntry(item.request.pages, tokens, [item.count - 1] if item.sample else []))
@@ -229,4 +250,13 @@ class Engine:
         return outputs
 
     def stats(self) -> dict:
-        return {**self.counters, "scheduler": dict(self.scheduler.stats), "cache": self.runner.cache.stats()}
+        """Counters of the engine, the scheduler and the cache; the cache's figures are those of the requests (the one
+        page and slot of the padding rows are taken out)."""
+        cache = self.runner.cache.stats()
+        if self._padding is not None:
+            cache["live_requests"] -= 1
+            cache["slots_free"] += 1
+            for group in cache["groups"]:
+                group["used"] -= 1
+            cache["padding_rows"] = {"pages_per_group": 1, "slots": 1}
+        return {**self.counters, "scheduler": dict(self.scheduler.stats), "cache": cache}

@@ -203,6 +203,15 @@ class DecodeGraphs:
         return balanced
 
     @staticmethod
+    def batch_bucket(requests: int) -> int:
+        """The batch size whose captured step serves ``requests`` requests: every size up to 8, then four sizes to each
+        doubling (10, 12, 14, 16, 20, 24, ...), so that at most a fifth of a step's rows are padding."""
+        if requests <= 8:
+            return requests
+        step = 1 << (max(requests - 1, 1).bit_length() - 3)
+        return -(-requests // step) * step
+
+    @staticmethod
     def width_bucket(width: int) -> int:
         bucket = 16
         while bucket < width:
