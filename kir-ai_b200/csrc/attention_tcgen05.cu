@@ -136,8 +136,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
     constexpr int PANELS = Smem::panels;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    const int tile = gridDim.x - 1 - blockIdx.x;  // late tiles see the most keys: start them first
-    const int kv_head = blockIdx.y, req = blockIdx.z;
+    // CTAs are handed out in the order of their linear index, x fastest: the kv heads are x and the row tiles y, last
+    // tile first, so that of one prompt the tiles that see the most keys start first on every head, and the launch does
+    // not end with a head's heavy tiles that were handed out late
+    const int tile = gridDim.y - 1 - blockIdx.y;
+    const int kv_head = blockIdx.x, req = blockIdx.z;
     const int group = q_heads / kv_heads;
     const int q_begin = query_start[req];
     const int q_len = query_start[req + 1] - q_begin;
@@ -507,7 +510,8 @@ int launch(const void* q, const void* cache, void* out, const int* block_table, 
     auto kernel = attention_prefill_tc_kernel<D>;
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total);
     if (err != cudaSuccess) return (int)err;
-    dim3 grid((unsigned)(((long)max_query_len * group + TA_ROWS - 1) / TA_ROWS), kv_heads, requests);
+    dim3 grid(kv_heads, (unsigned)(((long)max_query_len * group + TA_ROWS - 1) / TA_ROWS), requests);
+    if (grid.y > 65535) return KIRAI_ERR_BAD_SIZE;
     return launch_pdl(kernel, grid, dim3(TA_THREADS), (size_t)Smem::total, stream, 1u, kv_map, (const bf16*)q, (bf16*)out,
                       block_table, query_start, context_len, q_heads, kv_heads, head_dim, q_row_stride, page_size, box_rows,
                       piece_rows, table_width, num_pages, window, scale * 1.4426950408889634f, error_flag);
