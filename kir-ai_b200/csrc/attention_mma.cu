@@ -779,12 +779,30 @@ __device__ __forceinline__ void decode_init_barriers(uint8_t* smem) {
 // HEADS: the group has at most 8 heads and they are the MMA's columns (keys fill its rows);
 // otherwise the group's (at most 16) heads are the rows, as in the prompt kernel.
 // Grid (splits, kv_heads, requests): every request's keys are cut into the same number of ranges.
-template <int D, bool HEADS>
+// CLUSTER: the CTAs of one (request, kv head), one per range of keys, are a thread-block cluster (at most 8), and their
+// partial results meet in shared memory: every CTA leaves its group rows (unnormalised output, maximum, sum) in a
+// buffer of its own, the cluster synchronises, and each CTA merges a share of the output's elements from all the
+// buffers (distributed shared memory), in the order of the ranges and with the arithmetic of
+// attention_merge_splits_kernel, and stores them.  No partial result goes to global memory and no second kernel runs.
+__device__ __forceinline__ void decode_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t local_address, uint32_t rank) {
+    uint32_t remote;
+    float value;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(remote) : "memory");
+    return value;
+}
+#define DECODE_MAX_CLUSTER 8
+
+template <int D, bool HEADS, bool CLUSTER>
 __global__ void __launch_bounds__(DecodeTile<D>::WARPS * 32)
 attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs args, bf16* __restrict__ out,
                         float* __restrict__ partial, const int* __restrict__ context_len, int num_splits) {
     pdl_launch_dependents();
-    constexpr int BN = DecodeSmem<D>::BN;
+    using Smem = DecodeSmem<D>;
+    constexpr int BN = Smem::BN;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int split = blockIdx.x, kv_head = blockIdx.y, req = blockIdx.z;
@@ -798,6 +816,41 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs a
     const int t_end = min(last_tile + 1, t_begin + per_split);
     if (threadIdx.x == 0) sm100::tma_prefetch_descriptor(&kv_map);
     decode_init_barriers<D>(smem);
+    if (CLUSTER) {
+        // this CTA's result stays in shared memory, behind the buffer in which its warps were merged
+        static_assert(Smem::ring_bytes >= Smem::merge_bytes + 16 * (D + 2) * 4, "the exchange buffer lies in the ring");
+        float* exchange = reinterpret_cast<float*>(smem + Smem::q_bytes + Smem::merge_bytes);
+        const int stride = args.head_dim + 2;
+        decode_attend_range<D, HEADS>(kv_map, args, smem, req, kv_head, pos, key_lo, last_tile, t_begin, t_end, 0, true, out,
+                                      exchange, (long)stride);
+        decode_cluster_sync();  // every range's result is in its CTA's buffer
+        const uint32_t base = sm100::smem_addr(exchange);
+        const int head_dim = args.head_dim, total = group * head_dim;
+        for (int e = split + num_splits * (int)threadIdx.x; e < total; e += num_splits * (int)blockDim.x) {
+            const int row = e / head_dim, col = e % head_dim;
+            const uint32_t row_address = base + (uint32_t)(row * stride) * 4u;
+            float m[DECODE_MAX_CLUSTER], m_all = -INFINITY;
+#pragma unroll
+            for (int r = 0; r < DECODE_MAX_CLUSTER; ++r) {
+                m[r] = r < num_splits ? ld_cluster_f32(row_address + (uint32_t)head_dim * 4u, (uint32_t)r) : -INFINITY;
+                m_all = fmaxf(m_all, m[r]);
+            }
+            float acc = 0.0f, l_all = 0.0f;
+#pragma unroll
+            for (int r = 0; r < DECODE_MAX_CLUSTER; ++r) {
+                if (r < num_splits) {
+                    const float value = ld_cluster_f32(row_address + (uint32_t)col * 4u, (uint32_t)r);
+                    const float sum = ld_cluster_f32(row_address + (uint32_t)(head_dim + 1) * 4u, (uint32_t)r);
+                    const float weight = m[r] == -INFINITY ? 0.0f : exp2f(m[r] - m_all);
+                    acc += value * weight;
+                    l_all += sum * weight;
+                }
+            }
+            out[((size_t)req * args.q_heads + kv_head * group + row) * head_dim + col] = from_f32<bf16>(l_all > 0.0f ? acc / l_all : 0.0f);
+        }
+        decode_cluster_sync();  // nobody leaves while its buffer may still be read
+        return;
+    }
     float* dst_partial = num_splits == 1 ? nullptr
         : partial + (((size_t)req * args.q_heads + kv_head * group) * num_splits + split) * (args.head_dim + 2);
     decode_attend_range<D, HEADS>(kv_map, args, smem, req, kv_head, pos, key_lo, last_tile, t_begin, t_end, 0, true, out,
@@ -1020,12 +1073,19 @@ int decode_launch(const void* q, const void* cache, void* out, float* partial, c
     CUtensorMap kv_map;
     const uint64_t rows = (uint64_t)num_pages * 2 * kv_heads * page_size;
     if (!tmap::bf16_2d_sw128(&kv_map, cache, rows, head_dim, head_dim, box_rows, 64)) return KIRAI_ERR_BAD_ALIGN;
-    auto kernel = (q_heads / kv_heads <= 8) ? attention_decode_kernel<D, true> : attention_decode_kernel<D, false>;
+    const bool heads = q_heads / kv_heads <= 8;
+    // a few ranges whose partial results the caller gave no room for: their CTAs merge as a cluster
+    const bool cluster = num_splits > 1 && num_splits <= DECODE_MAX_CLUSTER && partial == nullptr;
+    auto kernel = cluster ? (heads ? attention_decode_kernel<D, true, true> : attention_decode_kernel<D, false, true>)
+                          : (heads ? attention_decode_kernel<D, true, false> : attention_decode_kernel<D, false, false>);
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total);
     if (err != cudaSuccess) return (int)err;
     const DecodeArgs args{(const bf16*)q, block_table, q_heads, kv_heads, head_dim, q_row_stride, page_size, box_rows,
                           table_width, num_pages, window, scale * 1.4426950408889634f, error_flag};
     dim3 grid(num_splits, kv_heads, requests);
+    if (cluster)
+        return launch_pdl_cluster(kernel, grid, dim3(Smem::DC_WARPS * 32), (size_t)Smem::total, stream, dim3(num_splits, 1, 1),
+                                  kv_map, args, (bf16*)out, partial, context_len, num_splits);
     int status = launch_pdl(kernel, grid, dim3(Smem::DC_WARPS * 32), (size_t)Smem::total, stream, 1u, kv_map, args,
                             (bf16*)out, partial, context_len, num_splits);
     if (status || num_splits == 1) return status;
@@ -1090,7 +1150,9 @@ KIRAI_EXPORT int kirai_attention_prefill_bf16(const void* q, const void* cache, 
 }
 
 // Attention for a batch in which every request brings exactly one token (token r belongs to request r).
-// With num_splits > 1, partial must hold requests * q_heads * num_splits * (head_dim + 2) floats.
+// With num_splits > 1 and a buffer `partial` of requests * q_heads * num_splits * (head_dim + 2) floats, the ranges'
+// results go through that buffer and a second kernel merges them.  With partial null and num_splits <= 8, the CTAs
+// of a request and kv head form a cluster and merge in shared memory: one kernel, nothing written but the result.
 KIRAI_EXPORT int kirai_attention_decode_bf16(const void* q, const void* cache, void* out, float* partial,
                                              const int* block_table, const int* context_len, int requests,
                                              int q_heads, int kv_heads, int head_dim, long q_row_stride, int page_size,
@@ -1101,7 +1163,7 @@ KIRAI_EXPORT int kirai_attention_decode_bf16(const void* q, const void* cache, v
     if (bad) return bad;
     if (q_heads / kv_heads > 16) return KIRAI_ERR_UNSUPPORTED;  // the group's heads are the rows of one m16 tile
     if (num_splits < 1 || num_splits > 65535 || requests > 65535) return KIRAI_ERR_BAD_SIZE;
-    if (num_splits > 1 && !partial) return KIRAI_ERR_BAD_SIZE;
+    if (num_splits > DECODE_MAX_CLUSTER && !partial) return KIRAI_ERR_BAD_SIZE;  // up to 8 ranges merge without a buffer
 #define KIRAI_DC(D) \
     return decode_launch<D>(q, cache, out, partial, block_table, context_len, requests, q_heads, kv_heads, head_dim, \
                             q_row_stride, page_size, table_width, num_pages, window, scale, num_splits, error_flag, \

@@ -334,17 +334,23 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.T
     return out
 
 
+DECODE_CLUSTER = 8  # ranges of one (request, kv head) whose CTAs can merge as a thread-block cluster
+
+
 def decode_splits(requests: int, kv_heads: int, max_context_len: int, tile: int = 16, warps: int = 8) -> int:
     """How many CTAs share one (request, kv head) in the decode kernel.  A CTA's warps take
     key tiles in turn, so a CTA with n tiles runs ceil(n / warps) rounds plus a fixed cost (set-up,
-    merge); CTAs run in waves of 148.  The split count with the fewest estimated rounds wins."""
+    merge); CTAs run in waves of 148.  Up to DECODE_CLUSTER ranges merge inside the kernel (their CTAs are a
+    cluster); more need a buffer and a second kernel, about two rounds' time.  The split count with the fewest
+    estimated rounds wins.  (Clusters are used only while all CTAs run at once: in a launch of several waves the
+    pairs of CTAs that a cluster must place together left SMs idle, 10.34 against 10.14 ms a step at 64 requests.)"""
     pairs = max(1, requests * kv_heads)
     tiles = max(1, -(-max_context_len // tile))
     best, best_cost = 1, None
     for splits in range(1, min(64, tiles) + 1):
         waves = -(-pairs * splits // 148)
         rounds = -(-(-(-tiles // splits)) // warps) + 3
-        cost = waves * rounds + (1 if splits > 1 else 0)
+        cost = waves * rounds + (0 if splits == 1 else (0.75 if splits <= DECODE_CLUSTER and waves == 1 else 2.75))
         if best_cost is None or cost < best_cost:
             best, best_cost = splits, cost
     return best
@@ -368,7 +374,7 @@ def decode_plan(context_lens, kv_heads: int, window: Optional[int] = None, tile:
     tiles = [max(1, -(-n // tile)) for n in lens]
     waves = -(-len(lens) * kv_heads * splits // sms)
     rounds_split = -(-(-(-max(tiles) // splits)) // warps)
-    cost_split = waves * (rounds_split + 2.5) + (2.5 if splits > 1 else 0.0)
+    cost_split = waves * (rounds_split + 2.5) + (0.0 if splits == 1 else (0.75 if splits <= DECODE_CLUSTER and waves == 1 else 2.5))
     rounds_balanced = -(-(-(-kv_heads * sum(tiles) // sms)) // warps)
     cost_balanced = rounds_balanced + 9.5
     return cost_balanced < 0.92 * cost_split, splits
@@ -387,7 +393,8 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Te
         out = torch.empty((rows, q_heads * head_dim), dtype=q.dtype, device=q.device)
     assert out.shape == (rows, q_heads * head_dim) and out.dtype == q.dtype and out.is_contiguous()
     partial = None
-    if num_splits > 1:
+    # a few ranges, all CTAs running at once: they merge inside the kernel, as clusters; else through a buffer
+    if num_splits > DECODE_CLUSTER or (num_splits > 1 and rows * kv_heads * num_splits > sm_count(q.device)):
         partial = torch.empty((rows, q_heads, num_splits, head_dim + 2), dtype=torch.float32, device=q.device)
     _call("kirai_attention_decode_bf16", _ptr(q), _ptr(cache), _ptr(out), _ptr(partial), _ptr(block_table),
           _ptr(context_len), _i(rows), _i(q_heads), _i(kv_heads), _i(head_dim), _l(q_stride), _i(page_size),
