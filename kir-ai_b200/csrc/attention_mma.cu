@@ -540,7 +540,10 @@ struct DecodeSmem {
     static constexpr int body = q_bytes + (ring_bytes > merge_bytes ? ring_bytes : merge_bytes);
     static constexpr int table_entries = 1024;  // block-table entries kept in shared memory (longer ranges read global memory)
     static constexpr int prefix_entries = 1025;  // balanced kernel: where each request's tiles start (up to 1,024 requests)
-    static constexpr int total = body + DC_WARPS * DC_STAGES * 8 + table_entries * 4 + prefix_entries * 4 + 1024;  // + barriers, + slack to align to 1024
+    static constexpr int rope_offset = body + DC_WARPS * DC_STAGES * 8 + table_entries * 4 + prefix_entries * 4 + 12;  // 16-byte aligned
+    static constexpr int rope_bytes = D * 4;  // fused q/k preparation: cos [D / 2], sin [D / 2] of the request's position
+    static_assert(rope_offset % 16 == 0, "the cosines are read in 16-byte pieces");
+    static constexpr int total = rope_offset + rope_bytes + 1024;  // + slack to align to 1024
 };
 
 // What a decode CTA needs to attend one range of key tiles of one (request, kv head).
@@ -552,7 +555,120 @@ struct DecodeArgs {
     int page_size, box_rows, table_width, num_pages, window;
     float scale_log2;
     int* error_flag;
+    // Fused preparation (fuse != 0; head_dim is then the template's D): q points to the rows that the q, k, v product
+    // left, [requests, (q_heads + 2 kv_heads) * head_dim] with row stride q_row_stride, untouched.  Every CTA norms and
+    // rotates its group's query rows on the way into shared memory; the warp that takes the request's last key tile
+    // norms and rotates the new token's key, puts it and the value into that tile in shared memory and into their
+    // page (cache) for the steps to come.  Null weights skip the norm, null inv_freq the rotation.
+    int fuse;
+    const float* q_weight;
+    const float* k_weight;
+    const float* inv_freq;
+    float eps;
+    bf16* cache;
 };
+
+// Per-head RMSNorm and half-split rotation of the sixteen values that a lane holds of one head (eight adjacent values of
+// each half; LANES = D / 16 lanes share a head), the arithmetic of qk_norm_rope_kv_write_wide_kernel in elementwise.cu:
+// statistics, scale, weights and angles in 32-bit, one rounding to bf16 at the end.  Called by whole warps.
+template <int D>
+__device__ __forceinline__ void prepare_head(uint4& lo_raw, uint4& hi_raw, const float* __restrict__ weight,
+                                             const float* rope_s, bool rotate, float eps, int sub) {
+    constexpr int LANES = D / 16, HALF = D / 2;
+    float lo[8], hi[8];
+    {
+        const __nv_bfloat162* pl = reinterpret_cast<const __nv_bfloat162*>(&lo_raw);
+        const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&hi_raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 a = __bfloat1622float2(pl[j]), b = __bfloat1622float2(ph[j]);
+            lo[2 * j] = a.x, lo[2 * j + 1] = a.y, hi[2 * j] = b.x, hi[2 * j + 1] = b.y;
+        }
+    }
+    if (weight) {
+        float acc = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc = fmaf(lo[j], lo[j], fmaf(hi[j], hi[j], acc));
+#pragma unroll
+        for (int d = 1; d < LANES; d <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+        const float variance = acc / (float)D + eps;
+        const float scale = variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
+        const float4* wl = reinterpret_cast<const float4*>(weight + 8 * sub);
+        const float4* wh = reinterpret_cast<const float4*>(weight + HALF + 8 * sub);
+        const float4 w0 = wl[0], w1 = wl[1], w2 = wh[0], w3 = wh[1];
+        const float wlo[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        const float whi[8] = {w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) lo[j] = lo[j] * scale * wlo[j], hi[j] = hi[j] * scale * whi[j];
+    }
+    if (rotate) {
+        const float4* cs = reinterpret_cast<const float4*>(rope_s + 8 * sub);
+        const float4* sn = reinterpret_cast<const float4*>(rope_s + HALF + 8 * sub);
+        const float4 c0 = cs[0], c1 = cs[1], s0 = sn[0], s1 = sn[1];
+        const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float a = lo[j], b = hi[j];
+            lo[j] = a * c[j] - b * sv[j];
+            hi[j] = b * c[j] + a * sv[j];
+        }
+    }
+    __nv_bfloat162* pl = reinterpret_cast<__nv_bfloat162*>(&lo_raw);
+    __nv_bfloat162* ph = reinterpret_cast<__nv_bfloat162*>(&hi_raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        pl[j] = __floats2bfloat162_rn(lo[2 * j], lo[2 * j + 1]);
+        ph[j] = __floats2bfloat162_rn(hi[2 * j], hi[2 * j + 1]);
+    }
+}
+
+__device__ __forceinline__ void st_shared_16(uint32_t address, const uint4& v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(address), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// The new token's key (normed, rotated) and value into row `pos % BN` of the tile at k_s / v_s, which TMA has just
+// filled from the pages, and into the token's page.  Called by the whole warp that is about to attend that tile.
+template <int D, int BN>
+__device__ __forceinline__ void append_new_token(const DecodeArgs& args, const float* rope_s, const int* table, int req,
+                                                 int kv_head, int pos, uint32_t k_s, uint32_t v_s, int lane) {
+    constexpr int LANES = D / 16;
+    const int row = pos % BN;
+    const bf16* x = args.q + (size_t)req * args.q_row_stride;
+    const int logical = pos / args.page_size;
+    int page = logical < args.table_width ? table[logical] : -1;
+    if (page < 0 || page >= args.num_pages) {
+        if (lane == 0) atomicExch(args.error_flag, KIRAI_FLAG_NO_PAGE_WRITE);
+        page = -1;
+    }
+    const long slot_rows = (long)(pos % args.page_size);
+    // cache layer [pages][2][kv_heads][page_size][D]
+    bf16* k_dst = page < 0 ? nullptr : args.cache + ((((long)page * 2 + 0) * args.kv_heads + kv_head) * args.page_size + slot_rows) * D;
+    bf16* v_dst = page < 0 ? nullptr : args.cache + ((((long)page * 2 + 1) * args.kv_heads + kv_head) * args.page_size + slot_rows) * D;
+    const bool k_live = lane < LANES;
+    const uint4* xk = reinterpret_cast<const uint4*>(x + (size_t)(args.q_heads + kv_head) * D);
+    uint4 lo = make_uint4(0u, 0u, 0u, 0u), hi = lo;
+    if (k_live) {
+        lo = xk[lane];
+        hi = xk[lane + LANES];
+    }
+    prepare_head<D>(lo, hi, args.k_weight, rope_s, args.inv_freq != nullptr, args.eps, lane % LANES);
+    if (k_live) {
+        st_shared_16(k_s + tile_offset<BN>(row, lane), lo);
+        st_shared_16(k_s + tile_offset<BN>(row, lane + LANES), hi);
+        if (k_dst) {
+            reinterpret_cast<uint4*>(k_dst)[lane] = lo;
+            reinterpret_cast<uint4*>(k_dst)[lane + LANES] = hi;
+        }
+    }
+    const uint4* xv = reinterpret_cast<const uint4*>(x + (size_t)(args.q_heads + args.kv_heads + kv_head) * D);
+    for (int chunk = lane; chunk < D / 8; chunk += 32) {
+        const uint4 value = xv[chunk];
+        st_shared_16(v_s + tile_offset<BN>(row, chunk), value);
+        if (v_dst) reinterpret_cast<uint4*>(v_dst)[chunk] = value;
+    }
+    __syncwarp();
+}
 
 // The CTA's warps attend key tiles [t_begin, t_end) of (req, kv_head) for the query at position pos (the keys from
 // key_lo on; last_tile holds pos) and merge their states.  The result for the group's heads goes, unnormalised with
@@ -593,6 +709,11 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
         }
     }
     bool ok = true;
+    float* rope_s = reinterpret_cast<float*>(smem + Smem::rope_offset);
+    if (args.fuse && args.inv_freq) {
+        // the angles depend on the position only, which is constant during a step: before griddepcontrol.wait
+        for (int i = tid; i < D / 2; i += DC_WARPS * 32) sincosf((float)pos * args.inv_freq[i], &rope_s[D / 2 + i], &rope_s[i]);
+    }
     // Fills ring slot `slot` with key tile `t`.
     auto issue = [&](int t, int slot) {
         const uint32_t k_dst = ring + slot * 2 * Smem::tile_bytes;
@@ -617,7 +738,28 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
         pdl_wait();  // the queries, and the new token's key and value, are complete and visible
     }
     // the query rows (the group's heads), zero beyond the group and beyond head_dim
-    {
+    if (args.fuse) {
+        // raw rows of the q, k, v product: normed and rotated on the way in (head_dim == D here)
+        constexpr int CH = D / 8, LANES = D / 16, HEADS_PER_WARP = 32 / LANES;
+        for (int id = tid; id < (16 - group) * CH; id += DC_WARPS * 32)
+            *reinterpret_cast<uint4*>(smem + tile_offset<16>(group + id / CH, id % CH)) = make_uint4(0u, 0u, 0u, 0u);
+        __syncthreads();  // the cosines and sines are in place
+        for (int base = warp * HEADS_PER_WARP; base < group; base += DC_WARPS * HEADS_PER_WARP) {
+            const int r = base + lane / LANES, sub = lane % LANES;
+            const bool live = r < group;
+            const uint4* x = reinterpret_cast<const uint4*>(args.q + (size_t)req * args.q_row_stride + (size_t)(kv_head * group + (live ? r : 0)) * D);
+            uint4 lo = make_uint4(0u, 0u, 0u, 0u), hi = lo;
+            if (live) {
+                lo = x[sub];
+                hi = x[sub + LANES];
+            }
+            prepare_head<D>(lo, hi, args.q_weight, rope_s, args.inv_freq != nullptr, args.eps, sub);
+            if (live) {
+                *reinterpret_cast<uint4*>(smem + tile_offset<16>(r, sub)) = lo;
+                *reinterpret_cast<uint4*>(smem + tile_offset<16>(r, sub + LANES)) = hi;
+            }
+        }
+    } else {
         constexpr int CH = D / 8;
         const int chunks_used = head_dim / 8;
         for (int id = tid; id < 16 * CH; id += DC_WARPS * 32) {
@@ -655,6 +797,8 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
                 break;
             }
             const uint32_t k_s = ring + slot * 2 * Smem::tile_bytes;
+            if (args.fuse && my_first + k * DC_WARPS == last_tile)
+                append_new_token<D, BN>(args, rope_s, table, req, kv_head, pos, k_s, k_s + Smem::tile_bytes, lane);
             warp_attend_heads<D, BN>(st, q_b, k_s, k_s + Smem::tile_bytes, (my_first + k * DC_WARPS) * BN, key_lo, pos, scale_log2, lane);
             __syncwarp();
         }
@@ -707,6 +851,8 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
             break;
         }
         const uint32_t k_s = ring + slot * 2 * Smem::tile_bytes;
+        if (args.fuse && my_first + k * DC_WARPS == last_tile)
+            append_new_token<D, BN>(args, rope_s, table, req, kv_head, pos, k_s, k_s + Smem::tile_bytes, lane);
         warp_attend<D, BN, 16, Q_IN_REGS>(st, q_smem, 0, q_regs, k_s, k_s + Smem::tile_bytes, (my_first + k * DC_WARPS) * BN, lo, hi,
                                           scale_log2, lane);
         __syncwarp();
@@ -1040,6 +1186,14 @@ __global__ void attention_merge_splits_kernel(const float* __restrict__ partial,
     }
 }
 
+// What the decode kernels need to prepare queries and the new token's key themselves (see DecodeArgs).
+struct FuseQK {
+    const float* q_weight;
+    const float* k_weight;
+    const float* inv_freq;
+    float eps;
+};
+
 template <int D>
 int prefill_launch(const void* q, const void* cache, void* out, const int* block_table, const int* query_start,
                    const int* context_len, int requests, int max_query_len, int q_heads, int kv_heads, int head_dim,
@@ -1066,7 +1220,7 @@ template <int D>
 int decode_launch(const void* q, const void* cache, void* out, float* partial, const int* block_table,
                   const int* context_len, int requests, int q_heads, int kv_heads, int head_dim, long q_row_stride,
                   int page_size, int table_width, int num_pages, int window, float scale, int num_splits,
-                  int* error_flag, cudaStream_t stream) {
+                  int* error_flag, cudaStream_t stream, const FuseQK* fuse = nullptr) {
     using Smem = DecodeSmem<D>;
     const int box_rows = page_size < Smem::BN ? page_size : Smem::BN;
     if (Smem::BN % box_rows != 0 || page_size % box_rows != 0) return KIRAI_ERR_UNSUPPORTED;  // page sizes: powers of two
@@ -1080,8 +1234,13 @@ int decode_launch(const void* q, const void* cache, void* out, float* partial, c
                           : (heads ? attention_decode_kernel<D, true, false> : attention_decode_kernel<D, false, false>);
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total);
     if (err != cudaSuccess) return (int)err;
-    const DecodeArgs args{(const bf16*)q, block_table, q_heads, kv_heads, head_dim, q_row_stride, page_size, box_rows,
-                          table_width, num_pages, window, scale * 1.4426950408889634f, error_flag};
+    if (fuse && head_dim != D) return KIRAI_ERR_UNSUPPORTED;  // the fused preparation works on whole heads of 64, 128 or 256
+    DecodeArgs args{(const bf16*)q, block_table, q_heads, kv_heads, head_dim, q_row_stride, page_size, box_rows,
+                    table_width, num_pages, window, scale * 1.4426950408889634f, error_flag};
+    if (fuse) {
+        args.fuse = 1, args.q_weight = fuse->q_weight, args.k_weight = fuse->k_weight, args.inv_freq = fuse->inv_freq;
+        args.eps = fuse->eps, args.cache = (bf16*)const_cast<void*>(cache);
+    }
     dim3 grid(num_splits, kv_heads, requests);
     if (cluster)
         return launch_pdl_cluster(kernel, grid, dim3(Smem::DC_WARPS * 32), (size_t)Smem::total, stream, dim3(num_splits, 1, 1),
@@ -1097,7 +1256,7 @@ template <int D>
 int decode_balanced_launch(const void* q, const void* cache, void* out, float* partial, const int* block_table,
                            const int* context_len, int requests, int q_heads, int kv_heads, int head_dim,
                            long q_row_stride, int page_size, int table_width, int num_pages, int window, float scale,
-                           int ctas, int* error_flag, cudaStream_t stream) {
+                           int ctas, int* error_flag, cudaStream_t stream, const FuseQK* fuse = nullptr) {
     using Smem = DecodeSmem<D>;
     const int box_rows = page_size < Smem::BN ? page_size : Smem::BN;
     if (Smem::BN % box_rows != 0 || page_size % box_rows != 0) return KIRAI_ERR_UNSUPPORTED;  // page sizes: powers of two
@@ -1107,8 +1266,13 @@ int decode_balanced_launch(const void* q, const void* cache, void* out, float* p
     auto kernel = (q_heads / kv_heads <= 8) ? attention_decode_balanced_kernel<D, true> : attention_decode_balanced_kernel<D, false>;
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total);
     if (err != cudaSuccess) return (int)err;
-    const DecodeArgs args{(const bf16*)q, block_table, q_heads, kv_heads, head_dim, q_row_stride, page_size, box_rows,
-                          table_width, num_pages, window, scale * 1.4426950408889634f, error_flag};
+    if (fuse && head_dim != D) return KIRAI_ERR_UNSUPPORTED;  // the fused preparation works on whole heads of 64, 128 or 256
+    DecodeArgs args{(const bf16*)q, block_table, q_heads, kv_heads, head_dim, q_row_stride, page_size, box_rows,
+                    table_width, num_pages, window, scale * 1.4426950408889634f, error_flag};
+    if (fuse) {
+        args.fuse = 1, args.q_weight = fuse->q_weight, args.k_weight = fuse->k_weight, args.inv_freq = fuse->inv_freq;
+        args.eps = fuse->eps, args.cache = (bf16*)const_cast<void*>(cache);
+    }
     int status = launch_pdl(kernel, dim3(ctas), dim3(Smem::DC_WARPS * 32), (size_t)Smem::total, stream, 1u, kv_map, args,
                             (bf16*)out, partial, context_len, requests);
     if (status) return status;
@@ -1195,6 +1359,62 @@ KIRAI_EXPORT int kirai_attention_decode_balanced_bf16(const void* q, const void*
     if (head_dim <= 128) KIRAI_DCB(128);
     KIRAI_DCB(256);
 #undef KIRAI_DCB
+}
+
+// The two decode entry points with the preparation of queries and keys inside: `qkv` holds the rows that the q, k, v
+// product left, [requests, (q_heads + 2 kv_heads) * head_dim] (row stride in elements), and is not modified.  Per-head
+// RMSNorm of q and k (weights [head_dim], may be null), half-split rotation at position context_len - 1 (inv_freq
+// [head_dim / 2], may be null), the new token's key and value appended to their page of `cache`, then attention.
+// head_dim must be 64, 128 or 256; everything else as in the entry points above.
+KIRAI_EXPORT int kirai_attention_decode_qk_bf16(const void* qkv, void* cache, void* out, float* partial,
+                                                const int* block_table, const int* context_len, int requests,
+                                                int q_heads, int kv_heads, int head_dim, long qkv_row_stride,
+                                                int page_size, int table_width, int num_pages, int window, float scale,
+                                                int num_splits, const float* q_weight, const float* k_weight,
+                                                const float* inv_freq, float eps, int* error_flag, cudaStream_t stream) {
+    if (requests <= 0) return 0;
+    int bad = check_common(q_heads, kv_heads, head_dim, qkv_row_stride, qkv);
+    if (bad) return bad;
+    if (q_heads / kv_heads > 16) return KIRAI_ERR_UNSUPPORTED;
+    if (num_splits < 1 || num_splits > 65535 || requests > 65535) return KIRAI_ERR_BAD_SIZE;
+    if (num_splits > DECODE_MAX_CLUSTER && !partial) return KIRAI_ERR_BAD_SIZE;
+    if (((uintptr_t)q_weight | (uintptr_t)k_weight | (uintptr_t)inv_freq | (uintptr_t)cache) & 15) return KIRAI_ERR_BAD_ALIGN;
+    const FuseQK fuse{q_weight, k_weight, inv_freq, eps};
+#define KIRAI_DCQ(D) \
+    return decode_launch<D>(qkv, cache, out, partial, block_table, context_len, requests, q_heads, kv_heads, head_dim, \
+                            qkv_row_stride, page_size, table_width, num_pages, window, scale, num_splits, error_flag, \
+                            stream, &fuse)
+    if (head_dim == 64) KIRAI_DCQ(64);
+    if (head_dim == 128) KIRAI_DCQ(128);
+    if (head_dim == 256) KIRAI_DCQ(256);
+#undef KIRAI_DCQ
+    return KIRAI_ERR_UNSUPPORTED;
+}
+
+KIRAI_EXPORT int kirai_attention_decode_balanced_qk_bf16(const void* qkv, void* cache, void* out, float* partial,
+                                                         const int* block_table, const int* context_len, int requests,
+                                                         int q_heads, int kv_heads, int head_dim, long qkv_row_stride,
+                                                         int page_size, int table_width, int num_pages, int window,
+                                                         float scale, int ctas, const float* q_weight,
+                                                         const float* k_weight, const float* inv_freq, float eps,
+                                                         int* error_flag, cudaStream_t stream) {
+    if (requests <= 0) return 0;
+    int bad = check_common(q_heads, kv_heads, head_dim, qkv_row_stride, qkv);
+    if (bad) return bad;
+    if (q_heads / kv_heads > 16) return KIRAI_ERR_UNSUPPORTED;
+    if (ctas < 1 || ctas > 65535 || !partial) return KIRAI_ERR_BAD_SIZE;
+    if (requests > DECODE_MAX_REQUESTS) return KIRAI_ERR_UNSUPPORTED;
+    if (((uintptr_t)q_weight | (uintptr_t)k_weight | (uintptr_t)inv_freq | (uintptr_t)cache) & 15) return KIRAI_ERR_BAD_ALIGN;
+    const FuseQK fuse{q_weight, k_weight, inv_freq, eps};
+#define KIRAI_DCBQ(D) \
+    return decode_balanced_launch<D>(qkv, cache, out, partial, block_table, context_len, requests, q_heads, kv_heads, \
+                                     head_dim, qkv_row_stride, page_size, table_width, num_pages, window, scale, ctas, \
+                                     error_flag, stream, &fuse)
+    if (head_dim == 64) KIRAI_DCBQ(64);
+    if (head_dim == 128) KIRAI_DCBQ(128);
+    if (head_dim == 256) KIRAI_DCBQ(256);
+#undef KIRAI_DCBQ
+    return KIRAI_ERR_UNSUPPORTED;
 }
 
 // ----------------------------------------------------- decode without allocation

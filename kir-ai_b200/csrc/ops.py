@@ -481,6 +481,58 @@ def _decode_rows(q, cache, block_table, batch, rows: int, window: Optional[int],
     attention_decode(q, cache, block_table, context_len, window, scale, splits, out=out)
 
 
+def decode_prepares_qk(qkv: torch.Tensor, cache: Optional[torch.Tensor], batch, q_heads: int, kv_heads: int, head_dim: int) -> bool:
+    """Whether ``attention_decode_qk`` takes this step: every request brings one token, bfloat16, heads of 64, 128 or
+    256 in groups of at most 16, rows on 16-byte boundaries, and no more (request, kv head) pairs than SMs: with more,
+    every one of the many CTAs repeats the preparation, and the separate kernel, which runs beside the end of the
+    product before it, is faster (10.37 against 10.13 ms a step at 64 requests of the 8B shape; 3.29 against 3.31 ms
+    at one request)."""
+    return (cache is not None and batch.num_requests * kv_heads <= sm_count(qkv.device) and qkv.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and batch.decode_only
+            and head_dim in (64, 128, 256) and kv_heads > 0 and q_heads // kv_heads <= 16 and qkv.is_contiguous()
+            and qkv.data_ptr() % 16 == 0 and batch.num_requests == qkv.shape[0])
+
+
+def attention_decode_qk(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int, q_weight: Optional[torch.Tensor],
+                        k_weight: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], eps: float, cache: torch.Tensor,
+                        block_table: torch.Tensor, batch, window: Optional[int], scale: float) -> torch.Tensor:
+    """A decode step's attention with its preparation inside the kernel: ``qkv`` [R, (nq + 2 nkv) d] as the q, k, v
+    product left it (not modified).  Per-head RMSNorm of q and k, rotation at each request's position, the new token's
+    key and value appended to its page, attention over the pages: one kernel, where the separate path runs
+    ``qk_norm_rope_kv_write_`` and then the decode kernel.  The result equals that path's bit for bit."""
+    _need_cuda(qkv, q_weight, k_weight, inv_freq, cache, block_table, batch.context_len)
+    num_pages, c_heads, page_size, c_dim = _cache_dims(cache)
+    rows = qkv.shape[0]
+    assert (c_heads, c_dim) == (kv_heads, head_dim) and qkv.shape[1] == (q_heads + 2 * kv_heads) * head_dim
+    for w in (q_weight, k_weight):
+        assert w is None or (w.dtype == torch.float32 and w.numel() == head_dim and w.is_contiguous())
+    assert inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2 and inv_freq.is_contiguous())
+    context_len = batch.context_len
+    out = torch.empty((rows, q_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    balanced = getattr(batch, "decode_balanced", None)
+    longest = batch.max_context_len
+    if balanced is None:
+        lens = [start + count for start, count in zip(batch.start_positions, batch.query_lens)]
+        balanced, _ = decode_plan(lens, kv_heads, window, sms=sm_count(qkv.device))
+        longest = max(lens)
+    forced = os.environ.get("KIRAI_DECODE_BALANCED")
+    if forced in ("0", "1"):
+        balanced = forced == "1"
+    tail = (_ptr(q_weight), _ptr(k_weight), _ptr(inv_freq), _f(eps), _ptr(error_flag(qkv.device)), _stream())
+    common = (_ptr(block_table), _ptr(context_len), _i(rows), _i(q_heads), _i(kv_heads), _i(head_dim), _l(qkv.stride(0)),
+              _i(page_size), _i(block_table.shape[1]), _i(num_pages), _i(window or 0), _f(scale))
+    if balanced and rows <= 1024:
+        ctas = sm_count(qkv.device)
+        partial = torch.empty((ctas, 2, 16, head_dim + 2), dtype=torch.float32, device=qkv.device)
+        _call("kirai_attention_decode_balanced_qk_bf16", _ptr(qkv), _ptr(cache), _ptr(out), _ptr(partial), *common, _i(ctas), *tail)
+        return out
+    splits = decode_splits(rows, kv_heads, min(longest, window or longest))
+    partial = None
+    if splits > DECODE_CLUSTER or (splits > 1 and rows * kv_heads * splits > sm_count(qkv.device)):
+        partial = torch.empty((rows, q_heads, splits, head_dim + 2), dtype=torch.float32, device=qkv.device)
+    _call("kirai_attention_decode_qk_bf16", _ptr(qkv), _ptr(cache), _ptr(out), _ptr(partial), *common, _i(splits), *tail)
+    return out
+
+
 # ------------------------------------------------------------------------ linear
 def linear_plain(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """``x`` [M, K] times ``weight`` [N, K] transposed on the CUDA cores with 32-bit FMAs."""

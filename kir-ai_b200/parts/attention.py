@@ -107,6 +107,12 @@ class GQAttention(Mixer):
         qkv = self.qkv.forward(x)  # [T, (nq + 2 nkv) d]
         fused_table = self.position.fused_table() if isinstance(self.position, RotaryEmbedding) else None
         q = qkv[:, : nq * d].unflatten(1, (nq, d))
+        if ((self.position is None or fused_table is not None) and write_cache and nkv == self.kv_heads
+                and getattr(ops, "decode_prepares_qk", None) is not None
+                and ops.decode_prepares_qk(qkv, cache.kv, batch, nq, nkv, d)):
+            # every request brings one token: norm, rotation and the cache write happen inside the attention kernel
+            return ops.attention_decode_qk(qkv, nq, nkv, d, self.q_norm_weight, self.k_norm_weight, fused_table,
+                                           self.qk_norm_eps or 0.0, cache.kv, table, batch, self.window, self.scale)
         if self.position is None or fused_table is not None:
             ops.qk_norm_rope_kv_write_(qkv, nq, nkv, d, self.q_norm_weight, self.k_norm_weight, fused_table,
                                        self.qk_norm_eps or 0.0, cache.kv if write_cache else None, table,

@@ -289,6 +289,55 @@ def test_a_bounded_wait_that_runs_out_is_reported_and_the_device_stays_usable(op
         ops.wait_selftest(device, limit=1 << 21)
 
 
+@pytest.mark.parametrize("balanced", ["0", "1"])
+@pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,window,lengths",
+                         [(32, 8, 128, 16, None, [700, 33, 512, 129, 1]), (6, 2, 64, 4, 9, [40, 7, 16]), (4, 4, 256, 64, None, [300, 65]),
+                          (16, 1, 128, 8, 100, [260, 1, 17, 16, 130]), (8, 2, 128, 16, None, [4100])])
+def test_decode_attention_that_prepares_its_queries_and_keys(ops, monkeypatch, balanced, q_heads, kv_heads, head_dim, page_size, window, lengths):
+    """One kernel (per-head norm of q and k, rotation, the new token appended to its page, attention) against the two
+    that it replaces, on the same inputs: the attention rows and every byte of the cache must be equal, with either
+    way of cutting the keys (equal ranges per request, whose CTAs merge as clusters or through a buffer; one range per
+    SM), heads of 64, 128 and 256, groups of 1 to 16, a window, pages smaller and larger than a key tile."""
+    from types import SimpleNamespace
+
+    monkeypatch.setenv("KIRAI_DECODE_BALANCED", balanced)
+    dtype = torch.bfloat16
+    requests = len(lengths)
+    cache, table, keys, values = paged_setup(dtype, lengths, kv_heads, head_dim, page_size, seed=11)
+    for r, n in enumerate(lengths):  # the tokens before the new one are in the pages already
+        if n > 1:
+            pos = torch.arange(n - 1, dtype=torch.int32, device=DEV)
+            ops.kv_write(keys[r][: n - 1].to(DEV).contiguous(), values[r][: n - 1].to(DEV).contiguous(), cache, table,
+                         torch.full((n - 1,), r, dtype=torch.int32, device=DEV), pos)
+    width = (q_heads + 2 * kv_heads) * head_dim
+    qkv = rand(requests, width, dtype=dtype, seed=5)
+    q_weight, k_weight = 1.0 + 0.1 * rand(head_dim, seed=6), 1.0 + 0.1 * rand(head_dim, seed=7)
+    inv_freq = torch.pow(torch.tensor(10000.0), -torch.arange(head_dim // 2, dtype=torch.float32) * 2.0 / head_dim).to(DEV)
+    positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
+    context_len = torch.tensor(lengths, dtype=torch.int32, device=DEV)
+    rows = torch.arange(requests, dtype=torch.int32, device=DEV)
+    batch = SimpleNamespace(decode_only=True, num_requests=requests, context_len=context_len, max_context_len=max(lengths),
+                            start_positions=[n - 1 for n in lengths], query_lens=[1] * requests, decode_balanced=None,
+                            request_of_token=rows, positions=positions, num_decode=requests)
+    scale = head_dim ** -0.5
+    for weights in ((q_weight, k_weight, inv_freq), (None, None, inv_freq), (q_weight, k_weight, None)):
+        qw, kw, freq = weights
+        separate_cache, separate_qkv = cache.clone(), qkv.clone()
+        ops.qk_norm_rope_kv_write_(separate_qkv, q_heads, kv_heads, head_dim, qw, kw, freq, 1e-6, separate_cache, table, rows, positions, True)
+        q = separate_qkv[:, : q_heads * head_dim].unflatten(1, (q_heads, head_dim))
+        expected = ops.paged_attention(q, separate_cache, table, batch, window, scale)
+        fused_cache, fused_qkv = cache.clone(), qkv.clone()
+        assert ops.decode_prepares_qk(fused_qkv, fused_cache, batch, q_heads, kv_heads, head_dim)
+        crowd = SimpleNamespace(decode_only=True, num_requests=1 + ops.sm_count(torch.device(DEV)) // kv_heads)
+        assert not ops.decode_prepares_qk(fused_qkv.expand(crowd.num_requests, -1) if requests == 1 else fused_qkv, fused_cache, crowd, q_heads, kv_heads, head_dim)
+        got = ops.attention_decode_qk(fused_qkv, q_heads, kv_heads, head_dim, qw, kw, freq, 1e-6, fused_cache, table, batch, window, scale)
+        ops.check_device_errors(torch.device(DEV))
+        assert torch.equal(fused_qkv, qkv)                      # the product's rows are left as they were
+        assert torch.equal(fused_cache, separate_cache)         # the same key and value rows, in the same places
+        assert torch.equal(got, expected)
+        assert float(got.float().abs().max()) > 0.01
+
+
 def test_sampler_on_the_cases_of_the_reference(ops):
     """crates/llm-sampler/src/lib.rs:222-294 through the device sampler, all rows in one launch: greedy, the first of
     equal maxima, a draw inside the nucleus, and ties inside the nucleus taken in index order."""
@@ -528,6 +577,55 @@ def test_a_bounded_wait_that_runs_out_is_reported_and_the_device_stays_usable(op
     ops.check_device_errors(device)
     with pytest.raises(ops.KernelError, match="refused"):
         ops.wait_selftest(device, limit=1 << 21)
+
+
+@pytest.mark.parametrize("balanced", ["0", "1"])
+@pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,window,lengths",
+                         [(32, 8, 128, 16, None, [700, 33, 512, 129, 1]), (6, 2, 64, 4, 9, [40, 7, 16]), (4, 4, 256, 64, None, [300, 65]),
+                          (16, 1, 128, 8, 100, [260, 1, 17, 16, 130]), (8, 2, 128, 16, None, [4100])])
+def test_decode_attention_that_prepares_its_queries_and_keys(ops, monkeypatch, balanced, q_heads, kv_heads, head_dim, page_size, window, lengths):
+    """One kernel (per-head norm of q and k, rotation, the new token appended to its page, attention) against the two
+    that it replaces, on the same inputs: the attention rows and every byte of the cache must be equal, with either
+    way of cutting the keys (equal ranges per request, whose CTAs merge as clusters or through a buffer; one range per
+    SM), heads of 64, 128 and 256, groups of 1 to 16, a window, pages smaller and larger than a key tile."""
+    from types import SimpleNamespace
+
+    monkeypatch.setenv("KIRAI_DECODE_BALANCED", balanced)
+    dtype = torch.bfloat16
+    requests = len(lengths)
+    cache, table, keys, values = paged_setup(dtype, lengths, kv_heads, head_dim, page_size, seed=11)
+    for r, n in enumerate(lengths):  # the tokens before the new one are in the pages already
+        if n > 1:
+            pos = torch.arange(n - 1, dtype=torch.int32, device=DEV)
+            ops.kv_write(keys[r][: n - 1].to(DEV).contiguous(), values[r][: n - 1].to(DEV).contiguous(), cache, table,
+                         torch.full((n - 1,), r, dtype=torch.int32, device=DEV), pos)
+    width = (q_heads + 2 * kv_heads) * head_dim
+    qkv = rand(requests, width, dtype=dtype, seed=5)
+    q_weight, k_weight = 1.0 + 0.1 * rand(head_dim, seed=6), 1.0 + 0.1 * rand(head_dim, seed=7)
+    inv_freq = torch.pow(torch.tensor(10000.0), -torch.arange(head_dim // 2, dtype=torch.float32) * 2.0 / head_dim).to(DEV)
+    positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
+    context_len = torch.tensor(lengths, dtype=torch.int32, device=DEV)
+    rows = torch.arange(requests, dtype=torch.int32, device=DEV)
+    batch = SimpleNamespace(decode_only=True, num_requests=requests, context_len=context_len, max_context_len=max(lengths),
+                            start_positions=[n - 1 for n in lengths], query_lens=[1] * requests, decode_balanced=None,
+                            request_of_token=rows, positions=positions, num_decode=requests)
+    scale = head_dim ** -0.5
+    for weights in ((q_weight, k_weight, inv_freq), (None, None, inv_freq), (q_weight, k_weight, None)):
+        qw, kw, freq = weights
+        separate_cache, separate_qkv = cache.clone(), qkv.clone()
+        ops.qk_norm_rope_kv_write_(separate_qkv, q_heads, kv_heads, head_dim, qw, kw, freq, 1e-6, separate_cache, table, rows, positions, True)
+        q = separate_qkv[:, : q_heads * head_dim].unflatten(1, (q_heads, head_dim))
+        expected = ops.paged_attention(q, separate_cache, table, batch, window, scale)
+        fused_cache, fused_qkv = cache.clone(), qkv.clone()
+        assert ops.decode_prepares_qk(fused_qkv, fused_cache, batch, q_heads, kv_heads, head_dim)
+        crowd = SimpleNamespace(decode_only=True, num_requests=1 + ops.sm_count(torch.device(DEV)) // kv_heads)
+        assert not ops.decode_prepares_qk(fused_qkv.expand(crowd.num_requests, -1) if requests == 1 else fused_qkv, fused_cache, crowd, q_heads, kv_heads, head_dim)
+        got = ops.attention_decode_qk(fused_qkv, q_heads, kv_heads, head_dim, qw, kw, freq, 1e-6, fused_cache, table, batch, window, scale)
+        ops.check_device_errors(torch.device(DEV))
+        assert torch.equal(fused_qkv, qkv)                      # the product's rows are left as they were
+        assert torch.equal(fused_cache, separate_cache)         # the same key and value rows, in the same places
+        assert torch.equal(got, expected)
+        assert float(got.float().abs().max()) > 0.01
 
 
 def test_sampler_on_the_cases_of_the_reference(ops):
