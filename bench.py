@@ -323,7 +323,8 @@ def main() -> int:
             assert runner.cache.reserve(r.pages, ahead + 1)
         cache = runner.cache
         tables = [cache.block_table_array([r.pages for r in requests], g) for g in range(len(cache.groups))]
-        graph, fresh = engine.graphs.get(batch, max(t.shape[1] for t in tables))
+        # the captured step that the engine itself would replay for these requests (its choice of attention kernel)
+        graph, fresh = engine.graphs.get(batch, max(t.shape[1] for t in tables), [r.pages.length + 1 for r in requests])
         graph.load_inputs([r.token_at(r.computed) for r in requests], [r.pages.length for r in requests],
                           [r.pages.slot for r in requests], tables, [0.0] * batch, [1.0] * batch, [0.0] * batch)
         if fresh:
