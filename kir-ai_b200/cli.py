@@ -34,9 +34,12 @@ Options:
   --max-new-tokens <n>              Maximum generated tokens a request may ask for [default: 256]
   --max-prefill-tokens <n>          Token budget of a step (prompt portions are cut to it) [default: 2048]
   --max-concurrent-requests <n>     Requests running at a time [default: 4]
+  --prefill-chunk <n>               Longest portion of one prompt in a step [default: the step's budget]
   --page-size <n>                   Tokens per cache page [default: 16]
   --max-cache-tokens <n>            Size of the cache pool in tokens [default: from the limits above]
-  --log-level <level>               trace|debug|info|warn|error|off [default: info]
+  --num-pages <n>                   Size of the cache pool in pages (instead of --max-cache-tokens)
+  --log-level <level>               trace|debug|info|warn|error|off [default: info]; trace also marks every layer
+                                    call as an NVTX range
   -h, --help                        Print help
 """
 
@@ -141,14 +144,21 @@ def generate_command(args: List[str]) -> int:
         max_new_tokens=int(max_tokens) if max_tokens is not None else None,
         eos_token_id=int(eos) if eos is not None else None,
     )
+    cache_tokens = _int(args, "--max-cache-tokens", None)
+    num_pages = _int(args, "--num-pages", None)
+    if num_pages is not None:
+        if cache_tokens is not None:
+            raise SystemExit("give --max-cache-tokens or --num-pages, not both")
+        cache_tokens = num_pages * _int(args, "--page-size", 16)
     engine = Engine(
         snapshot if random_seed is None else None, config=config,
         random_weights_seed=int(random_seed) if random_seed is not None else None,
         dtype=flag_value(args, "--dtype") or "bfloat16",
         max_new_tokens=_int(args, "--max-new-tokens", 256), max_prefill_tokens=_int(args, "--max-prefill-tokens", 2048),
         max_concurrent_requests=_int(args, "--max-concurrent-requests", 4), page_size=_int(args, "--page-size", 16),
-        max_cache_tokens=_int(args, "--max-cache-tokens", None),
+        max_cache_tokens=cache_tokens, prefill_chunk=_int(args, "--prefill-chunk", None),
     )
+    engine.runner.model.nvtx = level == "trace"
     log(f"loaded {type(engine.runner.config).__name__}; generating for {len(prompts)} prompt(s)")
     for output in engine.generate(prompts, params):
         print(json.dumps({"token_ids": output.token_ids, "finish_reason": output.finish_reason,

@@ -764,6 +764,15 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
     }
 }
 
+static int sm_count() {
+    static const int count = [] {
+        int device = 0, value = 0;
+        if (cudaGetDevice(&device) != cudaSuccess) return 0;
+        if (cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+        return value;
+    }();
+    return count;
+}
 template <int BN, typename OutT, int EPI>
 static int launch_persistent(const void* A, const void* W, bool tiled, void* C, int M, int N, int K, long lda, long ldc,
                              const Epilogue& ep, int* error_flag, cudaStream_t stream) {
@@ -774,13 +783,9 @@ static int launch_persistent(const void* A, const void* W, bool tiled, void* C, 
     else if (!tmap::bf16_2d_sw128(&map_w, W, N, K, K, BN, GEMM_BK)) return KIRAI_ERR_BAD_ALIGN;
     if (tiled && ((uintptr_t)W & 15)) return KIRAI_ERR_BAD_ALIGN;
     const long tiles = (long)((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int device = 0;
-        cudaGetDevice(&device);
-        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0) sm_count = 148;
-    }
-    const unsigned grid = (unsigned)(tiles < sm_count ? tiles : sm_count);
+    const int sms = sm_count();
+    if (sms <= 0) return KIRAI_ERR_UNSUPPORTED;  // the device did not say how many SMs it has
+    const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
     auto kernel = gemm_tcgen05_persistent_kernel<BN, OutT, EPI>;
     const int smem_bytes = Smem::total(1) + (EPI == 2 ? 4 * 32 * 32 * 4 : 0);  // + the epilogue's staging buffers
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
@@ -789,15 +794,6 @@ static int launch_persistent(const void* A, const void* W, bool tiled, void* C, 
                       tiled ? (const uint8_t*)W : (const uint8_t*)nullptr, (OutT*)C, M, N, K, ldc, ep, error_flag);
 }
 
-static int sm_count() {
-    static const int count = [] {
-        int device = 0, value = 0;
-        if (cudaGetDevice(&device) != cudaSuccess) return 0;
-        if (cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
-        return value;
-    }();
-    return count;
-}
 static bool deep_rings() {
     static const bool on = [] {
         const char* text = getenv("KIRAI_GEMM_DEEP");
@@ -853,9 +849,11 @@ static int choose_splits(int M, int N, int K) {
     const int x_tiles = (N + GEMM_BM - 1) / GEMM_BM;
     const int max_splits = 4;
     const int k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
-    // about one CTA per SM; with more than 32 tokens a CTA with slots for 3 or 4 partial tiles
-    // fills an SM by itself and fewer, longer CTAs measured faster
-    const int target = M <= 32 ? 144 : 112;
+    // about one CTA per SM (a few SMs fewer, so that a launch fits one wave whatever the tile count is); with more
+    // than 32 tokens a CTA with slots for 3 or 4 partial tiles fills an SM by itself and fewer, longer CTAs measured
+    // faster: three quarters of the SMs
+    const int sms = sm_count() > 0 ? sm_count() : 148;
+    const int target = M <= 32 ? sms - 4 : 3 * sms / 4 + 1;
     int splits = (2 * target + x_tiles) / (2 * x_tiles);  // target / x_tiles, rounded
     if (splits > max_splits) splits = max_splits;
     while (splits > 1 && k_blocks / splits < 8) --splits;

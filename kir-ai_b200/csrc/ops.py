@@ -81,6 +81,7 @@ def _suffix(dtype: torch.dtype) -> str:
 
 
 launch_count = 0  # entry points called so far (each launches one to three kernels); read by measurements
+launch_counts: dict = {}  # the same by entry point: which kernels a step used, and how often (Engine.stats reports it)
 
 
 def _call(name: str, *args) -> None:
@@ -97,6 +98,7 @@ def _launch(name: str, *args) -> None:
     fn.restype = ctypes.c_int
     _check(fn(*args), name)
     launch_count += 1
+    launch_counts[name] = launch_counts.get(name, 0) + 1
 
 
 _i = ctypes.c_int
@@ -337,10 +339,14 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.T
 DECODE_CLUSTER = 8  # ranges of one (request, kv head) whose CTAs can merge as a thread-block cluster
 
 
-def decode_splits(requests: int, kv_heads: int, max_context_len: int, tile: int = 16, warps: int = 8) -> int:
+DEFAULT_SMS = 148  # for planning on a host without the device (tests); launches ask the device
+
+
+def decode_splits(requests: int, kv_heads: int, max_context_len: int, tile: int = 16, warps: int = 8,
+                  sms: int = DEFAULT_SMS) -> int:
     """How many CTAs share one (request, kv head) in the decode kernel.  A CTA's warps take
     key tiles in turn, so a CTA with n tiles runs ceil(n / warps) rounds plus a fixed cost (set-up,
-    merge); CTAs run in waves of 148.  Up to DECODE_CLUSTER ranges merge inside the kernel (their CTAs are a
+    merge); CTAs run in waves of ``sms``.  Up to DECODE_CLUSTER ranges merge inside the kernel (their CTAs are a
     cluster); more need a buffer and a second kernel, about two rounds' time.  The split count with the fewest
     estimated rounds wins.  (Clusters are used only while all CTAs run at once: in a launch of several waves the
     pairs of CTAs that a cluster must place together left SMs idle, 10.34 against 10.14 ms a step at 64 requests.)"""
@@ -348,7 +354,7 @@ def decode_splits(requests: int, kv_heads: int, max_context_len: int, tile: int 
     tiles = max(1, -(-max_context_len // tile))
     best, best_cost = 1, None
     for splits in range(1, min(64, tiles) + 1):
-        waves = -(-pairs * splits // 148)
+        waves = -(-pairs * splits // sms)
         rounds = -(-(-(-tiles // splits)) // warps) + 3
         cost = waves * rounds + (0 if splits == 1 else (0.75 if splits <= DECODE_CLUSTER and waves == 1 else 2.75))
         if best_cost is None or cost < best_cost:
@@ -357,7 +363,7 @@ def decode_splits(requests: int, kv_heads: int, max_context_len: int, tile: int 
 
 
 def decode_plan(context_lens, kv_heads: int, window: Optional[int] = None, tile: int = 16, warps: int = 8,
-                sms: int = 148) -> tuple:
+                sms: int = DEFAULT_SMS) -> tuple:
     """Which decode attention kernel a batch should take: (balanced, splits).
 
     The split kernel gives every request the same number of CTAs, so its time is that of the longest request and
@@ -370,7 +376,7 @@ def decode_plan(context_lens, kv_heads: int, window: Optional[int] = None, tile:
     if not lens:
         return False, 1
     longest = max(1, max(lens))
-    splits = decode_splits(len(lens), kv_heads, longest, tile, warps)
+    splits = decode_splits(len(lens), kv_heads, longest, tile, warps, sms)
     tiles = [max(1, -(-n // tile)) for n in lens]
     waves = -(-len(lens) * kv_heads * splits // sms)
     rounds_split = -(-(-(-max(tiles) // splits)) // warps)
@@ -477,7 +483,7 @@ def _decode_rows(q, cache, block_table, batch, rows: int, window: Optional[int],
     if balanced and rows <= 1024:
         attention_decode_balanced(q, cache, block_table, context_len, window, scale, out=out)
         return
-    splits = decode_splits(rows, kv_heads, min(longest, window or longest))
+    splits = decode_splits(rows, kv_heads, min(longest, window or longest), sms=sm_count(q.device))
     attention_decode(q, cache, block_table, context_len, window, scale, splits, out=out)
 
 
@@ -525,7 +531,7 @@ def attention_decode_qk(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim
         partial = torch.empty((ctas, 2, 16, head_dim + 2), dtype=torch.float32, device=qkv.device)
         _call("kirai_attention_decode_balanced_qk_bf16", _ptr(qkv), _ptr(cache), _ptr(out), _ptr(partial), *common, _i(ctas), *tail)
         return out
-    splits = decode_splits(rows, kv_heads, min(longest, window or longest))
+    splits = decode_splits(rows, kv_heads, min(longest, window or longest), sms=sm_count(qkv.device))
     partial = None
     if splits > DECODE_CLUSTER or (splits > 1 and rows * kv_heads * splits > sm_count(qkv.device)):
         partial = torch.empty((rows, q_heads, splits, head_dim + 2), dtype=torch.float32, device=qkv.device)
@@ -707,6 +713,7 @@ def flush_products() -> None:
         if status == 0:
             global launch_count
             launch_count += 1
+            launch_counts["kirai_gemm_chain_bf16"] = launch_counts.get("kirai_gemm_chain_bf16", 0) + 1
             return
         if status not in _REFUSALS:
             _check(status, "kirai_gemm_chain_bf16")

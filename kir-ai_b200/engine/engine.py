@@ -259,4 +259,5 @@ class Engine:
             for group in cache["groups"]:
                 group["used"] -= 1
             cache["padding_rows"] = {"pages_per_group": 1, "slots": 1}
-        return {**self.counters, "scheduler": dict(self.scheduler.stats), "cache": cache}
+        return {**self.counters, "scheduler": dict(self.scheduler.stats), "cache": cache,
+                "kernel_launches": dict(self.runner.rt.ops.launch_counts)}

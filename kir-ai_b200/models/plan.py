@@ -106,6 +106,8 @@ class DecoderModel:
         self.rt = rt
         # with parts that touch activations through the kernels only, a step's small products are launched together
         self._kernels_only = plan.kernels_only() and hasattr(rt.ops, "chained_products")
+        self.nvtx = False  # True: every layer call is an NVTX range (the reference counts attempts and fallbacks per
+        # kernel instead, crates/llm-native-runtime/src/native_metrics.rs:7-70; here ops.launch_counts does that)
 
     def load(self, weights) -> "DecoderModel":
         for part in self.plan.parts():
@@ -114,6 +116,7 @@ class DecoderModel:
 
     def forward(self, batch, cache) -> tuple:
         """The residual stream [T, H] (32-bit) and the last block's not-yet-added output."""
+        nvtx = torch.cuda.nvtx if self.nvtx else None  # ranges around the layer calls, for a timeline tool
         with self.rt.ops.chained_products(self._kernels_only):
             resid = self.plan.embedding.forward(batch.token_ids)
             delta = None
@@ -121,7 +124,11 @@ class DecoderModel:
             for i, call in enumerate(order):
                 view = cache.layer_view(call.cache) if call.cache is not None else None
                 following = self.plan.blocks[order[i + 1].block] if i + 1 < len(order) else None
+                if nvtx:
+                    nvtx.range_push(f"layer call {i}: block {call.block}, {batch.num_tokens} tokens")
                 resid, delta = self.plan.blocks[call.block].forward(resid, delta, batch, view, call.write, following)
+                if nvtx:
+                    nvtx.range_pop()
         return resid, delta
 
     def logits(self, resid: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:

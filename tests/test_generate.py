@@ -78,27 +78,28 @@ def test_temperature_sampling_with_seed_float32(tiny):
 
 
 def test_greedy_generation_bfloat16_follows_plain(tiny):
-    """bfloat16 rounds activations, so a near-tie may resolve differently; wherever the engine's
-    token differs from the plain choice, the plain logits of the two tokens must be within the
-    bfloat16 tolerance, and the run is compared only up to that point."""
+    """bfloat16 rounds activations, so a near-tie may resolve differently from the plain implementation, and from
+    there on the two generate different texts.  The whole generation is followed all the same: at every step the
+    plain logits are computed for the prompt and the tokens that the ENGINE has generated so far, and the engine's
+    next token must be the plain maximum or within the bfloat16 bound of it.  Most steps must agree exactly."""
     from kirai_b200 import Engine, SamplingParams
 
     engine = Engine(tiny["folder"], dtype="bfloat16", page_size=tiny["page"], max_prefill_tokens=16,
                     max_concurrent_requests=2, max_new_tokens=16, max_cache_tokens=256)
     prompts = [random_tokens(n, tiny["raw"]["vocab_size"], 60 + n) for n in (6, 19, 33)]
-    outputs = engine.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=10))
-    agreed = 0
+    outputs = engine.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=12))
+    agreed = steps = 0
     for prompt, output in zip(prompts, outputs):
+        assert len(output.token_ids) == 12
         tokens = list(prompt)
         for token in output.token_ids:
             logits = plain.forward_logits(tiny["config"], tiny["weights"], tokens)[-1]
             best = plain.argmax_first(logits)
-            if token != best:
-                assert float(logits[best] - logits[token]) <= 0.02 * float(logits.abs().max())
-                break
-            agreed += 1
-            tokens.append(token)
-    assert agreed >= 20
+            assert float(logits[best] - logits[token]) <= 0.02 * float(logits.abs().max()), (len(tokens), token, best)
+            agreed += token == best
+            steps += 1
+            tokens.append(token)  # the engine's token, whichever it was: the next step is judged on the engine's own text
+    assert steps == 36 and agreed >= 30
 
 
 def test_eviction_and_recompute_give_the_same_tokens(tiny):
@@ -184,9 +185,14 @@ def test_abort_between_steps_leaves_the_others_untouched(tiny):
 def test_command_line(tiny):
     command = [sys.executable, os.path.join(ROOT, "bin", "kirai"), "generate", "--snapshot", tiny["folder"],
                "--prompt-ids", "5,17,3,44", "--prompt-ids", "9,8,7", "--max-tokens", "6", "--temperature", "0",
-               "--dtype", "float32", "--page-size", str(tiny["page"]), "--max-new-tokens", "16", "--log-level", "error"]
+               "--dtype", "float32", "--page-size", str(tiny["page"]), "--max-new-tokens", "16", "--log-level", "trace",
+               "--prefill-chunk", "3", "--num-pages", "24"]
     result = subprocess.run(command, capture_output=True, text=True, timeout=600)
     assert result.returncode == 0, result.stderr
+    stats = json.loads(result.stderr.strip().splitlines()[-1].split("[kirai] ", 1)[1])  # the last log line: the engine's counters
+    assert stats["cache"]["groups"][0]["pages"] == 24 + 1  # the pool asked for, and the page of the padding rows
+    # the prompt of four tokens went in two portions (3 + 1): one step more than its six tokens alone would take
+    assert stats["steps"] == 7 and stats["kernel_launches"]["kirai_sample_rows"] >= 1  # replays of captured steps call no entry point
     lines = [json.loads(line) for line in result.stdout.strip().splitlines()]
     assert len(lines) == 2
     for prompt, line in zip(([5, 17, 3, 44], [9, 8, 7]), lines):
