@@ -124,7 +124,7 @@ __device__ __forceinline__ long chain_range_begin(long total, int cta, int grid)
 // The CTA whose stretch holds box `box`.
 __device__ __forceinline__ int chain_owner(long box, long total, int grid) { return (int)(((box + 1) * grid + total - 1) / total) - 1; }
 
-__device__ __forceinline__ float chain_silu_mul(float gate, float up) { return gate * up * __frcp_rn(1.0f + __expf(-gate)); }
+__device__ __forceinline__ float chain_silu_mul(float gate, float up) { return __fdividef(gate * up, 1.0f + __expf(-gate)); }
 
 template <int BN>
 __global__ void __launch_bounds__(CHAIN_THREADS, 1)

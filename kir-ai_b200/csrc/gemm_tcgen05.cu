@@ -30,6 +30,9 @@
 // (row tile, k block) at index row_tile * ceil(K / 64) + k_block, zero-padded at the edges.  A tiled box is one
 // contiguous bulk copy; streaming whole boxes reads HBM about a sixth faster than gathering 128 rows of 128 bytes.
 #include <cstdlib>
+#include <map>
+#include <mutex>
+#include <tuple>
 
 #include "sm100.cuh"
 #include "tensor_map.cuh"
@@ -82,7 +85,20 @@ struct Epilogue {
     float* residual;
     const float* norm_weight;
     float* sumsq_out;
+    unsigned long long* stamps;  // null, or [CTAs][8] clock stamps (ns) of the streaming kernel, for measurements
 };
+
+// Clock stamps of one CTA of the streaming kernel, written only when a buffer is given: 0 the CTA starts, 1 the kernel
+// before has finished (activations may be read), 2 the first stage is in shared memory, 3 the last product is done,
+// 4 the partial tiles of the cluster are together, 5 the tile is stored.
+__device__ __forceinline__ void gemm_stamp(const Epilogue& ep, int which) {
+    if (ep.stamps) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        const size_t cta = ((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        ep.stamps[cta * 8 + which] = now;
+    }
+}
 
 __device__ __forceinline__ float row_scale_of(const Epilogue& ep, int m, int M) {
     float total = 0.0f;
@@ -129,10 +145,11 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t address, float value) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(address), "f"(value) : "memory");
 }
 
-// silu(gate) * up with the fast exponential and reciprocal (relative error about 2^-21, far below
-// the bf16 rounding of the result); the epilogue runs beside the next tile's MMAs and must be short.
+// silu(gate) * up with the fast exponential and the fast division (relative error about 2^-21, far below
+// the bf16 rounding of the result); the epilogue runs beside the next tile's MMAs and must be short.  (The correctly
+// rounded reciprocal, a sequence with a branch for special cases, made sixteen of these take 1.9 us a thread.)
 __device__ __forceinline__ float silu_mul(float gate, float up) {
-    return gate * up * __frcp_rn(1.0f + __expf(-gate));
+    return __fdividef(gate * up, 1.0f + __expf(-gate));
 }
 
 // SWAP false: X = A (rows m), Y = W (rows n), C[m, n].  SWAP true: X = W, Y = A.
@@ -168,6 +185,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const int num_kb = max(0, kb_end - kb_begin);
     const uint32_t rank = blockIdx.z;  // the cluster is (1, 1, splits) and the grid's z extent is splits
     pdl_launch_dependents();  // the next kernel may set itself up while this one streams
+    if (threadIdx.x == 0) gemm_stamp(ep, 0);
 
     if (threadIdx.x == 0) {
         tma_prefetch_descriptor(&map_x);
@@ -189,6 +207,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const uint32_t tmem_base = *tmem_slot;
     float res[16];  // EPI 2: the stream's values under this thread's 16 outputs
     float norm_w = 0.0f;
+    // Staged stores (SWAP): a thread holds one output column of 16 tokens, so storing from that layout takes 16 to 32
+    // narrow store instructions a thread, which measured 0.4 to 2.6 us at the end of a launch (longest when the next
+    // kernel's CTAs already stream beside it).  Where rows are 16-byte aligned the values go through shared memory
+    // (the idle ring; 132 floats to a token) and every thread stores 16 adjacent columns of one token in 16-byte pieces.
+    const bool c_aligned = ((uintptr_t)C & 15) == 0 && (ldc * (long)sizeof(OutT)) % 16 == 0;
+    const bool staged = SWAP && c_aligned &&
+                        (EPI == 2 ? (N % 8 == 0 && (((uintptr_t)ep.residual | (uintptr_t)ep.norm_weight) & 15) == 0)
+                                  : (EPI == 1 ? N % 16 == 0 : N % 8 == 0));
+    float4 res4[4], norm4[4];  // EPI 2, staged: the stream's values and the norm's weights under this thread's 16 columns of token y0 + tile_row / 8
     bool ok = true;
     const int lane_group = warp & 3;           // epilogue warps: tensor-memory lanes 32 (warp % 4) ..
     const int tile_row = lane_group * 32 + lane;
@@ -214,6 +241,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 if (y_first == 0) tma_load_2d(dst + Smem::x_bytes, &map_y, full, k, y0);
             }
             pdl_wait();  // what the kernel before wrote (the activations) is complete and visible
+            gemm_stamp(ep, 1);
             for (int i = 0; i < head; ++i) {
                 const uint32_t full = smem_addr(&full_bar[i]);
                 const uint32_t dst = smem_addr(smem + i * Smem::stage_bytes);
@@ -240,6 +268,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 const int s = i % STAGES;
                 const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
                 if (!mbar_wait(smem_addr(&full_bar[s]), phase)) { ok = false; break; }
+                if (i == 0) gemm_stamp(ep, 2);
                 tc_fence_after();
                 const uint32_t x_addr = smem_addr(smem + s * Smem::stage_bytes);
                 const uint64_t desc_x = smem_desc_k_major_sw128(x_addr);
@@ -263,13 +292,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 if (tile_row < BN) scale_s[tile_row] = (y0 + tile_row < M) ? row_scale_of(ep, y0 + tile_row, M) : 0.0f;
                 named_barrier_128();
             }
-            if (EPI == 2) {
+            if (EPI == 2 && staged) {
+                const int token = y0 + (tile_row >> 3), col = x0 + 16 * (tile_row & 7);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const bool inside = col + 4 * q + 4 <= N;
+                    res4[q] = (inside && token < M) ? *reinterpret_cast<const float4*>(ep.residual + (size_t)token * N + col + 4 * q)
+                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+                    norm4[q] = inside ? *reinterpret_cast<const float4*>(ep.norm_weight + col + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            } else if (EPI == 2) {
                 load_residual_column<BN>(ep, x0 + tile_row, y0, 0, M, N, res);
                 norm_w = x0 + tile_row < N ? ep.norm_weight[x0 + tile_row] : 0.0f;
             }
         }
         if (num_kb > 0) ok = mbar_wait(smem_addr(done_bar), 0);
         tc_fence_after();
+        if (tile_row == 0) gemm_stamp(ep, 3);
         if (splits > 1) {
             // store this CTA's partial tile into its slot in the first CTA (column-major: lanes side by side)
             const uint32_t slot = cluster_address(smem_addr(slots) + rank * (uint32_t)Smem::slot_bytes, 0);
@@ -290,6 +329,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         }
     }
     if (splits > 1) cluster_sync_all();  // every partial tile has arrived in the first CTA
+    if (threadIdx.x == 64) gemm_stamp(ep, 4);
 
     if (warp >= 2 && rank == 0) {
         const int x_row = x0 + tile_row;  // row of X that this thread holds
@@ -325,31 +365,52 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] *= SWAP ? scale_s[c0 + j] : my_scale;
             }
+            if (tile_row == 0) gemm_stamp(ep, 6);
+            if (SWAP && staged) {
+                float* stage = reinterpret_cast<float*>(smem);  // every product has read the ring: it is free
+                if (EPI == 1) {
+                    // this lane holds weight row x_row: rows 16k..16k+7 are gate rows, 16k+8..16k+15 their up rows
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float out = silu_mul(v[j], __shfl_xor_sync(0xffffffffu, v[j], 8));
+                        if ((lane & 8) == 0) stage[(c0 + j) * 132 + (tile_row >> 4) * 8 + (tile_row & 7)] = out;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) stage[(c0 + j) * 132 + tile_row] = v[j];
+                }
+                continue;
+            }
             if (EPI == 2 && SWAP) {
-                // this lane holds output column x_row of tokens y0 + c0 .. + 15
+                // this lane holds output column x_row of tokens y0 + c0 .. + 15.  The squares of the sums go to shared
+                // memory (the ring is idle: every product has read it), token by token, 132 floats to a token; they
+                // are added up after the loop.  (Sixteen warp reductions here, one after the other, took 2 us.)
+                float* sq_s = reinterpret_cast<float*>(smem);
+                const bool row_ok = x_row < x_rows;
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int y = y0 + c0 + j;
-                    float sq = 0.0f;
-                    if (x_row < x_rows && y < y_rows) {
-                        const float r = res[j] + v[j];
+                    const bool live = row_ok && y < y_rows;
+                    const float r = res[j] + v[j];
+                    if (live) {
                         ep.residual[(size_t)y * N + x_row] = r;
                         C[(size_t)y * ldc + x_row] = from_f32<OutT>(r * norm_w);
-                        sq = r * r;
                     }
-                    sq = warp_sum(sq);
-                    if (lane == 0) sumsq_s[lane_group * BN + c0 + j] = sq;
+                    sq_s[(c0 + j) * 132 + tile_row] = live ? r * r : 0.0f;
                 }
                 continue;
             }
             if (EPI == 1 && SWAP) {
                 // this lane holds weight row x_row: rows 16k..16k+7 are gate rows, 16k+8..16k+15 their up rows
+                float out[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const float partner = __shfl_xor_sync(0xffffffffu, v[j], 8);
-                    const int y = y0 + c0 + j;
-                    if ((lane & 8) == 0 && x_row < x_rows && y < y_rows)
-                        C[(size_t)y * ldc + (x_row >> 4) * 8 + (x_row & 7)] = from_f32<OutT>(silu_mul(v[j], partner));
+                for (int j = 0; j < 16; ++j) out[j] = silu_mul(v[j], __shfl_xor_sync(0xffffffffu, v[j], 8));
+                if ((lane & 8) == 0 && x_row < x_rows) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int y = y0 + c0 + j;
+                        if (y < y_rows) C[(size_t)y * ldc + (x_row >> 4) * 8 + (x_row & 7)] = from_f32<OutT>(out[j]);
+                    }
                 }
                 continue;
             }
@@ -400,17 +461,104 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 }
             }
         }
-        if (EPI == 2 && SWAP) {
-            // this tile's share of each token's sum of squares: the four warps' parts, added in order
+        if (tile_row == 0) gemm_stamp(ep, 7);
+        if (SWAP && staged) {
             named_barrier_128();
-            if (tile_row < BN && y0 + tile_row < M)
-                ep.sumsq_out[(size_t)blockIdx.x * M + y0 + tile_row] =
-                    (sumsq_s[tile_row] + sumsq_s[BN + tile_row]) + (sumsq_s[2 * BN + tile_row] + sumsq_s[3 * BN + tile_row]);
+            const float* stage = reinterpret_cast<const float*>(smem);
+            const int part = tile_row & 7;
+#pragma unroll 1
+            for (int base = 0; base < BN; base += 16) {
+                if (y0 + base >= y_rows) break;  // uniform
+                const int local = base + (tile_row >> 3), token = y0 + local;
+                if (EPI == 1) {
+                    // 64 outputs a token: eight to a thread
+                    const int col = (x0 >> 1) + 8 * part;
+                    if (token < y_rows && col + 8 <= (N >> 1)) {
+                        const float4 a = *reinterpret_cast<const float4*>(stage + local * 132 + 8 * part);
+                        const float4 b = *reinterpret_cast<const float4*>(stage + local * 132 + 8 * part + 4);
+                        __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w);
+                        __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
+                        *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(C) + (size_t)token * ldc + col) =
+                            make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
+                                       *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+                    }
+                    continue;
+                }
+                const int col = x0 + 16 * part;
+                float4 value[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) value[q] = *reinterpret_cast<const float4*>(stage + local * 132 + 16 * part + 4 * q);
+                float sq = 0.0f;
+                if (EPI == 2) {
+                    if (base > 0) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            res4[q] = (col + 4 * q + 4 <= N && token < M)
+                                          ? *reinterpret_cast<const float4*>(ep.residual + (size_t)token * N + col + 4 * q)
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        float4 sum = res4[q];
+                        sum.x += value[q].x, sum.y += value[q].y, sum.z += value[q].z, sum.w += value[q].w;
+                        if (token < M && col + 4 * q + 4 <= N) {
+                            *reinterpret_cast<float4*>(ep.residual + (size_t)token * N + col + 4 * q) = sum;
+                            sq += (sum.x * sum.x + sum.y * sum.y) + (sum.z * sum.z + sum.w * sum.w);
+                        }
+                        value[q] = make_float4(sum.x * norm4[q].x, sum.y * norm4[q].y, sum.z * norm4[q].z, sum.w * norm4[q].w);
+                    }
+                }
+                if (token < y_rows) {
+                    if (sizeof(OutT) == 2) {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            if (col + 8 * h + 8 <= N) {
+                                const float4 a = value[2 * h], b = value[2 * h + 1];
+                                __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w);
+                                __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
+                                *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(C) + (size_t)token * ldc + col + 8 * h) =
+                                    make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
+                                               *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            if (col + 4 * q + 4 <= N)
+                                *reinterpret_cast<float4*>(reinterpret_cast<float*>(C) + (size_t)token * ldc + col + 4 * q) = value[q];
+                    }
+                }
+                if (EPI == 2) {
+                    // this tile's share of the token's sum of squares: its eight threads, in a fixed order
+                    sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+                    sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+                    sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+                    if (part == 0 && token < M) ep.sumsq_out[(size_t)blockIdx.x * M + token] = sq;
+                }
+            }
+        } else if (EPI == 2 && SWAP) {
+            // this tile's share of each token's sum of squares: eight lanes add a token's 128 squares, sixteen each
+            // (rotated so that the 32 lanes of a warp read 32 banks), in a fixed order
+            named_barrier_128();
+            const float* sq_s = reinterpret_cast<const float*>(smem);
+            const int part = tile_row & 7;
+#pragma unroll 1
+            for (int base = 0; base < BN; base += 16) {
+                const int j = base + (tile_row >> 3);
+                float sum = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) sum += sq_s[j * 132 + part * 16 + ((i + (part >> 1)) & 15)];
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+                if (part == 0 && y0 + j < M) ep.sumsq_out[(size_t)blockIdx.x * M + y0 + j] = sum;
+            }
         }
     }
     if (!ok) atomicExch(error_flag, 4);
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) gemm_stamp(ep, 5);
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, tmem_columns<BN>());
@@ -802,6 +950,33 @@ static bool deep_rings() {
     return on;
 }
 
+// How many clusters of (1, 1, cluster_z) CTAs of `kernel` the device can hold at once, by its own account; asked once
+// per kernel, shared-memory size and cluster size.  A failed query counts as "all fit".
+template <typename Kernel>
+static long max_resident_clusters(Kernel kernel, int smem_bytes, int cluster_z) {
+    static std::mutex mutex;
+    static std::map<std::tuple<const void*, int, int>, long> known;
+    const auto key = std::make_tuple((const void*)kernel, smem_bytes, cluster_z);
+    std::lock_guard<std::mutex> lock(mutex);
+    auto found = known.find(key);
+    if (found != known.end()) return found->second;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(1, 1, (unsigned)cluster_z);
+    config.blockDim = dim3(GEMM_THREADS);
+    config.dynamicSmemBytes = (size_t)smem_bytes;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = 1, attribute.val.clusterDim.y = 1, attribute.val.clusterDim.z = (unsigned)cluster_z;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    int clusters = 0;
+    long answer = 1L << 40;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) == cudaSuccess && clusters > 0) answer = clusters;
+    else cudaGetLastError();  // a failed query leaves no error behind
+    known.emplace(key, answer);
+    return answer;
+}
+
 template <int BN, bool SWAP, typename OutT, int EPI>
 static int launch_config(const void* A, const void* W, bool tiled, void* C, int M, int N, int K, long lda, long ldc,
                          int splits, const Epilogue& ep, int* error_flag, cudaStream_t stream) {
@@ -819,27 +994,39 @@ static int launch_config(const void* A, const void* W, bool tiled, void* C, int 
     if (splits < 1) splits = 1;
     if (splits > Smem::max_splits) splits = Smem::max_splits;  // slots in the first CTA's shared memory
     if (splits > total_k_blocks) splits = total_k_blocks;
-    const int per_split = (total_k_blocks + splits - 1) / splits;
-    splits = (total_k_blocks + per_split - 1) / per_split;
-    dim3 grid((unsigned)((x_rows + GEMM_BM - 1) / GEMM_BM), (unsigned)((y_rows + BN - 1) / BN), (unsigned)splits);
-    if (grid.y > 65535) return KIRAI_ERR_BAD_SIZE;
     const uint8_t* boxes = tiled ? (const uint8_t*)W : (const uint8_t*)nullptr;
-    if constexpr (BN <= 32) {
-        // no more CTAs than SMs: one CTA per SM with the long ring (KIRAI_GEMM_DEEP=0 keeps the short one, to compare)
-        if ((long)grid.x * grid.y * grid.z <= sm_count() && deep_rings()) {
-            using Deep = GemmSmem<BN, true>;
-            auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT, EPI, true>;
-            cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Deep::total(Deep::max_splits));
-            if (err != cudaSuccess) return (int)err;
-            return launch_pdl(kernel, grid, dim3(GEMM_THREADS), (size_t)Deep::total(splits), stream, (unsigned)splits, map_x,
-                              map_y, boxes, (OutT*)C, M, N, K, ldc, per_split, splits, ep, error_flag);
+    // The CTAs of a tile are a cluster, and a cluster's CTAs must find room in one GPC at the same time: 48 clusters of
+    // 3 one-per-SM CTAs do not all fit a B200 (39 did; the other 9 started 7 us later, when the first had finished, and
+    // the q, k, v product of the 8B shape took 15 us in place of 9).  So the split count goes down until the device
+    // says that all clusters of the launch can be resident together.
+    for (;; --splits) {
+        const int per_split = (total_k_blocks + splits - 1) / splits;
+        const int used = (total_k_blocks + per_split - 1) / per_split;
+        dim3 grid((unsigned)((x_rows + GEMM_BM - 1) / GEMM_BM), (unsigned)((y_rows + BN - 1) / BN), (unsigned)used);
+        if (grid.y > 65535) return KIRAI_ERR_BAD_SIZE;
+        const long clusters = (long)grid.x * grid.y;
+        if constexpr (BN <= 32) {
+            // no more CTAs than SMs: one CTA per SM with the long ring (KIRAI_GEMM_DEEP=0 keeps the short one, to compare)
+            if (clusters * used <= sm_count() && deep_rings()) {
+                using Deep = GemmSmem<BN, true>;
+                auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT, EPI, true>;
+                cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Deep::total(Deep::max_splits));
+                if (err != cudaSuccess) return (int)err;
+                if (used > 1 && splits > 1 && clusters > max_resident_clusters(kernel, Deep::total(used), used)) continue;
+                return launch_pdl(kernel, grid, dim3(GEMM_THREADS), (size_t)Deep::total(used), stream, (unsigned)used, map_x,
+                                  map_y, boxes, (OutT*)C, M, N, K, ldc, per_split, used, ep, error_flag);
+            }
         }
+        auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT, EPI, false>;
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total(Smem::max_splits));
+        if (err != cudaSuccess) return (int)err;
+        // launches of more CTAs than SMs run in waves anyway; only a launch meant to be one wave is fitted
+        if (used > 1 && splits > 1 && clusters * used <= 2L * sm_count() &&
+            clusters > max_resident_clusters(kernel, Smem::total(used), used))
+            continue;
+        return launch_pdl(kernel, grid, dim3(GEMM_THREADS), (size_t)Smem::total(used), stream, (unsigned)used, map_x, map_y,
+                          boxes, (OutT*)C, M, N, K, ldc, per_split, used, ep, error_flag);
     }
-    auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT, EPI, false>;
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total(Smem::max_splits));
-    if (err != cudaSuccess) return (int)err;
-    return launch_pdl(kernel, grid, dim3(GEMM_THREADS), (size_t)Smem::total(splits), stream, (unsigned)splits, map_x, map_y,
-                      boxes, (OutT*)C, M, N, K, ldc, per_split, splits, ep, error_flag);
 }
 
 // Split count for the swapped (few tokens) case, which is bound by the weight
@@ -892,6 +1079,11 @@ KIRAI_EXPORT long kirai_gemm_bf16_tiled_bytes(int N, int K) {
     return (long)((N + GEMM_BM - 1) / GEMM_BM) * ((K + GEMM_BK - 1) / GEMM_BK) * GEMM_BOX_BYTES;
 }
 
+// Measurements: while a buffer is set, every launch of the streaming kernel writes its CTAs' clock stamps (see
+// gemm_stamp) to the next 8 * 1,024 words of it.  Null (the default) switches the stamps off.
+static unsigned long long* g_gemm_stamps = nullptr;
+KIRAI_EXPORT void kirai_gemm_bf16_set_stamps(unsigned long long* buffer) { g_gemm_stamps = buffer; }
+
 // The one entry point of the tensor-core product, A[M, K] (row stride lda) times W[N, K] transposed.
 //   tiled:  W is in the tiled form described at the top of this file, else row-major.
 //   form 0: C[M, N] bf16.  1: C[M, N] float.  2: C[M, N / 2] = silu(gate) * up, W's rows in groups of 8 gate rows
@@ -904,7 +1096,8 @@ KIRAI_EXPORT int kirai_gemm_bf16_general(const void* A, const void* W, int tiled
                                          long ldc, int splits, int form, const float* row_sumsq, int row_parts,
                                          float row_count, float row_eps, float* residual, const float* norm_weight,
                                          float* sumsq_out, int* error_flag, cudaStream_t stream) {
-    Epilogue ep{row_sumsq, row_sumsq ? row_parts : 0, row_count, row_eps, nullptr, nullptr, nullptr};
+    Epilogue ep{row_sumsq, row_sumsq ? row_parts : 0, row_count, row_eps, nullptr, nullptr, nullptr, g_gemm_stamps};
+    if (g_gemm_stamps) g_gemm_stamps += 8 * 1024;  // the next launch's stamps follow (up to 1,024 CTAs a launch)
     if (row_sumsq && row_parts <= 0) return KIRAI_ERR_BAD_SIZE;
     switch (form) {
         case 0: return gemm_dispatch<bf16, 0>(A, W, tiled != 0, C, M, N, K, lda, ldc, splits, ep, error_flag, stream);
