@@ -50,7 +50,10 @@ using namespace sm100;
 // there are fewer tiles than two waves (but see DEEP below); the many-token case takes as many stages as fit.
 // DEEP (weight-streaming case, BN <= 32): a launch with no more CTAs than SMs gains nothing from a second CTA per
 // SM; its CTAs take a longer ring instead, because 4 stages of 16 KB in each of 128 CTAs are 8 MB in flight, fewer
-// than the memory system needs to run at its rate (about 1.5 us of latency x 6.4 TB/s).
+// than the memory system needs to run at its rate (about 1.5 us of latency x 6.4 TB/s).  Ten stages for up to 16
+// tokens (the 96 CTAs of the 8B shape's q, k, v product then stream at the memory's rate: 7 stages 9.5 us, 10 stages 8.5).
+// Tried on top of this and taken out: the partial tiles of a cluster row by row, sent with 16-byte stores (no faster:
+// what the first CTA waits for at the end of a split product is the slowest of its cluster, not the stores).
 template <int BN, bool DEEP = false>
 struct GemmSmem {
     static constexpr bool streaming = BN <= 64;
@@ -59,9 +62,9 @@ struct GemmSmem {
     static constexpr int stage_bytes = x_bytes + y_bytes;
     static constexpr int max_splits = BN <= 64 ? 4 : 1;  // up to 128 KB of slots beside the 96 KB ring
     static constexpr int slot_bytes = BN * GEMM_BM * 4;  // one 32-bit partial tile
-    static constexpr int stages = streaming ? (DEEP ? (BN <= 16 ? 7 : 6) : 4) : (200 * 1024 / stage_bytes);
-    static constexpr int barrier_bytes = 2048;  // barriers [0, 128), row scales [128, 384), partial sums of squares [512, 1536)
-    static_assert(!streaming || (2 * stages + 1) * 8 + 4 <= 128, "the streaming kernel's barriers must end before the row scales");
+    static constexpr int stages = streaming ? (DEEP ? (BN <= 16 ? 10 : 7) : 4) : (200 * 1024 / stage_bytes);
+    static constexpr int barrier_bytes = 2048;  // barriers [0, 256), row scales [256, 512), partial sums of squares [512, 1536)
+    static_assert(!streaming || (2 * stages + 1) * 8 + 4 <= 256, "the streaming kernel's barriers must end before the row scales");
     static_assert(!DEEP || BN <= 32, "the long ring is for the smallest tiles");
     static constexpr int ctas_per_sm = streaming && !DEEP ? 2 : 1;
     static constexpr int total(int splits) {  // + slack to align the base to 1024 bytes
@@ -168,7 +171,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + STAGES * Smem::stage_bytes);
-    float* scale_s = reinterpret_cast<float*>(smem + STAGES * Smem::stage_bytes + 128);   // [BN] row scales of this tile's tokens
+    float* scale_s = reinterpret_cast<float*>(smem + STAGES * Smem::stage_bytes + 256);   // [BN] row scales of this tile's tokens
     float* sumsq_s = reinterpret_cast<float*>(smem + STAGES * Smem::stage_bytes + 512);   // [4 warps][BN]
     float* slots = reinterpret_cast<float*>(smem + STAGES * Smem::stage_bytes + Smem::barrier_bytes);  // [splits][BN][128], used in the first CTA
     uint64_t* full_bar = bars;                 // [STAGES] TMA -> MMA
