@@ -566,7 +566,20 @@ struct DecodeArgs {
     const float* inv_freq;
     float eps;
     bf16* cache;
+    unsigned long long* stamps;  // null, or [CTAs][8] clock stamps (ns) of the decode kernel, for measurements
 };
+
+// Clock stamps of one CTA of the decode kernel (split form), written only when a buffer is given: 0 the CTA starts,
+// 1 the kernel before has finished, 2 the queries are in shared memory, 3 the warps have attended their tiles,
+// 4 the CTA's result is merged, 5 the cluster has met, 6 the output rows are stored.
+__device__ __forceinline__ void decode_stamp(const DecodeArgs& args, int which) {
+    if (args.stamps && threadIdx.x == 0) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        const size_t cta = ((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        args.stamps[cta * 8 + which] = now;
+    }
+}
 
 // Per-head RMSNorm and half-split rotation of the sixteen values that a lane holds of one head (eight adjacent values of
 // each half; LANES = D / 16 lanes share a head), the arithmetic of qk_norm_rope_kv_write_wide_kernel in elementwise.cu:
@@ -736,6 +749,7 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
             }
         }
         pdl_wait();  // the queries, and the new token's key and value, are complete and visible
+        decode_stamp(args, 1);
     }
     // the query rows (the group's heads), zero beyond the group and beyond head_dim
     if (args.fuse) {
@@ -771,6 +785,7 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
         }
     }
     __syncthreads();
+    decode_stamp(args, 2);
 
     constexpr int MS = D + 2;
     if (HEADS) {
@@ -804,6 +819,7 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
         }
         if (!ok && lane == 0) atomicExch(args.error_flag, 4);
         __syncthreads();  // every warp is done with its ring: it becomes the merge buffer
+        decode_stamp(args, 3);
         const int g = lane >> 2, t = lane & 3;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -947,6 +963,7 @@ __global__ void __launch_bounds__(DecodeTile<D>::WARPS * 32)
 attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs args, bf16* __restrict__ out,
                         float* __restrict__ partial, const int* __restrict__ context_len, int num_splits) {
     pdl_launch_dependents();
+    decode_stamp(args, 0);
     using Smem = DecodeSmem<D>;
     constexpr int BN = Smem::BN;
     extern __shared__ uint8_t smem_raw[];
@@ -969,7 +986,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs a
         const int stride = args.head_dim + 2;
         decode_attend_range<D, HEADS>(kv_map, args, smem, req, kv_head, pos, key_lo, last_tile, t_begin, t_end, 0, true, out,
                                       exchange, (long)stride);
+        decode_stamp(args, 4);
         decode_cluster_sync();  // every range's result is in its CTA's buffer
+        decode_stamp(args, 5);
         const uint32_t base = sm100::smem_addr(exchange);
         const int head_dim = args.head_dim, total = group * head_dim;
         for (int e = split + num_splits * (int)threadIdx.x; e < total; e += num_splits * (int)blockDim.x) {
@@ -994,6 +1013,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs a
             }
             out[((size_t)req * args.q_heads + kv_head * group + row) * head_dim + col] = from_f32<bf16>(l_all > 0.0f ? acc / l_all : 0.0f);
         }
+        decode_stamp(args, 6);
         decode_cluster_sync();  // nobody leaves while its buffer may still be read
         return;
     }
@@ -1186,6 +1206,10 @@ __global__ void attention_merge_splits_kernel(const float* __restrict__ partial,
     }
 }
 
+// Measurements: while a buffer is set, every launch of the split decode kernel writes its CTAs' clock stamps (see
+// decode_stamp) to the next 8 * 1,024 words of it.  Null (the default) switches the stamps off.
+unsigned long long* g_decode_stamps = nullptr;
+
 // What the decode kernels need to prepare queries and the new token's key themselves (see DecodeArgs).
 struct FuseQK {
     const float* q_weight;
@@ -1241,6 +1265,8 @@ int decode_launch(const void* q, const void* cache, void* out, float* partial, c
         args.fuse = 1, args.q_weight = fuse->q_weight, args.k_weight = fuse->k_weight, args.inv_freq = fuse->inv_freq;
         args.eps = fuse->eps, args.cache = (bf16*)const_cast<void*>(cache);
     }
+    args.stamps = g_decode_stamps;
+    if (g_decode_stamps) g_decode_stamps += 8 * 1024;  // the next launch's stamps follow
     dim3 grid(num_splits, kv_heads, requests);
     if (cluster)
         return launch_pdl_cluster(kernel, grid, dim3(Smem::DC_WARPS * 32), (size_t)Smem::total, stream, dim3(num_splits, 1, 1),
@@ -1416,6 +1442,8 @@ KIRAI_EXPORT int kirai_attention_decode_balanced_qk_bf16(const void* qkv, void* 
 #undef KIRAI_DCBQ
     return KIRAI_ERR_UNSUPPORTED;
 }
+
+KIRAI_EXPORT void kirai_attention_decode_set_stamps(unsigned long long* buffer) { g_decode_stamps = buffer; }
 
 // ----------------------------------------------------- decode without allocation
 // The same decode kernels, with the splits' partial results in a file-scope device array
