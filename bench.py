@@ -177,6 +177,74 @@ def generate_workload(which: str) -> int:
     return 0
 
 
+def decode_stamps(batch: int, context: int, layers: int) -> int:
+    """Clock stamps of the kernels of one captured decode step: every CTA of the weight-streaming products and of the
+    decode attention writes %globaltimer at a few places (csrc/gemm_tcgen05.cu::gemm_stamp, csrc/attention_mma.cu::
+    decode_stamp) while a buffer is set.  Prints, per kernel of the second layer, first CTA .. last CTA in us after the
+    kernel before had finished.  A measurement aid: the stamps cost a little time themselves."""
+    import ctypes
+
+    import torch
+
+    import kirai_b200  # noqa: F401
+    from kirai_b200 import Engine
+    from kirai_b200.csrc import ops
+    from kirai_b200.engine.batch import StepEntry
+    from kirai_b200.registry import config_from_dict
+
+    raw = dict(QWEN3_8B)
+    raw["num_hidden_layers"] = layers
+    engine = Engine(config=config_from_dict(raw), random_weights_seed=2, dtype="bfloat16", page_size=16, max_new_tokens=512,
+                    max_prefill_tokens=2048, max_concurrent_requests=batch, max_cache_tokens=batch * (context + 256))
+    runner, cache = engine.runner, engine.runner.cache
+    generator = torch.Generator().manual_seed(1)
+    requests = [cache.open(i) for i in range(batch)]
+    for request in requests:
+        prompt = torch.randint(0, raw["vocab_size"], (context - 40,), generator=generator).tolist()
+        for first in range(0, len(prompt), 2048):
+            runner.step([StepEntry(request, prompt[first : first + 2048], [])], check_errors=False)
+    for request in requests:
+        assert cache.reserve(request, 32)
+    tables = [cache.block_table_array(requests, g) for g in range(len(cache.groups))]
+    graph, _ = engine.graphs.get(batch, max(t.shape[1] for t in tables), [r.length + 1 for r in requests])
+    graph.load_inputs([1] * batch, [r.length for r in requests], [r.slot for r in requests], tables, [0.0] * batch, [1.0] * batch, [0.0] * batch)
+    products = layers * 4 + 1  # per step: q/k/v, o, gate/up, down of every layer, and the output head
+    gemm = torch.zeros((2 * products + 2) * 8192, dtype=torch.int64, device="cuda:0")
+    attention = torch.zeros((2 * layers + 2) * 8192, dtype=torch.int64, device="cuda:0")
+    lib = ops.library()
+    lib.kirai_gemm_bf16_set_stamps(ctypes.c_void_p(gemm.data_ptr()))
+    lib.kirai_attention_decode_set_stamps(ctypes.c_void_p(attention.data_ptr()))
+    graph.capture()  # a warm run, then the capture: the captured launches write to the second half of the buffers
+    lib.kirai_gemm_bf16_set_stamps(ctypes.c_void_p(0))
+    lib.kirai_attention_decode_set_stamps(ctypes.c_void_p(0))
+    for _ in range(5):
+        graph.replay()
+    torch.cuda.synchronize()
+    ops.check_device_errors(runner.rt.device)
+
+    def show(name, stamps, columns):
+        stamps = stamps[stamps[:, 0] > 0]
+        if not len(stamps):
+            print(f"{name:10s} no stamps (another kernel variant ran)")
+            return
+        relative = (stamps - stamps[:, 1].min()) / 1e3
+        cells = []
+        for index, label in columns:
+            seen = relative[:, index][stamps[:, index] > 0]
+            if len(seen):
+                cells.append(f"{label} {float(seen.min()):6.2f} .. {float(seen.max()):6.2f}")
+        print(f"{name:10s} {len(stamps):4d} CTAs | " + " | ".join(cells))
+
+    gemm_columns = [(0, "start"), (2, "first stage"), (3, "products done"), (4, "cluster met"), (6, "tiles summed"), (7, "values stored"), (5, "end")]
+    attention_columns = [(0, "start"), (2, "queries in"), (3, "attended"), (4, "merged"), (5, "cluster met"), (6, "stored")]
+    per_launch = gemm[products * 8192 :].view(-1, 1024, 8).cpu().double()
+    names = ["q/k/v", "o", "gate/up", "down"]
+    show("attention", attention[layers * 8192 :].view(-1, 1024, 8).cpu().double()[1], attention_columns)
+    for index, name in enumerate(names):
+        show(name if index else "q/k/v next", per_launch[4 + (index or 4)], gemm_columns)
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -191,11 +259,13 @@ def main() -> int:
     parser.add_argument("--points", default="1,64", help="other decode batches to measure (comma separated, '' for none)")
     parser.add_argument("--no-check", action="store_true",
                         help="skip the check of the captured decode step against the step function before each timing")
-    parser.add_argument("--workload", default="decode", choices=["decode", "serving-4b", "batch-32b"],
+    parser.add_argument("--workload", default="decode", choices=["decode", "serving-4b", "batch-32b", "decode-stamps"],
                         help="decode: the contract's measurement (default).  serving-4b: 64 requests with prompts of "
                              "128..4096 tokens, 512-token prefill portions mixed with decode, 256 new tokens each, greedy, "
                              "Qwen3-4B shape.  batch-32b: 16 requests of 8,064 prompt tokens, 128 new tokens at temperature 1, "
-                             "Qwen3-32B shape.  Both run through Engine.generate and print their own one line.")
+                             "Qwen3-32B shape.  Both run through Engine.generate and print their own one line.  decode-stamps: "
+                             "the kernels' own clock stamps inside one captured decode step (--batch, --context, --layers; "
+                             "4 layers are enough), a table instead of the JSON line.")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -207,6 +277,8 @@ def main() -> int:
         return 2
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
+    if args.workload == "decode-stamps":
+        return decode_stamps(args.batch, args.context, min(args.layers, 4) if args.layers == QWEN3_8B["num_hidden_layers"] else args.layers)
     if args.workload != "decode":
         return generate_workload(args.workload)
 
