@@ -138,6 +138,15 @@ def wait_selftest(device: torch.device, limit: int = 10_000, arrive: bool = Fals
     return int(polls.item())
 
 
+def stream_read(data: torch.Tensor) -> None:
+    """Reads ``data`` (a multiple of 16 KB) once, one CTA per SM, with bulk copies into shared memory, and drops it: a
+    measurement of what a read-only stream reaches on this device (time it with CUDA events)."""
+    _need_cuda(data)
+    assert data.is_contiguous() and (data.numel() * data.element_size()) % 16384 == 0
+    _call("kirai_stream_read", _ptr(data), _l(data.numel() * data.element_size()), _i(sm_count(data.device)),
+          _ptr(error_flag(data.device)), _stream())
+
+
 # ------------------------------------------------------------------- embedding
 def embedding(table, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Rows ``ids`` of ``table`` [V, H] (a tensor, or a ``TiledWeight`` shared with the output head) widened to

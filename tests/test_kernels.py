@@ -338,6 +338,16 @@ def test_decode_attention_that_prepares_its_queries_and_keys(ops, monkeypatch, b
         assert float(got.float().abs().max()) > 0.01
 
 
+def test_read_only_stream_kernel_runs_and_reports_nothing(ops):
+    """The kernel that measures what a read-only stream reaches: whole 16 KB boxes only, no error word."""
+    data = torch.zeros(37 * 16384, dtype=torch.uint8, device=DEV)  # fewer boxes than SMs: some CTAs have nothing to read
+    ops.stream_read(data)
+    ops.stream_read(torch.zeros(1000 * 16384, dtype=torch.uint8, device=DEV))
+    ops.check_device_errors(torch.device(DEV))
+    with pytest.raises(AssertionError):
+        ops.stream_read(torch.zeros(1000, dtype=torch.uint8, device=DEV))
+
+
 def test_sampler_on_the_cases_of_the_reference(ops):
     """crates/llm-sampler/src/lib.rs:222-294 through the device sampler, all rows in one launch: greedy, the first of
     equal maxima, a draw inside the nucleus, and ties inside the nucleus taken in index order."""
@@ -626,6 +636,16 @@ def test_decode_attention_that_prepares_its_queries_and_keys(ops, monkeypatch, b
         assert torch.equal(fused_cache, separate_cache)         # the same key and value rows, in the same places
         assert torch.equal(got, expected)
         assert float(got.float().abs().max()) > 0.01
+
+
+def test_read_only_stream_kernel_runs_and_reports_nothing(ops):
+    """The kernel that measures what a read-only stream reaches: whole 16 KB boxes only, no error word."""
+    data = torch.zeros(37 * 16384, dtype=torch.uint8, device=DEV)  # fewer boxes than SMs: some CTAs have nothing to read
+    ops.stream_read(data)
+    ops.stream_read(torch.zeros(1000 * 16384, dtype=torch.uint8, device=DEV))
+    ops.check_device_errors(torch.device(DEV))
+    with pytest.raises(AssertionError):
+        ops.stream_read(torch.zeros(1000, dtype=torch.uint8, device=DEV))
 
 
 def test_sampler_on_the_cases_of_the_reference(ops):
