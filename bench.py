@@ -236,7 +236,7 @@ def decode_stamps(batch: int, context: int, layers: int) -> int:
         print(f"{name:10s} {len(stamps):4d} CTAs | " + " | ".join(cells))
 
     gemm_columns = [(0, "start"), (2, "first stage"), (3, "products done"), (4, "cluster met"), (6, "tiles summed"), (7, "values stored"), (5, "end")]
-    attention_columns = [(0, "start"), (2, "queries in"), (3, "attended"), (4, "merged"), (5, "cluster met"), (6, "stored")]
+    attention_columns = [(0, "start"), (2, "queries in"), (3, "attended"), (4, "merged and stored")]
     per_launch = gemm[products * 8192 :].view(-1, 1024, 8).cpu().double()
     names = ["q/k/v", "o", "gate/up", "down"]
     show("attention", attention[layers * 8192 :].view(-1, 1024, 8).cpu().double()[1], attention_columns)

@@ -541,7 +541,8 @@ struct DecodeSmem {
     static constexpr int table_entries = 1024;  // block-table entries kept in shared memory (longer ranges read global memory)
     static constexpr int prefix_entries = 1025;  // balanced kernel: where each request's tiles start (up to 1,024 requests)
     static constexpr int rope_offset = body + DC_WARPS * DC_STAGES * 8 + table_entries * 4 + prefix_entries * 4 + 12;  // 16-byte aligned
-    static constexpr int rope_bytes = D * 4;  // fused q/k preparation: cos [D / 2], sin [D / 2] of the request's position
+    // fused q/k preparation: cos [D / 2], sin [D / 2] of the request's position, then the q and the k norm's weights [D] each
+    static constexpr int rope_bytes = 3 * D * 4;
     static_assert(rope_offset % 16 == 0, "the cosines are read in 16-byte pieces");
     static constexpr int total = rope_offset + rope_bytes + 1024;  // + slack to align to 1024
 };
@@ -571,7 +572,7 @@ struct DecodeArgs {
 
 // Clock stamps of one CTA of the decode kernel (split form), written only when a buffer is given: 0 the CTA starts,
 // 1 the kernel before has finished, 2 the queries are in shared memory, 3 the warps have attended their tiles,
-// 4 the CTA's result is merged, 5 the cluster has met, 6 the output rows are stored.
+// 4 the CTA's result is merged and stored.
 __device__ __forceinline__ void decode_stamp(const DecodeArgs& args, int which) {
     if (args.stamps && threadIdx.x == 0) {
         unsigned long long now;
@@ -643,7 +644,7 @@ __device__ __forceinline__ void st_shared_16(uint32_t address, const uint4& v) {
 // The new token's key (normed, rotated) and value into row `pos % BN` of the tile at k_s / v_s, which TMA has just
 // filled from the pages, and into the token's page.  Called by the whole warp that is about to attend that tile.
 template <int D, int BN>
-__device__ __forceinline__ void append_new_token(const DecodeArgs& args, const float* rope_s, const int* table, int req,
+__device__ __forceinline__ void append_new_token(const DecodeArgs& args, const float* rope_s, const float* k_weight, const int* table, int req,
                                                  int kv_head, int pos, uint32_t k_s, uint32_t v_s, int lane) {
     constexpr int LANES = D / 16;
     const int row = pos % BN;
@@ -665,7 +666,7 @@ __device__ __forceinline__ void append_new_token(const DecodeArgs& args, const f
         lo = xk[lane];
         hi = xk[lane + LANES];
     }
-    prepare_head<D>(lo, hi, args.k_weight, rope_s, args.inv_freq != nullptr, args.eps, lane % LANES);
+    prepare_head<D>(lo, hi, k_weight, rope_s, args.inv_freq != nullptr, args.eps, lane % LANES);
     if (k_live) {
         st_shared_16(k_s + tile_offset<BN>(row, lane), lo);
         st_shared_16(k_s + tile_offset<BN>(row, lane + LANES), hi);
@@ -708,25 +709,54 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
     uint64_t* bars = (uint64_t*)(smem + Smem::body) + warp * DC_STAGES;
     float* merge = reinterpret_cast<float*>(smem + Smem::q_bytes);  // [warps][16][D + 2], over the ring
 
-    // The pages of this range's keys: copied to shared memory once, because a lookup in global memory
-    // for every tile would put its latency in front of every TMA issue.
+    // What the set-up reads from global memory (block table, rotation frequencies, norm weights) is constant during a
+    // step and is asked for in one go, before anything waits for any of it: a CTA that starts late (its SM was busy
+    // with the kernel before) has these round trips in front of its first key tile, one after the other if each
+    // load waited for the one before.
+    constexpr int THREADS = DC_WARPS * 32;
+    constexpr int PER_THREAD = (D + THREADS - 1) / THREADS;
+    float* rope_s = reinterpret_cast<float*>(smem + Smem::rope_offset);
+    float* q_weight_s = args.q_weight ? rope_s + D : nullptr;
+    float* k_weight_s = args.k_weight ? rope_s + 2 * D : nullptr;
+    const bool rotate = args.fuse && args.inv_freq;
+    float freq[PER_THREAD], wq[PER_THREAD], wk[PER_THREAD];
+#pragma unroll
+    for (int i = 0; i < PER_THREAD; ++i) {
+        const int d = tid + i * THREADS;
+        freq[i] = rotate && d < D / 2 ? args.inv_freq[d] : 0.0f;
+        wq[i] = args.fuse && first && q_weight_s && d < D ? args.q_weight[d] : 0.0f;
+        wk[i] = args.fuse && first && k_weight_s && d < D ? args.k_weight[d] : 0.0f;
+    }
+    // The pages of this request's keys: copied to shared memory once, because a lookup in global memory for every
+    // tile would put its latency in front of every TMA issue.  A table that fits is copied whole, which needs no
+    // context length; of a longer one this range's part.
     const int* table = args.block_table + (long)req * table_width;
     {
         int* table_s = reinterpret_cast<int*>(smem + Smem::body + DC_WARPS * DC_STAGES * 8);
-        const int first_page = (t_begin * BN) / page_size;
-        const int last_page = min(table_width - 1, (min(t_end, last_tile + 1) * BN - 1) / page_size);
-        if (last_page - first_page < Smem::table_entries) {
-            for (int i = first_page + tid; i <= last_page; i += DC_WARPS * 32) table_s[i - first_page] = table[i];
-            table = table_s - first_page;
-            __syncthreads();
+        if (table_width <= Smem::table_entries) {
+            for (int i = tid; i < table_width; i += THREADS) table_s[i] = table[i];
+            table = table_s;
+        } else {
+            const int first_page = (t_begin * BN) / page_size;
+            const int last_page = min(table_width - 1, (min(t_end, last_tile + 1) * BN - 1) / page_size);
+            if (last_page - first_page < Smem::table_entries) {
+                for (int i = first_page + tid; i <= last_page; i += THREADS) table_s[i - first_page] = table[i];
+                table = table_s - first_page;
+            }
         }
     }
     bool ok = true;
-    float* rope_s = reinterpret_cast<float*>(smem + Smem::rope_offset);
-    if (args.fuse && args.inv_freq) {
-        // the angles depend on the position only, which is constant during a step: before griddepcontrol.wait
-        for (int i = tid; i < D / 2; i += DC_WARPS * 32) sincosf((float)pos * args.inv_freq[i], &rope_s[D / 2 + i], &rope_s[i]);
+#pragma unroll
+    for (int i = 0; i < PER_THREAD; ++i) {
+        const int d = tid + i * THREADS;
+        // the angles depend on the position only
+        if (rotate && d < D / 2) sincosf((float)pos * freq[i], &rope_s[D / 2 + d], &rope_s[d]);
+        if (args.fuse && first && d < D) {
+            if (q_weight_s) q_weight_s[d] = wq[i];
+            if (k_weight_s) k_weight_s[d] = wk[i];
+        }
     }
+    __syncthreads();  // the table is in place (and, for the query rows further down, angles and weights)
     // Fills ring slot `slot` with key tile `t`.
     auto issue = [&](int t, int slot) {
         const uint32_t k_dst = ring + slot * 2 * Smem::tile_bytes;
@@ -734,7 +764,8 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
                                  table_width, args.num_pages, kv_heads, kv_head, page_size, args.box_rows, lane);
     };
 
-    // this warp's tiles: t_begin + warp, + DC_WARPS, ...; the ring runs DC_STAGES - 1 tiles ahead
+    // this warp's tiles: t_begin + warp, + DC_WARPS, ...; the ring holds DC_STAGES of them: a slot is asked for the tile
+    // DC_STAGES further on as soon as its tile has been attended
     const int my_first = t_begin + warp;
     const int my_count = my_first < t_end ? (t_end - my_first + DC_WARPS - 1) / DC_WARPS : 0;
     // Everything up to here read only what is constant during a step (context lengths, block tables).  Keys and
@@ -742,7 +773,7 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
     // this one has finished, all but the request's last tile, which holds the token that this step appends.
     uint32_t early = 0u;
     if (first) {
-        for (int k = 0; k < DC_STAGES - 1 && k < my_count; ++k) {
+        for (int k = 0; k < DC_STAGES && k < my_count; ++k) {
             if (my_first + k * DC_WARPS < last_tile) {
                 issue(my_first + k * DC_WARPS, (k_base + k) % DC_STAGES);
                 early |= 1u << k;
@@ -757,7 +788,6 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
         constexpr int CH = D / 8, LANES = D / 16, HEADS_PER_WARP = 32 / LANES;
         for (int id = tid; id < (16 - group) * CH; id += DC_WARPS * 32)
             *reinterpret_cast<uint4*>(smem + tile_offset<16>(group + id / CH, id % CH)) = make_uint4(0u, 0u, 0u, 0u);
-        __syncthreads();  // the cosines and sines are in place
         for (int base = warp * HEADS_PER_WARP; base < group; base += DC_WARPS * HEADS_PER_WARP) {
             const int r = base + lane / LANES, sub = lane % LANES;
             const bool live = r < group;
@@ -767,7 +797,7 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
                 lo = x[sub];
                 hi = x[sub + LANES];
             }
-            prepare_head<D>(lo, hi, args.q_weight, rope_s, args.inv_freq != nullptr, args.eps, sub);
+            prepare_head<D>(lo, hi, q_weight_s, rope_s, args.inv_freq != nullptr, args.eps, sub);
             if (live) {
                 *reinterpret_cast<uint4*>(smem + tile_offset<16>(r, sub)) = lo;
                 *reinterpret_cast<uint4*>(smem + tile_offset<16>(r, sub + LANES)) = hi;
@@ -801,11 +831,9 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
         }
         HeadState<D> st;
         st.init();
-        for (int k = 0; k < DC_STAGES - 1 && k < my_count; ++k)
+        for (int k = 0; k < DC_STAGES && k < my_count; ++k)
             if (!((early >> k) & 1u)) issue(my_first + k * DC_WARPS, (k_base + k) % DC_STAGES);
         for (int k = 0; k < my_count; ++k) {
-            const int ahead = k + DC_STAGES - 1;
-            if (ahead < my_count) issue(my_first + ahead * DC_WARPS, (k_base + ahead) % DC_STAGES);
             const int slot = (k_base + k) % DC_STAGES;
             if (!sm100::mbar_wait(sm100::smem_addr(&bars[slot]), (uint32_t)((k_base + k) / DC_STAGES) & 1u)) {
                 ok = false;
@@ -813,9 +841,10 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
             }
             const uint32_t k_s = ring + slot * 2 * Smem::tile_bytes;
             if (args.fuse && my_first + k * DC_WARPS == last_tile)
-                append_new_token<D, BN>(args, rope_s, table, req, kv_head, pos, k_s, k_s + Smem::tile_bytes, lane);
+                append_new_token<D, BN>(args, rope_s, k_weight_s, table, req, kv_head, pos, k_s, k_s + Smem::tile_bytes, lane);
             warp_attend_heads<D, BN>(st, q_b, k_s, k_s + Smem::tile_bytes, (my_first + k * DC_WARPS) * BN, key_lo, pos, scale_log2, lane);
             __syncwarp();
+            if (k + DC_STAGES < my_count) issue(my_first + (k + DC_STAGES) * DC_WARPS, slot);
         }
         if (!ok && lane == 0) atomicExch(args.error_flag, 4);
         __syncthreads();  // every warp is done with its ring: it becomes the merge buffer
@@ -856,11 +885,9 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
     }
     WarpState<D> st;
     st.init();
-    for (int k = 0; k < DC_STAGES - 1 && k < my_count; ++k)
+    for (int k = 0; k < DC_STAGES && k < my_count; ++k)
             if (!((early >> k) & 1u)) issue(my_first + k * DC_WARPS, (k_base + k) % DC_STAGES);
     for (int k = 0; k < my_count; ++k) {
-        const int ahead = k + DC_STAGES - 1;
-        if (ahead < my_count) issue(my_first + ahead * DC_WARPS, (k_base + ahead) % DC_STAGES);
         const int slot = (k_base + k) % DC_STAGES;
         if (!sm100::mbar_wait(sm100::smem_addr(&bars[slot]), (uint32_t)((k_base + k) / DC_STAGES) & 1u)) {
             ok = false;
@@ -868,10 +895,11 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
         }
         const uint32_t k_s = ring + slot * 2 * Smem::tile_bytes;
         if (args.fuse && my_first + k * DC_WARPS == last_tile)
-            append_new_token<D, BN>(args, rope_s, table, req, kv_head, pos, k_s, k_s + Smem::tile_bytes, lane);
+            append_new_token<D, BN>(args, rope_s, k_weight_s, table, req, kv_head, pos, k_s, k_s + Smem::tile_bytes, lane);
         warp_attend<D, BN, 16, Q_IN_REGS>(st, q_smem, 0, q_regs, k_s, k_s + Smem::tile_bytes, (my_first + k * DC_WARPS) * BN, lo, hi,
                                           scale_log2, lane);
         __syncwarp();
+        if (k + DC_STAGES < my_count) issue(my_first + (k + DC_STAGES) * DC_WARPS, slot);
     }
     if (!ok && lane == 0) atomicExch(args.error_flag, 4);
     __syncthreads();  // every warp is done with its ring: it becomes the merge buffer
@@ -941,24 +969,12 @@ __device__ __forceinline__ void decode_init_barriers(uint8_t* smem) {
 // HEADS: the group has at most 8 heads and they are the MMA's columns (keys fill its rows);
 // otherwise the group's (at most 16) heads are the rows, as in the prompt kernel.
 // Grid (splits, kv_heads, requests): every request's keys are cut into the same number of ranges.
-// CLUSTER: the CTAs of one (request, kv head), one per range of keys, are a thread-block cluster (at most 8), and their
-// partial results meet in shared memory: every CTA leaves its group rows (unnormalised output, maximum, sum) in a
-// buffer of its own, the cluster synchronises, and each CTA merges a share of the output's elements from all the
-// buffers (distributed shared memory), in the order of the ranges and with the arithmetic of
-// attention_merge_splits_kernel, and stores them.  No partial result goes to global memory and no second kernel runs.
-__device__ __forceinline__ void decode_cluster_sync() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float ld_cluster_f32(uint32_t local_address, uint32_t rank) {
-    uint32_t remote;
-    float value;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(remote) : "memory");
-    return value;
-}
-#define DECODE_MAX_CLUSTER 8
-
-template <int D, bool HEADS, bool CLUSTER>
+// The ranges' partial results go through `partial` and attention_merge_splits_kernel.  (Merging them inside this
+// kernel was built twice and taken out again: as thread-block clusters through distributed shared memory, which must
+// be placed inside one GPC and therefore started late beside the product before them, 3.07 against 3.00 ms a step at
+// one request and 8 ranges, equal at 8 requests; and by the CTA of a pair that finishes last, behind a fence and a
+// counter, 3.06 against 2.98 ms at 16 ranges.)
+template <int D, bool HEADS>
 __global__ void __launch_bounds__(DecodeTile<D>::WARPS * 32)
 attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs args, bf16* __restrict__ out,
                         float* __restrict__ partial, const int* __restrict__ context_len, int num_splits) {
@@ -979,48 +995,11 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs a
     const int t_end = min(last_tile + 1, t_begin + per_split);
     if (threadIdx.x == 0) sm100::tma_prefetch_descriptor(&kv_map);
     decode_init_barriers<D>(smem);
-    if (CLUSTER) {
-        // this CTA's result stays in shared memory, behind the buffer in which its warps were merged
-        static_assert(Smem::ring_bytes >= Smem::merge_bytes + 16 * (D + 2) * 4, "the exchange buffer lies in the ring");
-        float* exchange = reinterpret_cast<float*>(smem + Smem::q_bytes + Smem::merge_bytes);
-        const int stride = args.head_dim + 2;
-        decode_attend_range<D, HEADS>(kv_map, args, smem, req, kv_head, pos, key_lo, last_tile, t_begin, t_end, 0, true, out,
-                                      exchange, (long)stride);
-        decode_stamp(args, 4);
-        decode_cluster_sync();  // every range's result is in its CTA's buffer
-        decode_stamp(args, 5);
-        const uint32_t base = sm100::smem_addr(exchange);
-        const int head_dim = args.head_dim, total = group * head_dim;
-        for (int e = split + num_splits * (int)threadIdx.x; e < total; e += num_splits * (int)blockDim.x) {
-            const int row = e / head_dim, col = e % head_dim;
-            const uint32_t row_address = base + (uint32_t)(row * stride) * 4u;
-            float m[DECODE_MAX_CLUSTER], m_all = -INFINITY;
-#pragma unroll
-            for (int r = 0; r < DECODE_MAX_CLUSTER; ++r) {
-                m[r] = r < num_splits ? ld_cluster_f32(row_address + (uint32_t)head_dim * 4u, (uint32_t)r) : -INFINITY;
-                m_all = fmaxf(m_all, m[r]);
-            }
-            float acc = 0.0f, l_all = 0.0f;
-#pragma unroll
-            for (int r = 0; r < DECODE_MAX_CLUSTER; ++r) {
-                if (r < num_splits) {
-                    const float value = ld_cluster_f32(row_address + (uint32_t)col * 4u, (uint32_t)r);
-                    const float sum = ld_cluster_f32(row_address + (uint32_t)(head_dim + 1) * 4u, (uint32_t)r);
-                    const float weight = m[r] == -INFINITY ? 0.0f : exp2f(m[r] - m_all);
-                    acc += value * weight;
-                    l_all += sum * weight;
-                }
-            }
-            out[((size_t)req * args.q_heads + kv_head * group + row) * head_dim + col] = from_f32<bf16>(l_all > 0.0f ? acc / l_all : 0.0f);
-        }
-        decode_stamp(args, 6);
-        decode_cluster_sync();  // nobody leaves while its buffer may still be read
-        return;
-    }
     float* dst_partial = num_splits == 1 ? nullptr
         : partial + (((size_t)req * args.q_heads + kv_head * group) * num_splits + split) * (args.head_dim + 2);
     decode_attend_range<D, HEADS>(kv_map, args, smem, req, kv_head, pos, key_lo, last_tile, t_begin, t_end, 0, true, out,
                                   dst_partial, (long)num_splits * (args.head_dim + 2));
+    decode_stamp(args, 4);
 }
 
 // How the balanced kernel and its merge cut the work: the key tiles of all (request, kv head) pairs form one
@@ -1252,10 +1231,7 @@ int decode_launch(const void* q, const void* cache, void* out, float* partial, c
     const uint64_t rows = (uint64_t)num_pages * 2 * kv_heads * page_size;
     if (!tmap::bf16_2d_sw128(&kv_map, cache, rows, head_dim, head_dim, box_rows, 64)) return KIRAI_ERR_BAD_ALIGN;
     const bool heads = q_heads / kv_heads <= 8;
-    // a few ranges whose partial results the caller gave no room for: their CTAs merge as a cluster
-    const bool cluster = num_splits > 1 && num_splits <= DECODE_MAX_CLUSTER && partial == nullptr;
-    auto kernel = cluster ? (heads ? attention_decode_kernel<D, true, true> : attention_decode_kernel<D, false, true>)
-                          : (heads ? attention_decode_kernel<D, true, false> : attention_decode_kernel<D, false, false>);
+    auto kernel = heads ? attention_decode_kernel<D, true> : attention_decode_kernel<D, false>;
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total);
     if (err != cudaSuccess) return (int)err;
     if (fuse && head_dim != D) return KIRAI_ERR_UNSUPPORTED;  // the fused preparation works on whole heads of 64, 128 or 256
@@ -1268,9 +1244,6 @@ int decode_launch(const void* q, const void* cache, void* out, float* partial, c
     args.stamps = g_decode_stamps;
     if (g_decode_stamps) g_decode_stamps += 8 * 1024;  // the next launch's stamps follow
     dim3 grid(num_splits, kv_heads, requests);
-    if (cluster)
-        return launch_pdl_cluster(kernel, grid, dim3(Smem::DC_WARPS * 32), (size_t)Smem::total, stream, dim3(num_splits, 1, 1),
-                                  kv_map, args, (bf16*)out, partial, context_len, num_splits);
     int status = launch_pdl(kernel, grid, dim3(Smem::DC_WARPS * 32), (size_t)Smem::total, stream, 1u, kv_map, args,
                             (bf16*)out, partial, context_len, num_splits);
     if (status || num_splits == 1) return status;
@@ -1341,8 +1314,7 @@ KIRAI_EXPORT int kirai_attention_prefill_bf16(const void* q, const void* cache, 
 
 // Attention for a batch in which every request brings exactly one token (token r belongs to request r).
 // With num_splits > 1 and a buffer `partial` of requests * q_heads * num_splits * (head_dim + 2) floats, the ranges'
-// results go through that buffer and a second kernel merges them.  With partial null and num_splits <= 8, the CTAs
-// of a request and kv head form a cluster and merge in shared memory: one kernel, nothing written but the result.
+// results go through that buffer and a second kernel merges them.
 KIRAI_EXPORT int kirai_attention_decode_bf16(const void* q, const void* cache, void* out, float* partial,
                                              const int* block_table, const int* context_len, int requests,
                                              int q_heads, int kv_heads, int head_dim, long q_row_stride, int page_size,
@@ -1353,7 +1325,7 @@ KIRAI_EXPORT int kirai_attention_decode_bf16(const void* q, const void* cache, v
     if (bad) return bad;
     if (q_heads / kv_heads > 16) return KIRAI_ERR_UNSUPPORTED;  // the group's heads are the rows of one m16 tile
     if (num_splits < 1 || num_splits > 65535 || requests > 65535) return KIRAI_ERR_BAD_SIZE;
-    if (num_splits > DECODE_MAX_CLUSTER && !partial) return KIRAI_ERR_BAD_SIZE;  // up to 8 ranges merge without a buffer
+    if (num_splits > 1 && !partial) return KIRAI_ERR_BAD_SIZE;  // the ranges' results need room
 #define KIRAI_DC(D) \
     return decode_launch<D>(q, cache, out, partial, block_table, context_len, requests, q_heads, kv_heads, head_dim, \
                             q_row_stride, page_size, table_width, num_pages, window, scale, num_splits, error_flag, \
@@ -1403,7 +1375,7 @@ KIRAI_EXPORT int kirai_attention_decode_qk_bf16(const void* qkv, void* cache, vo
     if (bad) return bad;
     if (q_heads / kv_heads > 16) return KIRAI_ERR_UNSUPPORTED;
     if (num_splits < 1 || num_splits > 65535 || requests > 65535) return KIRAI_ERR_BAD_SIZE;
-    if (num_splits > DECODE_MAX_CLUSTER && !partial) return KIRAI_ERR_BAD_SIZE;
+    if (num_splits > 1 && !partial) return KIRAI_ERR_BAD_SIZE;
     if (((uintptr_t)q_weight | (uintptr_t)k_weight | (uintptr_t)inv_freq | (uintptr_t)cache) & 15) return KIRAI_ERR_BAD_ALIGN;
     const FuseQK fuse{q_weight, k_weight, inv_freq, eps};
 #define KIRAI_DCQ(D) \

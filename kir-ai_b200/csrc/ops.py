@@ -345,27 +345,25 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.T
     return out
 
 
-DECODE_CLUSTER = 8  # ranges of one (request, kv head) whose CTAs can merge as a thread-block cluster
-
-
 DEFAULT_SMS = 148  # for planning on a host without the device (tests); launches ask the device
 
 
 def decode_splits(requests: int, kv_heads: int, max_context_len: int, tile: int = 16, warps: int = 8,
                   sms: int = DEFAULT_SMS) -> int:
-    """How many CTAs share one (request, kv head) in the decode kernel.  A CTA's warps take
-    key tiles in turn, so a CTA with n tiles runs ceil(n / warps) rounds plus a fixed cost (set-up,
-    merge); CTAs run in waves of ``sms``.  Up to DECODE_CLUSTER ranges merge inside the kernel (their CTAs are a
-    cluster); more need a buffer and a second kernel, about two rounds' time.  The split count with the fewest
-    estimated rounds wins.  (Clusters are used only while all CTAs run at once: in a launch of several waves the
-    pairs of CTAs that a cluster must place together left SMs idle, 10.34 against 10.14 ms a step at 64 requests.)"""
+    """How many CTAs share one (request, kv head) in the decode kernel.  A CTA's warps take key tiles in turn, so a
+    CTA with n tiles runs ceil(n / warps) rounds plus a fixed cost (set-up, merge); CTAs run in waves of ``sms``; more
+    than one range needs the buffer and the second kernel, about three rounds' time.  A launch that fills all but a
+    few SMs pays one round more: the kernel after it finds no SM on which to start early and fetch its weights
+    (3.15 against 3.06 ms a step with 144 and with 128 CTAs at two requests of 4,096 tokens, 3.11 against 2.98 at one).
+    The split count with the fewest estimated rounds wins."""
     pairs = max(1, requests * kv_heads)
     tiles = max(1, -(-max_context_len // tile))
     best, best_cost = 1, None
     for splits in range(1, min(64, tiles) + 1):
-        waves = -(-pairs * splits // sms)
+        ctas = pairs * splits
+        waves = -(-ctas // sms)
         rounds = -(-(-(-tiles // splits)) // warps) + 3
-        cost = waves * rounds + (0 if splits == 1 else (0.75 if splits <= DECODE_CLUSTER and waves == 1 else 2.75))
+        cost = waves * rounds + (0 if splits == 1 else 2.75) + (1.0 if waves == 1 and ctas > sms - 12 else 0.0)
         if best_cost is None or cost < best_cost:
             best, best_cost = splits, cost
     return best
@@ -389,7 +387,7 @@ def decode_plan(context_lens, kv_heads: int, window: Optional[int] = None, tile:
     tiles = [max(1, -(-n // tile)) for n in lens]
     waves = -(-len(lens) * kv_heads * splits // sms)
     rounds_split = -(-(-(-max(tiles) // splits)) // warps)
-    cost_split = waves * (rounds_split + 2.5) + (0.0 if splits == 1 else (0.75 if splits <= DECODE_CLUSTER and waves == 1 else 2.5))
+    cost_split = waves * (rounds_split + 2.5) + (0.0 if splits == 1 else 2.5)
     rounds_balanced = -(-(-(-kv_heads * sum(tiles) // sms)) // warps)
     cost_balanced = rounds_balanced + 9.5
     return cost_balanced < 0.92 * cost_split, splits
@@ -408,8 +406,7 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Te
         out = torch.empty((rows, q_heads * head_dim), dtype=q.dtype, device=q.device)
     assert out.shape == (rows, q_heads * head_dim) and out.dtype == q.dtype and out.is_contiguous()
     partial = None
-    # a few ranges, all CTAs running at once: they merge inside the kernel, as clusters; else through a buffer
-    if num_splits > DECODE_CLUSTER or (num_splits > 1 and rows * kv_heads * num_splits > sm_count(q.device)):
+    if num_splits > 1:  # the ranges' results go through a buffer and a second kernel
         partial = torch.empty((rows, q_heads, num_splits, head_dim + 2), dtype=torch.float32, device=q.device)
     _call("kirai_attention_decode_bf16", _ptr(q), _ptr(cache), _ptr(out), _ptr(partial), _ptr(block_table),
           _ptr(context_len), _i(rows), _i(q_heads), _i(kv_heads), _i(head_dim), _l(q_stride), _i(page_size),
@@ -542,7 +539,7 @@ def attention_decode_qk(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim
         return out
     splits = decode_splits(rows, kv_heads, min(longest, window or longest), sms=sm_count(qkv.device))
     partial = None
-    if splits > DECODE_CLUSTER or (splits > 1 and rows * kv_heads * splits > sm_count(qkv.device)):
+    if splits > 1:
         partial = torch.empty((rows, q_heads, splits, head_dim + 2), dtype=torch.float32, device=qkv.device)
     _call("kirai_attention_decode_qk_bf16", _ptr(qkv), _ptr(cache), _ptr(out), _ptr(partial), *common, _i(splits), *tail)
     return out

@@ -92,11 +92,6 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
                  : "memory");
 }
 
-// Asks for `bytes` contiguous bytes (16-byte aligned, a multiple of 16) to be brought into L2.
-__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(src)), "r"(bytes) : "memory");
-}
-
 // ------------------------------------------------------------- tensor memory
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t columns) {  // whole warp; columns: power of 2 >= 32
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(columns) : "memory");

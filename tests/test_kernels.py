@@ -296,7 +296,7 @@ def test_a_bounded_wait_that_runs_out_is_reported_and_the_device_stays_usable(op
 def test_decode_attention_that_prepares_its_queries_and_keys(ops, monkeypatch, balanced, q_heads, kv_heads, head_dim, page_size, window, lengths):
     """One kernel (per-head norm of q and k, rotation, the new token appended to its page, attention) against the two
     that it replaces, on the same inputs: the attention rows and every byte of the cache must be equal, with either
-    way of cutting the keys (equal ranges per request, whose CTAs merge as clusters or through a buffer; one range per
+    way of cutting the keys (equal ranges per request, merged through a buffer; one range per
     SM), heads of 64, 128 and 256, groups of 1 to 16, a window, pages smaller and larger than a key tile."""
     from types import SimpleNamespace
 
@@ -497,192 +497,6 @@ def test_argmax_and_sampling(ops, vocab):
                 assert abs(place - int(rank[expected])) <= 1, (row, draw, got[row], expected)
 
 
-@pytest.mark.parametrize("rows", [1, 8, 16, 23, 64])
-@pytest.mark.parametrize("hidden,q_width,inter,qkv_width", [(200, 136, 328, 264), (4096, 4096, 1536, 6144), (128, 64, 16, 96)])
-def test_products_held_back_and_launched_as_one_kernel(ops, monkeypatch, rows, hidden, q_width, inter, qkv_width):
-    """A layer's products (output projection with the residual and the next norm, gate/up with SwiGLU, down with the
-    residual and the norm, the next q/k/v) through ``chained_products`` as one persistent kernel, against the same
-    calls launched one by one and against 32-bit arithmetic; twice in a row, since the kernel leaves its counters for
-    its next launch."""
-    eps = 1e-6
-    bf = torch.bfloat16
-    monkeypatch.setattr(ops, "chain_products", True)
-    w_o, w_gate, w_up = rand(hidden, q_width, dtype=bf, scale=0.05), rand(inter, hidden, dtype=bf, scale=0.05, seed=1), rand(inter, hidden, dtype=bf, scale=0.05, seed=2)
-    w_down, w_qkv = rand(hidden, inter, dtype=bf, scale=0.05, seed=3), rand(qkv_width, hidden, dtype=bf, scale=0.05, seed=4)
-    norm1, norm2 = 1.0 + 0.1 * rand(hidden, seed=5), 1.0 + 0.1 * rand(hidden, seed=6)
-    tiled = {name: ops.tile_weight(w) for name, w in (("o", w_o), ("down", w_down), ("qkv", w_qkv))}
-    tiled["gate_up"] = ops.tile_weight(ops.interleave_gate_up(w_gate, w_up))
-    x = rand(rows, q_width, dtype=bf, seed=7)
-    stream0 = rand(rows, hidden, scale=2.0, seed=8)
-
-    def layer(stream):
-        rows1, sumsq1 = ops.linear_residual_norm(x, tiled["o"], stream, norm1)
-        act = ops.linear_tcgen05(rows1, tiled["gate_up"], swiglu=True, row_scale=(sumsq1, hidden, eps))
-        rows2, sumsq2 = ops.linear_residual_norm(act, tiled["down"], stream, norm2)
-        return ops.linear_tcgen05(rows2, tiled["qkv"], row_scale=(sumsq2, hidden, eps))
-
-    single_stream = stream0.clone()
-    single = layer(single_stream)
-    before = ops.launch_count
-    for attempt in range(2):
-        chained_stream = stream0.clone()
-        with ops.chained_products():
-            chained = layer(chained_stream)
-            assert ops.chaining()
-        ops.check_device_errors(torch.device(DEV))
-        assert not ops.chaining()
-        # 32-bit arithmetic on the same bf16 inputs, with the roundings to bf16 where the kernels round
-        r1 = stream0 + x.float() @ w_o.float().T
-        n1 = (r1 * norm1).to(bf).float() * torch.rsqrt((r1 ** 2).mean(-1, keepdim=True) + eps)
-        gate, up = n1 @ w_gate.float().T, n1 @ w_up.float().T
-        a = (gate / (1.0 + torch.exp(-gate)) * up).to(bf).float()
-        r2 = r1 + a @ w_down.float().T
-        n2 = (r2 * norm2).to(bf).float() * torch.rsqrt((r2 ** 2).mean(-1, keepdim=True) + eps)
-        expected = n2 @ w_qkv.float().T
-        scale = float(expected.abs().max())
-        assert float((chained.float() - expected).abs().max()) <= tol(bf, scale)
-        assert float((chained_stream - r2).abs().max()) <= tol(bf, float(r2.abs().max()))
-        assert float((chained.float() - single.float()).abs().max()) <= tol(bf, scale)
-        assert float((chained_stream - single_stream).abs().max()) <= tol(bf, float(r2.abs().max()))
-    assert ops.launch_count - before == 2  # four products, one launch, each time
-
-
-def test_products_held_back_go_out_before_any_other_kernel(ops, monkeypatch):
-    """Launch order is kept: a kernel of another kind, asked for while products are held back, sees their results."""
-    bf = torch.bfloat16
-    monkeypatch.setattr(ops, "chain_products", True)
-    w1, w2 = ops.tile_weight(rand(256, 128, dtype=bf, scale=0.1)), ops.tile_weight(rand(128, 256, dtype=bf, scale=0.1, seed=1))
-    x = rand(5, 128, dtype=bf, seed=2)
-    stream = torch.zeros(5, 128, device=DEV)
-    with ops.chained_products():
-        y = ops.linear_tcgen05(ops.linear_tcgen05(x, w1), w2)
-        ops.add_into_residual(stream, y)  # not a product: the two held back are launched first
-        z = ops.linear_tcgen05(y, w1)     # held back until the block ends
-    expected = (x.float() @ w1.row_major().float().T).to(bf).float() @ w2.row_major().float().T
-    assert float((stream - expected).abs().max()) <= tol(bf, float(expected.abs().max()))
-    assert float((z.float() - y.float() @ w1.row_major().float().T).abs().max()) <= tol(bf, float(z.float().abs().max()))
-    with pytest.raises(RuntimeError, match="boom"):
-        with ops.chained_products():
-            ops.linear_tcgen05(x, w1)
-            raise RuntimeError("boom")
-    assert not ops.chaining() and ops.linear_tcgen05(x, w1).shape == (5, 256)  # nothing stayed behind
-    ops.check_device_errors(torch.device(DEV))
-
-
-def test_a_bounded_wait_that_runs_out_is_reported_and_the_device_stays_usable(ops):
-    """Every barrier wait in the kernels gives up after a number of polls, sets the device error word and lets the
-    kernel return.  The self-test kernel waits for a barrier that nothing completes: the host must read "a bounded
-    wait ... ran out", and the launches after it must run as if nothing had happened."""
-    device = torch.device(DEV)
-    assert ops.wait_selftest(device, limit=10_000, arrive=True) == 0   # the control: an answered wait is no error
-    ops.check_device_errors(device)
-    assert ops.wait_selftest(device, limit=10_000) == 10_000
-    with pytest.raises(ops.KernelError, match="bounded wait inside a kernel ran out"):
-        ops.check_device_errors(device)
-    ops.check_device_errors(device)  # reading the word cleared it
-    x = rand(5, 64, dtype=torch.bfloat16)
-    w = rand(24, 64, dtype=torch.bfloat16, seed=1)
-    out = ops.linear(x, w)  # a tensor-core product with its own barrier waits, right after
-    assert float((out.float() - x.float() @ w.float().T).abs().max()) <= tol(torch.bfloat16, 8.0)
-    ops.check_device_errors(device)
-    with pytest.raises(ops.KernelError, match="refused"):
-        ops.wait_selftest(device, limit=1 << 21)
-
-
-@pytest.mark.parametrize("balanced", ["0", "1"])
-@pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,window,lengths",
-                         [(32, 8, 128, 16, None, [700, 33, 512, 129, 1]), (6, 2, 64, 4, 9, [40, 7, 16]), (4, 4, 256, 64, None, [300, 65]),
-                          (16, 1, 128, 8, 100, [260, 1, 17, 16, 130]), (8, 2, 128, 16, None, [4100])])
-def test_decode_attention_that_prepares_its_queries_and_keys(ops, monkeypatch, balanced, q_heads, kv_heads, head_dim, page_size, window, lengths):
-    """One kernel (per-head norm of q and k, rotation, the new token appended to its page, attention) against the two
-    that it replaces, on the same inputs: the attention rows and every byte of the cache must be equal, with either
-    way of cutting the keys (equal ranges per request, whose CTAs merge as clusters or through a buffer; one range per
-    SM), heads of 64, 128 and 256, groups of 1 to 16, a window, pages smaller and larger than a key tile."""
-    from types import SimpleNamespace
-
-    monkeypatch.setenv("KIRAI_DECODE_BALANCED", balanced)
-    dtype = torch.bfloat16
-    requests = len(lengths)
-    cache, table, keys, values = paged_setup(dtype, lengths, kv_heads, head_dim, page_size, seed=11)
-    for r, n in enumerate(lengths):  # the tokens before the new one are in the pages already
-        if n > 1:
-            pos = torch.arange(n - 1, dtype=torch.int32, device=DEV)
-            ops.kv_write(keys[r][: n - 1].to(DEV).contiguous(), values[r][: n - 1].to(DEV).contiguous(), cache, table,
-                         torch.full((n - 1,), r, dtype=torch.int32, device=DEV), pos)
-    width = (q_heads + 2 * kv_heads) * head_dim
-    qkv = rand(requests, width, dtype=dtype, seed=5)
-    q_weight, k_weight = 1.0 + 0.1 * rand(head_dim, seed=6), 1.0 + 0.1 * rand(head_dim, seed=7)
-    inv_freq = torch.pow(torch.tensor(10000.0), -torch.arange(head_dim // 2, dtype=torch.float32) * 2.0 / head_dim).to(DEV)
-    positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
-    context_len = torch.tensor(lengths, dtype=torch.int32, device=DEV)
-    rows = torch.arange(requests, dtype=torch.int32, device=DEV)
-    batch = SimpleNamespace(decode_only=True, num_requests=requests, context_len=context_len, max_context_len=max(lengths),
-                            start_positions=[n - 1 for n in lengths], query_lens=[1] * requests, decode_balanced=None,
-                            request_of_token=rows, positions=positions, num_decode=requests)
-    scale = head_dim ** -0.5
-    for weights in ((q_weight, k_weight, inv_freq), (None, None, inv_freq), (q_weight, k_weight, None)):
-        qw, kw, freq = weights
-        separate_cache, separate_qkv = cache.clone(), qkv.clone()
-        ops.qk_norm_rope_kv_write_(separate_qkv, q_heads, kv_heads, head_dim, qw, kw, freq, 1e-6, separate_cache, table, rows, positions, True)
-        q = separate_qkv[:, : q_heads * head_dim].unflatten(1, (q_heads, head_dim))
-        expected = ops.paged_attention(q, separate_cache, table, batch, window, scale)
-        fused_cache, fused_qkv = cache.clone(), qkv.clone()
-        assert ops.decode_prepares_qk(fused_qkv, fused_cache, batch, q_heads, kv_heads, head_dim)
-        crowd = SimpleNamespace(decode_only=True, num_requests=1 + ops.sm_count(torch.device(DEV)) // kv_heads)
-        assert not ops.decode_prepares_qk(fused_qkv.expand(crowd.num_requests, -1) if requests == 1 else fused_qkv, fused_cache, crowd, q_heads, kv_heads, head_dim)
-        got = ops.attention_decode_qk(fused_qkv, q_heads, kv_heads, head_dim, qw, kw, freq, 1e-6, fused_cache, table, batch, window, scale)
-        ops.check_device_errors(torch.device(DEV))
-        assert torch.equal(fused_qkv, qkv)                      # the product's rows are left as they were
-        assert torch.equal(fused_cache, separate_cache)         # the same key and value rows, in the same places
-        assert torch.equal(got, expected)
-        assert float(got.float().abs().max()) > 0.01
-
-
-def test_read_only_stream_kernel_runs_and_reports_nothing(ops):
-    """The kernel that measures what a read-only stream reaches: whole 16 KB boxes only, no error word."""
-    data = torch.zeros(37 * 16384, dtype=torch.uint8, device=DEV)  # fewer boxes than SMs: some CTAs have nothing to read
-    ops.stream_read(data)
-    ops.stream_read(torch.zeros(1000 * 16384, dtype=torch.uint8, device=DEV))
-    ops.check_device_errors(torch.device(DEV))
-    with pytest.raises(AssertionError):
-        ops.stream_read(torch.zeros(1000, dtype=torch.uint8, device=DEV))
-
-
-def test_sampler_on_the_cases_of_the_reference(ops):
-    """crates/llm-sampler/src/lib.rs:222-294 through the device sampler, all rows in one launch: greedy, the first of
-    equal maxima, a draw inside the nucleus, and ties inside the nucleus taken in index order."""
-    from test_plain_reference import REFERENCE_TOP_P_CASES
-
-    width = 4
-    rows = [([-1.0, 0.25, 3.5, 3.0], 0.0, 1.0, 0.0, 2), ([1.0, 2.0, 2.0, -1e30], 0.0, 1.0, 0.0, 1)]
-    rows += [(logits + [-1e30] * (width - len(logits)), t, p, draw, token) for logits, t, p, draw, token in REFERENCE_TOP_P_CASES]
-    logits = torch.tensor([r[0] for r in rows], device=DEV)
-    column = lambda i: torch.tensor([r[i] for r in rows], dtype=torch.float32, device=DEV)  # noqa: E731
-    got = ops.sample_rows(logits, column(1), column(2), column(3)).tolist()
-    assert got == [r[4] for r in rows]
-    assert ops.argmax_rows(logits).tolist()[:2] == [2, 1]
-    ops.check_device_errors(torch.device(DEV))
-
-
-def test_a_row_without_a_maximum_sets_the_error_word_and_stays_in_bounds(ops):
-    """All NaN or all -inf: no entry is greater than -inf.  Token 0 is written (nothing is read at a made-up index)
-    and the device error word says so; rows beside it are sampled as usual."""
-    logits = torch.randn(4, 300, device=DEV)
-    logits[1] = float("nan")
-    logits[2] = float("-inf")
-    zeros, ones = torch.zeros(4, device=DEV), torch.ones(4, device=DEV)
-    for temperature in (zeros, ones):
-        got = ops.sample_rows(logits, temperature, ones, zeros + 0.5).tolist()
-        assert got[1] == 0 and got[2] == 0 and 0 <= got[0] < 300 and 0 <= got[3] < 300
-        with pytest.raises(ops.KernelError, match="no maximum"):
-            ops.check_device_errors(torch.device(DEV))
-    assert ops.argmax_rows(logits).tolist()[1:3] == [0, 0]
-    with pytest.raises(ops.KernelError, match="no maximum"):
-        ops.check_device_errors(torch.device(DEV))
-    assert ops.argmax_rows(logits[:1]).tolist() == [int(logits[0].argmax())]
-    ops.check_device_errors(torch.device(DEV))
-
-
 @pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,window",
                          [(6, 2, 48, 8, None), (5, 5, 16, 4, 7), (8, 2, 128, 16, 40), (32, 8, 128, 16, None),
                           (3, 1, 80, 1, None), (4, 2, 256, 64, 33), (16, 1, 64, 16, None),
@@ -801,6 +615,27 @@ def test_tensor_core_attention_finds_a_far_key(ops):
     assert float((out[0, 0] - values[0][far, 0].float()).abs().max()) > 0.5
     out = ops.attention_decode(q, cache, table, ctx, 777 - far, head_dim ** -0.5, 2).float().cpu().unflatten(1, (q_heads, head_dim))
     assert float((out[0, 0] - values[0][far, 0].float()).abs().max()) <= 2e-2
+
+
+@pytest.mark.parametrize("q_heads,kv_heads,head_dim", [(8, 2, 128), (32, 2, 64), (3, 1, 256)])
+def test_decode_attention_cut_into_any_number_of_ranges(ops, q_heads, kv_heads, head_dim):
+    """Every number of ranges from 2 to 18 and some beyond (more ranges than key tiles too: the empty ones must not
+    count) against one range, whose result needs no merge: the merge may differ from it by rounding only."""
+    dtype, page_size, length = torch.bfloat16, 16, 1500
+    cache, table, keys, values = paged_setup(dtype, [length], kv_heads, head_dim, page_size, seed=21)
+    ops.kv_write(keys[0].to(DEV).contiguous(), values[0].to(DEV).contiguous(), cache, table,
+                 torch.zeros(length, dtype=torch.int32, device=DEV), torch.arange(length, dtype=torch.int32, device=DEV))
+    q = rand(1, q_heads, head_dim, dtype=dtype, seed=22)
+    ctx = torch.tensor([length], dtype=torch.int32, device=DEV)
+    scale = head_dim ** -0.5
+    one = ops.attention_decode(q, cache, table, ctx, None, scale, 1).float()
+    plain = ops.paged_attention_plain(q, cache, table, torch.zeros(1, dtype=torch.int32, device=DEV),
+                                      torch.tensor([length - 1], dtype=torch.int32, device=DEV), None, scale).float()
+    assert float((one - plain).abs().max()) <= 2.5e-2
+    for splits in list(range(2, 19)) + [33, 64, 100]:
+        got = ops.attention_decode(q, cache, table, ctx, None, scale, splits)
+        assert float((got.float() - one).abs().max()) <= 1e-2, splits
+    ops.check_device_errors(q.device)
 
 
 @pytest.mark.parametrize("m,inter,k,splits", [(1, 128, 64, 0), (5, 200, 136, 0), (16, 1000, 512, 3), (64, 1536, 1032, 8),
