@@ -23,6 +23,8 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+E2E_SETTLE_STEPS = 24  # untimed engine steps between the prompt phase and the end-to-end warm-up (see measure_decode)
+
 QWEN3_8B = dict(
     architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=4096, intermediate_size=12288,
     num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128, vocab_size=151936,
@@ -301,7 +303,7 @@ def main() -> int:
     context = args.context
     torch.cuda.set_device(0)
     # what a request may generate while the others are still being filled, and while it is warmed up and timed twice
-    new_token_cap = max_batch * -(-context // args.prefill_tokens) + 4 * (warmup + steps) + 64
+    new_token_cap = max_batch * -(-context // args.prefill_tokens) + 4 * (warmup + steps) + E2E_SETTLE_STEPS + 64
     engine = Engine(config=config, random_weights_seed=2, dtype="bfloat16", page_size=page_size,
                     max_new_tokens=new_token_cap, max_prefill_tokens=args.prefill_tokens, max_concurrent_requests=max_batch,
                     max_cache_tokens=max_batch * (context + 256))
@@ -372,13 +374,15 @@ def main() -> int:
         # token per fill step; start them that much lower so that all end near the context length.
         budget = args.prefill_tokens
         fill_steps = batch * -(-context // budget)
-        filled = max(16, context - (2 * (warmup + steps) + 4) - fill_steps)
+        filled = max(16, context - (2 * (warmup + steps) + 4 + E2E_SETTLE_STEPS) - fill_steps)
         params = SamplingParams(temperature=0.0, max_new_tokens=new_token_cap, ignore_eos=True)
         requests = [engine.add_request(random_prompt(filled), params) for _ in range(batch)]
         while any(r.pending > 1 or not r.output for r in requests):
             engine.step()  # prompt portions under the token budget, then the first sampled tokens
-        # (a) through the Python entry point: host tokens in and out every step
-        for _ in range(warmup):
+        # (a) through the Python entry point: host tokens in and out every step.  The prompt phase just before ran
+        # under the power cap; the clocks take about ten decode steps to come back (4.05 falling to 3.65 ms a step
+        # at 8 requests), so a fixed number of steps settles them before the warm-up steps that the caller asked for.
+        for _ in range(E2E_SETTLE_STEPS + warmup):
             engine.step()
         torch.cuda.synchronize()
         launches_before = engine.counters["graph_steps"]
@@ -472,7 +476,8 @@ def main() -> int:
                                            "frac": results[b]["gbs"] / peaks["hbm_gbs"],
                                            "e2e": results[b]["e2e_tokens_per_s"]} for b in batches},
         "e2e": {"value": main_result["e2e_tokens_per_s"], "unit": "tokens/s", "ms_per_step": main_result["e2e_ms"],
-                "h2d_bytes_per_step": main_result["h2d"], "d2h_bytes_per_step": main_result["d2h"]},
+                "h2d_bytes_per_step": main_result["h2d"], "d2h_bytes_per_step": main_result["d2h"],
+                "settle_steps": E2E_SETTLE_STEPS},
         "gpu_launches": main_result["kernels"] * steps,
         "clocks": clock_record,
         "checked": bool(checks) and all(b in checks for b in batches),
