@@ -573,6 +573,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 // run side by side share a weight tile in L2).  Tensor memory holds two accumulators of BN
 // columns: while the epilogue warps read one back, convert and store it, the MMA thread already
 // fills the other with the next tile, and the TMA warp runs ahead across tile borders.
+// Tried and taken out: the last wave shared out evenly (its tiles' k-blocks cut into one range per SM, partial tiles
+// through a workspace, summed in the order of the ranges by the CTA that counts last).  Even with the sums left out
+// the 8B shapes at 2,048 tokens gained 0 to 4 % (q, k, v 99 to 95 us, o 72 to 71, gate/up 283 to 282, down 166 to
+// 160): a wave that leaves SMs idle runs its tiles faster, the products being bound by the power cap and by L2, and
+// the partial tiles' way through memory cost more than that (o 90 us with them).
 // The residual-and-norm epilogue of one 128 x BN tile for one warp (32 rows), with coalesced global accesses.  A
 // thread holds a row of the accumulator, so touching the 32-bit stream from that layout costs a cache-line
 // wavefront per row and instruction, eight times the lines' worth; measured, the epilogue then took longer than
