@@ -240,7 +240,8 @@ class DecodeGraphs:
         key = (num_requests, self.width_bucket(table_width), balanced)
         graph = self.graphs.get(key)
         if graph is None:
-            if self.pool is None:
+            if self.pool is None or not self.graphs:
+                # (a pool whose graphs have all been dropped is gone; its handle must not be used again)
                 self.pool = torch.cuda.graph_pool_handle()
             graph = DecodeGraph(self.runner, key[0], key[1], balanced, self.pool)
             self.graphs[key] = graph
