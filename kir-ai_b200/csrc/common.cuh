@@ -128,3 +128,31 @@ static inline int launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, s
     if (err != cudaSuccess) return (int)err;
     return (int)cudaGetLastError();
 }
+
+// The same with thread-block clusters of any shape.
+template <typename... Params, typename... Args>
+static inline int launch_pdl_clusters(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                      dim3 cluster, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    unsigned count = 0;
+    if (pdl_enabled()) {
+        attrs[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[count].val.programmaticStreamSerializationAllowed = 1;
+        ++count;
+    }
+    attrs[count].id = cudaLaunchAttributeClusterDimension;
+    attrs[count].val.clusterDim.x = cluster.x;
+    attrs[count].val.clusterDim.y = cluster.y;
+    attrs[count].val.clusterDim.z = cluster.z;
+    ++count;
+    config.attrs = attrs;
+    config.numAttrs = count;
+    const cudaError_t err = cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+    if (err != cudaSuccess) return (int)err;
+    return (int)cudaGetLastError();
+}

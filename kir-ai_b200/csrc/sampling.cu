@@ -257,12 +257,303 @@ sample_rows_kernel(const float* __restrict__ logits, float* __restrict__ probs_s
     if (threadIdx.x == 0) out[r] = chosen;
 }
 
+// ------------------------------------------------------------------ one row over a cluster of eight CTAs
+// The same arithmetic with a row's vocabulary cut into eight contiguous slices, one per CTA of a thread-block
+// cluster.  A CTA keeps its slice of the probabilities in shared memory, so the passes of the two searches read no
+// global memory (one block per row read its 600 KB row from L2 in every one of up to 62 passes: 0.9 to 1.6 ms a step
+// for rows with a temperature), and the CTAs exchange their partial results through distributed shared memory: each
+// leaves its numbers in a slot of its own, the cluster synchronises, and every CTA adds the eight slots in rank order,
+// so all of them hold the same bits and take the same branches.  Each search step tries seven values at once.
+#define SC_CTAS 8
+#define SC_THREADS 1024
+
+#define SC_TRIES 7  // values that a search step tries at once: the candidates shrink to an eighth a step
+
+struct SampleExchange {
+    float f[2][8];  // this CTA's contribution to the reduction in flight; two in turn, so that one cluster barrier a
+    int i[2][2];    // reduction is enough (a slot is written again only after the barrier that follows its reading)
+};
+
+__device__ __forceinline__ uint32_t sc_rank() {
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    return rank;
+}
+__device__ __forceinline__ void sc_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t sc_remote(const void* local, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ float sc_load_f32(const float* local, uint32_t rank) {
+    float value;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(sc_remote(local, rank)) : "memory");
+    return value;
+}
+__device__ __forceinline__ int sc_load_s32(const int* local, uint32_t rank) {
+    int value;
+    asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(value) : "r"(sc_remote(local, rank)) : "memory");
+    return value;
+}
+
+// Block-wide sums of COUNT numbers at once (two block barriers for all of them); every thread gets the results, and
+// the order of the additions depends only on the block size.  scratch: 32 * COUNT floats of shared memory.
+template <int COUNT>
+__device__ __forceinline__ void sc_block_sums(float (&values)[COUNT], float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int j = 0; j < COUNT; ++j) values[j] = warp_sum(values[j]);
+    __syncthreads();
+    if (lane == 0) {
+#pragma unroll
+        for (int j = 0; j < COUNT; ++j) scratch[warp * COUNT + j] = values[j];
+    }
+    __syncthreads();
+    const int warps = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int j = 0; j < COUNT; ++j) values[j] = warp_sum(lane < warps ? scratch[lane * COUNT + j] : 0.0f);
+}
+
+// Sums over the cluster of numbers that every thread of this CTA holds (its CTA's partial results), in rank order.
+// One thread per number reads the eight slots (every thread doing so was 57,000 remote loads a CTA and step) and
+// hands the totals on through `totals` (8 floats of shared memory).
+template <int COUNT>
+__device__ __forceinline__ void sc_cluster_sum(float (&values)[COUNT], SampleExchange* ex, int& turn, float* totals) {
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int j = 0; j < COUNT; ++j) ex->f[turn][j] = values[j];
+    }
+    sc_sync();
+    if (threadIdx.x < COUNT) {
+        float total = 0.0f;
+        for (uint32_t q = 0; q < SC_CTAS; ++q) total += sc_load_f32(&ex->f[turn][threadIdx.x], q);
+        totals[threadIdx.x] = total;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < COUNT; ++j) values[j] = totals[j];
+    turn ^= 1;  // (totals is written again only behind the next cluster barrier, which every thread reaches after this)
+}
+
+// G(v) = sum of the row's probabilities greater than v, for COUNT values at once.
+template <int COUNT>
+__device__ __forceinline__ void sc_sums_greater(const float* probs_s, int count, const float (&v)[COUNT], float (&g)[COUNT],
+                                                float* scratch, SampleExchange* ex, int& turn) {
+#pragma unroll
+    for (int j = 0; j < COUNT; ++j) g[j] = 0.0f;
+    for (int i = threadIdx.x; i < count; i += blockDim.x) {
+        const float p = probs_s[i];
+#pragma unroll
+        for (int j = 0; j < COUNT; ++j)
+            if (p > v[j]) g[j] += p;
+    }
+    sc_block_sums<COUNT>(g, scratch);
+    sc_cluster_sum<COUNT>(g, ex, turn, scratch + 32 * COUNT);
+}
+__device__ __forceinline__ float sc_sum_greater(const float* probs_s, int count, float value, float* scratch,
+                                                SampleExchange* ex, int& turn) {
+    const float v[1] = {value};
+    float g[1];
+    sc_sums_greater<1>(probs_s, count, v, g, scratch, ex, turn);
+    return g[0];
+}
+
+// Smallest probability value v (a bit pattern in [0, hi_bits]) with G(v) < target; requires G(hi_bits) < target.
+// G does not grow with v, so SC_TRIES values cut the candidates [lo, hi] into SC_TRIES + 1 parts a step: everything
+// up to the last value that fails is out, the first value that passes is the new upper end.
+__device__ float sc_boundary_value(const float* probs_s, int count, float target, unsigned hi_bits, float* scratch,
+                                   SampleExchange* ex, int& turn) {
+    unsigned lo = 0u, hi = hi_bits;
+    while (lo < hi) {
+        unsigned m[SC_TRIES];
+        float v[SC_TRIES], g[SC_TRIES];
+#pragma unroll
+        for (int j = 0; j < SC_TRIES; ++j) {
+            m[j] = lo + (unsigned)(((unsigned long long)(hi - lo) * (unsigned)(j + 1)) / (SC_TRIES + 1));
+            v[j] = __uint_as_float(m[j]);
+        }
+        sc_sums_greater<SC_TRIES>(probs_s, count, v, g, scratch, ex, turn);
+        unsigned new_lo = lo, new_hi = hi;
+        bool passed = false;
+#pragma unroll
+        for (int j = 0; j < SC_TRIES; ++j) {
+            if (!passed) {
+                if (g[j] < target) new_hi = m[j], passed = true;
+                else new_lo = m[j] + 1u;
+            }
+        }
+        lo = new_lo, hi = new_hi;
+    }
+    return __uint_as_float(hi);
+}
+
+// Index (in the row) of the n-th entry equal to `value` in index order, -1 if there are fewer; the slices lie in
+// rank order, so the CTA that holds the n-th entry is found from the CTAs' counts.  Every CTA returns the same.
+__device__ int sc_nth_equal(const float* probs_s, int count, int first, float value, int n, int* s_counts,
+                            float* scratch, SampleExchange* ex, int& turn) {
+    int mine = 0;
+    for (int i = threadIdx.x; i < count; i += blockDim.x) mine += (probs_s[i] == value);
+    const int in_slice = (int)(block_sum((float)mine, scratch) + 0.5f);  // a slice has fewer than 2^24 entries
+    if (threadIdx.x == 0) ex->i[turn][0] = in_slice;
+    sc_sync();
+    int before = 0, owner = -1;
+    for (uint32_t q = 0; q < SC_CTAS; ++q) {
+        const int have = sc_load_s32(&ex->i[turn][0], q);
+        if (owner < 0 && before + have >= n) owner = (int)q;
+        if (owner < 0) before += have;
+    }
+    turn ^= 1;
+    int found = -1;
+    if (owner == (int)sc_rank()) found = nth_equal(probs_s, count, value, n - before, s_counts);  // the block's own search
+    if (threadIdx.x == 0) ex->i[turn][0] = found < 0 ? -1 : first + found;
+    sc_sync();
+    const int result = owner < 0 ? -1 : sc_load_s32(&ex->i[turn][0], (uint32_t)owner);
+    turn ^= 1;
+    return result;
+}
+
+__global__ void __launch_bounds__(SC_THREADS)
+sample_rows_cluster_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+                           const float* __restrict__ top_p, const float* __restrict__ draw, int* __restrict__ out,
+                           int vocab, int per, int* __restrict__ error_flag) {
+    pdl_launch_dependents();
+    extern __shared__ float probs_s[];  // [per] this CTA's slice: logits first, then probabilities
+    __shared__ float scratch[32 * 8 + 8];  // block sums of up to 8 numbers, then the cluster's totals
+    __shared__ int s_counts[SC_THREADS];
+    __shared__ SampleExchange ex;
+    const int r = blockIdx.y;
+    const uint32_t rank = sc_rank();
+    const int first = (int)rank * per;
+    const int count = max(0, min(per, vocab - first));
+    const float* row = logits + (size_t)r * vocab + first;
+    int turn = 0;
+    pdl_wait();
+    const float temp = temperature[r];
+    // the slice into shared memory, and its greatest logit (lowest index on ties)
+    float best = -INFINITY;
+    int best_index = 0x7fffffff;
+    for (int i = threadIdx.x; i < count; i += blockDim.x) {
+        const float v = row[i];
+        probs_s[i] = v;
+        if (v > best) best = v, best_index = first + i;
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+        const int other_index = __shfl_xor_sync(0xffffffffu, best_index, offset);
+        argmax_combine(best, best_index, other, other_index);
+    }
+    {
+        __shared__ float s_val[32];
+        __shared__ int s_idx[32];
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        if (lane == 0) s_val[warp] = best, s_idx[warp] = best_index;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int w = 1; w < SC_THREADS / 32; ++w) argmax_combine(best, best_index, s_val[w], s_idx[w]);
+            ex.f[turn][0] = best, ex.i[turn][0] = best_index;
+        }
+    }
+    sc_sync();
+    best = -INFINITY, best_index = 0x7fffffff;
+    for (uint32_t q = 0; q < SC_CTAS; ++q)
+        argmax_combine(best, best_index, sc_load_f32(&ex.f[turn][0], q), sc_load_s32(&ex.i[turn][0], q));
+    turn ^= 1;
+    const bool greedy = !(temp > 0.0f);
+    if (best_index == 0x7fffffff || greedy) {
+        if (rank == 0) {
+            if (best_index == 0x7fffffff) no_maximum(out, r, error_flag);
+            else if (threadIdx.x == 0) out[r] = best_index;
+        }
+        sc_sync();  // nobody leaves while its slot may still be read
+        return;
+    }
+    const float max_scaled = best / temp;
+    float acc = 0.0f;
+    for (int i = threadIdx.x; i < count; i += blockDim.x) {
+        const float e = expf(probs_s[i] / temp - max_scaled);
+        probs_s[i] = e;
+        acc += e;
+    }
+    float sums[1] = {block_sum(acc, scratch)};
+    sc_cluster_sum<1>(sums, &ex, turn, scratch + 32 * 8);
+    const float total = sums[0];
+    for (int i = threadIdx.x; i < count; i += blockDim.x) probs_s[i] = probs_s[i] / total;
+    __syncthreads();
+    const float p_max = 1.0f / total;  // exp(0) / total: the probability of the greatest logit, nothing is greater
+    const unsigned hi_bits = __float_as_uint(p_max);
+
+    const float want = top_p[r];
+    float nucleus_total;
+    float nucleus_value = 0.0f;
+    int nucleus_ties = 0x7fffffff;
+    const float all = sc_sum_greater(probs_s, count, -1.0f, scratch, &ex, turn);
+    if (want >= 1.0f || all < want) {
+        nucleus_total = all;
+    } else {
+        nucleus_value = sc_boundary_value(probs_s, count, want, hi_bits, scratch, &ex, turn);
+        const float above = sc_sum_greater(probs_s, count, nucleus_value, scratch, &ex, turn);
+        float running = above;
+        int n = 0;
+        do {
+            running += nucleus_value;
+            ++n;
+        } while (running < want && n < vocab);
+        nucleus_ties = n;
+        nucleus_total = running;
+    }
+    const float threshold = draw[r] * nucleus_total;
+    int chosen;
+    if (!(threshold > 0.0f)) {
+        chosen = best_index;
+    } else {
+        float value = sc_boundary_value(probs_s, count, threshold, hi_bits, scratch, &ex, turn);
+        int n;
+        if (value < nucleus_value) {
+            value = nucleus_value;
+            n = nucleus_ties;
+        } else {
+            const float above = sc_sum_greater(probs_s, count, value, scratch, &ex, turn);
+            float running = above;
+            n = 0;
+            do {
+                running += value;
+                ++n;
+            } while (running < threshold && n < vocab);
+            if (value == nucleus_value && n > nucleus_ties) n = nucleus_ties;
+        }
+        chosen = sc_nth_equal(probs_s, count, first, value, n, s_counts, scratch, &ex, turn);
+        if (chosen < 0) {  // fewer ties than counted (rounding): the last of them
+            int mine = 0;
+            for (int i = threadIdx.x; i < count; i += blockDim.x) mine += (probs_s[i] == value);
+            float ties[1] = {block_sum((float)mine, scratch)};
+            sc_cluster_sum<1>(ties, &ex, turn, scratch + 32 * 8);
+            const int total_ties = (int)(ties[0] + 0.5f);
+            chosen = total_ties > 0 ? sc_nth_equal(probs_s, count, first, value, total_ties, s_counts, scratch, &ex, turn) : best_index;
+        }
+    }
+    if (rank == 0 && threadIdx.x == 0) out[r] = chosen;
+    sc_sync();  // nobody leaves while its slots may still be read
+}
+
 // probs_scratch: [rows, vocab] floats, overwritten.  temperature <= 0 means greedy for that row.
 KIRAI_EXPORT int kirai_sample_rows(const float* logits, float* probs_scratch, const float* temperature,
                                    const float* top_p, const float* draw, int* out, int rows, int vocab,
                                    int* error_flag, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return KIRAI_ERR_BAD_SIZE;
+    // a row over a cluster of eight CTAs while an eighth of it fits a CTA's shared memory beside a second CTA's, and
+    // the grid takes the rows; else one block per row, which reads its row from global memory in every pass
+    const int per = (((vocab + SC_CTAS - 1) / SC_CTAS) + 3) & ~3;
+    const size_t slice_bytes = (size_t)per * sizeof(float);
+    if (slice_bytes <= 100 * 1024 && rows <= 65535 && vocab >= SC_CTAS * 32) {
+        cudaError_t err = cudaFuncSetAttribute(sample_rows_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)slice_bytes);
+        if (err != cudaSuccess) return (int)err;
+        return launch_pdl_clusters(sample_rows_cluster_kernel, dim3(SC_CTAS, rows), dim3(SC_THREADS), slice_bytes, stream,
+                                   dim3(SC_CTAS, 1, 1), logits, temperature, top_p, draw, out, vocab, per, error_flag);
+    }
     const int pdl_status = launch_pdl(sample_rows_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, 1u, logits, probs_scratch, temperature, top_p, draw, out, vocab, error_flag);
     return pdl_status;
 }
