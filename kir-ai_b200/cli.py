@@ -97,7 +97,6 @@ def generate_command(args: List[str]) -> int:
         if level in ("trace", "debug", "info"):
             print(f"[kirai] {message}", file=sys.stderr, flush=True)
 
-    from .config.base import read_config_json
     from .registry import config_from_dict, load_config
     from .sampling.params import SamplingParams
 

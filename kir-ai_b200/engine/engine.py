@@ -12,7 +12,6 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import List, Optional, Sequence, Union
 
-import torch
 
 from ..sampling import rng
 from ..sampling.params import SamplingParams

@@ -16,7 +16,7 @@ from typing import Optional, Sequence
 
 import torch
 
-from .batch import StepBatch, StepEntry, build_batch
+from .batch import StepEntry, build_batch
 
 
 class OutOfPages(RuntimeError):

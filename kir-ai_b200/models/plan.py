@@ -16,7 +16,7 @@ from typing import Dict, List, Optional
 
 import torch
 
-from ..parts.base import KVCacheNeed, Norm, Runtime, StateNeed, WeightSpec
+from ..parts.base import Norm, Runtime, WeightSpec
 from ..parts.block import Block
 from ..parts.embedding import Embedding, OutputHead
 

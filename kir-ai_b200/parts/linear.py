@@ -8,7 +8,6 @@ and reads them under their stored names
 """
 from __future__ import annotations
 
-import os
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch

@@ -14,7 +14,6 @@ sequence from scratch.
 from __future__ import annotations
 
 import json
-import math
 import os
 import struct
 from typing import Dict, List, Optional, Sequence

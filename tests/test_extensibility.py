@@ -12,7 +12,7 @@ import pytest
 import torch
 
 import plain_qwen3 as plain
-from part_helpers import DEV, tolerance
+from part_helpers import tolerance
 
 pytestmark = pytest.mark.gpu
 DTYPES = [torch.float32, torch.bfloat16]
@@ -329,7 +329,7 @@ def test_a_captured_step_refuses_parts_that_read_host_lists(tmp_path):
 def test_plan_validation_refuses_bad_orders():
     define_toys()
     from kirai_b200.models.plan import LayerCall, PlanError
-    from kirai_b200.registry import plan_for_config, resolve
+    from kirai_b200.registry import resolve
 
     config_class, build = resolve("ToyHybridForCausalLM")
     plan = build(config_class())

@@ -3,7 +3,6 @@
 on so few pages that they are used again; in 32-bit and in bfloat16."""
 import numpy as np
 import pytest
-import torch
 
 import plain_qwen3 as plain
 from replay_client import Replay

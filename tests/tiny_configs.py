@@ -2,7 +2,6 @@
 and helpers that write them as model folders with random weights."""
 from __future__ import annotations
 
-import os
 
 import torch
 
