@@ -497,6 +497,37 @@ def test_argmax_and_sampling(ops, vocab):
                 assert abs(place - int(rank[expected])) <= 1, (row, draw, got[row], expected)
 
 
+@pytest.mark.parametrize("vocab", [200, 1024, 4104])  # 200: one block per row; the others: a row over a cluster of CTAs
+def test_sampling_among_many_equal_probabilities(ops, vocab):
+    """Logits that take four values only: most entries tie with hundreds of others, inside the nucleus and at its
+    edge.  Equal probabilities are ordered by index.  For every draw the sampled entry's stretch of the exact running
+    sum in that order must hold the threshold, up to the rounding of 32-bit sums (ties enter the kernel's sum one by
+    one, as the reference's sequential walk adds them, and a thousand additions of one small value round the same
+    way each time); with top-p the entry must lie inside the exact nucleus, up to the same rounding."""
+    generator = torch.Generator().manual_seed(vocab)
+    logits = torch.randint(0, 4, (4, vocab), generator=generator).float()
+    temperatures = torch.tensor([1.0, 0.5, 1.0, 2.0])
+    top_ps = torch.tensor([1.0, 1.0, 0.6, 0.3])
+    dev = logits.to(DEV)
+    for draw in (0.0, 0.1, 0.37, 0.5, 0.75, 0.93, 0.999999):
+        got = ops.sample_rows(dev, temperatures.to(DEV), top_ps.to(DEV), torch.full((4,), draw).to(DEV)).tolist()
+        for row in range(4):
+            probs = torch.softmax(logits[row].double() / float(temperatures[row]), 0)
+            order = torch.argsort(-probs, stable=True)  # ties by index
+            running = torch.cumsum(probs[order], 0)
+            top_p = float(top_ps[row])
+            last = vocab - 1 if top_p >= 1.0 else min(int(torch.searchsorted(running, torch.tensor(top_p, dtype=torch.float64))), vocab - 1)
+            threshold = draw * float(running[last])
+            rank = torch.empty(vocab, dtype=torch.long)
+            rank[order] = torch.arange(vocab)
+            place = int(rank[got[row]])
+            before = float(running[place - 1]) if place > 0 else 0.0
+            slack = 1e-4
+            assert before - slack <= threshold <= float(running[place]) + slack, (row, draw, got[row], place)
+            assert before <= float(running[last]) + slack, (row, draw, got[row], place, last)  # inside the nucleus
+    ops.check_device_errors(torch.device(DEV))
+
+
 @pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,window",
                          [(6, 2, 48, 8, None), (5, 5, 16, 4, 7), (8, 2, 128, 16, 40), (32, 8, 128, 16, None),
                           (3, 1, 80, 1, None), (4, 2, 256, 64, 33), (16, 1, 64, 16, None),
