@@ -58,7 +58,15 @@ def _check(status: int, name: str) -> None:
     raise KernelError(f"{name}: CUDA error {status} at launch")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> ctypes.c_void_p:
+    """The current device's current stream.  Asked of the library's C entry points where it has them: the public
+    call builds a stream object on the way and took 5 us of the 25 us that a launch cost the host."""
+    if _raw_stream is not None and _raw_device is not None:
+        return ctypes.c_void_p(_raw_stream(_raw_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
