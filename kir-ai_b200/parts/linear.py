@@ -40,14 +40,13 @@ class Linear(Part):
             return self.rt.ops.linear_tcgen05(x.rows, self.weight, out_dtype, row_scale=x.row_scale())
         return self.rt.ops.linear(x, self.weight, out_dtype)
 
-    # Largest batch for which a norm is folded into the products around it.  Measured on the 8B layer sizes:
-    # a decode step of one request gains 4 %, batches of 8 to 32 gain nothing, and from 64 rows on the separate
-    # norm kernel wins, because the product after it loads its first weight tiles while the norm runs.
-    FUSED_NORM_MAX_ROWS = 16
-    # Where products are held back and run as one persistent kernel, the separate norm would cut that kernel in
-    # two, and the weight stream that a folded norm once delayed runs on regardless: every batch that the
-    # weight-streaming products take (up to 64 rows) has its norms folded in.
-    FUSED_NORM_MAX_ROWS_CHAINED = 64
+    # Largest batch for which a norm is folded into the products around it: every batch that the weight-streaming
+    # products take.  Measured on the 8B layer sizes (ms a decode step, folded against separate): one request 4 %
+    # faster, 24 requests of 2,048 tokens 4.42, 32 requests 4.70 against 4.83, 48 of 1,024 tokens 4.84 against 4.97,
+    # 64 of 4,096 tokens 9.51 against 9.54.  (Before the epilogue stored through shared memory it took 2.4 to 3.8 us a
+    # product and lost from 17 rows on.)  The many-token kernel's epilogue of this kind is slower than the separate
+    # norm kernel, beside which the next product already loads its first weight tiles.
+    FUSED_NORM_MAX_ROWS = 64
 
     def on_tensor_cores(self) -> bool:
         """Whether this layer's products run on the tensor-core kernel, which alone has the fused epilogues."""
@@ -55,9 +54,7 @@ class Linear(Part):
 
     def fuses_norms(self, rows: int) -> bool:
         """Whether a batch of ``rows`` tokens should have the norms next to this product folded into it."""
-        chaining = getattr(self.rt.ops, "chaining", None)
-        limit = self.FUSED_NORM_MAX_ROWS_CHAINED if chaining is not None and chaining() else self.FUSED_NORM_MAX_ROWS
-        return self.on_tensor_cores() and rows <= limit
+        return self.on_tensor_cores() and rows <= self.FUSED_NORM_MAX_ROWS
 
     def forward_into_norm(self, x: torch.Tensor, resid: torch.Tensor, spec: FusedNormSpec) -> UnscaledNorm:
         """resid += x W^T in place; returns the sum's rows under the norm ``spec`` without their 1 / rms factor."""
