@@ -865,7 +865,9 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Te
     rows = logits.shape[0]
     for t in (temperature, top_p, draw):
         assert t.dtype == torch.float32 and t.numel() == rows and t.is_contiguous()
-    scratch = torch.empty_like(logits)
+    needs_scratch = library().kirai_sample_rows_needs_scratch
+    needs_scratch.restype = ctypes.c_int
+    scratch = torch.empty_like(logits) if needs_scratch(_i(rows), _i(logits.shape[1])) else None
     out = torch.empty(rows, dtype=torch.int32, device=logits.device)
     _call("kirai_sample_rows", _ptr(logits), _ptr(scratch), _ptr(temperature), _ptr(top_p), _ptr(draw), _ptr(out),
           _i(rows), _i(logits.shape[1]), _ptr(error_flag(logits.device)), _stream())

@@ -538,22 +538,32 @@ sample_rows_cluster_kernel(const float* __restrict__ logits, const float* __rest
     sc_sync();  // nobody leaves while its slots may still be read
 }
 
-// probs_scratch: [rows, vocab] floats, overwritten.  temperature <= 0 means greedy for that row.
+// Whether a row of `vocab` logits goes over a cluster of eight CTAs: an eighth of it fits a CTA's shared memory beside
+// a second CTA's, and every CTA has something to do.  Otherwise one block takes the row and reads it from global
+// memory in every pass, which needs the scratch rows.
+static bool sample_rows_over_a_cluster(int rows, int vocab, int* per_out) {
+    const int per = (((vocab + SC_CTAS - 1) / SC_CTAS) + 3) & ~3;
+    if (per_out) *per_out = per;
+    return (size_t)per * sizeof(float) <= 100 * 1024 && rows <= 65535 && vocab >= SC_CTAS * 32;
+}
+KIRAI_EXPORT int kirai_sample_rows_needs_scratch(int rows, int vocab) { return sample_rows_over_a_cluster(rows, vocab, nullptr) ? 0 : 1; }
+
+// probs_scratch: [rows, vocab] floats, overwritten (may be null where kirai_sample_rows_needs_scratch says 0).
+// temperature <= 0 means greedy for that row.
 KIRAI_EXPORT int kirai_sample_rows(const float* logits, float* probs_scratch, const float* temperature,
                                    const float* top_p, const float* draw, int* out, int rows, int vocab,
                                    int* error_flag, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return KIRAI_ERR_BAD_SIZE;
-    // a row over a cluster of eight CTAs while an eighth of it fits a CTA's shared memory beside a second CTA's, and
-    // the grid takes the rows; else one block per row, which reads its row from global memory in every pass
-    const int per = (((vocab + SC_CTAS - 1) / SC_CTAS) + 3) & ~3;
-    const size_t slice_bytes = (size_t)per * sizeof(float);
-    if (slice_bytes <= 100 * 1024 && rows <= 65535 && vocab >= SC_CTAS * 32) {
+    int per = 0;
+    if (sample_rows_over_a_cluster(rows, vocab, &per)) {
+        const size_t slice_bytes = (size_t)per * sizeof(float);
         cudaError_t err = cudaFuncSetAttribute(sample_rows_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)slice_bytes);
         if (err != cudaSuccess) return (int)err;
         return launch_pdl_clusters(sample_rows_cluster_kernel, dim3(SC_CTAS, rows), dim3(SC_THREADS), slice_bytes, stream,
                                    dim3(SC_CTAS, 1, 1), logits, temperature, top_p, draw, out, vocab, per, error_flag);
     }
+    if (!probs_scratch) return KIRAI_ERR_BAD_SIZE;
     const int pdl_status = launch_pdl(sample_rows_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, 1u, logits, probs_scratch, temperature, top_p, draw, out, vocab, error_flag);
     return pdl_status;
 }
