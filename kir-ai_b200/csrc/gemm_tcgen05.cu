@@ -54,21 +54,31 @@ using namespace sm100;
 // tokens (the 96 CTAs of the 8B shape's q, k, v product then stream at the memory's rate: 7 stages 9.5 us, 10 stages 8.5).
 // Tried on top of this and taken out: the partial tiles of a cluster row by row, sent with 16-byte stores (no faster:
 // what the first CTA waits for at the end of a split product is the slowest of its cluster, not the stores).
-template <int BN, bool DEEP = false>
+// STREAM (the swapped, weight-streaming kernel) with BN = 128 (65 to 128 tokens): a partial tile is 64 KB, so the slots
+// do not fit beside a ring.  They lie IN the first CTA's ring instead, which is free once its products are done: the
+// cluster meets once before the partial tiles are sent (LATE), the first CTA keeps its own in tensor memory, and the
+// staged stores go through the rest of the ring 64 tokens at a time.  One CTA per SM with six stages and up to three
+// splits where the launch fits the SMs, else three stages, two CTAs per SM and no split.
+template <int BN, bool DEEP = false, bool STREAM = (BN <= 64)>
 struct GemmSmem {
-    static constexpr bool streaming = BN <= 64;
+    static constexpr bool streaming = STREAM;
+    static constexpr bool late_slots = STREAM && BN > 64;
     static constexpr int x_bytes = GEMM_BM * GEMM_BK * 2;
     static constexpr int y_bytes = BN * GEMM_BK * 2;
     static constexpr int stage_bytes = x_bytes + y_bytes;
-    static constexpr int max_splits = BN <= 64 ? 4 : 1;  // up to 128 KB of slots beside the 96 KB ring
+    static constexpr int max_splits = !STREAM ? 1 : (BN <= 64 ? 4 : (DEEP ? 3 : 1));  // BN <= 64: up to 128 KB of slots beside the ring
     static constexpr int slot_bytes = BN * GEMM_BM * 4;  // one 32-bit partial tile
-    static constexpr int stages = streaming ? (DEEP ? (BN <= 16 ? 10 : 7) : 4) : (200 * 1024 / stage_bytes);
-    static constexpr int barrier_bytes = 2048;  // barriers [0, 256), row scales [256, 512), partial sums of squares [512, 1536)
+    static constexpr int stages = !STREAM ? (200 * 1024 / stage_bytes)
+                                          : (BN > 64 ? (DEEP ? 6 : 3) : (DEEP ? (BN <= 16 ? 10 : 7) : 4));
+    static constexpr int barrier_bytes = 2048;  // barriers [0, 256), row scales [256, 256 + 4 BN)
+    static constexpr int stage_tokens = BN < 64 ? BN : 64;  // tokens that the staged stores take through shared memory at a time
     static_assert(!streaming || (2 * stages + 1) * 8 + 4 <= 256, "the streaming kernel's barriers must end before the row scales");
-    static_assert(!DEEP || BN <= 32, "the long ring is for the smallest tiles");
+    static_assert(!DEEP || BN <= 32 || late_slots, "the long ring is for the smallest tiles and for the widest");
+    static_assert(!late_slots || (max_splits - 1) * slot_bytes + stage_tokens * 132 * 4 <= stages * stage_bytes,
+                  "the other CTAs' partial tiles and the staged tokens lie in the ring");
     static constexpr int ctas_per_sm = streaming && !DEEP ? 2 : 1;
     static constexpr int total(int splits) {  // + slack to align the base to 1024 bytes
-        return stages * stage_bytes + barrier_bytes + (splits > 1 ? splits * slot_bytes : 0) + 1024;
+        return stages * stage_bytes + barrier_bytes + (splits > 1 && !late_slots ? splits * slot_bytes : 0) + 1024;
     }
 };
 
@@ -162,18 +172,20 @@ __device__ __forceinline__ float silu_mul(float gate, float up) {
 // EPI 0 stores C.  EPI 1 expects W's rows interleaved in eights (8 gate rows, the 8 matching up
 // rows, ...) and stores silu(gate) * up, [M, N / 2].
 template <int BN, bool SWAP, typename OutT, int EPI, bool DEEP>
-__global__ void __launch_bounds__(GEMM_THREADS, GemmSmem<BN, DEEP>::ctas_per_sm)
+__global__ void __launch_bounds__(GEMM_THREADS, GemmSmem<BN, DEEP, true>::ctas_per_sm)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                     const uint8_t* __restrict__ w_tiled, OutT* __restrict__ C, int M, int N, int K, long ldc,
                     int k_blocks_per_split, int splits, Epilogue ep, int* __restrict__ error_flag) {
-    using Smem = GemmSmem<BN, DEEP>;
+    using Smem = GemmSmem<BN, DEEP, true>;
     constexpr int STAGES = Smem::stages;
+    constexpr bool LATE = Smem::late_slots;  // the other CTAs' partial tiles lie in the first CTA's ring (see GemmSmem)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + STAGES * Smem::stage_bytes);
     float* scale_s = reinterpret_cast<float*>(smem + STAGES * Smem::stage_bytes + 256);   // [BN] row scales of this tile's tokens
-    float* sumsq_s = reinterpret_cast<float*>(smem + STAGES * Smem::stage_bytes + 512);   // [4 warps][BN]
-    float* slots = reinterpret_cast<float*>(smem + STAGES * Smem::stage_bytes + Smem::barrier_bytes);  // [splits][BN][128], used in the first CTA
+    // used in the first CTA: [splits][BN][128] behind the barriers, or (LATE) [splits - 1][BN][128] from the ring's start
+    float* slots = LATE ? reinterpret_cast<float*>(smem)
+                        : reinterpret_cast<float*>(smem + STAGES * Smem::stage_bytes + Smem::barrier_bytes);
     uint64_t* full_bar = bars;                 // [STAGES] TMA -> MMA
     uint64_t* empty_bar = bars + STAGES;       // [STAGES] MMA -> TMA
     uint64_t* done_bar = bars + 2 * STAGES;    // accumulator complete
@@ -312,23 +324,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         if (num_kb > 0) ok = mbar_wait(smem_addr(done_bar), 0);
         tc_fence_after();
         if (tile_row == 0) gemm_stamp(ep, 3);
-        if (splits > 1) {
-            // store this CTA's partial tile into its slot in the first CTA (column-major: lanes side by side)
-            const uint32_t slot = cluster_address(smem_addr(slots) + rank * (uint32_t)Smem::slot_bytes, 0);
+    }
+    // LATE: the first CTA's ring takes the partial tiles, so nothing is sent before every CTA of the cluster has
+    // seen its last product finish (all threads arrive here, the epilogue warps after their wait for the accumulator)
+    if (splits > 1 && LATE) cluster_sync_all();
+    if (warp >= 2 && splits > 1 && (!LATE || rank != 0)) {
+        // store this CTA's partial tile into its slot in the first CTA (column-major: lanes side by side); LATE: the
+        // first CTA keeps its own in tensor memory and slot 0 belongs to the second
+        const uint32_t slot = cluster_address(smem_addr(slots) + (LATE ? rank - 1u : rank) * (uint32_t)Smem::slot_bytes, 0);
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                uint32_t r[16];
-                if (num_kb > 0 && ok) {
-                    tmem_load_32x16(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)c0, r);
-                    tmem_load_wait();
-                } else {
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+            uint32_t r[16];
+            if (num_kb > 0 && ok) {
+                tmem_load_32x16(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)c0, r);
+                tmem_load_wait();
+            } else {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) r[j] = 0u;
-                }
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    st_cluster_f32(slot + (uint32_t)(((c0 + j) * GEMM_BM + tile_row) * 4), __uint_as_float(r[j]));
+                for (int j = 0; j < 16; ++j) r[j] = 0u;
             }
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                st_cluster_f32(slot + (uint32_t)(((c0 + j) * GEMM_BM + tile_row) * 4), __uint_as_float(r[j]));
         }
     }
     if (splits > 1) cluster_sync_all();  // every partial tile has arrived in the first CTA
@@ -339,12 +355,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         const int x_rows = SWAP ? N : M;
         const int y_rows = SWAP ? M : N;
         const float my_scale = (!SWAP && ep.row_sumsq && x_row < M) ? row_scale_of(ep, x_row, M) : 1.0f;
+        // The staged stores take Smem::stage_tokens tokens at a time through shared memory: all of a tile of up to 64
+        // tokens through the idle ring; of 128 tokens (LATE) two halves through what the partial tiles leave of it.
+        constexpr int HALF = Smem::stage_tokens;
+        float* const stage = reinterpret_cast<float*>(smem) + (LATE ? (size_t)(splits - 1) * (BN * GEMM_BM) : 0);
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 16) {
+        for (int h0 = 0; h0 < BN; h0 += HALF) {
+        if (y0 + h0 >= y_rows) break;  // uniform across the CTA
+#pragma unroll 1
+        for (int c0 = h0; c0 < h0 + HALF; c0 += 16) {
             if (y0 + c0 >= y_rows) break;  // uniform across the warp
             if (EPI == 2 && SWAP && c0 > 0) load_residual_column<BN>(ep, x_row, y0, c0, M, N, res);
             float v[16];
-            if (splits > 1) {
+            if (splits > 1 && LATE) {
+                // this CTA's own partial tile from tensor memory, then the others' in rank order
+                uint32_t r[16];
+                if (num_kb > 0 && ok) {
+                    tmem_load_32x16(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)c0, r);
+                    tmem_load_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = 0u;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+                for (int other = 1; other < splits; ++other) {
+                    const float* slot = slots + (size_t)(other - 1) * (BN * GEMM_BM);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] += slot[(c0 + j) * GEMM_BM + tile_row];
+                }
+            } else if (splits > 1) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] = slots[(c0 + j) * GEMM_BM + tile_row];
                 for (int other = 1; other < splits; ++other) {
@@ -370,17 +410,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             }
             if (tile_row == 0) gemm_stamp(ep, 6);
             if (SWAP && staged) {
-                float* stage = reinterpret_cast<float*>(smem);  // every product has read the ring: it is free
+                // (every product has read the ring: it is free)
                 if (EPI == 1) {
                     // this lane holds weight row x_row: rows 16k..16k+7 are gate rows, 16k+8..16k+15 their up rows
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const float out = silu_mul(v[j], __shfl_xor_sync(0xffffffffu, v[j], 8));
-                        if ((lane & 8) == 0) stage[(c0 + j) * 132 + (tile_row >> 4) * 8 + (tile_row & 7)] = out;
+                        if ((lane & 8) == 0) stage[(c0 - h0 + j) * 132 + (tile_row >> 4) * 8 + (tile_row & 7)] = out;
                     }
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) stage[(c0 + j) * 132 + tile_row] = v[j];
+                    for (int j = 0; j < 16; ++j) stage[(c0 - h0 + j) * 132 + tile_row] = v[j];
                 }
                 continue;
             }
@@ -467,18 +507,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         if (tile_row == 0) gemm_stamp(ep, 7);
         if (SWAP && staged) {
             named_barrier_128();
-            const float* stage = reinterpret_cast<const float*>(smem);
             const int part = tile_row & 7;
 #pragma unroll 1
-            for (int base = 0; base < BN; base += 16) {
+            for (int base = h0; base < h0 + HALF; base += 16) {
                 if (y0 + base >= y_rows) break;  // uniform
                 const int local = base + (tile_row >> 3), token = y0 + local;
                 if (EPI == 1) {
                     // 64 outputs a token: eight to a thread
                     const int col = (x0 >> 1) + 8 * part;
                     if (token < y_rows && col + 8 <= (N >> 1)) {
-                        const float4 a = *reinterpret_cast<const float4*>(stage + local * 132 + 8 * part);
-                        const float4 b = *reinterpret_cast<const float4*>(stage + local * 132 + 8 * part + 4);
+                        const float4 a = *reinterpret_cast<const float4*>(stage + (local - h0) * 132 + 8 * part);
+                        const float4 b = *reinterpret_cast<const float4*>(stage + (local - h0) * 132 + 8 * part + 4);
                         __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w);
                         __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
                         *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(C) + (size_t)token * ldc + col) =
@@ -490,7 +529,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 const int col = x0 + 16 * part;
                 float4 value[4];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) value[q] = *reinterpret_cast<const float4*>(stage + local * 132 + 16 * part + 4 * q);
+                for (int q = 0; q < 4; ++q) value[q] = *reinterpret_cast<const float4*>(stage + (local - h0) * 132 + 16 * part + 4 * q);
                 float sq = 0.0f;
                 if (EPI == 2) {
                     if (base > 0) {
@@ -539,9 +578,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     if (part == 0 && token < M) ep.sumsq_out[(size_t)blockIdx.x * M + token] = sq;
                 }
             }
-        } else if (EPI == 2 && SWAP) {
+            if (h0 + HALF < BN) named_barrier_128();  // the next half is staged where this one was read
+        }
+        }  // halves
+        if (EPI == 2 && SWAP && !staged) {
             // this tile's share of each token's sum of squares: eight lanes add a token's 128 squares, sixteen each
-            // (rotated so that the 32 lanes of a warp read 32 banks), in a fixed order
+            // (rotated so that the 32 lanes of a warp read 32 banks), in a fixed order.  (Tiles of up to 64 tokens only:
+            // the launch gives wider tiles to this kernel only where the staged stores apply.)
             named_barrier_128();
             const float* sq_s = reinterpret_cast<const float*>(smem);
             const int part = tile_row & 7;
@@ -988,7 +1031,7 @@ static long max_resident_clusters(Kernel kernel, int smem_bytes, int cluster_z) 
 template <int BN, bool SWAP, typename OutT, int EPI>
 static int launch_config(const void* A, const void* W, bool tiled, void* C, int M, int N, int K, long lda, long ldc,
                          int splits, const Epilogue& ep, int* error_flag, cudaStream_t stream) {
-    using Smem = GemmSmem<BN>;
+    using Smem = GemmSmem<BN, false, true>;
     CUtensorMap map_x, map_y;
     const void* x_ptr = SWAP ? W : A;
     const void* y_ptr = SWAP ? A : W;
@@ -1000,7 +1043,9 @@ static int launch_config(const void* A, const void* W, bool tiled, void* C, int 
     else if (!tmap::bf16_2d_sw128(&map_x, x_ptr, x_rows, K, x_stride, GEMM_BM, GEMM_BK)) return KIRAI_ERR_BAD_ALIGN;
     const int total_k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
     if (splits < 1) splits = 1;
-    if (splits > Smem::max_splits) splits = Smem::max_splits;  // slots in the first CTA's shared memory
+    int max_splits = Smem::max_splits;
+    if constexpr (BN == 128) max_splits = GemmSmem<BN, true, true>::max_splits;  // (tiles of 128 tokens split only with the long ring)
+    if (splits > max_splits) splits = max_splits;  // slots in the first CTA's shared memory
     if (splits > total_k_blocks) splits = total_k_blocks;
     const uint8_t* boxes = tiled ? (const uint8_t*)W : (const uint8_t*)nullptr;
     // The CTAs of a tile are a cluster, and a cluster's CTAs must find room in one GPC at the same time: 48 clusters of
@@ -1013,10 +1058,10 @@ static int launch_config(const void* A, const void* W, bool tiled, void* C, int 
         dim3 grid((unsigned)((x_rows + GEMM_BM - 1) / GEMM_BM), (unsigned)((y_rows + BN - 1) / BN), (unsigned)used);
         if (grid.y > 65535) return KIRAI_ERR_BAD_SIZE;
         const long clusters = (long)grid.x * grid.y;
-        if constexpr (BN <= 32) {
+        if constexpr (BN <= 32 || BN == 128) {
             // no more CTAs than SMs: one CTA per SM with the long ring (KIRAI_GEMM_DEEP=0 keeps the short one, to compare)
             if (clusters * used <= sm_count() && deep_rings()) {
-                using Deep = GemmSmem<BN, true>;
+                using Deep = GemmSmem<BN, true, true>;
                 auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT, EPI, true>;
                 cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Deep::total(Deep::max_splits));
                 if (err != cudaSuccess) return (int)err;
@@ -1025,6 +1070,7 @@ static int launch_config(const void* A, const void* W, bool tiled, void* C, int 
                                   map_y, boxes, (OutT*)C, M, N, K, ldc, per_split, used, ep, error_flag);
             }
         }
+        if (used > Smem::max_splits) continue;  // (tiles of 128 tokens split only with the long ring)
         auto kernel = gemm_tcgen05_kernel<BN, SWAP, OutT, EPI, false>;
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total(Smem::max_splits));
         if (err != cudaSuccess) return (int)err;
@@ -1055,6 +1101,14 @@ static int choose_splits(int M, int N, int K) {
     return splits < 1 ? 1 : splits;
 }
 
+// Whether the epilogue of the weight-streaming kernel can store through shared memory (its `staged` condition), which
+// tiles of 128 tokens need.
+static bool streams_wide_tiles(const void* C, long ldc, size_t element, int N, int epi, const Epilogue& ep) {
+    if (((uintptr_t)C & 15) != 0 || (ldc * (long)element) % 16 != 0) return false;
+    if (epi == 2) return N % 8 == 0 && (((uintptr_t)ep.residual | (uintptr_t)ep.norm_weight) & 15) == 0;
+    return epi == 1 ? N % 16 == 0 : N % 8 == 0;
+}
+
 template <typename OutT, int EPI>
 static int gemm_dispatch(const void* A, const void* W, bool tiled, void* C, int M, int N, int K, long lda, long ldc,
                          int splits, const Epilogue& ep, int* error_flag, cudaStream_t stream) {
@@ -1062,23 +1116,30 @@ static int gemm_dispatch(const void* A, const void* W, bool tiled, void* C, int 
     if (K <= 0) return KIRAI_ERR_BAD_SIZE;
     if (K % 8 != 0 || lda % 8 != 0) return KIRAI_ERR_BAD_ALIGN;  // TMA needs 16-byte row strides
     if (EPI == 1 && N % 16 != 0) return KIRAI_ERR_BAD_SIZE;      // whole groups of 8 gate + 8 up rows
-    if (splits <= 0) splits = M <= 64 ? choose_splits(M, N, K) : 1;
+    if (splits <= 0) splits = M <= 128 ? choose_splits(M, N, K) : 1;
 #define KIRAI_GEMM_CASE(BN, SWAP) \
     return launch_config<BN, SWAP, OutT, EPI>(A, W, tiled, C, M, N, K, lda, ldc, splits, ep, error_flag, stream)
     if (M <= 16) KIRAI_GEMM_CASE(16, true);
     if (M <= 32) KIRAI_GEMM_CASE(32, true);
     if (M <= 64) KIRAI_GEMM_CASE(64, true);
+    // 65 to 128 tokens: still bound by the weight stream, which the many-token kernel below leaves to 16 to 96 CTAs
+    // (230 us for the four products of an 8B layer against 66 us at 64 tokens).  The weight-streaming kernel takes
+    // them where its staged stores apply (they do for every 16-byte aligned output).
+    if (M <= 128 && streams_wide_tiles(C, ldc, sizeof(OutT), N, EPI, ep)) KIRAI_GEMM_CASE(128, true);
+    if (M <= 128 && EPI == 2 && N % 8 == 0) return KIRAI_ERR_BAD_ALIGN;  // see kirai_gemm_bf16_residual_parts
 #undef KIRAI_GEMM_CASE
     if (N <= 128) return launch_persistent<128, OutT, EPI>(A, W, tiled, C, M, N, K, lda, ldc, ep, error_flag, stream);
     return launch_persistent<256, OutT, EPI>(A, W, tiled, C, M, N, K, lda, ldc, ep, error_flag, stream);
 }
 
 // Split count that the entry points pick for splits <= 0.
-KIRAI_EXPORT int kirai_gemm_bf16_auto_splits(int M, int N, int K) { return M <= 64 ? choose_splits(M, N, K) : 1; }
+KIRAI_EXPORT int kirai_gemm_bf16_auto_splits(int M, int N, int K) { return M <= 128 ? choose_splits(M, N, K) : 1; }
 
 // How many parts the residual-and-norm form writes into sumsq_out for a product of this shape.
 KIRAI_EXPORT int kirai_gemm_bf16_residual_parts(int M, int N) {
-    if (M <= 64) return (N + GEMM_BM - 1) / GEMM_BM;
+    // (65 to 128 tokens go to the weight-streaming kernel where whole 16-byte pieces can be stored; form 3 with such a
+    // shape and buffers that are not 16-byte aligned is refused rather than sent to the kernel with the other layout)
+    if (M <= 64 || (M <= 128 && N % 8 == 0)) return (N + GEMM_BM - 1) / GEMM_BM;
     return N <= 128 ? 1 : (N + 255) / 256;
 }
 
