@@ -58,22 +58,23 @@ using namespace sm100;
 // do not fit beside a ring.  They lie IN the first CTA's ring instead, which is free once its products are done: the
 // cluster meets once before the partial tiles are sent (LATE), the first CTA keeps its own in tensor memory, and the
 // staged stores go through the rest of the ring 64 tokens at a time.  One CTA per SM with six stages and up to three
-// splits where the launch fits the SMs, else three stages, two CTAs per SM and no split.
+// splits where the launch fits the SMs, else three stages, two CTAs per SM and no split.  Tiles of 64 tokens take the
+// same way where the launch fits the SMs (eight stages, up to four splits), and slots beside a ring of four otherwise.
 template <int BN, bool DEEP = false, bool STREAM = (BN <= 64)>
 struct GemmSmem {
     static constexpr bool streaming = STREAM;
-    static constexpr bool late_slots = STREAM && BN > 64;
+    static constexpr bool late_slots = STREAM && (BN > 64 || (BN == 64 && DEEP));
     static constexpr int x_bytes = GEMM_BM * GEMM_BK * 2;
     static constexpr int y_bytes = BN * GEMM_BK * 2;
     static constexpr int stage_bytes = x_bytes + y_bytes;
     static constexpr int max_splits = !STREAM ? 1 : (BN <= 64 ? 4 : (DEEP ? 3 : 1));  // BN <= 64: up to 128 KB of slots beside the ring
     static constexpr int slot_bytes = BN * GEMM_BM * 4;  // one 32-bit partial tile
     static constexpr int stages = !STREAM ? (200 * 1024 / stage_bytes)
-                                          : (BN > 64 ? (DEEP ? 6 : 3) : (DEEP ? (BN <= 16 ? 10 : 7) : 4));
+                                          : (BN > 64 ? (DEEP ? 6 : 3) : (DEEP ? (BN <= 16 ? 10 : (BN <= 32 ? 7 : 8)) : 4));
     static constexpr int barrier_bytes = 2048;  // barriers [0, 256), row scales [256, 256 + 4 BN)
     static constexpr int stage_tokens = BN < 64 ? BN : 64;  // tokens that the staged stores take through shared memory at a time
     static_assert(!streaming || (2 * stages + 1) * 8 + 4 <= 256, "the streaming kernel's barriers must end before the row scales");
-    static_assert(!DEEP || BN <= 32 || late_slots, "the long ring is for the smallest tiles and for the widest");
+    static_assert(!DEEP || BN <= 32 || late_slots, "a long ring beside slots is for the smallest tiles");
     static_assert(!late_slots || (max_splits - 1) * slot_bytes + stage_tokens * 132 * 4 <= stages * stage_bytes,
                   "the other CTAs' partial tiles and the staged tokens lie in the ring");
     static constexpr int ctas_per_sm = streaming && !DEEP ? 2 : 1;
@@ -428,7 +429,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 // this lane holds output column x_row of tokens y0 + c0 .. + 15.  The squares of the sums go to shared
                 // memory (the ring is idle: every product has read it), token by token, 132 floats to a token; they
                 // are added up after the loop.  (Sixteen warp reductions here, one after the other, took 2 us.)
-                float* sq_s = reinterpret_cast<float*>(smem);
+                float* sq_s = stage;  // (behind the partial tiles where those lie in the ring)
                 const bool row_ok = x_row < x_rows;
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
@@ -586,7 +587,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             // (rotated so that the 32 lanes of a warp read 32 banks), in a fixed order.  (Tiles of up to 64 tokens only:
             // the launch gives wider tiles to this kernel only where the staged stores apply.)
             named_barrier_128();
-            const float* sq_s = reinterpret_cast<const float*>(smem);
+            const float* sq_s = stage;
             const int part = tile_row & 7;
 #pragma unroll 1
             for (int base = 0; base < BN; base += 16) {
@@ -1058,7 +1059,7 @@ static int launch_config(const void* A, const void* W, bool tiled, void* C, int 
         dim3 grid((unsigned)((x_rows + GEMM_BM - 1) / GEMM_BM), (unsigned)((y_rows + BN - 1) / BN), (unsigned)used);
         if (grid.y > 65535) return KIRAI_ERR_BAD_SIZE;
         const long clusters = (long)grid.x * grid.y;
-        if constexpr (BN <= 32 || BN == 128) {
+        if constexpr (BN <= 128) {
             // no more CTAs than SMs: one CTA per SM with the long ring (KIRAI_GEMM_DEEP=0 keeps the short one, to compare)
             if (clusters * used <= sm_count() && deep_rings()) {
                 using Deep = GemmSmem<BN, true, true>;
