@@ -6,12 +6,15 @@ its names and defaults where it has them: ``--snapshot``, ``--max-new-tokens``
 (256), ``--max-prefill-tokens`` (2048), ``--max-concurrent-requests`` (4),
 ``--log-level``.  The reference has no ``generate`` subcommand (it serves HTTP);
 the request options take the names of its API fields: ``--temperature``,
-``--top-p``, ``--max-tokens``.  Prompts are token ids; text needs a tokenizer,
-which is outside this engine.
+``--top-p``, ``--max-tokens``.  Prompts are token ids.  Text (``--prompt``, and a
+``text`` field in the output) is offered where the model folder holds a
+tokenizer.json and the ``tokenizers`` package is installed; the engine itself
+knows token ids only.
 """
 from __future__ import annotations
 
 import json
+import os
 import sys
 from typing import List, Optional
 
@@ -25,6 +28,8 @@ Options:
   --write-snapshot <path>           With --random-weights: write the model folder there and exit
   --prompt-ids <ids>                Comma-separated token ids; repeat the flag for several prompts
   --prompt-file <path>              JSON file with a list of prompts (lists of token ids)
+  --prompt <text>                   A prompt as text; needs tokenizer.json in the model folder and the `tokenizers`
+                                    package.  With a tokenizer present the output lines carry the generated text too
   --max-tokens <n>                  Tokens to generate per request [default: --max-new-tokens]
   --temperature <t>                 0 = greedy [default: 1.0, range 0..2]
   --top-p <p>                       Nucleus mass [default: 1.0, range (0,1]]
@@ -85,6 +90,21 @@ def _float(args, flag, default):
         raise SystemExit(f"{flag} expects a number, got {value!r}")
 
 
+def _load_tokenizer(snapshot: Optional[str]):
+    """The tokenizer of a model folder, if it has a tokenizer.json and the `tokenizers` package is installed; else None.
+    Text is a convenience of the command line only: the engine takes and gives token ids."""
+    if snapshot is None:
+        return None
+    path = os.path.join(snapshot, "tokenizer.json")
+    if not os.path.isfile(path):
+        return None
+    try:
+        from tokenizers import Tokenizer
+    except ImportError:
+        return None
+    return Tokenizer.from_file(path)
+
+
 def generate_command(args: List[str]) -> int:
     if has_flag(args, "--help") or has_flag(args, "-h"):
         print(HELP)
@@ -122,9 +142,14 @@ def generate_command(args: List[str]) -> int:
     elif snapshot is None:
         raise SystemExit("kirai generate needs --snapshot <path> (or --random-weights <seed> with --config)")
 
+    tokenizer = _load_tokenizer(snapshot)
     prompts = []
     for text in flag_values(args, "--prompt-ids"):
         prompts.append([int(t) for t in text.replace(" ", "").split(",") if t])
+    for text in flag_values(args, "--prompt"):
+        if tokenizer is None:
+            raise SystemExit("--prompt needs tokenizer.json in the model folder and the `tokenizers` package; give --prompt-ids")
+        prompts.append(list(tokenizer.encode(text).ids))
     prompt_file = flag_value(args, "--prompt-file")
     if prompt_file:
         with open(prompt_file) as handle:
@@ -160,8 +185,11 @@ def generate_command(args: List[str]) -> int:
     engine.runner.model.nvtx = level == "trace"
     log(f"loaded {type(engine.runner.config).__name__}; generating for {len(prompts)} prompt(s)")
     for output in engine.generate(prompts, params):
-        print(json.dumps({"token_ids": output.token_ids, "finish_reason": output.finish_reason,
-                          "prompt_tokens": output.prompt_tokens, "completion_tokens": output.completion_tokens}))
+        line = {"token_ids": output.token_ids, "finish_reason": output.finish_reason,
+                "prompt_tokens": output.prompt_tokens, "completion_tokens": output.completion_tokens}
+        if tokenizer is not None:
+            line["text"] = tokenizer.decode(output.token_ids)
+        print(json.dumps(line))
     log(json.dumps(engine.stats()))
     return 0
 

@@ -198,3 +198,30 @@ def test_command_line(tiny):
     for prompt, line in zip(([5, 17, 3, 44], [9, 8, 7]), lines):
         assert line["token_ids"] == plain.greedy_generate(tiny["config"], tiny["weights"], prompt, 6)
         assert line["finish_reason"] == "length" and line["prompt_tokens"] == len(prompt)
+
+
+def test_command_line_with_text(tiny, tmp_path):
+    """With a tokenizer.json in the model folder, --prompt takes text and the output lines carry the generated text."""
+    tokenizers = pytest.importorskip("tokenizers")
+    import shutil
+
+    folder = str(tmp_path / "with_tokenizer")
+    shutil.copytree(tiny["folder"], folder)
+    vocab = {f"w{i}": i for i in range(tiny["raw"]["vocab_size"])}
+    tokenizer = tokenizers.Tokenizer(tokenizers.models.WordLevel(vocab, unk_token="w0"))
+    tokenizer.pre_tokenizer = tokenizers.pre_tokenizers.Whitespace()
+    tokenizer.decoder = tokenizers.decoders.Fuse()
+    tokenizer.save(os.path.join(folder, "tokenizer.json"))
+    base = [sys.executable, os.path.join(ROOT, "bin", "kirai"), "generate", "--snapshot", folder, "--max-tokens", "5",
+            "--temperature", "0", "--dtype", "float32", "--page-size", str(tiny["page"]), "--max-new-tokens", "16", "--log-level", "off"]
+    by_text = subprocess.run(base + ["--prompt", "w5 w17 w3 w44"], capture_output=True, text=True, timeout=600)
+    by_ids = subprocess.run(base + ["--prompt-ids", "5,17,3,44"], capture_output=True, text=True, timeout=600)
+    assert by_text.returncode == 0, by_text.stderr
+    assert by_ids.returncode == 0, by_ids.stderr
+    text_line, ids_line = json.loads(by_text.stdout.strip().splitlines()[-1]), json.loads(by_ids.stdout.strip().splitlines()[-1])
+    assert text_line["token_ids"] == ids_line["token_ids"] == plain.greedy_generate(tiny["config"], tiny["weights"], [5, 17, 3, 44], 5)
+    assert text_line["prompt_tokens"] == 4
+    assert text_line["text"] == "".join(f"w{t}" for t in text_line["token_ids"]) == ids_line["text"]
+    # without a tokenizer in the folder, text is refused with a message that says what is missing
+    refused = subprocess.run([a if a != folder else tiny["folder"] for a in base] + ["--prompt", "w5"], capture_output=True, text=True, timeout=600)
+    assert refused.returncode != 0 and "tokenizer.json" in refused.stderr
