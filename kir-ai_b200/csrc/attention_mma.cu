@@ -544,7 +544,12 @@ struct DecodeSmem {
     // fused q/k preparation: cos [D / 2], sin [D / 2] of the request's position, then the q and the k norm's weights [D] each
     static constexpr int rope_bytes = 3 * D * 4;
     static_assert(rope_offset % 16 == 0, "the cosines are read in 16-byte pieces");
-    static constexpr int total = rope_offset + rope_bytes + 1024;  // + slack to align to 1024
+    // a pair of CTAs that shares a (request, kv head): the second CTA's rows, written by it into the first CTA's
+    // shared memory; outside the ring, which the first CTA may still be streaming through (heads up to 128 only:
+    // wider heads leave no room)
+    static constexpr int pair_offset = rope_offset + rope_bytes;
+    static constexpr int pair_bytes = D <= 128 ? 16 * (D + 2) * 4 : 0;
+    static constexpr int total = pair_offset + pair_bytes + 1024;  // + slack to align to 1024
 };
 
 // What a decode CTA needs to attend one range of key tiles of one (request, kv head).
@@ -974,7 +979,12 @@ __device__ __forceinline__ void decode_init_barriers(uint8_t* smem) {
 // be placed inside one GPC and therefore started late beside the product before them, 3.07 against 3.00 ms a step at
 // one request and 8 ranges, equal at 8 requests; and by the CTA of a pair that finishes last, behind a fence and a
 // counter, 3.06 against 2.98 ms at 16 ranges.)
-template <int D, bool HEADS>
+// PAIR: exactly two ranges, whose CTAs are a thread-block cluster of two.  The second CTA writes its rows straight
+// into a slot in the first CTA's shared memory (its last loop stores through a pointer mapped to the first CTA), the two
+// meet once, and the first CTA adds its own rows and the slot's, in that order and with the arithmetic of
+// attention_merge_splits_kernel, and stores the result: no buffer in global memory and no second kernel, whose way
+// through a kernel boundary cost 4.5 us a layer at 8 requests.
+template <int D, bool HEADS, bool PAIR>
 __global__ void __launch_bounds__(DecodeTile<D>::WARPS * 32)
 attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs args, bf16* __restrict__ out,
                         float* __restrict__ partial, const int* __restrict__ context_len, int num_splits) {
@@ -995,6 +1005,41 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs a
     const int t_end = min(last_tile + 1, t_begin + per_split);
     if (threadIdx.x == 0) sm100::tma_prefetch_descriptor(&kv_map);
     decode_init_barriers<D>(smem);
+    if (PAIR) {
+        const int stride = args.head_dim + 2;
+        float* own = reinterpret_cast<float*>(smem + Smem::q_bytes + Smem::merge_bytes);  // this CTA's rows, behind its warps' merge buffer
+        float* slot = reinterpret_cast<float*>(smem + Smem::pair_offset);                  // in the first CTA: the second CTA's rows
+        float* dst = own;
+        if (split == 1) {
+            // the same place in the first CTA's shared memory, as an address that ordinary stores take
+            unsigned long long mapped;
+            asm volatile("mapa.u64 %0, %1, %2;" : "=l"(mapped) : "l"((unsigned long long)(uintptr_t)slot), "r"(0u));
+            dst = reinterpret_cast<float*>((uintptr_t)mapped);
+        }
+        decode_attend_range<D, HEADS>(kv_map, args, smem, req, kv_head, pos, key_lo, last_tile, t_begin, t_end, 0, true, out,
+                                      dst, (long)stride);
+        // the rows are in place in the first CTA (release), which may read them after the meeting (acquire)
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (split == 0) {
+            const int head_dim = args.head_dim;
+            for (int e = threadIdx.x; e < group * head_dim; e += blockDim.x) {
+                const int row = e / head_dim, col = e % head_dim;
+                const float* a = own + row * stride;
+                const float* b = slot + row * stride;
+                const float m_all = fmaxf(a[head_dim], b[head_dim]);
+                const float wa = a[head_dim] == -INFINITY ? 0.0f : exp2f(a[head_dim] - m_all);
+                const float wb = b[head_dim] == -INFINITY ? 0.0f : exp2f(b[head_dim] - m_all);
+                float acc = 0.0f, l_all = 0.0f;
+                acc += a[col] * wa;
+                l_all += a[head_dim + 1] * wa;
+                acc += b[col] * wb;
+                l_all += b[head_dim + 1] * wb;
+                out[((size_t)req * args.q_heads + kv_head * group + row) * head_dim + col] = from_f32<bf16>(l_all > 0.0f ? acc / l_all : 0.0f);
+            }
+        }
+        decode_stamp(args, 4);
+        return;
+    }
     float* dst_partial = num_splits == 1 ? nullptr
         : partial + (((size_t)req * args.q_heads + kv_head * group) * num_splits + split) * (args.head_dim + 2);
     decode_attend_range<D, HEADS>(kv_map, args, smem, req, kv_head, pos, key_lo, last_tile, t_begin, t_end, 0, true, out,
@@ -1231,7 +1276,11 @@ int decode_launch(const void* q, const void* cache, void* out, float* partial, c
     const uint64_t rows = (uint64_t)num_pages * 2 * kv_heads * page_size;
     if (!tmap::bf16_2d_sw128(&kv_map, cache, rows, head_dim, head_dim, box_rows, 64)) return KIRAI_ERR_BAD_ALIGN;
     const bool heads = q_heads / kv_heads <= 8;
-    auto kernel = heads ? attention_decode_kernel<D, true> : attention_decode_kernel<D, false>;
+    // two ranges and no buffer: the pair merges in the first CTA's shared memory
+    const bool pair = num_splits == 2 && partial == nullptr;
+    if (pair && Smem::pair_bytes == 0) return KIRAI_ERR_UNSUPPORTED;
+    auto kernel = pair ? (heads ? attention_decode_kernel<D, true, true> : attention_decode_kernel<D, false, true>)
+                       : (heads ? attention_decode_kernel<D, true, false> : attention_decode_kernel<D, false, false>);
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total);
     if (err != cudaSuccess) return (int)err;
     if (fuse && head_dim != D) return KIRAI_ERR_UNSUPPORTED;  // the fused preparation works on whole heads of 64, 128 or 256
@@ -1244,6 +1293,9 @@ int decode_launch(const void* q, const void* cache, void* out, float* partial, c
     args.stamps = g_decode_stamps;
     if (g_decode_stamps) g_decode_stamps += 8 * 1024;  // the next launch's stamps follow
     dim3 grid(num_splits, kv_heads, requests);
+    if (pair)
+        return launch_pdl_clusters(kernel, grid, dim3(Smem::DC_WARPS * 32), (size_t)Smem::total, stream, dim3(2, 1, 1), kv_map,
+                                   args, (bf16*)out, partial, context_len, num_splits);
     int status = launch_pdl(kernel, grid, dim3(Smem::DC_WARPS * 32), (size_t)Smem::total, stream, 1u, kv_map, args,
                             (bf16*)out, partial, context_len, num_splits);
     if (status || num_splits == 1) return status;
@@ -1325,7 +1377,7 @@ KIRAI_EXPORT int kirai_attention_decode_bf16(const void* q, const void* cache, v
     if (bad) return bad;
     if (q_heads / kv_heads > 16) return KIRAI_ERR_UNSUPPORTED;  // the group's heads are the rows of one m16 tile
     if (num_splits < 1 || num_splits > 65535 || requests > 65535) return KIRAI_ERR_BAD_SIZE;
-    if (num_splits > 1 && !partial) return KIRAI_ERR_BAD_SIZE;  // the ranges' results need room
+    if (num_splits > 2 && !partial) return KIRAI_ERR_BAD_SIZE;  // more than a pair of ranges needs room for their results
 #define KIRAI_DC(D) \
     return decode_launch<D>(q, cache, out, partial, block_table, context_len, requests, q_heads, kv_heads, head_dim, \
                             q_row_stride, page_size, table_width, num_pages, window, scale, num_splits, error_flag, \
@@ -1375,7 +1427,7 @@ KIRAI_EXPORT int kirai_attention_decode_qk_bf16(const void* qkv, void* cache, vo
     if (bad) return bad;
     if (q_heads / kv_heads > 16) return KIRAI_ERR_UNSUPPORTED;
     if (num_splits < 1 || num_splits > 65535 || requests > 65535) return KIRAI_ERR_BAD_SIZE;
-    if (num_splits > 1 && !partial) return KIRAI_ERR_BAD_SIZE;
+    if (num_splits > 2 && !partial) return KIRAI_ERR_BAD_SIZE;
     if (((uintptr_t)q_weight | (uintptr_t)k_weight | (uintptr_t)inv_freq | (uintptr_t)cache) & 15) return KIRAI_ERR_BAD_ALIGN;
     const FuseQK fuse{q_weight, k_weight, inv_freq, eps};
 #define KIRAI_DCQ(D) \

@@ -360,7 +360,8 @@ def decode_splits(requests: int, kv_heads: int, max_context_len: int, tile: int 
                   sms: int = DEFAULT_SMS) -> int:
     """How many CTAs share one (request, kv head) in the decode kernel.  A CTA's warps take key tiles in turn, so a
     CTA with n tiles runs ceil(n / warps) rounds plus a fixed cost (set-up, merge); CTAs run in waves of ``sms``; more
-    than one range needs the buffer and the second kernel, about three rounds' time.  A launch that fills all but a
+    than one range needs the buffer and the second kernel, about three rounds' time (a pair of ranges that merges in
+    the kernel, see ``decode_pair_merges``, one round).  A launch that fills all but a
     few SMs pays one round more: the kernel after it finds no SM on which to start early and fetch its weights
     (3.15 against 3.06 ms a step with 144 and with 128 CTAs at two requests of 4,096 tokens, 3.11 against 2.98 at one).
     The split count with the fewest estimated rounds wins."""
@@ -371,10 +372,18 @@ def decode_splits(requests: int, kv_heads: int, max_context_len: int, tile: int 
         ctas = pairs * splits
         waves = -(-ctas // sms)
         rounds = -(-(-(-tiles // splits)) // warps) + 3
-        cost = waves * rounds + (0 if splits == 1 else 2.75) + (1.0 if waves == 1 and ctas > sms - 12 else 0.0)
+        merge = 0.0 if splits == 1 else (1.0 if decode_pair_merges(pairs, splits, 128, sms) else 2.75)
+        cost = waves * rounds + merge + (1.0 if waves == 1 and ctas > sms - 12 else 0.0)
         if best_cost is None or cost < best_cost:
             best, best_cost = splits, cost
     return best
+
+
+def decode_pair_merges(pairs: int, splits: int, head_dim: int, sms: int) -> bool:
+    """Whether the two ranges of every (request, kv head) merge inside the decode kernel, as a cluster of two CTAs
+    whose second writes its rows into the first one's shared memory: exactly two ranges, all CTAs running at once
+    (in a launch of several waves the pairs that a cluster must place together left SMs idle), heads of up to 128."""
+    return splits == 2 and 2 * pairs <= sms and head_dim <= 128
 
 
 def decode_plan(context_lens, kv_heads: int, window: Optional[int] = None, tile: int = 16, warps: int = 8,
@@ -395,7 +404,7 @@ def decode_plan(context_lens, kv_heads: int, window: Optional[int] = None, tile:
     tiles = [max(1, -(-n // tile)) for n in lens]
     waves = -(-len(lens) * kv_heads * splits // sms)
     rounds_split = -(-(-(-max(tiles) // splits)) // warps)
-    cost_split = waves * (rounds_split + 2.5) + (0.0 if splits == 1 else 2.5)
+    cost_split = waves * (rounds_split + 2.5) + (0.0 if splits == 1 else (1.0 if decode_pair_merges(len(lens) * kv_heads, splits, 128, sms) else 2.5))
     rounds_balanced = -(-(-(-kv_heads * sum(tiles) // sms)) // warps)
     cost_balanced = rounds_balanced + 9.5
     return cost_balanced < 0.92 * cost_split, splits
@@ -414,7 +423,8 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Te
         out = torch.empty((rows, q_heads * head_dim), dtype=q.dtype, device=q.device)
     assert out.shape == (rows, q_heads * head_dim) and out.dtype == q.dtype and out.is_contiguous()
     partial = None
-    if num_splits > 1:  # the ranges' results go through a buffer and a second kernel
+    if num_splits > 1 and not decode_pair_merges(rows * kv_heads, num_splits, head_dim, sm_count(q.device)):
+        # the ranges' results go through a buffer and a second kernel
         partial = torch.empty((rows, q_heads, num_splits, head_dim + 2), dtype=torch.float32, device=q.device)
     _call("kirai_attention_decode_bf16", _ptr(q), _ptr(cache), _ptr(out), _ptr(partial), _ptr(block_table),
           _ptr(context_len), _i(rows), _i(q_heads), _i(kv_heads), _i(head_dim), _l(q_stride), _i(page_size),
@@ -497,7 +507,8 @@ def _decode_rows(q, cache, block_table, batch, rows: int, window: Optional[int],
     if balanced and rows <= 1024:
         attention_decode_balanced(q, cache, block_table, context_len, window, scale, out=out)
         return
-    splits = decode_splits(rows, kv_heads, min(longest, window or longest), sms=sm_count(q.device))
+    # (a captured step says how many ranges, planned for its requests' lengths; else the longest context decides)
+    splits = getattr(batch, "decode_splits", None) or decode_splits(rows, kv_heads, min(longest, window or longest), sms=sm_count(q.device))
     attention_decode(q, cache, block_table, context_len, window, scale, splits, out=out)
 
 
@@ -545,9 +556,9 @@ def attention_decode_qk(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim
         partial = torch.empty((ctas, 2, 16, head_dim + 2), dtype=torch.float32, device=qkv.device)
         _call("kirai_attention_decode_balanced_qk_bf16", _ptr(qkv), _ptr(cache), _ptr(out), _ptr(partial), *common, _i(ctas), *tail)
         return out
-    splits = decode_splits(rows, kv_heads, min(longest, window or longest), sms=sm_count(qkv.device))
+    splits = getattr(batch, "decode_splits", None) or decode_splits(rows, kv_heads, min(longest, window or longest), sms=sm_count(qkv.device))
     partial = None
-    if splits > 1:
+    if splits > 1 and not decode_pair_merges(rows * kv_heads, splits, head_dim, sm_count(qkv.device)):
         partial = torch.empty((rows, q_heads, splits, head_dim + 2), dtype=torch.float32, device=qkv.device)
     _call("kirai_attention_decode_qk_bf16", _ptr(qkv), _ptr(cache), _ptr(out), _ptr(partial), *common, _i(splits), *tail)
     return out

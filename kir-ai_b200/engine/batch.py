@@ -50,6 +50,8 @@ class StepBatch:
     num_decode: int = 0
     # which decode attention kernel a step of single tokens takes (None: decided from the lengths above)
     decode_balanced: Optional[bool] = None
+    # into how many ranges that kernel cuts a request's keys (None or 0: decided from the longest context above)
+    decode_splits: Optional[int] = None
 
     @property
     def decode_only(self) -> bool:

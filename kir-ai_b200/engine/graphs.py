@@ -35,7 +35,8 @@ class NotOnHost:
 
 
 class DecodeGraph:
-    def __init__(self, runner, num_requests: int, table_width: int, balanced_attention: bool = False, pool=None):
+    def __init__(self, runner, num_requests: int, table_width: int, balanced_attention: bool = False, pool=None,
+                 attention_splits: int = 0):
         self.runner = runner
         self.pool = pool  # the memory pool that the captures of one runner share for their temporaries (None: its own)
         self.num_requests = B = num_requests
@@ -70,7 +71,7 @@ class DecodeGraph:
             request_of_token=self.fixed[:B], query_start=self.fixed, context_len=self.context_len, slots=self.slots,
             block_tables=self.tables, want_rows=self.fixed[:B], query_lens=[1] * B,
             start_positions=NotOnHost("start_positions", "positions"), slot_ids=NotOnHost("slot_ids", "slots"), max_query_len=1, max_context_len=table_width * runner.cache.page_size, num_want=B,
-            num_decode=B, decode_balanced=balanced_attention,
+            num_decode=B, decode_balanced=balanced_attention, decode_splits=attention_splits or None,
         )
         self.tokens_out: Optional[torch.Tensor] = None
         self.logits_out: Optional[torch.Tensor] = None  # [B, V] float32 of the last replay (for checks; nothing reads it otherwise)
@@ -194,23 +195,26 @@ class LaunchedStep:
 
 
 class DecodeGraphs:
-    """The captured decode steps of a runner, by (requests, table width bucket, decode attention kernel)."""
+    """The captured decode steps of a runner, by (requests, table width bucket, decode attention kernel and its ranges)."""
 
     def __init__(self, runner):
         self.runner = runner
-        self.graphs: Dict[Tuple[int, int, bool], DecodeGraph] = {}
+        self.graphs: Dict[Tuple[int, int, bool, int], DecodeGraph] = {}
         self.pool = None  # made with the first graph: one pool for the temporaries of all captures, which never run at once
 
-    def _balanced(self, context_lens: Sequence[int]) -> bool:
-        """The cheaper decode attention kernel by the model in ops.decode_plan, over the layers' cache needs
-        (all of a model's attention layers take the same kernel in one captured step: the widest need decides)."""
+    def _plan(self, context_lens: Sequence[int]) -> Tuple[bool, int]:
+        """The cheaper decode attention kernel and, for the split kernel, its number of ranges, by the model in
+        ops.decode_plan over the layers' cache needs (all of a model's attention layers take the same kernel in one
+        captured step: the widest need decides).  The ranges are planned for the lengths that the requests have, not
+        for the longest that the block tables' bucket could hold: at 7 requests of 4,100 tokens that is 2 ranges, not
+        the 5 that 8,192 tokens would want (3.55 against 3.67 ms a step)."""
         ops = self.runner.rt.ops
         groups = list(self.runner.cache.groups)
         if not groups:
-            return False
+            return False, 0
         need = max(groups, key=lambda g: g.window or (1 << 60))
-        balanced, _ = ops.decode_plan(context_lens, need.kv_heads, need.window, sms=ops.sm_count(self.runner.rt.device))
-        return balanced
+        balanced, splits = ops.decode_plan(context_lens, need.kv_heads, need.window, sms=ops.sm_count(self.runner.rt.device))
+        return balanced, (0 if balanced else splits)
 
     @staticmethod
     def batch_bucket(requests: int) -> int:
@@ -234,16 +238,16 @@ class DecodeGraphs:
             ) -> Tuple[DecodeGraph, bool]:
         """The graph for this shape and whether it still has to be captured.  ``context_lens`` (the requests'
         lengths after this step) choose between the two decode attention kernels; each has its own capture."""
-        balanced = False
+        balanced, splits = False, 0
         if context_lens is not None:
-            balanced = self._balanced(context_lens)
-        key = (num_requests, self.width_bucket(table_width), balanced)
+            balanced, splits = self._plan(context_lens)
+        key = (num_requests, self.width_bucket(table_width), balanced, splits)
         graph = self.graphs.get(key)
         if graph is None:
             if self.pool is None or not self.graphs:
                 # (a pool whose graphs have all been dropped is gone; its handle must not be used again)
                 self.pool = torch.cuda.graph_pool_handle()
-            graph = DecodeGraph(self.runner, key[0], key[1], balanced, self.pool)
+            graph = DecodeGraph(self.runner, key[0], key[1], balanced, self.pool, splits)
             self.graphs[key] = graph
         return graph, graph.graph is None
 
