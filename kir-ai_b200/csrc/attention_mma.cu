@@ -979,11 +979,12 @@ __device__ __forceinline__ void decode_init_barriers(uint8_t* smem) {
 // be placed inside one GPC and therefore started late beside the product before them, 3.07 against 3.00 ms a step at
 // one request and 8 ranges, equal at 8 requests; and by the CTA of a pair that finishes last, behind a fence and a
 // counter, 3.06 against 2.98 ms at 16 ranges.)
-// PAIR: exactly two ranges, whose CTAs are a thread-block cluster of two.  The second CTA writes its rows straight
-// into a slot in the first CTA's shared memory (its last loop stores through a pointer mapped to the first CTA), the two
-// meet once, and the first CTA adds its own rows and the slot's, in that order and with the arithmetic of
-// attention_merge_splits_kernel, and stores the result: no buffer in global memory and no second kernel, whose way
-// through a kernel boundary cost 4.5 us a layer at 8 requests.
+// PAIR: two to four ranges, whose CTAs are a thread-block cluster.  Every CTA but the first writes its rows straight
+// into a slot of its own in the first CTA's shared memory (its last loop stores through a pointer mapped to the first
+// CTA), the cluster meets once, and the first CTA adds its own rows and the slots', in rank order and with the
+// arithmetic of attention_merge_splits_kernel, and stores the result: no buffer in global memory and no second kernel,
+// whose way through a kernel boundary cost 4.5 us a layer at 8 requests.  The slots (group rows each) share
+// DecodeSmem::pair_bytes, which the launch checks.
 template <int D, bool HEADS, bool PAIR>
 __global__ void __launch_bounds__(DecodeTile<D>::WARPS * 32)
 attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs args, bf16* __restrict__ out,
@@ -1008,12 +1009,12 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs a
     if (PAIR) {
         const int stride = args.head_dim + 2;
         float* own = reinterpret_cast<float*>(smem + Smem::q_bytes + Smem::merge_bytes);  // this CTA's rows, behind its warps' merge buffer
-        float* slot = reinterpret_cast<float*>(smem + Smem::pair_offset);                  // in the first CTA: the second CTA's rows
+        float* slots = reinterpret_cast<float*>(smem + Smem::pair_offset);  // in the first CTA: the other CTAs' rows, [rank - 1][group][stride]
         float* dst = own;
-        if (split == 1) {
-            // the same place in the first CTA's shared memory, as an address that ordinary stores take
+        if (split > 0) {
+            // this CTA's slot in the first CTA's shared memory, as an address that ordinary stores take
             unsigned long long mapped;
-            asm volatile("mapa.u64 %0, %1, %2;" : "=l"(mapped) : "l"((unsigned long long)(uintptr_t)slot), "r"(0u));
+            asm volatile("mapa.u64 %0, %1, %2;" : "=l"(mapped) : "l"((unsigned long long)(uintptr_t)(slots + (size_t)(split - 1) * group * stride)), "r"(0u));
             dst = reinterpret_cast<float*>((uintptr_t)mapped);
         }
         decode_attend_range<D, HEADS>(kv_map, args, smem, req, kv_head, pos, key_lo, last_tile, t_begin, t_end, 0, true, out,
@@ -1024,16 +1025,15 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs a
             const int head_dim = args.head_dim;
             for (int e = threadIdx.x; e < group * head_dim; e += blockDim.x) {
                 const int row = e / head_dim, col = e % head_dim;
-                const float* a = own + row * stride;
-                const float* b = slot + row * stride;
-                const float m_all = fmaxf(a[head_dim], b[head_dim]);
-                const float wa = a[head_dim] == -INFINITY ? 0.0f : exp2f(a[head_dim] - m_all);
-                const float wb = b[head_dim] == -INFINITY ? 0.0f : exp2f(b[head_dim] - m_all);
+                float m_all = own[row * stride + head_dim];
+                for (int r = 1; r < num_splits; ++r) m_all = fmaxf(m_all, slots[((size_t)(r - 1) * group + row) * stride + head_dim]);
                 float acc = 0.0f, l_all = 0.0f;
-                acc += a[col] * wa;
-                l_all += a[head_dim + 1] * wa;
-                acc += b[col] * wb;
-                l_all += b[head_dim + 1] * wb;
+                for (int r = 0; r < num_splits; ++r) {
+                    const float* src = r == 0 ? own + row * stride : slots + ((size_t)(r - 1) * group + row) * stride;
+                    const float weight = src[head_dim] == -INFINITY ? 0.0f : exp2f(src[head_dim] - m_all);
+                    acc += src[col] * weight;
+                    l_all += src[head_dim + 1] * weight;
+                }
                 out[((size_t)req * args.q_heads + kv_head * group + row) * head_dim + col] = from_f32<bf16>(l_all > 0.0f ? acc / l_all : 0.0f);
             }
         }
@@ -1276,9 +1276,9 @@ int decode_launch(const void* q, const void* cache, void* out, float* partial, c
     const uint64_t rows = (uint64_t)num_pages * 2 * kv_heads * page_size;
     if (!tmap::bf16_2d_sw128(&kv_map, cache, rows, head_dim, head_dim, box_rows, 64)) return KIRAI_ERR_BAD_ALIGN;
     const bool heads = q_heads / kv_heads <= 8;
-    // two ranges and no buffer: the pair merges in the first CTA's shared memory
-    const bool pair = num_splits == 2 && partial == nullptr;
-    if (pair && Smem::pair_bytes == 0) return KIRAI_ERR_UNSUPPORTED;
+    // a few ranges and no buffer: they merge in the first CTA's shared memory, if their rows fit its slots
+    const bool pair = num_splits >= 2 && num_splits <= 8 && partial == nullptr;
+    if (pair && (size_t)(num_splits - 1) * (q_heads / kv_heads) * (head_dim + 2) * 4 > (size_t)Smem::pair_bytes) return KIRAI_ERR_UNSUPPORTED;
     auto kernel = pair ? (heads ? attention_decode_kernel<D, true, true> : attention_decode_kernel<D, false, true>)
                        : (heads ? attention_decode_kernel<D, true, false> : attention_decode_kernel<D, false, false>);
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total);
@@ -1294,8 +1294,8 @@ int decode_launch(const void* q, const void* cache, void* out, float* partial, c
     if (g_decode_stamps) g_decode_stamps += 8 * 1024;  // the next launch's stamps follow
     dim3 grid(num_splits, kv_heads, requests);
     if (pair)
-        return launch_pdl_clusters(kernel, grid, dim3(Smem::DC_WARPS * 32), (size_t)Smem::total, stream, dim3(2, 1, 1), kv_map,
-                                   args, (bf16*)out, partial, context_len, num_splits);
+        return launch_pdl_clusters(kernel, grid, dim3(Smem::DC_WARPS * 32), (size_t)Smem::total, stream, dim3(num_splits, 1, 1),
+                                   kv_map, args, (bf16*)out, partial, context_len, num_splits);
     int status = launch_pdl(kernel, grid, dim3(Smem::DC_WARPS * 32), (size_t)Smem::total, stream, 1u, kv_map, args,
                             (bf16*)out, partial, context_len, num_splits);
     if (status || num_splits == 1) return status;
@@ -1364,6 +1364,39 @@ KIRAI_EXPORT int kirai_attention_prefill_bf16(const void* q, const void* cache, 
 #undef KIRAI_PF
 }
 
+// How many clusters of `cluster` CTAs of the decode kernel the device can hold at once, 0 if it refuses the size.
+// A CTA of this kernel fills an SM, so a cluster needs that many free SMs inside one GPC, and how many SMs the GPCs
+// have differs from chip to chip (clusters of 3: 39 on one B200, 45 on another): whoever plans a launch whose ranges
+// merge as clusters, and which should run as one wave, asks here.
+template <int D>
+int decode_resident_clusters(bool heads, int cluster) {
+    using Smem = DecodeSmem<D>;
+    auto kernel = heads ? attention_decode_kernel<D, true, true> : attention_decode_kernel<D, false, true>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::total) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(cluster, 1, 1), config.blockDim = dim3(Smem::DC_WARPS * 32), config.dynamicSmemBytes = (size_t)Smem::total;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = (unsigned)cluster, attribute.val.clusterDim.y = 1, attribute.val.clusterDim.z = 1;
+    config.attrs = &attribute, config.numAttrs = 1;
+    int resident = 0;
+    if (cudaOccupancyMaxActiveClusters(&resident, kernel, &config) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return resident;
+}
+
+KIRAI_EXPORT int kirai_attention_decode_resident_clusters(int head_dim, int group, int cluster) {
+    if (cluster < 1 || cluster > 8 || group < 1 || group > 16 || head_dim < 1 || head_dim > 256) return 0;
+    if (head_dim <= 64) return decode_resident_clusters<64>(group <= 8, cluster);
+    if (head_dim <= 128) return decode_resident_clusters<128>(group <= 8, cluster);
+    return decode_resident_clusters<256>(group <= 8, cluster);
+}
+
 // Attention for a batch in which every request brings exactly one token (token r belongs to request r).
 // With num_splits > 1 and a buffer `partial` of requests * q_heads * num_splits * (head_dim + 2) floats, the ranges'
 // results go through that buffer and a second kernel merges them.
@@ -1377,7 +1410,7 @@ KIRAI_EXPORT int kirai_attention_decode_bf16(const void* q, const void* cache, v
     if (bad) return bad;
     if (q_heads / kv_heads > 16) return KIRAI_ERR_UNSUPPORTED;  // the group's heads are the rows of one m16 tile
     if (num_splits < 1 || num_splits > 65535 || requests > 65535) return KIRAI_ERR_BAD_SIZE;
-    if (num_splits > 2 && !partial) return KIRAI_ERR_BAD_SIZE;  // more than a pair of ranges needs room for their results
+    if (num_splits > 8 && !partial) return KIRAI_ERR_BAD_SIZE;  // (up to 8 ranges may merge without a buffer, if their rows fit)
 #define KIRAI_DC(D) \
     return decode_launch<D>(q, cache, out, partial, block_table, context_len, requests, q_heads, kv_heads, head_dim, \
                             q_row_stride, page_size, table_width, num_pages, window, scale, num_splits, error_flag, \
@@ -1427,7 +1460,7 @@ KIRAI_EXPORT int kirai_attention_decode_qk_bf16(const void* qkv, void* cache, vo
     if (bad) return bad;
     if (q_heads / kv_heads > 16) return KIRAI_ERR_UNSUPPORTED;
     if (num_splits < 1 || num_splits > 65535 || requests > 65535) return KIRAI_ERR_BAD_SIZE;
-    if (num_splits > 2 && !partial) return KIRAI_ERR_BAD_SIZE;
+    if (num_splits > 8 && !partial) return KIRAI_ERR_BAD_SIZE;
     if (((uintptr_t)q_weight | (uintptr_t)k_weight | (uintptr_t)inv_freq | (uintptr_t)cache) & 15) return KIRAI_ERR_BAD_ALIGN;
     const FuseQK fuse{q_weight, k_weight, inv_freq, eps};
 #define KIRAI_DCQ(D) \

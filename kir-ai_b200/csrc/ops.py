@@ -357,7 +357,7 @@ DEFAULT_SMS = 148  # for planning on a host without the device (tests); launches
 
 
 def decode_splits(requests: int, kv_heads: int, max_context_len: int, tile: int = 16, warps: int = 8,
-                  sms: int = DEFAULT_SMS) -> int:
+                  sms: int = DEFAULT_SMS, room=None) -> int:
     """How many CTAs share one (request, kv head) in the decode kernel.  A CTA's warps take key tiles in turn, so a
     CTA with n tiles runs ceil(n / warps) rounds plus a fixed cost (set-up, merge); CTAs run in waves of ``sms``; more
     than one range needs the buffer and the second kernel, about three rounds' time (a pair of ranges that merges in
@@ -365,6 +365,7 @@ def decode_splits(requests: int, kv_heads: int, max_context_len: int, tile: int 
     few SMs pays one round more: the kernel after it finds no SM on which to start early and fetch its weights
     (3.15 against 3.06 ms a step with 144 and with 128 CTAs at two requests of 4,096 tokens, 3.11 against 2.98 at one).
     The split count with the fewest estimated rounds wins."""
+    room = room or _default_cluster_room(sms)
     pairs = max(1, requests * kv_heads)
     tiles = max(1, -(-max_context_len // tile))
     best, best_cost = 1, None
@@ -372,22 +373,51 @@ def decode_splits(requests: int, kv_heads: int, max_context_len: int, tile: int 
         ctas = pairs * splits
         waves = -(-ctas // sms)
         rounds = -(-(-(-tiles // splits)) // warps) + 3
-        merge = 0.0 if splits == 1 else (1.0 if decode_pair_merges(pairs, splits, 128, sms) else 2.75)
+        merge = 0.0 if splits == 1 else (1.0 if decode_pair_merges(pairs, splits, 128, room) else 2.75)
         cost = waves * rounds + merge + (1.0 if waves == 1 and ctas > sms - 12 else 0.0)
         if best_cost is None or cost < best_cost:
             best, best_cost = splits, cost
     return best
 
 
-def decode_pair_merges(pairs: int, splits: int, head_dim: int, sms: int) -> bool:
-    """Whether the two ranges of every (request, kv head) merge inside the decode kernel, as a cluster of two CTAs
-    whose second writes its rows into the first one's shared memory: exactly two ranges, all CTAs running at once
-    (in a launch of several waves the pairs that a cluster must place together left SMs idle), heads of up to 128."""
-    return splits == 2 and 2 * pairs <= sms and head_dim <= 128
+DECODE_CLUSTER_RANGES = 4  # ranges of a (request, kv head) that may merge inside the decode kernel
+
+
+def _default_cluster_room(sms: int):
+    """Clusters of a size that a device of ``sms`` SMs is taken to hold at once when nobody asked it (planning on a
+    host without the device): what one B200 said for clusters of one-per-SM CTAs, scaled."""
+    return lambda cluster: {1: sms, 2: sms // 2, 3: (sms * 39) // 148, 4: (sms * 33) // 148}.get(cluster, 0)
+
+
+_cluster_rooms: dict = {}
+
+
+def decode_cluster_room(device: torch.device, head_dim: int, group: int = 1):
+    """cluster size -> how many clusters of the decode kernel ``device`` holds at once (0: it refuses the size).  A CTA
+    of that kernel fills an SM and a cluster must lie inside one GPC, so the answer is the device's to give: chips of
+    one kind differ in the SMs of their GPCs."""
+    key = (torch.device(device), head_dim, group <= 8)
+    if key not in _cluster_rooms:
+        with torch.cuda.device(key[0]):
+            fn = getattr(library(), "kirai_attention_decode_resident_clusters")
+            fn.restype = ctypes.c_int
+            _cluster_rooms[key] = [0] + [int(fn(_i(head_dim), _i(group), _i(c))) for c in range(1, DECODE_CLUSTER_RANGES + 1)]
+    counts = _cluster_rooms[key]
+    return lambda cluster: counts[cluster] if 0 < cluster < len(counts) else 0
+
+
+def decode_pair_merges(pairs: int, splits: int, head_dim: int, room, group: int = 4) -> bool:
+    """Whether the ranges of every (request, kv head) merge inside the decode kernel, as a cluster of CTAs that write
+    their rows into slots in the first one's shared memory: two to four ranges, all clusters running at once (``room``:
+    cluster size -> how many the device holds; in a launch of several waves the CTAs that a cluster must place
+    together left SMs idle: 6 requests as 48 clusters of 3, of which 39 to 45 fit, 3.92 against 3.44 ms a step), heads
+    of up to 128, and the other CTAs' rows (``group`` each) fitting the slots' 16 rows."""
+    return (2 <= splits <= DECODE_CLUSTER_RANGES and pairs <= room(splits) and head_dim <= 128
+            and (splits - 1) * group <= 16)
 
 
 def decode_plan(context_lens, kv_heads: int, window: Optional[int] = None, tile: int = 16, warps: int = 8,
-                sms: int = DEFAULT_SMS) -> tuple:
+                sms: int = DEFAULT_SMS, room=None) -> tuple:
     """Which decode attention kernel a batch should take: (balanced, splits).
 
     The split kernel gives every request the same number of CTAs, so its time is that of the longest request and
@@ -400,11 +430,12 @@ def decode_plan(context_lens, kv_heads: int, window: Optional[int] = None, tile:
     if not lens:
         return False, 1
     longest = max(1, max(lens))
-    splits = decode_splits(len(lens), kv_heads, longest, tile, warps, sms)
+    room = room or _default_cluster_room(sms)
+    splits = decode_splits(len(lens), kv_heads, longest, tile, warps, sms, room)
     tiles = [max(1, -(-n // tile)) for n in lens]
     waves = -(-len(lens) * kv_heads * splits // sms)
     rounds_split = -(-(-(-max(tiles) // splits)) // warps)
-    cost_split = waves * (rounds_split + 2.5) + (0.0 if splits == 1 else (1.0 if decode_pair_merges(len(lens) * kv_heads, splits, 128, sms) else 2.5))
+    cost_split = waves * (rounds_split + 2.5) + (0.0 if splits == 1 else (1.0 if decode_pair_merges(len(lens) * kv_heads, splits, 128, room) else 2.5))
     rounds_balanced = -(-(-(-kv_heads * sum(tiles) // sms)) // warps)
     cost_balanced = rounds_balanced + 9.5
     return cost_balanced < 0.92 * cost_split, splits
@@ -423,7 +454,7 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Te
         out = torch.empty((rows, q_heads * head_dim), dtype=q.dtype, device=q.device)
     assert out.shape == (rows, q_heads * head_dim) and out.dtype == q.dtype and out.is_contiguous()
     partial = None
-    if num_splits > 1 and not decode_pair_merges(rows * kv_heads, num_splits, head_dim, sm_count(q.device)):
+    if num_splits > 1 and not decode_pair_merges(rows * kv_heads, num_splits, head_dim, decode_cluster_room(q.device, head_dim, q_heads // kv_heads), q_heads // kv_heads):
         # the ranges' results go through a buffer and a second kernel
         partial = torch.empty((rows, q_heads, num_splits, head_dim + 2), dtype=torch.float32, device=q.device)
     _call("kirai_attention_decode_bf16", _ptr(q), _ptr(cache), _ptr(out), _ptr(partial), _ptr(block_table),
@@ -492,6 +523,7 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
 def _decode_rows(q, cache, block_table, batch, rows: int, window: Optional[int], scale: float, out: torch.Tensor) -> None:
     """The decode attention of the first ``rows`` requests of ``batch`` (one token each)."""
     kv_heads = cache.shape[2]
+    room = decode_cluster_room(q.device, q.shape[2], q.shape[1] // kv_heads)
     context_len = batch.context_len[:rows]
     # the batch may say which kernel (a captured step does: its lengths change between replays); otherwise
     # the host's copy of the lengths decides; KIRAI_DECODE_BALANCED=0 or 1 overrides both
@@ -499,7 +531,7 @@ def _decode_rows(q, cache, block_table, batch, rows: int, window: Optional[int],
     longest = batch.max_context_len
     if balanced is None:
         lens = [start + count for start, count in zip(batch.start_positions[:rows], batch.query_lens[:rows])]
-        balanced, _ = decode_plan(lens, kv_heads, window, sms=sm_count(q.device))
+        balanced, _ = decode_plan(lens, kv_heads, window, sms=sm_count(q.device), room=room)
         longest = max(lens)
     forced = os.environ.get("KIRAI_DECODE_BALANCED")
     if forced in ("0", "1"):
@@ -508,7 +540,7 @@ def _decode_rows(q, cache, block_table, batch, rows: int, window: Optional[int],
         attention_decode_balanced(q, cache, block_table, context_len, window, scale, out=out)
         return
     # (a captured step says how many ranges, planned for its requests' lengths; else the longest context decides)
-    splits = getattr(batch, "decode_splits", None) or decode_splits(rows, kv_heads, min(longest, window or longest), sms=sm_count(q.device))
+    splits = getattr(batch, "decode_splits", None) or decode_splits(rows, kv_heads, min(longest, window or longest), sms=sm_count(q.device), room=room)
     attention_decode(q, cache, block_table, context_len, window, scale, splits, out=out)
 
 
@@ -541,9 +573,10 @@ def attention_decode_qk(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim
     out = torch.empty((rows, q_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     balanced = getattr(batch, "decode_balanced", None)
     longest = batch.max_context_len
+    room = decode_cluster_room(qkv.device, head_dim, q_heads // kv_heads)
     if balanced is None:
         lens = [start + count for start, count in zip(batch.start_positions, batch.query_lens)]
-        balanced, _ = decode_plan(lens, kv_heads, window, sms=sm_count(qkv.device))
+        balanced, _ = decode_plan(lens, kv_heads, window, sms=sm_count(qkv.device), room=room)
         longest = max(lens)
     forced = os.environ.get("KIRAI_DECODE_BALANCED")
     if forced in ("0", "1"):
@@ -556,9 +589,9 @@ def attention_decode_qk(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim
         partial = torch.empty((ctas, 2, 16, head_dim + 2), dtype=torch.float32, device=qkv.device)
         _call("kirai_attention_decode_balanced_qk_bf16", _ptr(qkv), _ptr(cache), _ptr(out), _ptr(partial), *common, _i(ctas), *tail)
         return out
-    splits = getattr(batch, "decode_splits", None) or decode_splits(rows, kv_heads, min(longest, window or longest), sms=sm_count(qkv.device))
+    splits = getattr(batch, "decode_splits", None) or decode_splits(rows, kv_heads, min(longest, window or longest), sms=sm_count(qkv.device), room=room)
     partial = None
-    if splits > 1 and not decode_pair_merges(rows * kv_heads, splits, head_dim, sm_count(qkv.device)):
+    if splits > 1 and not decode_pair_merges(rows * kv_heads, splits, head_dim, room, q_heads // kv_heads):
         partial = torch.empty((rows, q_heads, splits, head_dim + 2), dtype=torch.float32, device=qkv.device)
     _call("kirai_attention_decode_qk_bf16", _ptr(qkv), _ptr(cache), _ptr(out), _ptr(partial), *common, _i(splits), *tail)
     return out

@@ -213,7 +213,9 @@ class DecodeGraphs:
         if not groups:
             return False, 0
         need = max(groups, key=lambda g: g.window or (1 << 60))
-        balanced, splits = ops.decode_plan(context_lens, need.kv_heads, need.window, sms=ops.sm_count(self.runner.rt.device))
+        device = self.runner.rt.device
+        balanced, splits = ops.decode_plan(context_lens, need.kv_heads, need.window, sms=ops.sm_count(device),
+                                           room=ops.decode_cluster_room(device, need.head_dim))
         return balanced, (0 if balanced else splits)
 
     @staticmethod
