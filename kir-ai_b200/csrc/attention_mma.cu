@@ -979,7 +979,7 @@ __device__ __forceinline__ void decode_init_barriers(uint8_t* smem) {
 // be placed inside one GPC and therefore started late beside the product before them, 3.07 against 3.00 ms a step at
 // one request and 8 ranges, equal at 8 requests; and by the CTA of a pair that finishes last, behind a fence and a
 // counter, 3.06 against 2.98 ms at 16 ranges.)
-// PAIR: two to four ranges, whose CTAs are a thread-block cluster.  Every CTA but the first writes its rows straight
+// PAIR: two to five ranges, whose CTAs are a thread-block cluster.  Every CTA but the first writes its rows straight
 // into a slot of its own in the first CTA's shared memory (its last loop stores through a pointer mapped to the first
 // CTA), the cluster meets once, and the first CTA adds its own rows and the slots', in rank order and with the
 // arithmetic of attention_merge_splits_kernel, and stores the result: no buffer in global memory and no second kernel,

@@ -380,13 +380,13 @@ def decode_splits(requests: int, kv_heads: int, max_context_len: int, tile: int 
     return best
 
 
-DECODE_CLUSTER_RANGES = 4  # ranges of a (request, kv head) that may merge inside the decode kernel
+DECODE_CLUSTER_RANGES = 5  # ranges of a (request, kv head) that may merge inside the decode kernel
 
 
 def _default_cluster_room(sms: int):
     """Clusters of a size that a device of ``sms`` SMs is taken to hold at once when nobody asked it (planning on a
     host without the device): what one B200 said for clusters of one-per-SM CTAs, scaled."""
-    return lambda cluster: {1: sms, 2: sms // 2, 3: (sms * 39) // 148, 4: (sms * 33) // 148}.get(cluster, 0)
+    return lambda cluster: {1: sms, 2: sms // 2, 3: (sms * 39) // 148, 4: (sms * 33) // 148, 5: (sms * 26) // 148}.get(cluster, 0)
 
 
 _cluster_rooms: dict = {}
@@ -408,7 +408,7 @@ def decode_cluster_room(device: torch.device, head_dim: int, group: int = 1):
 
 def decode_pair_merges(pairs: int, splits: int, head_dim: int, room, group: int = 4) -> bool:
     """Whether the ranges of every (request, kv head) merge inside the decode kernel, as a cluster of CTAs that write
-    their rows into slots in the first one's shared memory: two to four ranges, all clusters running at once (``room``:
+    their rows into slots in the first one's shared memory: two to five ranges, all clusters running at once (``room``:
     cluster size -> how many the device holds; in a launch of several waves the CTAs that a cluster must place
     together left SMs idle: 6 requests as 48 clusters of 3, of which 39 to 45 fit, 3.92 against 3.44 ms a step), heads
     of up to 128, and the other CTAs' rows (``group`` each) fitting the slots' 16 rows."""
