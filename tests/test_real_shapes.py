@@ -90,6 +90,9 @@ BATCHES = {
     "eight_equal": [4100] * 8,
     "eight_unequal": [4200, 37, 4111, 1500, 64, 2300, 900, 4160],
     "twenty": [4200, 37, 4111, 1500, 64, 2300, 900, 4160, 15, 16, 17, 3000, 4096, 4095, 1, 2048, 333, 4250, 129, 640],
+    # a hundred short requests: the products take tiles of 128 tokens through the weight-streaming kernel, in the decode
+    # step and in the prompts of 65 to 128 tokens that fill the caches
+    "hundred": [(i * 37) % 290 + 1 for i in range(100)],
 }
 
 
@@ -98,7 +101,7 @@ def test_captured_decode_steps_at_long_contexts(model, long_reference, dtype):
     """What a benchmark of decode steps times, checked: the captured decode step, and the step queued behind it that
     takes its tokens from the first on the device, against the step function on the same cache state (logits, both
     steps) and against the plain implementation (first step), at real layer widths, contexts beyond 4,096 tokens,
-    batches of 1, 8 and 20, equal and unequal lengths."""
+    batches of 1, 8, 20 and 100, equal and unequal lengths."""
     from kirai_b200.engine.batch import StepEntry
     from kirai_b200.engine.graphs import DecodeGraphs, captured_and_eager_logits
     from kirai_b200.engine.runner import ModelRunner
@@ -107,7 +110,7 @@ def test_captured_decode_steps_at_long_contexts(model, long_reference, dtype):
     scale = float(np.abs(reference).max())
     bound = 1e-4 if dtype == "float32" else 0.02 * scale
     most = max(sum(lengths) for lengths in BATCHES.values()) + 3400  # and the two requests of the mixed step
-    runner = ModelRunner.from_folder(model["folder"], dtype=dtype, page_size=16, max_tokens=most + 64 * 22, num_slots=22)
+    runner = ModelRunner.from_folder(model["folder"], dtype=dtype, page_size=16, max_tokens=most + 64 * 104, num_slots=104)
     graphs = DecodeGraphs(runner)
     kernels_seen = set()
     for name, lengths in BATCHES.items():
