@@ -180,6 +180,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     using Smem = GemmSmem<BN, DEEP, true>;
     constexpr int STAGES = Smem::stages;
     constexpr bool LATE = Smem::late_slots;  // the other CTAs' partial tiles lie in the first CTA's ring (see GemmSmem)
+    // Tiles of 32 tokens and more, split along K: every CTA of the cluster sums and stores a share of the tile's
+    // 16-token chunks (chunk c belongs to CTA c % splits) instead of the first CTA all of it.  A CTA sends the chunks
+    // it does not own to their owners and keeps its own in tensor memory; an owner adds the partial chunks in rank
+    // order, which is the order in which the first CTA added whole tiles, so the sums are the same bits.  (With the
+    // first CTA doing everything, a product of 64 tokens spent 3.7 us sending, 3.6 us adding and 4 us storing after
+    // its last MMA; the o projection of the 8B shape took 18 us at 64 tokens and 8 us at 16.)
+    const bool scatter = SWAP && BN >= 32 && splits > 1;
+    constexpr int CHUNKS = BN / 16;
+    const int owned_chunks = scatter ? (CHUNKS + splits - 1) / splits : CHUNKS;  // the most that one CTA owns
+    const int first_c0 = scatter ? 16 * (int)blockIdx.z : 0;  // this CTA's first chunk of tokens (none if beyond the tile)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + STAGES * Smem::stage_bytes);
@@ -302,14 +312,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     } else {
         pdl_wait();  // the output buffer may still be read by the kernel before this one
         // what the epilogue reads from global memory is fetched while the products run
-        if (rank == 0 && SWAP) {
+        if ((rank == 0 || scatter) && SWAP) {
             if (ep.row_sumsq) {
                 // the scales of this tile's tokens, computed once by the first BN threads
                 if (tile_row < BN) scale_s[tile_row] = (y0 + tile_row < M) ? row_scale_of(ep, y0 + tile_row, M) : 0.0f;
                 named_barrier_128();
             }
             if (EPI == 2 && staged) {
-                const int token = y0 + (tile_row >> 3), col = x0 + 16 * (tile_row & 7);
+                const int token = y0 + first_c0 + (tile_row >> 3), col = x0 + 16 * (tile_row & 7);
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const bool inside = col + 4 * q + 4 <= N;
@@ -318,7 +328,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     norm4[q] = inside ? *reinterpret_cast<const float4*>(ep.norm_weight + col + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
             } else if (EPI == 2) {
-                load_residual_column<BN>(ep, x0 + tile_row, y0, 0, M, N, res);
+                load_residual_column<BN>(ep, x0 + tile_row, y0, first_c0, M, N, res);
                 norm_w = x0 + tile_row < N ? ep.norm_weight[x0 + tile_row] : 0.0f;
             }
         }
@@ -329,9 +339,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     // LATE: the first CTA's ring takes the partial tiles, so nothing is sent before every CTA of the cluster has
     // seen its last product finish (all threads arrive here, the epilogue warps after their wait for the accumulator)
     if (splits > 1 && LATE) cluster_sync_all();
-    if (warp >= 2 && splits > 1 && (!LATE || rank != 0)) {
-        // store this CTA's partial tile into its slot in the first CTA (column-major: lanes side by side); LATE: the
-        // first CTA keeps its own in tensor memory and slot 0 belongs to the second
+    if (warp >= 2 && scatter) {
+        // every chunk of 16 tokens that another CTA owns goes to that CTA: its slot [sender][chunk / splits], the senders
+        // in rank order without the owner itself, 16 x 128 floats column-major (lanes side by side)
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+            const uint32_t owner = (uint32_t)(c0 >> 4) % (uint32_t)splits;
+            if (owner == rank) continue;
+            const uint32_t sender = rank < owner ? rank : rank - 1u;
+            const uint32_t slot = cluster_address(
+                smem_addr(slots) + ((sender * (uint32_t)owned_chunks + (uint32_t)(c0 >> 4) / (uint32_t)splits) * (16u * GEMM_BM)) * 4u, owner);
+            uint32_t r[16];
+            if (num_kb > 0 && ok) {
+                tmem_load_32x16(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)c0, r);
+                tmem_load_wait();
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) r[j] = 0u;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) st_cluster_f32(slot + (uint32_t)((j * GEMM_BM + tile_row) * 4), __uint_as_float(r[j]));
+        }
+    } else if (warp >= 2 && splits > 1 && (!LATE || rank != 0)) {
+        // (tiles of 16 tokens) store this CTA's partial tile into its slot in the first CTA (column-major: lanes side by side)
         const uint32_t slot = cluster_address(smem_addr(slots) + (LATE ? rank - 1u : rank) * (uint32_t)Smem::slot_bytes, 0);
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -348,10 +378,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 st_cluster_f32(slot + (uint32_t)(((c0 + j) * GEMM_BM + tile_row) * 4), __uint_as_float(r[j]));
         }
     }
-    if (splits > 1) cluster_sync_all();  // every partial tile has arrived in the first CTA
+    if (splits > 1) cluster_sync_all();  // every partial tile (or chunk) has arrived where it is added
     if (threadIdx.x == 64) gemm_stamp(ep, 4);
 
-    if (warp >= 2 && rank == 0) {
+    if (warp >= 2 && (rank == 0 || scatter)) {
         const int x_row = x0 + tile_row;  // row of X that this thread holds
         const int x_rows = SWAP ? N : M;
         const int y_rows = SWAP ? M : N;
@@ -359,17 +389,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         // The staged stores take Smem::stage_tokens tokens at a time through shared memory: all of a tile of up to 64
         // tokens through the idle ring; of 128 tokens (LATE) two halves through what the partial tiles leave of it.
         constexpr int HALF = Smem::stage_tokens;
-        float* const stage = reinterpret_cast<float*>(smem) + (LATE ? (size_t)(splits - 1) * (BN * GEMM_BM) : 0);
+        float* const stage = reinterpret_cast<float*>(smem) + (LATE ? (size_t)(splits - 1) * owned_chunks * (16 * GEMM_BM) : 0);
 #pragma unroll 1
         for (int h0 = 0; h0 < BN; h0 += HALF) {
         if (y0 + h0 >= y_rows) break;  // uniform across the CTA
 #pragma unroll 1
         for (int c0 = h0; c0 < h0 + HALF; c0 += 16) {
             if (y0 + c0 >= y_rows) break;  // uniform across the warp
-            if (EPI == 2 && SWAP && c0 > 0) load_residual_column<BN>(ep, x_row, y0, c0, M, N, res);
+            if (scatter && (uint32_t)(c0 >> 4) % (uint32_t)splits != rank) continue;  // another CTA's chunk
+            if (EPI == 2 && SWAP && c0 != first_c0) load_residual_column<BN>(ep, x_row, y0, c0, M, N, res);
             float v[16];
-            if (splits > 1 && LATE) {
-                // this CTA's own partial tile from tensor memory, then the others' in rank order
+            if (scatter) {
+                // the partial chunks in rank order: the other CTAs' from the slots, this CTA's own from tensor memory
                 uint32_t r[16];
                 if (num_kb > 0 && ok) {
                     tmem_load_32x16(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)c0, r);
@@ -378,12 +409,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 #pragma unroll
                     for (int j = 0; j < 16; ++j) r[j] = 0u;
                 }
+                const int local = (c0 >> 4) / splits;
+                for (int q = 0; q < splits; ++q) {
+                    if ((uint32_t)q == rank) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
-                for (int other = 1; other < splits; ++other) {
-                    const float* slot = slots + (size_t)(other - 1) * (BN * GEMM_BM);
+                        for (int j = 0; j < 16; ++j) v[j] = q == 0 ? __uint_as_float(r[j]) : v[j] + __uint_as_float(r[j]);
+                    } else {
+                        const float* slot = slots + ((size_t)((uint32_t)q < rank ? q : q - 1) * owned_chunks + local) * (16 * GEMM_BM);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] += slot[(c0 + j) * GEMM_BM + tile_row];
+                        for (int j = 0; j < 16; ++j) v[j] = q == 0 ? slot[j * GEMM_BM + tile_row] : v[j] + slot[j * GEMM_BM + tile_row];
+                    }
                 }
             } else if (splits > 1) {
 #pragma unroll
@@ -512,6 +547,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 #pragma unroll 1
             for (int base = h0; base < h0 + HALF; base += 16) {
                 if (y0 + base >= y_rows) break;  // uniform
+                if (scatter && (uint32_t)(base >> 4) % (uint32_t)splits != rank) continue;  // another CTA's chunk
                 const int local = base + (tile_row >> 3), token = y0 + local;
                 if (EPI == 1) {
                     // 64 outputs a token: eight to a thread
@@ -533,7 +569,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 for (int q = 0; q < 4; ++q) value[q] = *reinterpret_cast<const float4*>(stage + (local - h0) * 132 + 16 * part + 4 * q);
                 float sq = 0.0f;
                 if (EPI == 2) {
-                    if (base > 0) {
+                    if (base != first_c0) {
 #pragma unroll
                         for (int q = 0; q < 4; ++q)
                             res4[q] = (col + 4 * q + 4 <= N && token < M)
@@ -591,6 +627,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             const int part = tile_row & 7;
 #pragma unroll 1
             for (int base = 0; base < BN; base += 16) {
+                if (scatter && (uint32_t)(base >> 4) % (uint32_t)splits != rank) continue;  // another CTA's chunk
                 const int j = base + (tile_row >> 3);
                 float sum = 0.0f;
 #pragma unroll
