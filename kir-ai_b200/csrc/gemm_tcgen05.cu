@@ -54,12 +54,13 @@ using namespace sm100;
 // tokens (the 96 CTAs of the 8B shape's q, k, v product then stream at the memory's rate: 7 stages 9.5 us, 10 stages 8.5).
 // Tried on top of this and taken out: the partial tiles of a cluster row by row, sent with 16-byte stores (no faster:
 // what the first CTA waits for at the end of a split product is the slowest of its cluster, not the stores).
-// STREAM (the swapped, weight-streaming kernel) with BN = 128 (65 to 128 tokens): a partial tile is 64 KB, so the slots
-// do not fit beside a ring.  They lie IN the first CTA's ring instead, which is free once its products are done: the
-// cluster meets once before the partial tiles are sent (LATE), the first CTA keeps its own in tensor memory, and the
-// staged stores go through the rest of the ring 64 tokens at a time.  One CTA per SM with six stages and up to three
-// splits where the launch fits the SMs, else three stages, two CTAs per SM and no split.  Tiles of 64 tokens take the
-// same way where the launch fits the SMs (eight stages, up to four splits), and slots beside a ring of four otherwise.
+// STREAM (the swapped, weight-streaming kernel) with BN = 128 (65 to 128 tokens): a partial tile is 64 KB, so slots
+// for the other CTAs' partial results do not fit beside a ring.  They lie IN the receiving CTA's ring instead, which is
+// free once its products are done: the cluster meets once before anything is sent (LATE), every CTA keeps the chunks it
+// owns in tensor memory (see `scatter` in the kernel), and the staged stores go through the rest of the ring 64 tokens
+// at a time.  One CTA per SM with six stages and up to three splits where the launch fits the SMs, else three stages,
+// two CTAs per SM and no split.  Tiles of 64 tokens take the same way where the launch fits the SMs (eight stages,
+// up to four splits), and slots beside a ring of four otherwise.
 template <int BN, bool DEEP = false, bool STREAM = (BN <= 64)>
 struct GemmSmem {
     static constexpr bool streaming = STREAM;
@@ -179,7 +180,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     int k_blocks_per_split, int splits, Epilogue ep, int* __restrict__ error_flag) {
     using Smem = GemmSmem<BN, DEEP, true>;
     constexpr int STAGES = Smem::stages;
-    constexpr bool LATE = Smem::late_slots;  // the other CTAs' partial tiles lie in the first CTA's ring (see GemmSmem)
+    constexpr bool LATE = Smem::late_slots;  // what other CTAs send lies in the receiver's ring (see GemmSmem)
     // Tiles of 32 tokens and more, split along K: every CTA of the cluster sums and stores a share of the tile's
     // 16-token chunks (chunk c belongs to CTA c % splits) instead of the first CTA all of it.  A CTA sends the chunks
     // it does not own to their owners and keeps its own in tensor memory; an owner adds the partial chunks in rank
@@ -194,7 +195,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + STAGES * Smem::stage_bytes);
     float* scale_s = reinterpret_cast<float*>(smem + STAGES * Smem::stage_bytes + 256);   // [BN] row scales of this tile's tokens
-    // used in the first CTA: [splits][BN][128] behind the barriers, or (LATE) [splits - 1][BN][128] from the ring's start
+    // what other CTAs of the cluster send: behind the barriers, or (LATE) from the ring's start.  Tiles of 16 tokens:
+    // [splits][BN][128] in the first CTA; wider tiles: [senders][owned chunks][16][128] in every CTA (see `scatter`)
     float* slots = LATE ? reinterpret_cast<float*>(smem)
                         : reinterpret_cast<float*>(smem + STAGES * Smem::stage_bytes + Smem::barrier_bytes);
     uint64_t* full_bar = bars;                 // [STAGES] TMA -> MMA
@@ -336,8 +338,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         tc_fence_after();
         if (tile_row == 0) gemm_stamp(ep, 3);
     }
-    // LATE: the first CTA's ring takes the partial tiles, so nothing is sent before every CTA of the cluster has
-    // seen its last product finish (all threads arrive here, the epilogue warps after their wait for the accumulator)
+    // LATE: the receivers' rings take what is sent, so nothing is sent before every CTA of the cluster has seen its
+    // last product finish (all threads arrive here, the epilogue warps after their wait for the accumulator)
     if (splits > 1 && LATE) cluster_sync_all();
     if (warp >= 2 && scatter) {
         // every chunk of 16 tokens that another CTA owns goes to that CTA: its slot [sender][chunk / splits], the senders
@@ -360,9 +362,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 #pragma unroll
             for (int j = 0; j < 16; ++j) st_cluster_f32(slot + (uint32_t)((j * GEMM_BM + tile_row) * 4), __uint_as_float(r[j]));
         }
-    } else if (warp >= 2 && splits > 1 && (!LATE || rank != 0)) {
+    } else if (warp >= 2 && splits > 1) {
         // (tiles of 16 tokens) store this CTA's partial tile into its slot in the first CTA (column-major: lanes side by side)
-        const uint32_t slot = cluster_address(smem_addr(slots) + (LATE ? rank - 1u : rank) * (uint32_t)Smem::slot_bytes, 0);
+        const uint32_t slot = cluster_address(smem_addr(slots) + rank * (uint32_t)Smem::slot_bytes, 0);
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
             uint32_t r[16];
@@ -387,7 +389,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         const int y_rows = SWAP ? M : N;
         const float my_scale = (!SWAP && ep.row_sumsq && x_row < M) ? row_scale_of(ep, x_row, M) : 1.0f;
         // The staged stores take Smem::stage_tokens tokens at a time through shared memory: all of a tile of up to 64
-        // tokens through the idle ring; of 128 tokens (LATE) two halves through what the partial tiles leave of it.
+        // tokens through the idle ring; of 128 tokens two halves; LATE: through what the received chunks leave of it.
         constexpr int HALF = Smem::stage_tokens;
         float* const stage = reinterpret_cast<float*>(smem) + (LATE ? (size_t)(splits - 1) * owned_chunks * (16 * GEMM_BM) : 0);
 #pragma unroll 1
