@@ -64,21 +64,26 @@ using namespace sm100;
 template <int BN, bool DEEP = false, bool STREAM = (BN <= 64)>
 struct GemmSmem {
     static constexpr bool streaming = STREAM;
-    static constexpr bool late_slots = STREAM && (BN > 64 || (BN == 64 && DEEP));
+    static constexpr bool late_slots = STREAM && (BN > 64 || (BN == 64 && DEEP));  // (tiles of 256 tokens: one CTA per SM and four stages, DEEP or not)
     static constexpr int x_bytes = GEMM_BM * GEMM_BK * 2;
     static constexpr int y_bytes = BN * GEMM_BK * 2;
     static constexpr int stage_bytes = x_bytes + y_bytes;
-    static constexpr int max_splits = !STREAM ? 1 : (BN <= 64 ? 4 : (DEEP ? 3 : 1));  // BN <= 64: up to 128 KB of slots beside the ring
+    static constexpr int max_splits = !STREAM ? 1 : (BN <= 64 ? 4 : (DEEP || BN > 128 ? 3 : 1));  // BN <= 64: up to 128 KB of slots beside the ring
     static constexpr int slot_bytes = BN * GEMM_BM * 4;  // one 32-bit partial tile
     static constexpr int stages = !STREAM ? (200 * 1024 / stage_bytes)
-                                          : (BN > 64 ? (DEEP ? 6 : 3) : (DEEP ? (BN <= 16 ? 10 : (BN <= 32 ? 7 : 8)) : 4));
-    static constexpr int barrier_bytes = 2048;  // barriers [0, 256), row scales [256, 256 + 4 BN)
+                                          : (BN > 128 ? 4 : (BN > 64 ? (DEEP ? 6 : 3) : (DEEP ? (BN <= 16 ? 10 : (BN <= 32 ? 7 : 8)) : 4)));
+    static constexpr int barrier_bytes = 2048;  // barriers [0, 256), row scales [256, 256 + 4 BN) (BN <= 256)
     static constexpr int stage_tokens = BN < 64 ? BN : 64;  // tokens that the staged stores take through shared memory at a time
     static_assert(!streaming || (2 * stages + 1) * 8 + 4 <= 256, "the streaming kernel's barriers must end before the row scales");
     static_assert(!DEEP || BN <= 32 || late_slots, "a long ring beside slots is for the smallest tiles");
-    static_assert(!late_slots || (max_splits - 1) * slot_bytes + stage_tokens * 132 * 4 <= stages * stage_bytes,
-                  "the other CTAs' partial tiles and the staged tokens lie in the ring");
-    static constexpr int ctas_per_sm = streaming && !DEEP ? 2 : 1;
+    // LATE: what a CTA receives (from each other CTA the 16-token chunks that it owns, 8 KB each) and the staged tokens
+    // lie in its ring; the most is received with two splits (half the tile from one sender) or with max_splits
+    static constexpr int chunks = BN / 16;
+    static constexpr int most_received = (((chunks + 1) / 2) > (max_splits - 1) * ((chunks + max_splits - 1) / max_splits)
+                                              ? (chunks + 1) / 2 : (max_splits - 1) * ((chunks + max_splits - 1) / max_splits)) * 16 * GEMM_BM * 4;
+    static_assert(!late_slots || max_splits == 1 || most_received + stage_tokens * 132 * 4 <= stages * stage_bytes,
+                  "the other CTAs' partial chunks and the staged tokens lie in the ring");
+    static constexpr int ctas_per_sm = streaming && !DEEP && BN <= 128 ? 2 : 1;
     static constexpr int total(int splits) {  // + slack to align the base to 1024 bytes
         return stages * stage_bytes + barrier_bytes + (splits > 1 && !late_slots ? splits * slot_bytes : 0) + 1024;
     }
@@ -317,7 +322,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         if ((rank == 0 || scatter) && SWAP) {
             if (ep.row_sumsq) {
                 // the scales of this tile's tokens, computed once by the first BN threads
-                if (tile_row < BN) scale_s[tile_row] = (y0 + tile_row < M) ? row_scale_of(ep, y0 + tile_row, M) : 0.0f;
+                for (int t = tile_row; t < BN; t += GEMM_BM) scale_s[t] = (y0 + t < M) ? row_scale_of(ep, y0 + t, M) : 0.0f;
                 named_barrier_128();
             }
             if (EPI == 2 && staged) {
@@ -1098,7 +1103,7 @@ static int launch_config(const void* A, const void* W, bool tiled, void* C, int 
         dim3 grid((unsigned)((x_rows + GEMM_BM - 1) / GEMM_BM), (unsigned)((y_rows + BN - 1) / BN), (unsigned)used);
         if (grid.y > 65535) return KIRAI_ERR_BAD_SIZE;
         const long clusters = (long)grid.x * grid.y;
-        if constexpr (BN <= 128) {
+        if constexpr (BN <= 128) {  // (tiles of 256 tokens have one configuration: four stages, one CTA per SM)
             // no more CTAs than SMs: one CTA per SM with the long ring (KIRAI_GEMM_DEEP=0 keeps the short one, to compare)
             if (clusters * used <= sm_count() && deep_rings()) {
                 using Deep = GemmSmem<BN, true, true>;
@@ -1156,7 +1161,7 @@ static int gemm_dispatch(const void* A, const void* W, bool tiled, void* C, int 
     if (K <= 0) return KIRAI_ERR_BAD_SIZE;
     if (K % 8 != 0 || lda % 8 != 0) return KIRAI_ERR_BAD_ALIGN;  // TMA needs 16-byte row strides
     if (EPI == 1 && N % 16 != 0) return KIRAI_ERR_BAD_SIZE;      // whole groups of 8 gate + 8 up rows
-    if (splits <= 0) splits = M <= 128 ? choose_splits(M, N, K) : 1;
+    if (splits <= 0) splits = M <= 256 ? choose_splits(M, N, K) : 1;
 #define KIRAI_GEMM_CASE(BN, SWAP) \
     return launch_config<BN, SWAP, OutT, EPI>(A, W, tiled, C, M, N, K, lda, ldc, splits, ep, error_flag, stream)
     if (M <= 16) KIRAI_GEMM_CASE(16, true);
@@ -1166,20 +1171,27 @@ static int gemm_dispatch(const void* A, const void* W, bool tiled, void* C, int 
     // (230 us for the four products of an 8B layer against 66 us at 64 tokens).  The weight-streaming kernel takes
     // them where its staged stores apply (they do for every 16-byte aligned output).
     if (M <= 128 && streams_wide_tiles(C, ldc, sizeof(OutT), N, EPI, ep)) KIRAI_GEMM_CASE(128, true);
-    if (M <= 128 && EPI == 2 && N % 8 == 0) return KIRAI_ERR_BAD_ALIGN;  // see kirai_gemm_bf16_residual_parts
+    // 129 to 256 tokens: tiles of 256 tokens fill an SM each, so only launches of no more tiles than SMs (the 8B shape's
+    // gate/up product, 192 tiles, ran as two waves: 99 us against 59 us in the many-token kernel; its down product, 32
+    // tiles split three ways, 38 against 67)
+    const bool one_wave = (N + GEMM_BM - 1) / GEMM_BM <= sm_count();
+    if (M <= 256 && one_wave && streams_wide_tiles(C, ldc, sizeof(OutT), N, EPI, ep)) KIRAI_GEMM_CASE(256, true);
+    if (M <= 256 && EPI == 2 && N % 8 == 0 && (M <= 128 || one_wave)) return KIRAI_ERR_BAD_ALIGN;  // see kirai_gemm_bf16_residual_parts
 #undef KIRAI_GEMM_CASE
     if (N <= 128) return launch_persistent<128, OutT, EPI>(A, W, tiled, C, M, N, K, lda, ldc, ep, error_flag, stream);
     return launch_persistent<256, OutT, EPI>(A, W, tiled, C, M, N, K, lda, ldc, ep, error_flag, stream);
 }
 
 // Split count that the entry points pick for splits <= 0.
-KIRAI_EXPORT int kirai_gemm_bf16_auto_splits(int M, int N, int K) { return M <= 128 ? choose_splits(M, N, K) : 1; }
+KIRAI_EXPORT int kirai_gemm_bf16_auto_splits(int M, int N, int K) { return M <= 256 ? choose_splits(M, N, K) : 1; }
 
 // How many parts the residual-and-norm form writes into sumsq_out for a product of this shape.
 KIRAI_EXPORT int kirai_gemm_bf16_residual_parts(int M, int N) {
-    // (65 to 128 tokens go to the weight-streaming kernel where whole 16-byte pieces can be stored; form 3 with such a
+    // (65 to 256 tokens go to the weight-streaming kernel where whole 16-byte pieces can be stored, above 128 tokens
+    // only launches of no more tiles than SMs; form 3 with such a
     // shape and buffers that are not 16-byte aligned is refused rather than sent to the kernel with the other layout)
-    if (M <= 64 || (M <= 128 && N % 8 == 0)) return (N + GEMM_BM - 1) / GEMM_BM;
+    if (M <= 64 || (M <= 128 && N % 8 == 0) || (M <= 256 && N % 8 == 0 && (N + GEMM_BM - 1) / GEMM_BM <= sm_count()))
+        return (N + GEMM_BM - 1) / GEMM_BM;
     return N <= 128 ? 1 : (N + 255) / 256;
 }
 

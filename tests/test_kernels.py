@@ -121,7 +121,7 @@ def test_linear_plain_float32_is_exact_enough(ops, m, n, k):
 
 @pytest.mark.parametrize("m,n,k", [(1, 128, 64), (3, 200, 136), (16, 1000, 512), (48, 520, 1032), (64, 4096, 264),
                                    (65, 264, 192), (100, 1000, 2080), (128, 4096, 4096), (129, 520, 1032),
-                                   (200, 96, 64), (300, 1000, 520), (1024, 768, 2048)])
+                                   (200, 96, 64), (256, 4096, 2112), (257, 264, 192), (300, 1000, 520), (1024, 768, 2048)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_linear_tcgen05_against_plain(ops, m, n, k, out_dtype):
     x, w = rand(m, k, dtype=torch.bfloat16, scale=0.5), rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=3)
@@ -132,7 +132,7 @@ def test_linear_tcgen05_against_plain(ops, m, n, k, out_dtype):
     bound = (2e-5 * math.sqrt(k) if out_dtype == torch.float32 else 1e-2) * float(expected.abs().max())
     assert float((out.float() - expected).abs().max()) <= bound
     assert float((out.float() - plain.float()).abs().max()) <= bound
-    if m <= 128:  # split along K between the CTAs of a cluster (up to 64 rows: slots beside the ring; up to 128: in it)
+    if m <= 256:  # split along K between the CTAs of a cluster (up to 64 rows: slots beside the ring; up to 256: in it)
         split = ops.linear_tcgen05(x, w, out_dtype, splits=3)
         assert float((split.float() - expected).abs().max()) <= bound
         two = ops.linear_tcgen05(x, w, out_dtype, splits=2)
@@ -149,7 +149,7 @@ def test_linear_tcgen05_against_plain(ops, m, n, k, out_dtype):
     tiled = ops.tile_weight(w)
     assert tiled.shape == (n, k) and torch.equal(tiled.row_major(), w)
     assert torch.equal(ops.linear_tcgen05(x, tiled, out_dtype), out)
-    if m <= 128:
+    if m <= 256:
         assert torch.equal(ops.linear_tcgen05(x, tiled, out_dtype, splits=3), split)
     assert torch.equal(ops.linear(wide[:, :k], tiled, out_dtype), out)
     ops.check_device_errors(torch.device(DEV))
@@ -673,7 +673,7 @@ def test_decode_attention_cut_into_any_number_of_ranges(ops, q_heads, kv_heads, 
 
 
 @pytest.mark.parametrize("m,inter,k,splits", [(1, 128, 64, 0), (5, 200, 136, 0), (16, 1000, 512, 3), (64, 1536, 1032, 8),
-                                              (65, 264, 192, 0), (128, 1536, 1032, 0), (100, 6144, 1024, 3),
+                                              (65, 264, 192, 0), (128, 1536, 1032, 0), (100, 6144, 1024, 3), (250, 1536, 2048, 2),
                                               (300, 1000, 520, 0), (1024, 768, 256, 0)])
 def test_linear_swiglu_epilogue(ops, m, inter, k, splits):
     x = rand(m, k, dtype=torch.bfloat16, scale=0.5)
@@ -694,7 +694,7 @@ def test_linear_swiglu_epilogue(ops, m, inter, k, splits):
 
 @pytest.mark.parametrize("m,n,k,splits", [(1, 128, 64, 0), (5, 200, 136, 0), (16, 1000, 512, 3), (40, 520, 1032, 4),
                                           (64, 1536, 264, 0), (65, 264, 192, 0), (128, 4096, 1032, 3), (70, 520, 2048, 2),
-                                          (300, 1000, 520, 0), (1024, 768, 256, 0)])
+                                          (256, 1024, 2048, 3), (180, 520, 520, 0), (300, 1000, 520, 0), (1024, 768, 256, 0)])
 def test_linear_residual_norm_epilogue_and_row_scaled_products(ops, m, n, k, splits):
     """The product whose epilogue adds into the 32-bit stream and leaves the next norm's rows without their
     1 / rms factor, and the products that apply that factor to their result, against the formulas."""
