@@ -357,7 +357,7 @@ DEFAULT_SMS = 148  # for planning on a host without the device (tests); launches
 
 
 def decode_splits(requests: int, kv_heads: int, max_context_len: int, tile: int = 16, warps: int = 8,
-                  sms: int = DEFAULT_SMS, room=None) -> int:
+                  sms: int = DEFAULT_SMS, room=None, head_dim: int = 128, group: int = 4) -> int:
     """How many CTAs share one (request, kv head) in the decode kernel.  A CTA's warps take key tiles in turn, so a
     CTA with n tiles runs ceil(n / warps) rounds plus a fixed cost (set-up, merge); CTAs run in waves of ``sms``; more
     than one range needs the buffer and the second kernel, about three rounds' time (a pair of ranges that merges in
@@ -373,7 +373,7 @@ def decode_splits(requests: int, kv_heads: int, max_context_len: int, tile: int 
         ctas = pairs * splits
         waves = -(-ctas // sms)
         rounds = -(-(-(-tiles // splits)) // warps) + 3
-        merge = 0.0 if splits == 1 else (1.0 if decode_pair_merges(pairs, splits, 128, room) else 2.75)
+        merge = 0.0 if splits == 1 else (1.0 if decode_pair_merges(pairs, splits, head_dim, room, group) else 2.75)
         cost = waves * rounds + merge + (1.0 if waves == 1 and ctas > sms - 12 else 0.0)
         if best_cost is None or cost < best_cost:
             best, best_cost = splits, cost
@@ -417,7 +417,7 @@ def decode_pair_merges(pairs: int, splits: int, head_dim: int, room, group: int 
 
 
 def decode_plan(context_lens, kv_heads: int, window: Optional[int] = None, tile: int = 16, warps: int = 8,
-                sms: int = DEFAULT_SMS, room=None) -> tuple:
+                sms: int = DEFAULT_SMS, room=None, head_dim: int = 128, group: int = 4) -> tuple:
     """Which decode attention kernel a batch should take: (balanced, splits).
 
     The split kernel gives every request the same number of CTAs, so its time is that of the longest request and
@@ -431,11 +431,11 @@ def decode_plan(context_lens, kv_heads: int, window: Optional[int] = None, tile:
         return False, 1
     longest = max(1, max(lens))
     room = room or _default_cluster_room(sms)
-    splits = decode_splits(len(lens), kv_heads, longest, tile, warps, sms, room)
+    splits = decode_splits(len(lens), kv_heads, longest, tile, warps, sms, room, head_dim, group)
     tiles = [max(1, -(-n // tile)) for n in lens]
     waves = -(-len(lens) * kv_heads * splits // sms)
     rounds_split = -(-(-(-max(tiles) // splits)) // warps)
-    cost_split = waves * (rounds_split + 2.5) + (0.0 if splits == 1 else (1.0 if decode_pair_merges(len(lens) * kv_heads, splits, 128, room) else 2.5))
+    cost_split = waves * (rounds_split + 2.5) + (0.0 if splits == 1 else (1.0 if decode_pair_merges(len(lens) * kv_heads, splits, head_dim, room, group) else 2.5))
     rounds_balanced = -(-(-(-kv_heads * sum(tiles) // sms)) // warps)
     cost_balanced = rounds_balanced + 9.5
     return cost_balanced < 0.92 * cost_split, splits
@@ -531,7 +531,8 @@ def _decode_rows(q, cache, block_table, batch, rows: int, window: Optional[int],
     longest = batch.max_context_len
     if balanced is None:
         lens = [start + count for start, count in zip(batch.start_positions[:rows], batch.query_lens[:rows])]
-        balanced, _ = decode_plan(lens, kv_heads, window, sms=sm_count(q.device), room=room)
+        balanced, _ = decode_plan(lens, kv_heads, window, sms=sm_count(q.device), room=room, head_dim=q.shape[2],
+                                  group=q.shape[1] // kv_heads)
         longest = max(lens)
     forced = os.environ.get("KIRAI_DECODE_BALANCED")
     if forced in ("0", "1"):
@@ -540,7 +541,8 @@ def _decode_rows(q, cache, block_table, batch, rows: int, window: Optional[int],
         attention_decode_balanced(q, cache, block_table, context_len, window, scale, out=out)
         return
     # (a captured step says how many ranges, planned for its requests' lengths; else the longest context decides)
-    splits = getattr(batch, "decode_splits", None) or decode_splits(rows, kv_heads, min(longest, window or longest), sms=sm_count(q.device), room=room)
+    splits = getattr(batch, "decode_splits", None) or decode_splits(rows, kv_heads, min(longest, window or longest), sms=sm_count(q.device),
+                                                                    room=room, head_dim=q.shape[2], group=q.shape[1] // kv_heads)
     attention_decode(q, cache, block_table, context_len, window, scale, splits, out=out)
 
 
@@ -576,7 +578,8 @@ def attention_decode_qk(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim
     room = decode_cluster_room(qkv.device, head_dim, q_heads // kv_heads)
     if balanced is None:
         lens = [start + count for start, count in zip(batch.start_positions, batch.query_lens)]
-        balanced, _ = decode_plan(lens, kv_heads, window, sms=sm_count(qkv.device), room=room)
+        balanced, _ = decode_plan(lens, kv_heads, window, sms=sm_count(qkv.device), room=room, head_dim=head_dim,
+                                  group=q_heads // kv_heads)
         longest = max(lens)
     forced = os.environ.get("KIRAI_DECODE_BALANCED")
     if forced in ("0", "1"):
@@ -589,7 +592,8 @@ def attention_decode_qk(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim
         partial = torch.empty((ctas, 2, 16, head_dim + 2), dtype=torch.float32, device=qkv.device)
         _call("kirai_attention_decode_balanced_qk_bf16", _ptr(qkv), _ptr(cache), _ptr(out), _ptr(partial), *common, _i(ctas), *tail)
         return out
-    splits = getattr(batch, "decode_splits", None) or decode_splits(rows, kv_heads, min(longest, window or longest), sms=sm_count(qkv.device), room=room)
+    splits = getattr(batch, "decode_splits", None) or decode_splits(rows, kv_heads, min(longest, window or longest), sms=sm_count(qkv.device),
+                                                                    room=room, head_dim=head_dim, group=q_heads // kv_heads)
     partial = None
     if splits > 1 and not decode_pair_merges(rows * kv_heads, splits, head_dim, room, q_heads // kv_heads):
         partial = torch.empty((rows, q_heads, splits, head_dim + 2), dtype=torch.float32, device=qkv.device)

@@ -215,7 +215,7 @@ class DecodeGraphs:
         need = max(groups, key=lambda g: g.window or (1 << 60))
         device = self.runner.rt.device
         balanced, splits = ops.decode_plan(context_lens, need.kv_heads, need.window, sms=ops.sm_count(device),
-                                           room=ops.decode_cluster_room(device, need.head_dim))
+                                           room=ops.decode_cluster_room(device, need.head_dim), head_dim=need.head_dim)
         return balanced, (0 if balanced else splits)
 
     @staticmethod
