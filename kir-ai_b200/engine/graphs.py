@@ -142,6 +142,8 @@ class DecodeGraph:
         with torch.cuda.stream(stream):
             self._body()
         torch.cuda.current_stream().wait_stream(stream)
+        # (waiting here for the device is cheaper than capturing beside a busy device: without this wait a run of 64
+        # requests with 16 captures took 3.4 to 4.0 s against 3.2 to 3.4 s)
         torch.cuda.synchronize()
         self.dev_ints.copy_(saved)  # undo the eager run's advance
         for layer, tensor in saved_state.items():
