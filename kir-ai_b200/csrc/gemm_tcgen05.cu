@@ -339,6 +339,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 norm_w = x0 + tile_row < N ? ep.norm_weight[x0 + tile_row] : 0.0f;
             }
         }
+        // (polling without sleeping here and in the load and MMA threads' waits measured no faster: 3.72 against 3.70 ms
+        // a decode step of 8 requests, 3.05 both ways at one)
         if (num_kb > 0) ok = mbar_wait(smem_addr(done_bar), 0);
         tc_fence_after();
         if (tile_row == 0) gemm_stamp(ep, 3);
