@@ -183,6 +183,35 @@ def test_decode_plan_prefers_the_balanced_kernel_only_for_uneven_or_badly_filled
     assert decode_plan([], 8) == (False, 1)
 
 
+def test_decode_plan_over_random_batches_respects_the_kernels_limits():
+    """Whatever the batch, the planner names a split count that the decode kernel takes (1 to 64 ranges, never more
+    ranges than key tiles), and ranges are merged inside the kernel only where the device said the clusters fit and
+    the other CTAs' rows fit the first one's slots."""
+    import random
+
+    import kirai_b200  # noqa: F401
+    from kirai_b200.csrc.ops import DECODE_CLUSTER_RANGES, decode_pair_merges, decode_plan, decode_splits
+
+    rnd = random.Random(4)
+    for _ in range(300):
+        sms = rnd.choice([16, 66, 132, 148])
+        counts = {1: sms, 2: sms // 2, 3: rnd.randint(0, sms // 3), 4: rnd.randint(0, sms // 4), 5: rnd.randint(0, sms // 5)}
+        room = lambda cluster: counts.get(cluster, 0)  # noqa: E731
+        kv_heads, group, head_dim = rnd.choice([1, 2, 8]), rnd.choice([1, 3, 4, 8, 16]), rnd.choice([64, 128, 256])
+        lens = [rnd.randint(1, rnd.choice([40, 5000, 40000])) for _ in range(rnd.randint(1, 70))]
+        window = rnd.choice([None, None, 512])
+        balanced, splits = decode_plan(lens, kv_heads, window, sms=sms, room=room, head_dim=head_dim, group=group)
+        longest = max(min(n, window) if window else n for n in lens)
+        assert isinstance(balanced, bool) and 1 <= splits <= min(64, -(-longest // 16))
+        assert splits == decode_splits(len(lens), kv_heads, longest, sms=sms, room=room, head_dim=head_dim, group=group)
+        pairs = len(lens) * kv_heads
+        for ranges in range(1, 9):
+            merges = decode_pair_merges(pairs, ranges, head_dim, room, group)
+            if merges:
+                assert 2 <= ranges <= DECODE_CLUSTER_RANGES and pairs <= counts[ranges] and head_dim <= 128
+                assert (ranges - 1) * group <= 16
+
+
 def drive_random_workload(scheduler_class, seed):
     """A random workload (arrivals over time, stop tokens, aborts, few pages and slots) through a scheduler; the
     trace of every decision and of what was left at the end."""
